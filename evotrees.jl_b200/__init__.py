@@ -1,0 +1,15 @@
+"""B200-native device path for EvoTrees: training (`fit`) and inference (`m(x)`) behind the reference's API.
+
+Drop-in scope: what `ext/EvoTreesCUDAExt` provides in the reference.  The compute lives in
+libevotrees_b200.so (hand-written sm_100a CUDA, C ABI in include/evb.h); this package is the host-side
+mirror of the reference's operator interface.
+"""
+from .learners import EvoTreeClassifier, EvoTreeMLE, EvoTreeRegressor, EvoTypes
+from .model import EvoTree, Tree, predict, predict_leaf_idx
+from .fit import Cache, fit, grow_evotree, grow_tree, init_core, init_core_binned, sample_round
+from .binning import binarize, get_edges
+from ._lib import EvbError
+
+__all__ = ["EvoTreeRegressor", "EvoTreeClassifier", "EvoTreeMLE", "EvoTypes", "EvoTree", "Tree", "predict",
+           "predict_leaf_idx", "fit", "init_core", "init_core_binned", "grow_evotree", "grow_tree", "sample_round",
+           "Cache", "binarize", "get_edges", "EvbError"]

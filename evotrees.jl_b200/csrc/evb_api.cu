@@ -1,0 +1,472 @@
+// C ABI of libevotrees_b200.so (declarations and per-function contracts: include/evb.h).
+#include "evb_internal.cuh"
+#include <stdarg.h>
+#include <string.h>
+#include <new>
+
+int32_t evb_launch_check_bins(evb_handle *h);
+int32_t evb_launch_init_state(evb_handle *h, const float *w_dev, const float *pred0_dev, const float *mu_dev);
+int32_t evb_launch_root_plan(evb_handle *h);
+int32_t evb_hist_geometry(const evb_handle *h, int F, HistGeom *g);
+int32_t evb_nccl_check(evb_handle *h);
+
+static thread_local char g_err[512] = "";
+void evb_set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+extern "C" const char *evb_last_error(void) { return g_err; }
+extern "C" int32_t evb_version(void) { return EVB_VERSION; }
+
+// ---- timing -----------------------------------------------------------------------------------------
+// tic/toc bracket one kernel class (brackets do not nest); the events are read after the stream is
+// synchronised at the end of evb_grow_tree.
+void evb_tic(evb_handle *h, int cls) {
+    (void)cls;
+    if (!h->timing) return;
+    while (h->ev_used + 2 > h->ev.size()) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess) { h->timing = false; return; }
+        h->ev.push_back(e);
+    }
+    cudaEventRecord(h->ev[h->ev_used], h->st);
+}
+void evb_toc(evb_handle *h, int cls) {
+    h->tm.launches[cls] += 1;
+    if (!h->timing) return;
+    cudaEventRecord(h->ev[h->ev_used + 1], h->st);
+    h->ev_class.push_back(cls);
+    h->ev_used += 2;
+}
+static void resolve_timing(evb_handle *h) {
+    if (!h->timing) return;
+    for (size_t i = 0; i < h->ev_used; i += 2) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, h->ev[i], h->ev[i + 1]) == cudaSuccess) h->tm.ms[h->ev_class[i / 2]] += ms;
+    }
+    float ms = 0.f;
+    if (h->ev_tot[0] && cudaEventElapsedTime(&ms, h->ev_tot[0], h->ev_tot[1]) == cudaSuccess) h->tm.ms[EVB_T_TREE_TOTAL] += ms;
+    h->ev_used = 0;
+    h->ev_class.clear();
+}
+
+struct BusyGuard {
+    evb_handle *h;
+    bool ok;
+    explicit BusyGuard(evb_handle *hh) : h(hh) { ok = __sync_bool_compare_and_swap(&h->busy, 0, 1); }
+    ~BusyGuard() { if (ok) __sync_lock_release(&h->busy); }
+};
+#define EVB_ENTER(h)                                                                   \
+    if (!(h)) { evb_set_error("null handle"); return EVB_ERR_ARG; }                    \
+    BusyGuard _guard(h);                                                               \
+    if (!_guard.ok) { evb_set_error("handle is in use by another thread"); return EVB_ERR_BUSY; } \
+    EVB_CUDA(cudaSetDevice((h)->dev))
+
+template <typename T>
+static cudaError_t dalloc(T **p, size_t count) { return cudaMalloc((void **)p, (count ? count : 1) * sizeof(T)); }
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Device block that travels to the host once per tree: [plan][err][feat][gain][w][pred][packed][bin][split]
+struct TreeBlockLayout {
+    size_t plan, err, feat, gain, w, pred, packed, bin, split, total;
+};
+static TreeBlockLayout tree_block_layout(int D, int nn, int K) {
+    TreeBlockLayout l;
+    size_t o = 0;
+    l.plan = o; o += align_up(sizeof(LevelPlan) * (D + 2), 16);
+    l.err = o; o += 16;
+    l.feat = o; o += align_up(sizeof(int32_t) * nn, 16);
+    l.gain = o; o += align_up(sizeof(float) * nn, 16);
+    l.w = o; o += align_up(sizeof(float) * nn, 16);
+    l.pred = o; o += align_up(sizeof(float) * nn * K, 16);
+    l.packed = o; o += align_up(sizeof(uint32_t) * nn, 16);
+    l.bin = o; o += align_up((size_t)nn, 16);
+    l.split = o; o += align_up((size_t)nn, 16);
+    l.total = o;
+    return l;
+}
+
+static void free_handle(evb_handle *h) {
+    if (!h) return;
+    cudaSetDevice(h->dev);
+    if (h->st) cudaStreamSynchronize(h->st);
+    evb_nccl_destroy(h);
+    void *ptrs[] = {h->xT, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
+                    h->js_d, h->seg_start, h->seg_cnt, h->gcnt, h->nleft, (h->gnleft != h->nleft) ? h->gnleft : nullptr, h->kind,
+                    h->bslot, h->nsum, h->plan /* base of the tree block */, h->cum, h->slot_node, h->item_node, h->item_left,
+                    h->item_lprefix, h->item_bits, h->scan_tmp, h->hist, h->hcomp, h->scratch};
+    for (void *p : ptrs) if (p) cudaFree(p);
+    if (h->h_tree) cudaFreeHost(h->h_tree);
+    for (cudaEvent_t e : h->ev) cudaEventDestroy(e);
+    for (cudaEvent_t e : h->ev_tot) if (e) cudaEventDestroy(e);
+    if (h->st) cudaStreamDestroy(h->st);
+    delete h;
+}
+
+extern "C" void evb_destroy(evb_handle *h) { free_handle(h); }
+
+static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int32_t nfeats, const uint8_t *x_bin, const void *y,
+                           int32_t y_dtype, int32_t ycols, const float *w, const float *pred0, const float *mu,
+                           const uint8_t *feattypes, const int32_t *monotone) {
+    h->p = *p;
+    h->K = p->K; h->C = 2 * p->K + 1; h->B = p->nbins; h->D = p->max_depth; h->nn = (1 << p->max_depth) - 1;
+    h->nfeats = nfeats; h->RS = (nfeats + 31) / 32 * 32; h->GS = (h->C + 3) / 4 * 4; h->n = nobs;
+    h->dev = p->device; h->y_dtype = y_dtype; h->ycols = ycols;
+    h->timing = (p->flags & EVB_FLAG_TIMING) != 0;
+    h->world = 1; h->rank = 0; h->F = nfeats;
+    cudaDeviceProp prop;
+    EVB_CUDA(cudaGetDeviceProperties(&prop, h->dev));
+    if (prop.major < 10) {
+        evb_set_error("device %d is sm_%d%d; this library is built for sm_100a only", h->dev, prop.major, prop.minor);
+        return EVB_ERR_CUDA;
+    }
+    h->num_sms = prop.multiProcessorCount;
+    EVB_CUDA(cudaStreamCreateWithFlags(&h->st, cudaStreamNonBlocking));
+    const int64_t n = nobs;
+    const int nids = h->nn + 2, C = h->C, K = h->K, D = h->D;
+
+    EVB_CUDA(dalloc(&h->xT, (size_t)n * h->RS));
+    EVB_CUDA(dalloc(&h->grad, (size_t)n * h->GS));
+    EVB_CUDA(dalloc(&h->pred, (size_t)n * K));
+    EVB_CUDA(dalloc(&h->nidx, (size_t)n));
+    EVB_CUDA(dalloc(&h->rows[0], (size_t)n));
+    EVB_CUDA(dalloc(&h->rows[1], (size_t)n));
+    EVB_CUDA(dalloc(&h->mask_d, (size_t)n));
+    EVB_CUDA(dalloc(&h->feattypes_d, (size_t)nfeats));
+    EVB_CUDA(dalloc(&h->mono_d, (size_t)nfeats));
+    EVB_CUDA(dalloc(&h->js_d, (size_t)nfeats));
+    EVB_CUDA(dalloc(&h->seg_start, (size_t)nids)); EVB_CUDA(dalloc(&h->seg_cnt, (size_t)nids));
+    EVB_CUDA(dalloc(&h->gcnt, (size_t)nids)); EVB_CUDA(dalloc(&h->nleft, (size_t)nids));
+    h->gnleft = h->nleft;
+    EVB_CUDA(dalloc(&h->kind, (size_t)nids)); EVB_CUDA(dalloc(&h->bslot, (size_t)nids));
+    EVB_CUDA(dalloc(&h->nsum, (size_t)nids * C));
+    EVB_CUDA(cudaMemset(h->nleft, 0, sizeof(int32_t) * nids));
+
+    const TreeBlockLayout L = tree_block_layout(D, h->nn, K);
+    unsigned char *blk = nullptr;
+    EVB_CUDA(dalloc(&blk, L.total));
+    EVB_CUDA(cudaMemset(blk, 0, L.total));
+    h->plan = (LevelPlan *)(blk + L.plan); h->d_err = (int *)(blk + L.err);
+    h->t_feat = (int32_t *)(blk + L.feat); h->t_gain = (float *)(blk + L.gain); h->t_w = (float *)(blk + L.w);
+    h->t_pred = (float *)(blk + L.pred); h->t_packed = (uint32_t *)(blk + L.packed); h->t_bin = blk + L.bin; h->t_split = blk + L.split;
+    h->h_tree_bytes = L.total;
+    EVB_CUDA(cudaMallocHost(&h->h_tree, L.total));
+
+    h->maxslots = evb_level_slots(D > 1 ? D - 1 : 1);
+    EVB_CUDA(dalloc(&h->cum, (size_t)h->maxslots + 1)); EVB_CUDA(dalloc(&h->slot_node, (size_t)h->maxslots));
+    h->max_items = (int)(n / EVB_PART_CHUNK) + (1 << (D > 1 ? D - 1 : 0)) + 2;
+    EVB_CUDA(dalloc(&h->item_node, (size_t)(1 << D) + 2));
+    EVB_CUDA(dalloc(&h->item_left, (size_t)h->max_items)); EVB_CUDA(dalloc(&h->item_lprefix, (size_t)h->max_items));
+    EVB_CUDA(dalloc(&h->item_bits, (size_t)h->max_items * (EVB_PART_CHUNK / 32)));
+    EVB_CUDA(dalloc(&h->scan_tmp, (size_t)(n / 2048 + 2)));
+
+    const bool keep_all = (p->flags & EVB_FLAG_KEEP_ALL_HIST) != 0;
+    h->hist_nodes = keep_all ? (1 << (D > 1 ? D - 1 : 0)) : (D >= 2 ? 1 << (D - 2) : 1);
+    const size_t FCB = (size_t)nfeats * C * h->B;
+    EVB_CUDA(dalloc(&h->hist, (size_t)h->hist_nodes * FCB));
+    EVB_CUDA(dalloc(&h->hcomp, (size_t)h->maxslots * FCB));
+    EVB_CHECK(evb_hist_configure(h));
+    EVB_CUDA(dalloc(&h->scratch, h->scratch_floats));
+
+    // ---- uploads: x_bin by blocks of columns, transposed to observation-major rows on the device
+    EVB_CUDA(cudaMemsetAsync(h->xT, 0, (size_t)n * h->RS, h->st));
+    {
+        int njc = (int)((size_t)(256u << 20) / (size_t)(n > 0 ? n : 1));
+        njc = njc / 4 * 4;
+        if (njc < 4) njc = 4;
+        if (njc > nfeats) njc = nfeats;
+        uint8_t *xcol = nullptr;
+        EVB_CUDA(dalloc(&xcol, (size_t)n * njc));
+        int32_t rc = EVB_OK;
+        for (int j0 = 0; j0 < nfeats && rc == EVB_OK; j0 += njc) {
+            const int nj = nfeats - j0 < njc ? nfeats - j0 : njc;
+            cudaError_t e = cudaMemcpyAsync(xcol, x_bin + (size_t)n * j0, (size_t)n * nj, cudaMemcpyHostToDevice, h->st);
+            if (e != cudaSuccess) { evb_set_error("CUDA error %s (x_bin upload)", cudaGetErrorString(e)); rc = EVB_ERR_CUDA; break; }
+            rc = evb_launch_transpose(h, xcol, n, n, j0, nj, h->xT, h->RS, h->st);
+            if (rc == EVB_OK && cudaStreamSynchronize(h->st) != cudaSuccess) { evb_set_error("CUDA error in transpose"); rc = EVB_ERR_CUDA; }
+        }
+        cudaFree(xcol);
+        EVB_CHECK(rc);
+    }
+    {
+        const size_t ybytes = (size_t)n * (y_dtype == EVB_U32 ? 4 : 4 * (size_t)ycols);
+        EVB_CUDA(cudaMalloc(&h->y, ybytes ? ybytes : 1));
+        EVB_CUDA(cudaMemcpyAsync(h->y, y, ybytes, cudaMemcpyHostToDevice, h->st));
+        float *w_d = nullptr, *p0_d = nullptr, *mu_d = nullptr;
+        if (w) { EVB_CUDA(dalloc(&w_d, (size_t)n)); EVB_CUDA(cudaMemcpyAsync(w_d, w, sizeof(float) * n, cudaMemcpyHostToDevice, h->st)); }
+        if (pred0) { EVB_CUDA(dalloc(&p0_d, (size_t)n * K)); EVB_CUDA(cudaMemcpyAsync(p0_d, pred0, sizeof(float) * n * K, cudaMemcpyHostToDevice, h->st)); }
+        else { EVB_CUDA(dalloc(&mu_d, (size_t)K)); EVB_CUDA(cudaMemcpyAsync(mu_d, mu, sizeof(float) * K, cudaMemcpyHostToDevice, h->st)); }
+        int32_t rc = evb_launch_init_state(h, w_d, p0_d, mu_d);
+        cudaStreamSynchronize(h->st);
+        if (w_d) cudaFree(w_d);
+        if (p0_d) cudaFree(p0_d);
+        if (mu_d) cudaFree(mu_d);
+        EVB_CHECK(rc);
+    }
+    {
+        std::vector<uint8_t> ft(nfeats, 1);
+        std::vector<int32_t> mo(nfeats, 0);
+        if (feattypes) memcpy(ft.data(), feattypes, nfeats);
+        if (monotone) memcpy(mo.data(), monotone, sizeof(int32_t) * nfeats);
+        EVB_CUDA(cudaMemcpy(h->feattypes_d, ft.data(), nfeats, cudaMemcpyHostToDevice));
+        EVB_CUDA(cudaMemcpy(h->mono_d, mo.data(), sizeof(int32_t) * nfeats, cudaMemcpyHostToDevice));
+    }
+    EVB_CHECK(evb_launch_check_bins(h));
+    int err = 0;
+    EVB_CUDA(cudaMemcpyAsync(&err, h->d_err, sizeof(int), cudaMemcpyDeviceToHost, h->st));
+    EVB_CUDA(cudaStreamSynchronize(h->st));
+    if (err == EVB_DERR_BIN_RANGE) {
+        evb_set_error("x_bin holds values outside 1..nbins (%d)", h->B);
+        return EVB_ERR_ARG;
+    }
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_create(evb_handle **out, const evb_params *p, int64_t nobs, int32_t nfeats, const uint8_t *x_bin,
+                              const void *y, int32_t y_dtype, int32_t ycols, const float *w, const float *pred0, const float *mu,
+                              const uint8_t *feattypes, const int32_t *monotone) {
+    if (!out) { evb_set_error("evb_create: out is null"); return EVB_ERR_ARG; }
+    *out = nullptr;
+    if (!p || !x_bin || !y || (!pred0 && !mu)) { evb_set_error("evb_create: null argument"); return EVB_ERR_ARG; }
+    if (nobs < 1 || nobs > 2000000000ll || nfeats < 1 || nfeats > 65535) { evb_set_error("evb_create: nobs/nfeats out of range"); return EVB_ERR_ARG; }
+    if (p->loss < 0 || p->loss > 3) { evb_set_error("evb_create: unknown loss %d", p->loss); return EVB_ERR_ARG; }
+    if (p->K < 1 || p->K > 32) { evb_set_error("evb_create: K=%d outside 1..32", p->K); return EVB_ERR_ARG; }
+    if ((p->loss == EVB_GAUSSIAN_MLE && (p->K % 2 != 0 || ycols != p->K / 2)) ||
+        ((p->loss == EVB_MSE || p->loss == EVB_LOGLOSS) && ycols != p->K) || (p->loss == EVB_MLOGLOSS && p->K < 2)) {
+        evb_set_error("evb_create: K=%d / ycols=%d inconsistent with the loss", p->K, ycols);
+        return EVB_ERR_ARG;
+    }
+    if ((p->loss == EVB_MLOGLOSS) != (y_dtype == EVB_U32) || (y_dtype != EVB_U32 && y_dtype != EVB_F32)) {
+        evb_set_error("evb_create: y_dtype must be EVB_U32 for mlogloss and EVB_F32 otherwise");
+        return EVB_ERR_ARG;
+    }
+    if (p->nbins < 2 || p->nbins > 255) { evb_set_error("evb_create: nbins=%d outside 2..255", p->nbins); return EVB_ERR_ARG; }
+    if (p->max_depth < 1 || p->max_depth > EVB_MAX_DEPTH) { evb_set_error("evb_create: max_depth=%d outside 1..%d", p->max_depth, EVB_MAX_DEPTH); return EVB_ERR_LIMIT; }
+    if (p->bagging_size < 1 || p->tree_type != 0) { evb_set_error("evb_create: bagging_size must be >= 1 and tree_type binary"); return EVB_ERR_ARG; }
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0) {
+        evb_set_error("no CUDA device available (%s): this library has no CPU fallback", cudaGetErrorString(e));
+        return EVB_ERR_CUDA;
+    }
+    if (p->device < 0 || p->device >= ndev) { evb_set_error("evb_create: device %d out of range", p->device); return EVB_ERR_ARG; }
+    EVB_CUDA(cudaSetDevice(p->device));
+    evb_handle *h = new (std::nothrow) evb_handle();
+    if (!h) { evb_set_error("out of host memory"); return EVB_ERR_ARG; }
+    memset(&h->tm, 0, sizeof(h->tm));
+    int32_t rc = create_impl(h, p, nobs, nfeats, x_bin, y, y_dtype, ycols, w, pred0, mu, feattypes, monotone);
+    if (rc != EVB_OK) { free_handle(h); return rc; }
+    *out = h;
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_comm_unique_id(uint8_t id[128]) {
+    if (!id) { evb_set_error("null id"); return EVB_ERR_ARG; }
+    return evb_nccl_unique_id(id);
+}
+
+extern "C" int32_t evb_comm_init(evb_handle *h, const uint8_t id[128], int32_t rank, int32_t world) {
+    EVB_ENTER(h);
+    if (!id || world < 1 || rank < 0 || rank >= world) { evb_set_error("evb_comm_init: bad rank/world"); return EVB_ERR_ARG; }
+    if (h->nccl_comm) { evb_set_error("evb_comm_init: communicator already initialised"); return EVB_ERR_ARG; }
+    if (world == 1) return EVB_OK;
+    EVB_CHECK(evb_nccl_init(h, id, rank, world));
+    int32_t *g = nullptr;
+    EVB_CUDA(dalloc(&g, (size_t)h->nn + 2));
+    EVB_CUDA(cudaMemset(g, 0, sizeof(int32_t) * (h->nn + 2)));
+    h->gnleft = g;
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_grow_tree(evb_handle *h, const uint8_t *row_mask, uint8_t mask_cond, const uint32_t *js, int32_t njs,
+                                 int32_t update_grads, int64_t *feat, uint8_t *cond_bin, float *w_node, float *gain,
+                                 float *leaf_pred, uint8_t *split) {
+    EVB_ENTER(h);
+    if (!js || njs < 1 || njs > h->nfeats || !feat || !cond_bin || !w_node || !gain || !leaf_pred || !split) {
+        evb_set_error("evb_grow_tree: invalid argument");
+        return EVB_ERR_ARG;
+    }
+    std::vector<uint32_t> js0(njs);
+    for (int i = 0; i < njs; ++i) {
+        if (js[i] < 1 || js[i] > (uint32_t)h->nfeats || (i > 0 && js[i] <= js[i - 1])) {
+            evb_set_error("evb_grow_tree: js must be strictly ascending within 1..nfeats");
+            return EVB_ERR_ARG;
+        }
+        js0[i] = js[i] - 1;
+    }
+    if (h->world > 1) EVB_CHECK(evb_nccl_check(h));
+    const int D = h->D;
+    if (h->timing) {
+        if (!h->ev_tot[0]) { EVB_CUDA(cudaEventCreate(&h->ev_tot[0])); EVB_CUDA(cudaEventCreate(&h->ev_tot[1])); }
+        cudaEventRecord(h->ev_tot[0], h->st);
+    }
+    evb_tic(h, EVB_T_H2D);
+    EVB_CUDA(cudaMemcpyAsync(h->js_d, js0.data(), sizeof(uint32_t) * njs, cudaMemcpyHostToDevice, h->st));
+    if (row_mask) EVB_CUDA(cudaMemcpyAsync(h->mask_d, row_mask, (size_t)h->n, cudaMemcpyHostToDevice, h->st));
+    evb_toc(h, EVB_T_H2D);
+    if (njs != h->F || h->hg.NFG != (njs + 31) / 32) {
+        HistGeom g;
+        h->F = njs;
+        EVB_CHECK(evb_hist_geometry(h, njs, &g));
+        const size_t need = (size_t)g.NUG * g.PG * g.UB * g.img_floats;
+        if (need > h->scratch_floats) {
+            EVB_CUDA(cudaStreamSynchronize(h->st));
+            EVB_CUDA(cudaFree(h->scratch));
+            h->scratch = nullptr;
+            EVB_CUDA(dalloc(&h->scratch, need));
+            h->scratch_floats = need;
+        }
+        h->hg = g;
+    }
+    if (update_grads) {
+        h->bag_idx = 0;
+        if (!h->grads_fresh) EVB_CHECK(evb_launch_grads(h));
+    }
+    h->grads_fresh = false;
+    EVB_CHECK(evb_launch_tree_reset(h));
+    EVB_CHECK(evb_launch_rows_init(h, row_mask != nullptr, mask_cond));
+    if (h->world > 1) {
+        evb_tic(h, EVB_T_ALLREDUCE);
+        int32_t s = evb_nccl_allreduce_i32(h, h->nleft, h->gnleft, 1);
+        evb_toc(h, EVB_T_ALLREDUCE);
+        EVB_CHECK(s);
+    }
+    EVB_CHECK(evb_launch_root_plan(h));
+    const int last = D > 1 ? D - 1 : 1;
+    const bool full_part = (h->p.flags & EVB_FLAG_FULL_PARTITION) != 0;
+    for (int level = 1; level <= last; ++level) {
+        EVB_CHECK(evb_launch_hist(h, level));
+        EVB_CHECK(evb_launch_hist_reduce(h, level));
+        if (h->world > 1) {
+            evb_tic(h, EVB_T_ALLREDUCE);
+            int32_t s = evb_nccl_allreduce_f64(h, h->hcomp, (size_t)evb_level_slots(level) * h->F * h->C * h->B);
+            evb_toc(h, EVB_T_ALLREDUCE);
+            EVB_CHECK(s);
+        }
+        EVB_CHECK(evb_launch_scan(h, level));
+        if (level < D - 1 || (full_part && level == D - 1)) EVB_CHECK(evb_launch_partition(h, level));
+    }
+    const bool fuse = h->bag_idx == h->p.bagging_size - 1;
+    EVB_CHECK(evb_launch_finalize(h, fuse));
+    h->grads_fresh = fuse;
+    h->bag_idx += 1;
+    evb_tic(h, EVB_T_D2H);
+    EVB_CUDA(cudaMemcpyAsync(h->h_tree, h->plan, h->h_tree_bytes, cudaMemcpyDeviceToHost, h->st));
+    evb_toc(h, EVB_T_D2H);
+    if (h->timing) cudaEventRecord(h->ev_tot[1], h->st);
+    h->tm.launches[EVB_T_H2D] -= 1; // copies, not kernels
+    h->tm.launches[EVB_T_D2H] -= 1;
+    EVB_CUDA(cudaStreamSynchronize(h->st));
+    resolve_timing(h);
+
+    const TreeBlockLayout L = tree_block_layout(D, h->nn, h->K);
+    const unsigned char *hb = (const unsigned char *)h->h_tree;
+    const int derr = *(const int *)(hb + L.err);
+    if (derr != EVB_DERR_NONE) {
+        evb_set_error("device self-check failed (code %d: %s)", derr,
+                      derr == EVB_DERR_WAIT_FULL ? "bounded wait for staged rows expired"
+                      : derr == EVB_DERR_WAIT_EMPTY ? "bounded wait for a free stage expired"
+                      : derr == EVB_DERR_PLAN ? "work list overflow" : "unknown");
+        cudaMemsetAsync(h->d_err, 0, sizeof(int), h->st);
+        return EVB_ERR_DEVICE;
+    }
+    const LevelPlan *hp = (const LevelPlan *)(hb + L.plan);
+    if (hp[1].n_sel == 0 && h->world == 1) {
+        evb_set_error("no subsample observation - choose larger rowsample");
+        return EVB_ERR_EMPTY;
+    }
+    for (int level = 1; level <= last; ++level) { h->tm.hist_rows += hp[level].R; h->tm.hist_nodes += hp[level].nbuild; }
+    h->tm.trees += 1;
+    const int nn = h->nn;
+    const int32_t *tf = (const int32_t *)(hb + L.feat);
+    for (int i = 0; i < nn; ++i) feat[i] = tf[i];
+    memcpy(gain, hb + L.gain, sizeof(float) * nn);
+    memcpy(w_node, hb + L.w, sizeof(float) * nn);
+    memcpy(leaf_pred, hb + L.pred, sizeof(float) * nn * h->K);
+    memcpy(cond_bin, hb + L.bin, nn);
+    memcpy(split, hb + L.split, nn);
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_get_pred(evb_handle *h, float *pred) {
+    EVB_ENTER(h);
+    if (!pred) { evb_set_error("null output"); return EVB_ERR_ARG; }
+    EVB_CUDA(cudaMemcpyAsync(pred, h->pred, sizeof(float) * h->n * h->K, cudaMemcpyDeviceToHost, h->st));
+    EVB_CUDA(cudaStreamSynchronize(h->st));
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_get_grads(evb_handle *h, float *grad) {
+    EVB_ENTER(h);
+    if (!grad) { evb_set_error("null output"); return EVB_ERR_ARG; }
+    // the device keeps padded records of GS floats; the reference layout is [C x nobs]
+    EVB_CUDA(cudaMemcpy2DAsync(grad, sizeof(float) * h->C, h->grad, sizeof(float) * h->GS, sizeof(float) * h->C, (size_t)h->n,
+                               cudaMemcpyDeviceToHost, h->st));
+    EVB_CUDA(cudaStreamSynchronize(h->st));
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_get_nidx(evb_handle *h, uint32_t *nidx, int32_t from_partition) {
+    EVB_ENTER(h);
+    if (!nidx) { evb_set_error("null output"); return EVB_ERR_ARG; }
+    if (from_partition) {
+        if (!(h->p.flags & EVB_FLAG_FULL_PARTITION)) {
+            evb_set_error("evb_get_nidx(from_partition=1) needs EVB_FLAG_FULL_PARTITION (the last level is otherwise not partitioned)");
+            return EVB_ERR_ARG;
+        }
+        uint32_t *tmp = nullptr;
+        EVB_CUDA(dalloc(&tmp, (size_t)h->n));
+        int32_t rc = evb_launch_nidx_from_partition(h, tmp);
+        if (rc == EVB_OK) {
+            cudaError_t e = cudaMemcpyAsync(nidx, tmp, sizeof(uint32_t) * h->n, cudaMemcpyDeviceToHost, h->st);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(h->st);
+            if (e != cudaSuccess) { evb_set_error("CUDA error %s", cudaGetErrorString(e)); rc = EVB_ERR_CUDA; }
+        }
+        cudaFree(tmp);
+        return rc;
+    }
+    EVB_CUDA(cudaMemcpyAsync(nidx, h->nidx, sizeof(uint32_t) * h->n, cudaMemcpyDeviceToHost, h->st));
+    EVB_CUDA(cudaStreamSynchronize(h->st));
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_get_hist(evb_handle *h, int32_t node, double *hist) {
+    EVB_ENTER(h);
+    if (!hist || node < 1 || node >= h->hist_nodes) {
+        evb_set_error("evb_get_hist: node %d is not retained (nodes 1..%d are)", node, h->hist_nodes - 1);
+        return EVB_ERR_ARG;
+    }
+    const int F = h->F, C = h->C, B = h->B;
+    const size_t FCB = (size_t)F * C * B;
+    std::vector<double> tmp(FCB);
+    EVB_CUDA(cudaMemcpyAsync(tmp.data(), h->hist + (size_t)node * FCB, sizeof(double) * FCB, cudaMemcpyDeviceToHost, h->st));
+    EVB_CUDA(cudaStreamSynchronize(h->st));
+    for (int f = 0; f < F; ++f)
+        for (int c = 0; c < C; ++c)
+            for (int b = 0; b < B; ++b) hist[c + (size_t)C * (b + (size_t)B * f)] = tmp[((size_t)f * C + c) * B + b];
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_get_node_sums(evb_handle *h, double *nsum) {
+    EVB_ENTER(h);
+    if (!nsum) { evb_set_error("null output"); return EVB_ERR_ARG; }
+    EVB_CUDA(cudaMemcpyAsync(nsum, h->nsum + h->C, sizeof(double) * h->C * h->nn, cudaMemcpyDeviceToHost, h->st));
+    EVB_CUDA(cudaStreamSynchronize(h->st));
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_get_timings(evb_handle *h, evb_timings *out) {
+    EVB_ENTER(h);
+    if (!out) { evb_set_error("null output"); return EVB_ERR_ARG; }
+    *out = h->tm;
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_reset_timings(evb_handle *h) {
+    EVB_ENTER(h);
+    memset(&h->tm, 0, sizeof(h->tm));
+    return EVB_OK;
+}

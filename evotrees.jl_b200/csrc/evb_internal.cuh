@@ -1,0 +1,162 @@
+// Internal declarations shared by the translation units of libevotrees_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+#include <vector>
+#include "../../include/evb.h"
+
+#define EVB_VERSION 1
+
+// ---- error plumbing -------------------------------------------------------------------------------
+void evb_set_error(const char *fmt, ...);
+#define EVB_CUDA(call)                                                                                \
+    do {                                                                                              \
+        cudaError_t _e = (call);                                                                      \
+        if (_e != cudaSuccess) {                                                                      \
+            evb_set_error("CUDA error %s at %s:%d (%s)", cudaGetErrorString(_e), __FILE__, __LINE__, #call); \
+            return EVB_ERR_CUDA;                                                                      \
+        }                                                                                             \
+    } while (0)
+#define EVB_CHECK(call)                    \
+    do {                                   \
+        int32_t _s = (call);               \
+        if (_s != EVB_OK) return _s;       \
+    } while (0)
+
+// device-side error codes written to evb_handle::d_err
+enum { EVB_DERR_NONE = 0, EVB_DERR_WAIT_FULL = 1, EVB_DERR_WAIT_EMPTY = 2, EVB_DERR_BIN_RANGE = 3, EVB_DERR_PLAN = 4 };
+
+// ---- geometry constants ---------------------------------------------------------------------------
+constexpr int EVB_TILE_ROWS = 32;    // rows per staged tile (one per producer lane)
+constexpr int EVB_PART_CHUNK = 2048; // rows per partition work item
+constexpr int EVB_PART_THREADS = 256;
+constexpr int EVB_MAX_UNITS_PER_BLOCK = 4;
+constexpr int EVB_MAX_DEPTH = 15;
+
+enum { EVB_KIND_NONE = 0, EVB_KIND_BUILD = 1, EVB_KIND_SUB = 2 };
+
+// Per-level plan, device resident.  Written by the plan kernels, read by hist / reduce / scan.
+struct LevelPlan {
+    int32_t nbuild;   // build slots used at this level
+    int32_t nitems;   // partition work items at this level
+    int64_t R;        // rows (local) inside build nodes
+    int32_t n_sel;    // rows selected by the row mask (root only)
+    int32_t pad;
+};
+
+struct HistGeom {
+    int BP;        // padded bins per image: 32/64/128/256
+    int NCH;       // channels per unit image (<= 4)
+    int NFG;       // feature groups of 32 slots
+    int NCT;       // channel groups of 4
+    int U;         // units = NFG*NCT
+    int UB;        // units (consumer warps) per block
+    int NUG;       // unit groups = ceil(U/UB)
+    int stages;    // staged tiles in flight
+    int G;         // row-range blocks (grid.x)
+    int PG;        // piece slots per unit group = G + max build slots
+    size_t smem;   // dynamic shared memory per block
+    size_t img_floats;   // floats per unit image in scratch: NCH*nbins*32
+};
+
+struct evb_handle {
+    evb_params p;
+    int K, C, B, D, nn;        // nn = 2^D-1
+    int nfeats, RS, GS;        // RS: bytes per row of xT (multiple of 32); GS: floats per grad record (multiple of 4)
+    int64_t n;                 // local rows
+    int dev, num_sms;
+    cudaStream_t st;
+    int busy;
+
+    // row data
+    uint8_t *xT;       // [n][RS]  observation-major bins (1..B), zero padded
+    float *grad;       // [n][GS]  g_1..g_K,h_1..h_K,w,(pad)
+    float *pred;       // [n][K]
+    void *y;           // float [n][ycols] or uint32 [n]
+    int y_dtype, ycols;
+    uint32_t *nidx;    // [n] leaf of each row from the training traversal
+    uint32_t *rows[2]; // [n] ping-pong row lists, segments ordered by node
+    uint8_t *mask_d;   // [n]
+    uint8_t *feattypes_d; // [nfeats]
+    int32_t *mono_d;      // [nfeats]
+    uint32_t *js_d;       // [nfeats] 0-based feature id per slot
+    int F;                // njs of the current tree
+    bool grads_fresh;     // gradients already computed for the next round (fused into finalize)
+    int bag_idx;
+
+    // node state, indexed by heap id 0..nn (0 unused); children of level D-1 nodes need ids < 2^D
+    int32_t *seg_start, *seg_cnt; // local row segment of each node
+    int32_t *gcnt;                // global (all ranks) row count
+    int32_t *nleft, *gnleft;      // left-child row count of split nodes, local / global (gnleft == nleft when world == 1)
+    uint8_t *kind;
+    int32_t *bslot;
+    double *nsum;                 // [nn+1][C]
+    // tree arrays (device), heap id - 1
+    int32_t *t_feat; uint8_t *t_bin; uint8_t *t_split; float *t_gain; float *t_w; float *t_pred;
+    uint32_t *t_packed;           // per node: feat0 | bin<<16 | split<<24 | numeric<<25 (for traversal)
+
+    // plans
+    LevelPlan *plan;       // [D+1]
+    int32_t *cum;          // [maxslots+1] exclusive prefix of build-node row counts (current level)
+    int32_t *slot_node;    // [maxslots]
+    int32_t *item_node, *item_chunk, *item_left, *item_lprefix; // partition items
+    uint32_t *item_bits;   // [max_items][EVB_PART_CHUNK/32]
+    int max_items, maxslots;
+    int32_t *scan_tmp;     // block counts for the mask compaction
+    int *d_err;            // device error word
+    int *h_err;            // pinned mirror
+
+    // histograms
+    HistGeom hg;
+    double *hist;     // [2^(D-2) nodes][F][C][B] retained for the subtraction trick
+    int hist_nodes;   // nodes with id < hist_nodes are retained
+    double *hcomp;    // [maxslots][F][C][B] freshly built histograms of the level (allreduce buffer)
+    float *scratch;   // [NUG][PG][UB][NCH][B][32] per-piece partial images
+    size_t scratch_floats;
+
+    // pinned host staging for tree outputs
+    void *h_tree; size_t h_tree_bytes;
+    LevelPlan *h_plan;
+
+    // multi-GPU
+    void *nccl_comm; int rank, world;
+
+    // timing
+    bool timing;
+    std::vector<cudaEvent_t> ev; // pairs
+    cudaEvent_t ev_tot[2];       // bracket of one whole evb_grow_tree
+    std::vector<int> ev_class;
+    size_t ev_used;
+    evb_timings tm;
+};
+
+// ---- launchers (each enqueues on h->st and returns a status) ---------------------------------------
+// evb_rows.cu
+int32_t evb_launch_transpose(evb_handle *h, const uint8_t *xcol_dev, int64_t ld, int64_t nrows, int j0, int nj, uint8_t *xT, int RS, cudaStream_t st);
+int32_t evb_launch_grads(evb_handle *h);
+int32_t evb_launch_rows_init(evb_handle *h, bool use_mask, uint8_t mask_cond);
+int32_t evb_launch_finalize(evb_handle *h, bool compute_grads);
+int32_t evb_launch_nidx_from_partition(evb_handle *h, uint32_t *out_dev);
+// evb_hist.cu
+int32_t evb_hist_configure(evb_handle *h);   // fills h->hg from p / nfeats (uses max F = nfeats)
+int32_t evb_launch_hist(evb_handle *h, int level);
+int32_t evb_launch_hist_reduce(evb_handle *h, int level);
+// evb_tree.cu
+int32_t evb_launch_tree_reset(evb_handle *h);
+int32_t evb_launch_scan(evb_handle *h, int level);
+int32_t evb_launch_partition(evb_handle *h, int level); // plan + flags + prefix (+allreduce) + level plan + scatter
+// evb_nccl.cpp
+int32_t evb_nccl_unique_id(uint8_t id[128]);
+int32_t evb_nccl_init(evb_handle *h, const uint8_t id[128], int rank, int world);
+int32_t evb_nccl_allreduce_f64(evb_handle *h, double *buf, size_t count);
+int32_t evb_nccl_allreduce_i32(evb_handle *h, const int32_t *src, int32_t *dst, size_t count);
+void evb_nccl_destroy(evb_handle *h);
+
+// timing helpers (evb_api.cu)
+void evb_tic(evb_handle *h, int cls);
+void evb_toc(evb_handle *h, int cls);
+
+static inline int evb_level_nodes(int level) { return 1 << (level - 1); }            // nodes at depth `level`
+static inline int evb_level_slots(int level) { return level <= 1 ? 1 : 1 << (level - 2); } // max build slots

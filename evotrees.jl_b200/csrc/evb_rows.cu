@@ -1,0 +1,501 @@
+// Row-parallel kernels: layout conversion of the binned matrix, loss gradients (`update_grads!`,
+// src/loss.jl:100-128, 219-236; GPU counterparts ext/EvoTreesKernelAbstractionsExt/loss.jl:106-191), row
+// subsampling (`subsample`, src/subsample.jl:6-38), the training `predict!` (src/predict.jl:1-62) fused with
+// the gradients of the next round, inference over all trees (`_predict`, src/predict.jl:118-136) and
+// `binarize` (src/fit-utils.jl:66-72).
+#include "evb_internal.cuh"
+
+namespace {
+
+constexpr unsigned FULL = 0xffffffffu;
+
+// ---------------------------------------------------------------------------------- scalar loss math
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }             // loss.jl:249-251
+__device__ __forceinline__ float softplusf_(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); } // loss.jl:257-260
+
+// gradient record of one row: rec[0..K) = g*w, rec[K..2K) = h*w, rec[2K] = w (kept)
+__device__ __forceinline__ void grad_row(int loss, int K, const float *p, const void *y, int ycols, long long i, float *rec) {
+    const float w = rec[2 * K];
+    if (loss == EVB_MSE) {
+        const float *yf = (const float *)y + (size_t)i * ycols;
+        for (int k = 0; k < K; ++k) { rec[k] = 2.0f * (p[k] - yf[k]) * w; rec[K + k] = 2.0f * w; }
+    } else if (loss == EVB_LOGLOSS) {
+        const float *yf = (const float *)y + (size_t)i * ycols;
+        for (int k = 0; k < K; ++k) {
+            const float s = sigmoidf_(p[k]);
+            rec[k] = (s - yf[k]) * w;
+            rec[K + k] = s * (1.0f - s) * w;
+        }
+    } else if (loss == EVB_MLOGLOSS) {
+        const uint32_t yi = ((const uint32_t *)y)[i];
+        float isum = 0.0f;
+        for (int k = 0; k < K; ++k) isum += expf(p[k]);
+        for (int k = 0; k < K; ++k) {
+            const float prob = expf(p[k]) / isum;
+            rec[k] = (((uint32_t)(k + 1) == yi) ? prob - 1.0f : prob) * w;
+            rec[K + k] = prob * (1.0f - prob) * w;
+        }
+    } else { // EVB_GAUSSIAN_MLE
+        const int Y = K / 2;
+        const float *yf = (const float *)y + (size_t)i * ycols;
+        for (int t = 0; t < Y; ++t) {
+            const float loc = p[2 * t], sr = p[2 * t + 1];
+            const float scale = softplusf_(sr), ds = sigmoidf_(sr);
+            const float resid = loc - yf[t];
+            const float s2 = scale * scale;
+            rec[2 * t] = resid / s2 * w;
+            rec[2 * t + 1] = (1.0f - resid * resid / s2) * ds / scale * w;
+            rec[2 * Y + 2 * t] = 1.0f / s2 * w;
+            rec[2 * Y + 2 * t + 1] = 2.0f * (ds / scale) * (ds / scale) * w;
+        }
+    }
+}
+
+// pred[:, i] += leaf with the loss-specific clamps of predict! (src/predict.jl:1-62)
+__device__ __forceinline__ void pred_add(int loss, int K, float *p, const float *leaf) {
+    if (loss == EVB_LOGLOSS) {
+        for (int k = 0; k < K; ++k) p[k] = fminf(fmaxf(p[k] + leaf[k], -15.0f), 15.0f);
+    } else if (loss == EVB_GAUSSIAN_MLE) {
+        for (int t = 0; t < K / 2; ++t) {
+            p[2 * t] += leaf[2 * t];
+            p[2 * t + 1] = fmaxf(-15.0f, p[2 * t + 1] + leaf[2 * t + 1]);
+        }
+    } else if (loss == EVB_MLOGLOSS) {
+        float m = -INFINITY;
+        for (int k = 0; k < K; ++k) { p[k] += leaf[k]; m = fmaxf(m, p[k]); }
+        for (int k = 0; k < K; ++k) p[k] = fmaxf(-15.0f, p[k] - m);
+    } else {
+        for (int k = 0; k < K; ++k) p[k] += leaf[k];
+    }
+}
+
+__device__ __forceinline__ int traverse(const uint32_t *packed, const uint8_t *xrow) {
+    int nid = 1;
+    uint32_t pk = packed[0];
+    while ((pk >> 24) & 1u) {
+        const uint32_t x = xrow[pk & 0xffffu], bin = (pk >> 16) & 0xffu;
+        const bool cond = ((pk >> 25) & 1u) ? (x <= bin) : (x == bin);
+        nid = (nid << 1) + (cond ? 0 : 1); // nid = nid << 1 + !cond (src/predict.jl:7)
+        pk = packed[nid - 1];
+    }
+    return nid;
+}
+
+// ---------------------------------------------------------------------------------- layout
+// xT[row][j] = xcol[j][row] for a block of columns; one thread = one row x 4 consecutive features
+__global__ void k_transpose(const uint8_t *xcol, long long ld, long long nrows, int j0, int nj, uint8_t *xT, int RS) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int jj = blockIdx.y * 4;
+    if (i >= nrows || jj >= nj) return;
+    uint8_t v[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        if (jj + q < nj) v[q] = xcol[(size_t)(jj + q) * ld + i];
+    uint8_t *dst = xT + (size_t)i * RS + j0 + jj;
+    if (((j0 + jj) & 3) == 0 && jj + 4 <= nj) {
+        *reinterpret_cast<uint32_t *>(dst) = (uint32_t)v[0] | ((uint32_t)v[1] << 8) | ((uint32_t)v[2] << 16) | ((uint32_t)v[3] << 24);
+    } else {
+        for (int q = 0; q < 4 && jj + q < nj; ++q) dst[q] = v[q];
+    }
+}
+
+// range check of the binned matrix: counts values outside 1..nbins
+__global__ void k_check_bins(const uint8_t *xT, long long n, int RS, int nfeats, int nbins, int *err) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    bool bad = false;
+    for (int j = 0; j < nfeats; ++j) {
+        const int v = xT[(size_t)i * RS + j];
+        bad |= (v < 1 || v > nbins);
+    }
+    if (bad) atomicCAS(err, 0, EVB_DERR_BIN_RANGE);
+}
+
+__global__ void k_init_state(float *grad, float *pred, const float *w, const float *pred0, const float *mu, long long n, int K, int GS) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float *rec = grad + (size_t)i * GS;
+    for (int c = 0; c < GS; ++c) rec[c] = 0.0f;
+    rec[2 * K] = w ? w[i] : 1.0f; // ∇[end, :] .= w (src/init.jl:173-174)
+    for (int k = 0; k < K; ++k) pred[(size_t)i * K + k] = pred0 ? pred0[(size_t)i * K + k] : mu[k];
+}
+
+// ---------------------------------------------------------------------------------- gradients
+__global__ void k_grads(int loss, int K, int GS, int ycols, long long n, const float *pred, const void *y, float *grad) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    grad_row(loss, K, pred + (size_t)i * K, y, ycols, i, grad + (size_t)i * GS);
+}
+
+// ---------------------------------------------------------------------------------- row sampling
+__global__ void k_rows_identity(uint32_t *rows, long long n, int32_t *nleft0) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) rows[i] = (uint32_t)i;
+    if (i == 0) nleft0[0] = (int32_t)n;
+}
+constexpr int SEL_CHUNK = 2048, SEL_THREADS = 256;
+__global__ void __launch_bounds__(SEL_THREADS) k_sel_count(const uint8_t *mask, uint8_t cond, long long n, int32_t *bcnt) {
+    __shared__ int s[SEL_THREADS / 32];
+    const long long base = (long long)blockIdx.x * SEL_CHUNK;
+    int c = 0;
+    for (int i8 = 0; i8 < SEL_CHUNK / SEL_THREADS; ++i8) {
+        const long long i = base + i8 * SEL_THREADS + threadIdx.x;
+        const bool sel = i < n && mask[i] <= cond;
+        c += __popc(__ballot_sync(FULL, sel));
+    }
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int w = 0; w < SEL_THREADS / 32; ++w) t += s[w];
+        bcnt[blockIdx.x] = t;
+    }
+}
+__global__ void __launch_bounds__(1024) k_sel_scan(int32_t *bcnt, int nblocks, int32_t *nleft0) {
+    __shared__ int sm[33];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int carry = 0;
+    for (int base = 0; base < nblocks; base += 1024) {
+        const int i = base + threadIdx.x;
+        const int v = i < nblocks ? bcnt[i] : 0;
+        int incl = v;
+        for (int d = 1; d < 32; d <<= 1) { int t = __shfl_up_sync(FULL, incl, d); if (lane >= d) incl += t; }
+        __syncthreads();
+        if (lane == 31) sm[wid] = incl;
+        __syncthreads();
+        if (wid == 0) {
+            int w = sm[lane], wi = w;
+            for (int d = 1; d < 32; d <<= 1) { int t = __shfl_up_sync(FULL, wi, d); if (lane >= d) wi += t; }
+            sm[lane] = wi - w;
+            if (lane == 31) sm[32] = wi;
+        }
+        __syncthreads();
+        if (i < nblocks) bcnt[i] = carry + sm[wid] + incl - v;
+        carry += sm[32];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) nleft0[0] = carry;
+}
+__global__ void __launch_bounds__(SEL_THREADS) k_sel_scatter(const uint8_t *mask, uint8_t cond, long long n, const int32_t *boff, uint32_t *rows) {
+    constexpr int NW = SEL_CHUNK / 32;
+    __shared__ uint32_t s_bits[NW];
+    __shared__ int s_pref[NW];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const long long base = (long long)blockIdx.x * SEL_CHUNK;
+    for (int i8 = 0; i8 < SEL_CHUNK / SEL_THREADS; ++i8) {
+        const long long i = base + i8 * SEL_THREADS + threadIdx.x;
+        const bool sel = i < n && mask[i] <= cond;
+        const unsigned bal = __ballot_sync(FULL, sel);
+        if (lane == 0) s_bits[i8 * (SEL_THREADS / 32) + wid] = bal;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int c0 = __popc(s_bits[2 * lane]), c1 = __popc(s_bits[2 * lane + 1]);
+        int incl = c0 + c1;
+        for (int d = 1; d < 32; d <<= 1) { int t = __shfl_up_sync(FULL, incl, d); if (lane >= d) incl += t; }
+        s_pref[2 * lane] = incl - c0 - c1;
+        s_pref[2 * lane + 1] = incl - c1;
+    }
+    __syncthreads();
+    const int off = boff[blockIdx.x];
+    for (int i8 = 0; i8 < SEL_CHUNK / SEL_THREADS; ++i8) {
+        const int pos = i8 * SEL_THREADS + threadIdx.x;
+        const uint32_t word = s_bits[pos >> 5];
+        if ((word >> lane) & 1u) rows[off + s_pref[pos >> 5] + __popc(word & ((1u << lane) - 1u))] = (uint32_t)(base + pos);
+    }
+}
+static_assert(SEL_CHUNK / 32 == 64, "k_sel_scatter assumes 64 ballot words");
+
+// ---------------------------------------------------------------------------------- training predict (+ next gradients)
+struct FinArgs {
+    const uint8_t *xT;
+    const uint32_t *t_packed;
+    const float *t_pred;
+    float *pred, *grad;
+    const void *y;
+    uint32_t *nidx;
+    long long n;
+    int RS, K, GS, loss, nn, ycols, compute_grads, packed_in_smem;
+};
+__global__ void __launch_bounds__(256) k_finalize(FinArgs a) {
+    extern __shared__ uint32_t s_packed[];
+    const uint32_t *packed = a.t_packed;
+    if (a.packed_in_smem) {
+        for (int i = threadIdx.x; i < a.nn; i += blockDim.x) s_packed[i] = a.t_packed[i];
+        __syncthreads();
+        packed = s_packed;
+    }
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.n) return;
+    const int nid = traverse(packed, a.xT + (size_t)i * a.RS);
+    a.nidx[i] = (uint32_t)nid;
+    float *p = a.pred + (size_t)i * a.K;
+    pred_add(a.loss, a.K, p, a.t_pred + (size_t)(nid - 1) * a.K);
+    if (a.compute_grads) grad_row(a.loss, a.K, p, a.y, a.ycols, i, a.grad + (size_t)i * a.GS);
+}
+
+// node of every sampled row from the row lists left by the partition kernels; one CTA per node
+__global__ void k_nidx_from_partition(const uint32_t *rows0, const uint32_t *rows1, const int32_t *seg_start,
+                                      const int32_t *seg_cnt, const uint8_t *t_split, int nn, uint32_t *out) {
+    for (int n = 1 + blockIdx.x; n <= nn; n += gridDim.x) {
+        const int cnt = seg_cnt[n];
+        if (cnt <= 0 || t_split[n - 1]) continue;
+        const int depth = 32 - __clz(n); // root = 1
+        const uint32_t *rows = ((depth - 1) & 1) ? rows1 : rows0;
+        const int s0 = seg_start[n];
+        for (int r = threadIdx.x; r < cnt; r += blockDim.x) out[rows[s0 + r]] = (uint32_t)n;
+    }
+}
+
+// ---------------------------------------------------------------------------------- inference
+struct PredArgs {
+    const uint8_t *xT;
+    const uint32_t *packed; // [ntrees][nn]
+    const float *leaf;      // [ntrees][nn][K]
+    float *out;             // [nobs_total x K] column-major, this chunk starts at row0
+    uint32_t *leaf_idx;     // [nobs_total x ntrees] column-major or NULL
+    long long n, row0, nobs_total;
+    int RS, K, loss, ntrees, nn, apply_link;
+};
+template <int KMAX>
+__global__ void __launch_bounds__(256) k_predict(PredArgs a) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.n) return;
+    const uint8_t *xrow = a.xT + (size_t)i * a.RS;
+    float p[KMAX];
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k) p[k] = 0.0f;
+    const int K = a.K;
+    for (int t = 0; t < a.ntrees; ++t) {
+        const int nid = traverse(a.packed + (size_t)t * a.nn, xrow);
+        if (a.leaf_idx) a.leaf_idx[(size_t)t * a.nobs_total + a.row0 + i] = (uint32_t)nid;
+        pred_add(a.loss, K, p, a.leaf + ((size_t)t * a.nn + nid - 1) * K);
+    }
+    if (a.apply_link) { // apply_prediction_link! (src/predict.jl:105-116)
+        if (a.loss == EVB_LOGLOSS) { for (int k = 0; k < K; ++k) p[k] = sigmoidf_(p[k]); }
+        else if (a.loss == EVB_GAUSSIAN_MLE) { for (int k = 1; k < K; k += 2) p[k] = softplusf_(p[k]); }
+        else if (a.loss == EVB_MLOGLOSS) {
+            float s = 0.0f;
+            for (int k = 0; k < K; ++k) { p[k] = expf(p[k]); s += p[k]; }
+            for (int k = 0; k < K; ++k) p[k] /= s;
+        }
+    }
+    for (int k = 0; k < K; ++k) a.out[(size_t)k * a.nobs_total + a.row0 + i] = p[k];
+}
+
+__global__ void k_pack_trees(const long long *feat, const uint8_t *bin, const uint8_t *split, const uint8_t *feattypes,
+                             long long total, uint32_t *packed) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    uint32_t pk = 0;
+    if (split[i]) {
+        const uint32_t f = (uint32_t)(feat[i] - 1);
+        pk = f | ((uint32_t)bin[i] << 16) | (1u << 24) | ((feattypes ? (feattypes[f] ? 1u : 0u) : 1u) << 25);
+    }
+    packed[i] = pk;
+}
+
+// ---------------------------------------------------------------------------------- binarize
+// searchsortedfirst(edges[j], x): 1 + number of edges strictly below x
+template <typename T>
+__global__ void __launch_bounds__(256) k_binarize(const T *x, long long ld, long long n, const T *edges, int nedges, uint8_t *out, long long ldo) {
+    extern __shared__ unsigned char s_raw[];
+    T *e = reinterpret_cast<T *>(s_raw);
+    const int j = blockIdx.y;
+    for (int q = threadIdx.x; q < nedges; q += blockDim.x) e[q] = edges[(size_t)j * nedges + q];
+    __syncthreads();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const T v = x[(size_t)j * ld + i];
+        int lo = 0, hi = nedges;
+        while (lo < hi) { const int mid = (lo + hi) >> 1; if (e[mid] < v) lo = mid + 1; else hi = mid; }
+        out[(size_t)j * ldo + i] = (uint8_t)(lo + 1);
+    }
+}
+
+} // namespace
+
+// =====================================================================================================
+int32_t evb_launch_transpose(evb_handle *, const uint8_t *xcol_dev, int64_t ld, int64_t nrows, int j0, int nj, uint8_t *xT,
+                             int RS, cudaStream_t st) {
+    dim3 grid((unsigned)((nrows + 255) / 256), (unsigned)((nj + 3) / 4));
+    k_transpose<<<grid, 256, 0, st>>>(xcol_dev, ld, nrows, j0, nj, xT, RS);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+int32_t evb_launch_check_bins(evb_handle *h) {
+    k_check_bins<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->xT, h->n, h->RS, h->nfeats, h->B, h->d_err);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+int32_t evb_launch_init_state(evb_handle *h, const float *w_dev, const float *pred0_dev, const float *mu_dev) {
+    k_init_state<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->grad, h->pred, w_dev, pred0_dev, mu_dev, h->n, h->K, h->GS);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+int32_t evb_launch_grads(evb_handle *h) {
+    evb_tic(h, EVB_T_GRADS);
+    k_grads<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->p.loss, h->K, h->GS, h->ycols, h->n, h->pred, h->y, h->grad);
+    evb_toc(h, EVB_T_GRADS);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+int32_t evb_launch_rows_init(evb_handle *h, bool use_mask, uint8_t mask_cond) {
+    evb_tic(h, EVB_T_ROWS_INIT);
+    if (!use_mask) {
+        k_rows_identity<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->rows[0], h->n, h->nleft);
+    } else {
+        const int nblocks = (int)((h->n + SEL_CHUNK - 1) / SEL_CHUNK);
+        k_sel_count<<<nblocks, SEL_THREADS, 0, h->st>>>(h->mask_d, mask_cond, h->n, h->scan_tmp);
+        k_sel_scan<<<1, 1024, 0, h->st>>>(h->scan_tmp, nblocks, h->nleft);
+        k_sel_scatter<<<nblocks, SEL_THREADS, 0, h->st>>>(h->mask_d, mask_cond, h->n, h->scan_tmp, h->rows[0]);
+    }
+    evb_toc(h, EVB_T_ROWS_INIT);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+int32_t evb_launch_finalize(evb_handle *h, bool compute_grads) {
+    FinArgs a;
+    a.xT = h->xT; a.t_packed = h->t_packed; a.t_pred = h->t_pred; a.pred = h->pred; a.grad = h->grad; a.y = h->y;
+    a.nidx = h->nidx; a.n = h->n; a.RS = h->RS; a.K = h->K; a.GS = h->GS; a.loss = h->p.loss; a.nn = h->nn;
+    a.ycols = h->ycols; a.compute_grads = compute_grads ? 1 : 0;
+    const size_t smem = (size_t)h->nn * 4;
+    a.packed_in_smem = smem <= 40 * 1024 ? 1 : 0;
+    evb_tic(h, EVB_T_FINALIZE);
+    k_finalize<<<(unsigned)((h->n + 255) / 256), 256, a.packed_in_smem ? smem : 0, h->st>>>(a);
+    evb_toc(h, EVB_T_FINALIZE);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+int32_t evb_launch_nidx_from_partition(evb_handle *h, uint32_t *out_dev) {
+    EVB_CUDA(cudaMemsetAsync(out_dev, 0, sizeof(uint32_t) * h->n, h->st));
+    int blocks = h->nn < 1024 ? h->nn : 1024;
+    k_nidx_from_partition<<<blocks, 256, 0, h->st>>>(h->rows[0], h->rows[1], h->seg_start, h->seg_cnt, h->t_split, h->nn, out_dev);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+// ---- stateless entry points -----------------------------------------------------------------------
+static int32_t check_device(int device) {
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0) {
+        evb_set_error("no CUDA device available (%s): this library has no CPU fallback", cudaGetErrorString(e));
+        return EVB_ERR_CUDA;
+    }
+    if (device < 0 || device >= ndev) { evb_set_error("device %d out of range (0..%d)", device, ndev - 1); return EVB_ERR_ARG; }
+    EVB_CUDA(cudaSetDevice(device));
+    return EVB_OK;
+}
+
+struct DevBuf {
+    void *p = nullptr;
+    ~DevBuf() { if (p) cudaFree(p); }
+    cudaError_t alloc(size_t bytes) { return cudaMalloc(&p, bytes ? bytes : 1); }
+    template <typename T> T *as() { return reinterpret_cast<T *>(p); }
+};
+
+extern "C" int32_t evb_predict(int32_t device, int32_t loss, int32_t K, int32_t ntrees, int32_t nn, const int64_t *feat,
+                               const uint8_t *cond_bin, const uint8_t *split, const float *leaf_pred, const uint8_t *x_bin,
+                               int64_t nobs, int32_t nfeats, const uint8_t *feattypes, int32_t apply_link, float *out,
+                               uint32_t *leaf_idx) {
+    if (!feat || !cond_bin || !split || !leaf_pred || !x_bin || !out || nobs < 0 || nfeats < 1 || nfeats > 65535 ||
+        ntrees < 0 || nn < 1 || K < 1 || K > 64 || loss < 0 || loss > 3) {
+        evb_set_error("evb_predict: invalid argument");
+        return EVB_ERR_ARG;
+    }
+    EVB_CHECK(check_device(device));
+    if (nobs == 0) return EVB_OK;
+    cudaStream_t st;
+    EVB_CUDA(cudaStreamCreate(&st));
+    const int RS = (nfeats + 31) / 32 * 32;
+    const long long total = (long long)ntrees * nn;
+    const int64_t chunk = nobs < (int64_t)4 << 20 ? nobs : (int64_t)4 << 20;
+    DevBuf d_feat, d_bin, d_split, d_ft, d_packed, d_leaf, d_xcol, d_xT, d_out, d_lidx;
+    int32_t rc = EVB_OK;
+    auto body = [&]() -> int32_t {
+        EVB_CUDA(d_feat.alloc(total * 8)); EVB_CUDA(d_bin.alloc(total)); EVB_CUDA(d_split.alloc(total));
+        EVB_CUDA(d_packed.alloc(total * 4)); EVB_CUDA(d_leaf.alloc((size_t)total * K * 4));
+        EVB_CUDA(d_xcol.alloc((size_t)chunk * nfeats)); EVB_CUDA(d_xT.alloc((size_t)chunk * RS));
+        EVB_CUDA(d_out.alloc((size_t)nobs * K * 4));
+        if (leaf_idx) EVB_CUDA(d_lidx.alloc((size_t)nobs * ntrees * 4));
+        if (feattypes) { EVB_CUDA(d_ft.alloc(nfeats)); EVB_CUDA(cudaMemcpyAsync(d_ft.p, feattypes, nfeats, cudaMemcpyHostToDevice, st)); }
+        EVB_CUDA(cudaMemcpyAsync(d_feat.p, feat, total * 8, cudaMemcpyHostToDevice, st));
+        EVB_CUDA(cudaMemcpyAsync(d_bin.p, cond_bin, total, cudaMemcpyHostToDevice, st));
+        EVB_CUDA(cudaMemcpyAsync(d_split.p, split, total, cudaMemcpyHostToDevice, st));
+        EVB_CUDA(cudaMemcpyAsync(d_leaf.p, leaf_pred, (size_t)total * K * 4, cudaMemcpyHostToDevice, st));
+        if (total > 0) {
+            k_pack_trees<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(d_feat.as<long long>(), d_bin.as<uint8_t>(), d_split.as<uint8_t>(),
+                                                                           feattypes ? d_ft.as<uint8_t>() : nullptr, total, d_packed.as<uint32_t>());
+            EVB_CUDA(cudaGetLastError());
+        }
+        EVB_CUDA(cudaMemsetAsync(d_xT.p, 0, (size_t)chunk * RS, st));
+        for (int64_t r0 = 0; r0 < nobs; r0 += chunk) {
+            const int64_t nr = nobs - r0 < chunk ? nobs - r0 : chunk;
+            EVB_CUDA(cudaMemcpy2DAsync(d_xcol.p, (size_t)chunk, x_bin + r0, (size_t)nobs, (size_t)nr, (size_t)nfeats, cudaMemcpyHostToDevice, st));
+            EVB_CHECK(evb_launch_transpose(nullptr, d_xcol.as<uint8_t>(), chunk, nr, 0, nfeats, d_xT.as<uint8_t>(), RS, st));
+            PredArgs a;
+            a.xT = d_xT.as<uint8_t>(); a.packed = d_packed.as<uint32_t>(); a.leaf = d_leaf.as<float>(); a.out = d_out.as<float>();
+            a.leaf_idx = leaf_idx ? d_lidx.as<uint32_t>() : nullptr; a.n = nr; a.row0 = r0; a.nobs_total = nobs; a.RS = RS; a.K = K;
+            a.loss = loss; a.ntrees = ntrees; a.nn = nn; a.apply_link = apply_link;
+            const unsigned blocks = (unsigned)((nr + 255) / 256);
+            if (K <= 1) k_predict<1><<<blocks, 256, 0, st>>>(a);
+            else if (K <= 2) k_predict<2><<<blocks, 256, 0, st>>>(a);
+            else if (K <= 8) k_predict<8><<<blocks, 256, 0, st>>>(a);
+            else k_predict<64><<<blocks, 256, 0, st>>>(a);
+            EVB_CUDA(cudaGetLastError());
+        }
+        EVB_CUDA(cudaMemcpyAsync(out, d_out.p, (size_t)nobs * K * 4, cudaMemcpyDeviceToHost, st));
+        if (leaf_idx) EVB_CUDA(cudaMemcpyAsync(leaf_idx, d_lidx.p, (size_t)nobs * ntrees * 4, cudaMemcpyDeviceToHost, st));
+        EVB_CUDA(cudaStreamSynchronize(st));
+        return EVB_OK;
+    };
+    rc = body();
+    cudaStreamSynchronize(st);
+    cudaStreamDestroy(st);
+    return rc;
+}
+
+extern "C" int32_t evb_binarize(int32_t device, const void *x, int32_t dtype, int64_t nobs, int32_t nfeats, const void *edges,
+                                int32_t nedges, uint8_t *x_bin) {
+    if (!x || !edges || !x_bin || nobs < 0 || nfeats < 1 || nedges < 1 || nedges > 254 || (dtype != EVB_F32 && dtype != EVB_F64)) {
+        evb_set_error("evb_binarize: invalid argument");
+        return EVB_ERR_ARG;
+    }
+    EVB_CHECK(check_device(device));
+    if (nobs == 0) return EVB_OK;
+    const size_t es = dtype == EVB_F32 ? 4 : 8;
+    cudaStream_t st;
+    EVB_CUDA(cudaStreamCreate(&st));
+    const int64_t chunk = nobs < (int64_t)4 << 20 ? nobs : (int64_t)4 << 20;
+    DevBuf d_x, d_e, d_o;
+    auto body = [&]() -> int32_t {
+        EVB_CUDA(d_x.alloc((size_t)chunk * nfeats * es)); EVB_CUDA(d_e.alloc((size_t)nedges * nfeats * es)); EVB_CUDA(d_o.alloc((size_t)chunk * nfeats));
+        EVB_CUDA(cudaMemcpyAsync(d_e.p, edges, (size_t)nedges * nfeats * es, cudaMemcpyHostToDevice, st));
+        for (int64_t r0 = 0; r0 < nobs; r0 += chunk) {
+            const int64_t nr = nobs - r0 < chunk ? nobs - r0 : chunk;
+            EVB_CUDA(cudaMemcpy2DAsync(d_x.p, (size_t)chunk * es, (const char *)x + (size_t)r0 * es, (size_t)nobs * es, (size_t)nr * es,
+                                       (size_t)nfeats, cudaMemcpyHostToDevice, st));
+            unsigned bx = (unsigned)((nr + 255) / 256);
+            if (bx > 4096) bx = 4096;
+            dim3 grid(bx, (unsigned)nfeats);
+            if (dtype == EVB_F32)
+                k_binarize<float><<<grid, 256, (size_t)nedges * 4, st>>>(d_x.as<float>(), chunk, nr, d_e.as<float>(), nedges, d_o.as<uint8_t>(), chunk);
+            else
+                k_binarize<double><<<grid, 256, (size_t)nedges * 8, st>>>(d_x.as<double>(), chunk, nr, d_e.as<double>(), nedges, d_o.as<uint8_t>(), chunk);
+            EVB_CUDA(cudaGetLastError());
+            EVB_CUDA(cudaMemcpy2DAsync(x_bin + r0, (size_t)nobs, d_o.p, (size_t)chunk, (size_t)nr, (size_t)nfeats, cudaMemcpyDeviceToHost, st));
+        }
+        EVB_CUDA(cudaStreamSynchronize(st));
+        return EVB_OK;
+    };
+    int32_t rc = body();
+    cudaStreamSynchronize(st);
+    cudaStreamDestroy(st);
+    return rc;
+}

@@ -1,0 +1,592 @@
+// Per-level tree growth on the device: sibling subtraction + split scan + split application
+// (`subtract_hist!`, `get_best_split`/`_scan_node!`, `_child_sums!`, `pred_leaf_cpu!`: src/fit-utils.jl:321-332,
+// 403-486, src/split.jl:1-117, src/predict.jl:198-247, src/fit.jl:85-137) and the stable row partition
+// (`split_set!`, src/fit-utils.jl:93-312; GPU counterpart `update_nodes_idx_kernel!`,
+// ext/EvoTreesKernelAbstractionsExt/fit-utils.jl:9-31).  Everything a level needs (active nodes, segment
+// bounds, build/subtract choice, work lists) lives in device memory, so the host enqueues a fixed sequence of
+// launches per level and never reads anything back until the tree is complete.
+#include "evb_internal.cuh"
+#include <float.h>
+
+namespace {
+
+constexpr unsigned FULL = 0xffffffffu;
+
+__device__ __forceinline__ double warp_incl_scan(double v, int lane) {
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        double t = __shfl_up_sync(FULL, v, d);
+        if (lane >= d) v += t;
+    }
+    return v;
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) v += __shfl_xor_sync(FULL, v, d);
+    return v;
+}
+__device__ __forceinline__ int warp_incl_scan_i(int v, int lane) {
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int t = __shfl_up_sync(FULL, v, d);
+        if (lane >= d) v += t;
+    }
+    return v;
+}
+// exclusive scan over the threads of a block (blockDim.x <= 1024, multiple of 32); returns the exclusive
+// prefix of v and writes the block total to *total.  `sm` is 33 ints of shared memory.
+__device__ __forceinline__ int block_excl_scan(int v, int *sm, int *total) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    int incl = warp_incl_scan_i(v, lane);
+    __syncthreads();
+    if (lane == 31) sm[wid] = incl;
+    __syncthreads();
+    if (wid == 0) {
+        int w = lane < nw ? sm[lane] : 0;
+        int wi = warp_incl_scan_i(w, lane);
+        sm[lane] = wi - w;
+        if (lane == 31) sm[32] = wi;
+    }
+    __syncthreads();
+    *total = sm[32];
+    return incl - v + sm[wid];
+}
+
+// ------------------------------------------------------------------------------------------ reset / root
+struct ResetArgs {
+    int32_t *seg_start, *seg_cnt, *gcnt, *nleft, *gnleft, *bslot, *t_feat;
+    uint8_t *kind, *t_bin, *t_split;
+    float *t_gain, *t_w, *t_pred;
+    uint32_t *t_packed;
+    double *nsum;
+    LevelPlan *plan;
+    int nids, nn, K, C, D;
+};
+__global__ void k_tree_reset(ResetArgs a) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < a.nids) {
+        a.seg_start[i] = 0; a.seg_cnt[i] = 0; a.gcnt[i] = 0; a.kind[i] = 0; a.bslot[i] = 0;
+        if (i > 0) { a.nleft[i] = 0; if (a.gnleft != a.nleft) a.gnleft[i] = 0; } // entry 0 carries the root count
+        for (int c = 0; c < a.C; ++c) a.nsum[(size_t)i * a.C + c] = 0.0;
+    }
+    if (i < a.nn) {
+        a.t_feat[i] = 0; a.t_bin[i] = 0; a.t_split[i] = 0; a.t_gain[i] = 0.f; a.t_w[i] = 0.f; a.t_packed[i] = 0u;
+        for (int k = 0; k < a.K; ++k) a.t_pred[(size_t)i * a.K + k] = 0.f;
+    }
+    if (i >= 2 && i <= a.D) { a.plan[i].nbuild = 0; a.plan[i].nitems = 0; a.plan[i].R = 0; }
+}
+
+struct RootArgs {
+    int32_t *seg_start, *seg_cnt, *gcnt, *bslot, *cum, *slot_node;
+    const int32_t *nleft, *gnleft;
+    uint8_t *kind;
+    LevelPlan *plan;
+};
+__global__ void k_root_plan(RootArgs a) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        const int nsel = a.nleft[0];
+        a.seg_start[1] = 0; a.seg_cnt[1] = nsel; a.gcnt[1] = a.gnleft[0];
+        a.kind[1] = EVB_KIND_BUILD; a.bslot[1] = 0;
+        a.cum[0] = 0; a.cum[1] = nsel; a.slot_node[0] = 1;
+        a.plan[1].nbuild = 1; a.plan[1].R = nsel; a.plan[1].n_sel = nsel; a.plan[1].nitems = 0;
+    }
+}
+
+// ------------------------------------------------------------------------------------------ split scan
+struct ScanArgs {
+    const double *hcomp;
+    double *hist, *nsum;
+    const uint8_t *kind;
+    const int32_t *bslot;
+    const uint32_t *js0;
+    const uint8_t *feattypes;
+    const int32_t *mono;
+    int32_t *t_feat;
+    uint8_t *t_bin, *t_split;
+    float *t_gain, *t_w, *t_pred;
+    uint32_t *t_packed;
+    int F, C, K, B, level, D, hist_nodes, loss;
+    double neb; // -eta / bagging_size
+    double lambda, L2, gamma, min_weight;
+};
+
+__device__ __forceinline__ double term_gh(double g, double h, double w, double lambda, double L2) {
+    return g * g / fmax(DBL_EPSILON, h + lambda * w + L2) / 2.0; // src/split.jl:1
+}
+// pred_leaf_cpu! for output row k (src/predict.jl:198-204, 224-234, 241-247)
+__device__ __forceinline__ float leaf_value(const ScanArgs &a, const double *s, int k) {
+    const int K = a.K, C = a.C;
+    double g, h;
+    if (a.loss == EVB_GAUSSIAN_MLE) {
+        const int Y = K / 2, t = k >> 1, j = k & 1;
+        g = s[2 * t + j];
+        h = s[2 * Y + 2 * t + j];
+    } else {
+        g = s[k];
+        h = s[K + k];
+    }
+    return (float)(a.neb * g / fmax(DBL_EPSILON, h + a.lambda * s[C - 1] + a.L2));
+}
+
+// one CTA per node of the level; warps stride over feature slots, lanes over bins
+__global__ void __launch_bounds__(256) k_scan(ScanArgs a) {
+    const int n = (1 << (a.level - 1)) + blockIdx.x;
+    const int kd = a.kind[n];
+    if (kd == EVB_KIND_NONE) return;
+    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+    const int C = a.C, K = a.K, B = a.B, F = a.F;
+    const size_t FCB = (size_t)F * C * B;
+    const double *hc = a.hcomp + (size_t)a.bslot[n] * FCB;
+    const bool sub = kd == EVB_KIND_SUB;
+    const double *hp = a.hist + (size_t)(n >> 1) * FCB;
+    const bool keep = n < a.hist_nodes;
+    double *hn = a.hist + (size_t)n * FCB;
+
+    __shared__ double s_sum[72], s_left[72];
+    __shared__ double s_gain[8];
+    __shared__ int s_slot[8], s_bin[8];
+    __shared__ int s_best_slot, s_best_bin;
+    __shared__ double s_best_gain;
+
+    if (n == 1) {
+        // root sums = sum over the bins of feature slot 0 (every sampled row has exactly one bin there);
+        // the reference sums the gradients of the sampled rows directly (src/fit.jl:66)
+        for (int c = wid; c < C; c += nw) {
+            double v = 0.0;
+            for (int b = lane; b < B; b += 32) v += hc[(size_t)c * B + b];
+            v = warp_sum(v);
+            if (lane == 0) a.nsum[(size_t)C + c] = v;
+        }
+        __syncthreads();
+    }
+    if (tid < C) s_sum[tid] = a.nsum[(size_t)n * C + tid];
+    __syncthreads();
+
+    const bool can_split = a.level < a.D;
+    double gain_p = 0.0;
+    const double w_p = s_sum[C - 1];
+    for (int k = 0; k < K; ++k) gain_p += term_gh(s_sum[k], s_sum[K + k], w_p, a.lambda, a.L2); // node_gain, split.jl:58-66
+
+    double best_gain = a.gamma; // get_best_split starts at gamma and takes strict improvements (fit-utils.jl:444-450)
+    int best_slot = -1, best_bin = -1;
+    const int nchk = (B + 31) >> 5;
+
+    if (can_split) {
+        for (int f = wid; f < F; f += nw) {
+            const uint32_t feat = a.js0[f];
+            const bool numeric = a.feattypes[feat] != 0;
+            const int constraint = a.mono[feat];
+            const int b_max = numeric ? B - 1 : B;
+            const size_t fo = (size_t)f * C * B;
+            auto val = [&](int c, int b) -> double {
+                const size_t o = fo + (size_t)c * B + b;
+                double v = hc[o];
+                if (sub) v = hp[o] - v; // subtract_hist!: parent - sibling (fit-utils.jl:321-332)
+                if (keep) hn[o] = v;
+                return v;
+            };
+            double wl[8], gacc[8];
+            unsigned okmask = 0xffu;
+            {
+                double carry = 0.0;
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    gacc[ch] = 0.0;
+                    wl[ch] = 0.0;
+                    if (ch < nchk) {
+                        const int b = ch * 32 + lane;
+                        double v = b < B ? val(C - 1, b) : 0.0;
+                        if (numeric) { v = warp_incl_scan(v, lane) + carry; carry = __shfl_sync(FULL, v, 31); }
+                        wl[ch] = v;
+                    }
+                }
+            }
+            for (int k = 0; k < K; ++k) {
+                double cg = 0.0, chh = 0.0;
+                const double sg = s_sum[k], sh = s_sum[K + k];
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    if (ch < nchk) {
+                        const int b = ch * 32 + lane;
+                        double gl = b < B ? val(k, b) : 0.0;
+                        double hl = b < B ? val(K + k, b) : 0.0;
+                        if (numeric) {
+                            gl = warp_incl_scan(gl, lane) + cg; cg = __shfl_sync(FULL, gl, 31);
+                            hl = warp_incl_scan(hl, lane) + chh; chh = __shfl_sync(FULL, hl, 31);
+                        }
+                        const double w_l = wl[ch], w_r = w_p - w_l;
+                        gacc[ch] += term_gh(gl, hl, w_l, a.lambda, a.L2) + term_gh(sg - gl, sh - hl, w_r, a.lambda, a.L2);
+                        if (k == 0 && constraint != 0) {
+                            // pred_scalar on left / right sums (src/predict.jl:205-208, 235-238)
+                            const double pl = a.neb * gl / fmax(DBL_EPSILON, hl + a.lambda * w_l + a.L2);
+                            const double pr = a.neb * (sg - gl) / fmax(DBL_EPSILON, (sh - hl) + a.lambda * w_r + a.L2);
+                            const bool ok = (constraint == -1 && pl > pr) || (constraint == 1 && pl < pr);
+                            if (!ok) okmask &= ~(1u << ch);
+                        }
+                    }
+                }
+            }
+            // candidate of this lane: lowest bin among its strict maxima
+            double lg = a.gamma;
+            int lb = 0x7fffffff;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+                if (ch < nchk) {
+                    const int b = ch * 32 + lane;
+                    const double w_l = wl[ch], w_r = w_p - w_l;
+                    if (b < b_max && w_l > a.min_weight && w_r > a.min_weight && ((okmask >> ch) & 1u)) {
+                        const double g = gacc[ch] - gain_p;
+                        if (g > lg) { lg = g; lb = b; }
+                    }
+                }
+            }
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) {
+                const double og = __shfl_xor_sync(FULL, lg, d);
+                const int ob = __shfl_xor_sync(FULL, lb, d);
+                if (og > lg || (og == lg && ob < lb)) { lg = og; lb = ob; }
+            }
+            if (lb != 0x7fffffff && lg > best_gain) { best_gain = lg; best_slot = f; best_bin = lb; }
+        }
+    }
+    if (lane == 0) { s_gain[wid] = best_gain; s_slot[wid] = best_slot; s_bin[wid] = best_bin; }
+    __syncthreads();
+    if (tid == 0) {
+        double bg = a.gamma; int bs = -1, bb = -1;
+        for (int w = 0; w < nw; ++w) {
+            if (s_slot[w] >= 0 && (s_gain[w] > bg || (s_gain[w] == bg && bs >= 0 && s_slot[w] < bs))) {
+                bg = s_gain[w]; bs = s_slot[w]; bb = s_bin[w];
+            }
+        }
+        s_best_gain = bg; s_best_slot = bs; s_best_bin = bb;
+    }
+    __syncthreads();
+    const int bs = s_best_slot, bb = s_best_bin;
+    if (bs >= 0) {
+        // _child_sums!: left = bins 1..bin of the winning feature (numeric) or that bin (categorical)
+        const uint32_t feat = a.js0[bs];
+        const bool numeric = a.feattypes[feat] != 0;
+        const size_t fo = (size_t)bs * C * B;
+        for (int c = wid; c < C; c += nw) {
+            double v = 0.0;
+            if (numeric) {
+                for (int b = lane; b <= bb; b += 32) {
+                    const size_t o = fo + (size_t)c * B + b;
+                    v += sub ? hp[o] - hc[o] : hc[o];
+                }
+                v = warp_sum(v);
+            } else {
+                const size_t o = fo + (size_t)c * B + bb;
+                v = sub ? hp[o] - hc[o] : hc[o];
+            }
+            if (lane == 0) s_left[c] = v;
+        }
+        __syncthreads();
+        const int nl = n << 1, nr = nl + 1;
+        if (tid < C) {
+            a.nsum[(size_t)nl * C + tid] = s_left[tid];
+            a.nsum[(size_t)nr * C + tid] = s_sum[tid] - s_left[tid];
+        }
+        if (tid == 0) {
+            a.t_w[n - 1] = (float)s_sum[C - 1];
+            a.t_gain[n - 1] = (float)s_best_gain;
+            a.t_bin[n - 1] = (uint8_t)(bb + 1);
+            a.t_feat[n - 1] = (int32_t)feat + 1;
+            a.t_split[n - 1] = 1;
+            a.t_packed[n - 1] = feat | ((uint32_t)(bb + 1) << 16) | (1u << 24) | ((numeric ? 1u : 0u) << 25);
+        }
+        if (a.level + 1 == a.D) {
+            // children sit at max depth: they are leaves (src/fit.jl:74-82)
+            __shared__ double s_right[72];
+            if (tid < C) s_right[tid] = s_sum[tid] - s_left[tid];
+            __syncthreads();
+            if (tid < K) {
+                a.t_pred[(size_t)(nl - 1) * K + tid] = leaf_value(a, s_left, tid);
+                a.t_pred[(size_t)(nr - 1) * K + tid] = leaf_value(a, s_right, tid);
+            }
+            if (tid == 0) { a.t_w[nl - 1] = (float)s_left[C - 1]; a.t_w[nr - 1] = (float)s_right[C - 1]; }
+        }
+    } else {
+        if (tid == 0) a.t_w[n - 1] = (float)s_sum[C - 1];
+        if (tid < K) a.t_pred[(size_t)(n - 1) * K + tid] = leaf_value(a, s_sum, tid);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ partition
+struct PartArgs {
+    const uint8_t *xT;
+    const uint32_t *rows_in;
+    uint32_t *rows_out;
+    const uint8_t *t_split;
+    const uint32_t *t_packed;
+    int32_t *seg_start, *seg_cnt, *gcnt, *nleft, *bslot, *cum, *slot_node;
+    const int32_t *gnleft;
+    uint8_t *kind;
+    int32_t *ibase;       // [level nodes + 1] exclusive prefix of items per node
+    int32_t *item_left, *item_lprefix;
+    uint32_t *item_bits;
+    LevelPlan *plan;
+    int RS, level, D, max_items;
+    int *err;
+};
+
+__global__ void __launch_bounds__(1024) k_part_plan(PartArgs a) {
+    __shared__ int sm[33];
+    const int lo = 1 << (a.level - 1), m = lo;
+    int carry = 0;
+    for (int base = 0; base < m; base += blockDim.x) {
+        const int i = base + threadIdx.x;
+        int cnt = 0;
+        if (i < m && a.t_split[lo + i - 1]) cnt = (a.seg_cnt[lo + i] + EVB_PART_CHUNK - 1) / EVB_PART_CHUNK;
+        int total;
+        const int ex = block_excl_scan(cnt, sm, &total);
+        if (i < m) a.ibase[i] = carry + ex;
+        carry += total;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        if (carry > a.max_items) { atomicCAS(a.err, 0, EVB_DERR_PLAN); carry = 0; }
+        a.ibase[m] = carry;
+        a.plan[a.level].nitems = carry;
+    }
+}
+
+__device__ __forceinline__ void item_lookup(const PartArgs &a, int item, int &n, int &chunk) {
+    const int m = 1 << (a.level - 1);
+    int l = 0, r = m - 1; // largest i with ibase[i] <= item
+    while (l < r) { const int mid = (l + r + 1) >> 1; if (a.ibase[mid] <= item) l = mid; else r = mid - 1; }
+    n = m + l;
+    chunk = item - a.ibase[l];
+}
+
+__global__ void __launch_bounds__(EVB_PART_THREADS) k_part_flags(PartArgs a) {
+    __shared__ int s_cnt[EVB_PART_THREADS / 32];
+    const int nitems = a.plan[a.level].nitems;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+        int n, chunk;
+        item_lookup(a, item, n, chunk);
+        const int start = a.seg_start[n] + chunk * EVB_PART_CHUNK;
+        const int cnt = min(EVB_PART_CHUNK, a.seg_cnt[n] - chunk * EVB_PART_CHUNK);
+        const uint32_t pk = a.t_packed[n - 1];
+        const uint32_t feat = pk & 0xffffu, bin = (pk >> 16) & 0xffu;
+        const bool numeric = (pk >> 25) & 1u;
+        int local = 0;
+#pragma unroll
+        for (int i8 = 0; i8 < EVB_PART_CHUNK / EVB_PART_THREADS; ++i8) {
+            const int pos = i8 * EVB_PART_THREADS + threadIdx.x;
+            bool left = false;
+            if (pos < cnt) {
+                const uint32_t row = a.rows_in[start + pos];
+                const uint32_t x = a.xT[(size_t)row * a.RS + feat];
+                left = numeric ? (x <= bin) : (x == bin); // split_set! predicate (fit-utils.jl:173, 291)
+            }
+            const unsigned bal = __ballot_sync(FULL, left);
+            if (lane == 0) {
+                a.item_bits[(size_t)item * (EVB_PART_CHUNK / 32) + i8 * (EVB_PART_THREADS / 32) + wid] = bal;
+                local += __popc(bal);
+            }
+        }
+        if (lane == 0) s_cnt[wid] = local;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int t = 0;
+            for (int w = 0; w < EVB_PART_THREADS / 32; ++w) t += s_cnt[w];
+            a.item_left[item] = t;
+        }
+        __syncthreads();
+    }
+}
+
+// warp per node: exclusive prefix of the left counts of the node's items, and the node's left total
+__global__ void k_part_prefix(PartArgs a) {
+    const int lo = 1 << (a.level - 1), m = lo;
+    const int lane = threadIdx.x & 31;
+    const int wglobal = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    for (int i = wglobal; i < m; i += nwarps) {
+        const int n = lo + i;
+        int running = 0;
+        if (a.t_split[n - 1]) {
+            const int j0 = a.ibase[i], j1 = a.ibase[i + 1];
+            for (int j = j0; j < j1; j += 32) {
+                const int v = (j + lane < j1) ? a.item_left[j + lane] : 0;
+                const int incl = warp_incl_scan_i(v, lane);
+                if (j + lane < j1) a.item_lprefix[j + lane] = running + incl - v;
+                running += __shfl_sync(FULL, incl, 31);
+            }
+        }
+        if (lane == 0) a.nleft[n] = running;
+    }
+}
+
+// children segments / counts, build-or-subtract choice (src/fit.jl:123-129: the child with fewer rows is
+// built, ties build the left child), build slots and the histogram plan of the next level
+__global__ void __launch_bounds__(1024) k_level_plan(PartArgs a) {
+    __shared__ int sm[33];
+    const int lo = 1 << (a.level - 1), m = lo;
+    const bool scan_children = a.level + 1 < a.D;
+    int carry_slot = 0, carry_rows = 0;
+    for (int base = 0; base < m; base += blockDim.x) {
+        const int i = base + threadIdx.x;
+        const int n = lo + i;
+        int sp = 0, cnt_build = 0, build_child = 0;
+        if (i < m && a.t_split[n - 1]) {
+            sp = 1;
+            const int L = n << 1, Rn = L + 1;
+            const int nl = a.nleft[n], gl = a.gnleft[n];
+            const int s0 = a.seg_start[n], c0 = a.seg_cnt[n], g0 = a.gcnt[n];
+            a.seg_start[L] = s0; a.seg_cnt[L] = nl; a.gcnt[L] = gl;
+            a.seg_start[Rn] = s0 + nl; a.seg_cnt[Rn] = c0 - nl; a.gcnt[Rn] = g0 - gl;
+            if (scan_children) {
+                const bool build_left = (g0 - gl) >= gl;
+                a.kind[L] = build_left ? EVB_KIND_BUILD : EVB_KIND_SUB;
+                a.kind[Rn] = build_left ? EVB_KIND_SUB : EVB_KIND_BUILD;
+                build_child = build_left ? L : Rn;
+                cnt_build = build_left ? nl : c0 - nl;
+            }
+        }
+        int tot_s, tot_r;
+        const int slot = carry_slot + block_excl_scan(scan_children ? sp : 0, sm, &tot_s);
+        __syncthreads();
+        const int cpre = carry_rows + block_excl_scan(cnt_build, sm, &tot_r);
+        if (sp && scan_children) {
+            a.bslot[n << 1] = slot; a.bslot[(n << 1) + 1] = slot;
+            a.slot_node[slot] = build_child;
+            a.cum[slot] = cpre;
+        }
+        carry_slot += tot_s; carry_rows += tot_r;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && a.level + 1 <= a.D) {
+        a.cum[carry_slot] = carry_rows;
+        a.plan[a.level + 1].nbuild = carry_slot;
+        a.plan[a.level + 1].R = carry_rows;
+    }
+}
+
+__global__ void __launch_bounds__(EVB_PART_THREADS) k_part_scatter(PartArgs a) {
+    constexpr int NW = EVB_PART_CHUNK / 32;
+    __shared__ uint32_t s_bits[NW];
+    __shared__ int s_pref[NW];
+    const int nitems = a.plan[a.level].nitems;
+    const int lane = threadIdx.x & 31;
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+        int n, chunk;
+        item_lookup(a, item, n, chunk);
+        const int start = a.seg_start[n] + chunk * EVB_PART_CHUNK;
+        const int cnt = min(EVB_PART_CHUNK, a.seg_cnt[n] - chunk * EVB_PART_CHUNK);
+        const int nL = a.nleft[n], lp = a.item_lprefix[item];
+        if (threadIdx.x < NW) s_bits[threadIdx.x] = a.item_bits[(size_t)item * NW + threadIdx.x];
+        __syncthreads();
+        if (threadIdx.x < 32) { // NW == 64: two words per lane
+            const int c0 = __popc(s_bits[2 * lane]), c1 = __popc(s_bits[2 * lane + 1]);
+            const int incl = warp_incl_scan_i(c0 + c1, lane);
+            s_pref[2 * lane] = incl - c0 - c1;
+            s_pref[2 * lane + 1] = incl - c1;
+        }
+        __syncthreads();
+        const int dstL = a.seg_start[n] + lp;
+        const int dstR = a.seg_start[n] + nL + (chunk * EVB_PART_CHUNK - lp);
+#pragma unroll
+        for (int i8 = 0; i8 < EVB_PART_CHUNK / EVB_PART_THREADS; ++i8) {
+            const int pos = i8 * EVB_PART_THREADS + threadIdx.x;
+            if (pos < cnt) {
+                const uint32_t row = a.rows_in[start + pos];
+                const uint32_t word = s_bits[pos >> 5];
+                const int before = s_pref[pos >> 5] + __popc(word & ((1u << lane) - 1u));
+                if ((word >> lane) & 1u) a.rows_out[dstL + before] = row;
+                else a.rows_out[dstR + (pos - before)] = row;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+PartArgs make_part_args(evb_handle *h, int level) {
+    PartArgs a;
+    a.xT = h->xT; a.rows_in = h->rows[(level - 1) & 1]; a.rows_out = h->rows[level & 1];
+    a.t_split = h->t_split; a.t_packed = h->t_packed;
+    a.seg_start = h->seg_start; a.seg_cnt = h->seg_cnt; a.gcnt = h->gcnt; a.nleft = h->nleft; a.gnleft = h->gnleft;
+    a.bslot = h->bslot; a.cum = h->cum; a.slot_node = h->slot_node; a.kind = h->kind;
+    a.ibase = h->item_node; a.item_left = h->item_left; a.item_lprefix = h->item_lprefix; a.item_bits = h->item_bits;
+    a.plan = h->plan; a.RS = h->RS; a.level = level; a.D = h->D; a.max_items = h->max_items; a.err = h->d_err;
+    return a;
+}
+
+} // namespace
+
+static_assert(EVB_PART_CHUNK == 2048 && EVB_PART_THREADS == 256, "k_part_scatter assumes 64 ballot words per item");
+
+int32_t evb_launch_tree_reset(evb_handle *h) {
+    ResetArgs a;
+    a.seg_start = h->seg_start; a.seg_cnt = h->seg_cnt; a.gcnt = h->gcnt; a.nleft = h->nleft; a.gnleft = h->gnleft;
+    a.bslot = h->bslot; a.t_feat = h->t_feat; a.kind = h->kind; a.t_bin = h->t_bin; a.t_split = h->t_split;
+    a.t_gain = h->t_gain; a.t_w = h->t_w; a.t_pred = h->t_pred; a.t_packed = h->t_packed; a.nsum = h->nsum;
+    a.plan = h->plan; a.nids = h->nn + 2; a.nn = h->nn; a.K = h->K; a.C = h->C; a.D = h->D;
+    const int threads = 256, blocks = (a.nids + threads - 1) / threads;
+    evb_tic(h, EVB_T_PLAN);
+    k_tree_reset<<<blocks, threads, 0, h->st>>>(a);
+    evb_toc(h, EVB_T_PLAN);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+int32_t evb_launch_root_plan(evb_handle *h) {
+    RootArgs a;
+    a.seg_start = h->seg_start; a.seg_cnt = h->seg_cnt; a.gcnt = h->gcnt; a.bslot = h->bslot; a.cum = h->cum;
+    a.slot_node = h->slot_node; a.nleft = h->nleft; a.gnleft = h->gnleft; a.kind = h->kind; a.plan = h->plan;
+    evb_tic(h, EVB_T_PLAN);
+    k_root_plan<<<1, 32, 0, h->st>>>(a);
+    evb_toc(h, EVB_T_PLAN);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+int32_t evb_launch_scan(evb_handle *h, int level) {
+    ScanArgs a;
+    a.hcomp = h->hcomp; a.hist = h->hist; a.nsum = h->nsum; a.kind = h->kind; a.bslot = h->bslot; a.js0 = h->js_d;
+    a.feattypes = h->feattypes_d; a.mono = h->mono_d; a.t_feat = h->t_feat; a.t_bin = h->t_bin; a.t_split = h->t_split;
+    a.t_gain = h->t_gain; a.t_w = h->t_w; a.t_pred = h->t_pred; a.t_packed = h->t_packed;
+    a.F = h->F; a.C = h->C; a.K = h->K; a.B = h->B; a.level = level; a.D = h->D; a.hist_nodes = h->hist_nodes;
+    a.loss = h->p.loss; a.neb = -h->p.eta / (double)h->p.bagging_size;
+    a.lambda = h->p.lambda; a.L2 = h->p.L2; a.gamma = h->p.gamma; a.min_weight = h->p.min_weight;
+    evb_tic(h, EVB_T_SCAN);
+    k_scan<<<evb_level_nodes(level), 256, 0, h->st>>>(a);
+    evb_toc(h, EVB_T_SCAN);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+int32_t evb_launch_partition(evb_handle *h, int level) {
+    PartArgs a = make_part_args(h, level);
+    const int m = evb_level_nodes(level);
+    int pgrid = h->num_sms * 8;
+    if (pgrid > h->max_items) pgrid = h->max_items;
+    if (pgrid < 1) pgrid = 1;
+    evb_tic(h, EVB_T_PLAN);
+    k_part_plan<<<1, 1024, 0, h->st>>>(a);
+    evb_toc(h, EVB_T_PLAN);
+    evb_tic(h, EVB_T_PARTITION);
+    k_part_flags<<<pgrid, EVB_PART_THREADS, 0, h->st>>>(a);
+    evb_toc(h, EVB_T_PARTITION);
+    evb_tic(h, EVB_T_PLAN);
+    int wblocks = (m * 32 + 255) / 256;
+    if (wblocks > h->num_sms * 4) wblocks = h->num_sms * 4;
+    k_part_prefix<<<wblocks, 256, 0, h->st>>>(a);
+    evb_toc(h, EVB_T_PLAN);
+    EVB_CUDA(cudaGetLastError());
+    if (h->world > 1) {
+        evb_tic(h, EVB_T_ALLREDUCE);
+        int32_t s = evb_nccl_allreduce_i32(h, h->nleft + m, h->gnleft + m, (size_t)m);
+        evb_toc(h, EVB_T_ALLREDUCE);
+        EVB_CHECK(s);
+    }
+    evb_tic(h, EVB_T_PLAN);
+    k_level_plan<<<1, 1024, 0, h->st>>>(a);
+    evb_toc(h, EVB_T_PLAN);
+    evb_tic(h, EVB_T_PARTITION);
+    k_part_scatter<<<pgrid, EVB_PART_THREADS, 0, h->st>>>(a);
+    evb_toc(h, EVB_T_PARTITION);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}

@@ -1,0 +1,251 @@
+"""Training driver mirroring `init_core` / `grow_evotree!` / `fit` of the reference's GPU extension
+(ext/EvoTreesKernelAbstractionsExt/init.jl:1-151, ext/.../fit.jl:1-21, src/fit.jl:388-437).
+
+The host keeps what the reference keeps on the host: the RNG (row mask bytes, column sample), the quantile
+edges, the initial bias and the `Tree` containers.  Everything else happens behind `evb_grow_tree`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+
+from . import _lib
+from .binning import binarize, get_edges
+from .learners import EvoTypes
+from .model import EvoTree, Tree
+
+
+def _logit(x):
+    return np.log(x / (1 - x))
+
+
+def _invsoftplus(x):
+    return x + math.log(-math.expm1(-x))  # src/loss.jl:266-268
+
+
+def init_target(loss: str, y_train: np.ndarray, offset):
+    """`_init_target` (src/init.jl:10-146) for the four losses of this path.
+    Returns K, y (device dtype), ycols, mu float32 [K], target_levels, offset (link space)."""
+    levels = None
+    if loss in ("mse", "logloss"):
+        y = np.ascontiguousarray(y_train, np.float32)
+        ycols = 1 if y.ndim == 1 else y.shape[1]
+        K = ycols
+        m = y.reshape(y.shape[0], -1).mean(axis=0, dtype=np.float32)
+        if loss == "logloss":
+            if y.min() < 0 or y.max() > 1:
+                raise ValueError("logloss targets must lie in [0, 1]")
+            mu = _logit(m).astype(np.float32)
+            if offset is not None:
+                offset = _logit(offset)
+        else:
+            mu = m.astype(np.float32)
+    elif loss == "mlogloss":
+        yt = np.asarray(y_train)
+        if yt.ndim != 1 or not (np.issubdtype(yt.dtype, np.integer) or yt.dtype == bool or yt.dtype.kind in "US"):
+            raise ValueError(f"Invalid target eltype: {yt.dtype}")
+        levels, codes = np.unique(yt, return_inverse=True)
+        K = int(levels.size)
+        if K < 2:
+            raise ValueError(f"Classification requires a target with at least 2 levels, got {K}")
+        y = (codes + 1).astype(np.uint32)
+        ycols = 1
+        prop = np.bincount(codes, minlength=K) / codes.size
+        mu = np.log(prop).astype(np.float32)
+        mu -= mu.max()
+        if offset is not None:
+            offset = np.log(offset)
+    elif loss == "gaussian_mle":
+        y = np.ascontiguousarray(y_train, np.float32)
+        ycols = 1 if y.ndim == 1 else y.shape[1]
+        K = 2 * ycols
+        y2 = y.reshape(y.shape[0], -1)
+        mu = np.empty(K, np.float32)
+        for t in range(ycols):
+            mu[2 * t] = y2[:, t].mean(dtype=np.float32)
+            mu[2 * t + 1] = _invsoftplus(float(np.std(y2[:, t].astype(np.float64), ddof=1)))
+        if offset is not None:
+            offset = np.array(offset, np.float32, copy=True)
+            offset[:, 1::2] = [[_invsoftplus(float(v)) for v in row] for row in offset[:, 1::2]]
+    else:
+        raise ValueError(loss)
+    return K, y, ycols, mu.astype(np.float32), levels, offset
+
+
+class Cache:
+    """Training cache: owns the device handle (counterpart of `CacheBaseGPU`,
+    ext/EvoTreesKernelAbstractionsExt/structs.jl).  It survives `fit` so that boosting can be resumed
+    (the reference's MLJ `update`, src/MLJ.jl:38-57)."""
+
+    def __init__(self):
+        self.handle = C.c_void_p()
+        self.rng = None
+        self.nobs = self.nfeats = 0
+        self.njs = 0
+        self.mask_cond = 255
+        self.use_mask = False
+        self.K = 1
+        self.nn = 0
+        self.feature_names = None
+
+    def close(self):
+        if self.handle:
+            _lib.lib().evb_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # read-backs used by the parity tests
+    def pred(self):
+        out = np.empty((self.nobs, self.K), np.float32)
+        _lib.check(_lib.lib().evb_get_pred(self.handle, _lib.ptr(out)))
+        return out
+
+    def grads(self):
+        out = np.empty((self.nobs, 2 * self.K + 1), np.float32)
+        _lib.check(_lib.lib().evb_get_grads(self.handle, _lib.ptr(out)))
+        return out
+
+    def nidx(self, from_partition: bool = False):
+        out = np.empty(self.nobs, np.uint32)
+        _lib.check(_lib.lib().evb_get_nidx(self.handle, _lib.ptr(out), C.c_int32(1 if from_partition else 0)))
+        return out
+
+    def hist(self, node: int, njs: int, nbins: int):
+        out = np.empty((njs, nbins, 2 * self.K + 1), np.float64)  # == Julia [C, B, njs]
+        _lib.check(_lib.lib().evb_get_hist(self.handle, C.c_int32(node), _lib.ptr(out)))
+        return out
+
+    def node_sums(self):
+        out = np.empty((self.nn, 2 * self.K + 1), np.float64)
+        _lib.check(_lib.lib().evb_get_node_sums(self.handle, _lib.ptr(out)))
+        return out
+
+    def timings(self) -> dict:
+        t = _lib.EvbTimings()
+        _lib.check(_lib.lib().evb_get_timings(self.handle, C.byref(t)))
+        return {"ms": {n: t.ms[i] for i, n in enumerate(_lib.TIMER_NAMES)},
+                "launches": {n: t.launches[i] for i, n in enumerate(_lib.TIMER_NAMES)},
+                "hist_rows": t.hist_rows, "hist_nodes": t.hist_nodes, "trees": t.trees}
+
+    def reset_timings(self):
+        _lib.check(_lib.lib().evb_reset_timings(self.handle))
+
+
+def make_params(params: EvoTypes, K: int, device: int, flags: int = 0) -> _lib.EvbParams:
+    return _lib.EvbParams(_lib.LOSS_CODES[params.loss], K, params.nbins, params.max_depth, params.bagging_size, 0,
+                          params.eta, params.lambda_, params.L2, params.gamma, params.min_weight, device, flags)
+
+
+def init_core_binned(params: EvoTypes, x_bin: np.ndarray, y, ycols: int, K: int, mu: np.ndarray, w=None, pred0=None,
+                     feattypes=None, device: int = 0, flags: int = 0, comm=None) -> Cache:
+    """Creates the device handle from an already binned matrix (uint8, Fortran order, values 1..nbins)."""
+    assert x_bin.dtype == np.uint8 and x_bin.flags.f_contiguous
+    nobs, nfeats = x_bin.shape
+    cache = Cache()
+    cache.nobs, cache.nfeats, cache.K, cache.nn = nobs, nfeats, K, 2 ** params.max_depth - 1
+    cache.njs = math.ceil(params.colsample * nfeats)            # src/init.jl:181
+    cache.mask_cond = int(np.uint8(round(255 * params.rowsample)))  # src/subsample.jl:9
+    cache.use_mask = params.rowsample < 1.0
+    cache.rng = np.random.default_rng(params.seed)
+    mono = np.zeros(nfeats, np.int32)
+    for k, v in params.monotone_constraints.items():
+        mono[int(k) - 1] = int(v)
+    ft = None if feattypes is None else np.ascontiguousarray(feattypes, np.uint8)
+    w32 = None if w is None else np.ascontiguousarray(w, np.float32)
+    if w32 is not None and (w32.size != nobs or w32.min() <= 0):
+        raise ValueError("weights must be positive and of length nobs")   # src/init.jl:165
+    p0 = None if pred0 is None else np.ascontiguousarray(pred0, np.float32)
+    cp = make_params(params, K, device, flags)
+    ydt = _lib.EVB_U32 if params.loss == "mlogloss" else _lib.EVB_F32
+    mu32 = np.ascontiguousarray(mu, np.float32)
+    _lib.check(_lib.lib().evb_create(C.byref(cache.handle), C.byref(cp), C.c_int64(nobs), C.c_int32(nfeats), _lib.ptr(x_bin),
+                                     _lib.ptr(y), C.c_int32(ydt), C.c_int32(ycols), _lib.ptr(w32), _lib.ptr(p0), _lib.ptr(mu32),
+                                     _lib.ptr(ft), _lib.ptr(mono)))
+    if comm is not None:
+        comm.attach(cache)
+    return cache
+
+
+def init_core(params: EvoTypes, x_train: np.ndarray, y_train, w_train=None, offset_train=None, feature_names=None,
+              device: int = 0, flags: int = 0, comm=None):
+    """`init_core(params, ::Type{<:GPU}, ...)`: edges + binarize + target / bias initialisation + device cache.
+    Returns (EvoTree, Cache).  With `comm` (multi-GPU) `x_train` / `y_train` are this rank's row shard and
+    the edges and the bias are computed from rank 0's shard and broadcast."""
+    x_train = np.asarray(x_train)
+    if x_train.dtype not in (np.float32, np.float64):
+        x_train = x_train.astype(np.float64)
+    if np.isnan(x_train).any():
+        raise ValueError("missing / NaN feature values are not supported")   # test/missings.jl
+    nobs, nfeats = x_train.shape
+    rng = np.random.default_rng(params.seed)
+    edges, featbins, feattypes = get_edges(x_train, params.nbins, rng)
+    offset = None if offset_train is None else np.array(offset_train, np.float32, copy=True).reshape(nobs, -1)
+    K, y, ycols, mu, levels, offset = init_target(params.loss, y_train, offset)
+    if comm is not None:
+        edges, mu = comm.broadcast_host(edges), comm.allreduce_bias(params.loss, y, mu, K)
+    x_bin = binarize(x_train, edges, device)
+    pred0 = None
+    if offset is not None:
+        mu = np.zeros_like(mu)                                               # src/init.jl:164
+        pred0 = np.ascontiguousarray(np.broadcast_to(mu, (nobs, K)) + offset, np.float32)
+    cache = init_core_binned(params, x_bin, y, ycols, K, mu, w_train, pred0, feattypes, device, flags, comm)
+    cache.rng = rng
+    names = [f"feat_{i + 1}" for i in range(nfeats)] if feature_names is None else [str(s) for s in feature_names]
+    if len(names) != nfeats:
+        raise ValueError("feature_names must have one entry per column of x_train")
+    cache.feature_names = names
+    info = {"nrounds": 0, "feature_names": names, "target_levels": levels, "edges": edges, "featbins": featbins,
+            "feattypes": feattypes}
+    m = EvoTree(params.loss, K, [Tree.bias(mu)], info)
+    return m, cache
+
+
+def sample_round(cache: Cache, params: EvoTypes):
+    """Row mask bytes and the ascending column sample of one bag (src/subsample.jl:7, src/fit.jl:16).
+    The mask is only drawn when rowsample < 1: with rowsample == 1 every byte passes `mask <= 255`."""
+    mask = cache.rng.integers(0, 256, size=cache.nobs, dtype=np.uint8) if cache.use_mask else None
+    if cache.njs >= cache.nfeats:
+        js = np.arange(1, cache.nfeats + 1, dtype=np.uint32)
+    else:
+        js = (np.sort(cache.rng.choice(cache.nfeats, size=cache.njs, replace=False)) + 1).astype(np.uint32)
+    return mask, js
+
+
+def grow_tree(cache: Cache, params: EvoTypes, mask, js, update_grads: bool) -> Tree:
+    """One `evb_grow_tree` call; returns the tree with the reference's `Tree` layout."""
+    t = Tree.empty(params.max_depth, cache.K)
+    js = np.ascontiguousarray(js, np.uint32)
+    _lib.check(_lib.lib().evb_grow_tree(cache.handle, _lib.ptr(mask), C.c_uint8(cache.mask_cond), _lib.ptr(js),
+                                        C.c_int32(js.size), C.c_int32(1 if update_grads else 0), _lib.ptr(t.feat),
+                                        _lib.ptr(t.cond_bin), _lib.ptr(t.w), _lib.ptr(t.gain), _lib.ptr(t.pred), _lib.ptr(t.split)))
+    return t
+
+
+def grow_evotree(m: EvoTree, cache: Cache, params: EvoTypes) -> None:
+    """`grow_evotree!(m, cache, params)`: one boosting round = bagging_size trees."""
+    for b in range(params.bagging_size):
+        mask, js = sample_round(cache, params)
+        m.trees.append(grow_tree(cache, params, mask, js, update_grads=(b == 0)))
+    m.info["nrounds"] += 1
+
+
+def fit(params: EvoTypes, *, x_train, y_train, w_train=None, offset_train=None, x_eval=None, y_eval=None,
+        feature_names=None, device: int = 0, return_cache: bool = False, comm=None, **_ignored):
+    """`fit(params; x_train, y_train, w_train, offset_train, feature_names)` (src/fit.jl:388-437).
+    Evaluation data / early stopping are not part of this device path yet and are rejected."""
+    if x_eval is not None or y_eval is not None:
+        raise NotImplementedError("x_eval / y_eval (eval metric tracking, early stopping) are not built for this device path")
+    m, cache = init_core(params, x_train, y_train, w_train, offset_train, feature_names, device, comm=comm)
+    for _ in range(params.nrounds):
+        grow_evotree(m, cache, params)
+    if return_cache:
+        return m, cache
+    cache.close()
+    return m

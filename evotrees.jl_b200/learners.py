@@ -1,0 +1,87 @@
+"""Learner configurations mirroring the reference's keyword constructors (src/learners.jl).
+
+Only the hyper-parameters that reach the device path are kept; names, defaults and validation follow
+`EvoTreeRegressor` (src/learners.jl:25-119), `EvoTreeClassifier` and `EvoTreeMLE` (min_weight defaults
+to 8 there) and `check_args` (src/learners.jl:522-552).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+_REG_LOSSES = ("mse", "logloss")
+_MLE_LOSSES = ("gaussian_mle",)
+
+
+def _check(name, value, lo, hi):
+    if not (lo <= value <= hi):
+        raise ValueError(f"Invalid value for parameter `{name}`: {value}. `{name}` must be between {lo} and {hi}.")
+
+
+@dataclass
+class EvoTypes:
+    loss: str = "mse"
+    nrounds: int = 100
+    bagging_size: int = 1
+    L2: float = 1.0
+    lambda_: float = 0.0
+    gamma: float = 0.0
+    eta: float = 0.1
+    max_depth: int = 6
+    min_weight: float = 1.0
+    rowsample: float = 1.0
+    colsample: float = 1.0
+    nbins: int = 64
+    monotone_constraints: dict = field(default_factory=dict)  # {feature (1-based): -1 | 0 | 1}
+    tree_type: str = "binary"
+    seed: int = 123
+    device: str = "gpu"
+    early_stopping_rounds: int = 2 ** 62
+    metric: str | None = None
+
+    _losses = ()
+
+    def __post_init__(self):
+        self.loss = str(self.loss)
+        if self.loss == "linear":
+            self.loss = "mse"
+        if self.loss == "logistic":
+            self.loss = "logloss"
+        if self.loss == "gaussian":
+            self.loss = "gaussian_mle"
+        if self.loss not in self._losses:
+            raise ValueError(f"Invalid loss. Must be one of: {list(self._losses)}")
+        self.check_args()
+
+    def check_args(self):
+        _check("nrounds", self.nrounds, 0, 2 ** 62)
+        _check("max_depth", self.max_depth, 1, 15)
+        _check("nbins", self.nbins, 2, 255)
+        _check("lambda", self.lambda_, 0.0, float("inf"))
+        _check("gamma", self.gamma, 0.0, float("inf"))
+        _check("min_weight", self.min_weight, 0.0, float("inf"))
+        _check("rowsample", self.rowsample, 2.220446049250313e-16, 1.0)
+        _check("colsample", self.colsample, 2.220446049250313e-16, 1.0)
+        _check("eta", self.eta, 0.0, float("inf"))
+        _check("bagging_size", self.bagging_size, 1, 2 ** 31)
+        if self.tree_type != "binary":
+            raise ValueError("Invalid input for `tree_type` parameter: only `binary` trees are built by this device path")
+        if self.device not in ("gpu", "cuda"):
+            raise ValueError("device must be :gpu / :cuda: this package has no CPU path")
+
+
+@dataclass
+class EvoTreeRegressor(EvoTypes):
+    _losses = _REG_LOSSES
+
+
+@dataclass
+class EvoTreeClassifier(EvoTypes):
+    loss: str = "mlogloss"
+    _losses = ("mlogloss",)
+
+
+@dataclass
+class EvoTreeMLE(EvoTypes):
+    loss: str = "gaussian_mle"
+    min_weight: float = 8.0
+    _losses = _MLE_LOSSES

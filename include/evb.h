@@ -1,0 +1,168 @@
+/*
+ * evb.h -- C ABI of libevotrees_b200.so: the EvoTrees training / inference hot path as hand-written
+ * sm_100a CUDA kernels.
+ *
+ * The library takes the place of the reference's GPU extension (ext/EvoTreesKernelAbstractionsExt/
+ * behind ext/EvoTreesCUDAExt.jl).  Host glue (Julia through `ccall`, or the Python mirror shipped in
+ * this repository) keeps everything that the reference keeps on the host: learner structs, the RNG
+ * (row mask bytes, column samples), quantile edges, the initial bias and the `Tree` / `EvoTree`
+ * containers.  The library owns all device memory behind an opaque handle.
+ *
+ * Conventions
+ *   - every function returns 0 on success and a negative `evb_status` otherwise; a message for the
+ *     last failure of the calling thread is available from evb_last_error();
+ *   - host arrays are caller-owned and only touched during the call;
+ *   - matrices use the reference's (Julia, column-major) layout; feature ids, node ids, class codes
+ *     and bins are 1-based at this boundary exactly as in the reference's `Tree` fields;
+ *   - one handle = one GPU = one shard of rows.  A handle must be used by one host thread at a time.
+ *   - there is no CPU fallback: every entry point fails with EVB_ERR_CUDA when no sm_100 GPU is usable.
+ */
+#ifndef EVB_H
+#define EVB_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define EVB_API __attribute__((visibility("default")))
+#else
+#define EVB_API
+#endif
+
+typedef struct evb_handle evb_handle;
+
+enum evb_status {
+    EVB_OK = 0,
+    EVB_ERR_ARG = -1,      /* invalid argument                                   */
+    EVB_ERR_CUDA = -2,     /* CUDA runtime error (message has the CUDA string)   */
+    EVB_ERR_NCCL = -3,     /* NCCL error or NCCL not loadable                    */
+    EVB_ERR_EMPTY = -4,    /* row subsample selected no row (src/subsample.jl:36) */
+    EVB_ERR_DEVICE = -5,   /* a kernel reported a failed self-check / bounded wait */
+    EVB_ERR_BUSY = -6,     /* handle used concurrently                           */
+    EVB_ERR_LIMIT = -7     /* size beyond a documented limit                     */
+};
+
+enum evb_loss { EVB_MSE = 0, EVB_LOGLOSS = 1, EVB_MLOGLOSS = 2, EVB_GAUSSIAN_MLE = 3 };
+enum evb_dtype { EVB_F32 = 0, EVB_U32 = 1, EVB_F64 = 2 };
+
+/* flags of evb_params.flags */
+#define EVB_FLAG_TIMING 1u         /* record a CUDA-event pair around every kernel class (see evb_get_timings) */
+#define EVB_FLAG_FULL_PARTITION 2u /* also partition the rows of the last split level (only evb_get_nidx(.., 1) reads that) */
+#define EVB_FLAG_KEEP_ALL_HIST 4u  /* retain the histograms of the last split level too (for evb_get_hist)               */
+
+/* Learner hyper-parameters needed on the device; filled by the glue from the reference's learner
+ * struct (src/learners.jl:1-23).  K is the number of prediction rows (1 mse/logloss, #classes for
+ * mlogloss, 2 for gaussian_mle); histogram channels are C = 2K+1 (g_1..g_K, h_1..h_K, w). */
+typedef struct {
+    int32_t loss;          /* enum evb_loss */
+    int32_t K;
+    int32_t nbins;         /* 2..255 */
+    int32_t max_depth;     /* 1..15 */
+    int32_t bagging_size;  /* >= 1 */
+    int32_t tree_type;     /* 0 = binary (the only one built) */
+    double eta, lambda, L2, gamma, min_weight;
+    int32_t device;        /* CUDA device ordinal of this shard */
+    uint32_t flags;
+} evb_params;
+
+/* Accumulated device time per kernel class since the last evb_reset_timings (EVB_FLAG_TIMING). */
+#define EVB_NTIMERS 12
+enum evb_timer {
+    EVB_T_GRADS = 0, EVB_T_ROWS_INIT = 1, EVB_T_HIST = 2, EVB_T_HIST_REDUCE = 3, EVB_T_ALLREDUCE = 4,
+    EVB_T_SCAN = 5, EVB_T_PARTITION = 6, EVB_T_PLAN = 7, EVB_T_FINALIZE = 8, EVB_T_D2H = 9,
+    EVB_T_H2D = 10, EVB_T_TREE_TOTAL = 11
+};
+typedef struct {
+    double ms[EVB_NTIMERS];        /* summed kernel time, milliseconds                                    */
+    int64_t launches[EVB_NTIMERS]; /* kernels launched in that class                                      */
+    int64_t hist_rows;             /* rows streamed by the histogram kernel (sum over levels and trees)   */
+    int64_t hist_nodes;            /* histograms built (build nodes, sum over levels and trees)           */
+    int64_t trees;                 /* trees grown                                                         */
+} evb_timings;
+
+EVB_API const char *evb_last_error(void);
+EVB_API int32_t evb_version(void);
+
+/*
+ * evb_create -- replaces `init_core(params, ::Type{<:GPU}, ...)` (ext/EvoTreesKernelAbstractionsExt/init.jl:1-151):
+ * uploads the binned matrix, targets, weights and initial predictions of this shard and allocates all
+ * training state.
+ *   x_bin      host, uint8 [nobs x nfeats] column-major, values 1..nbins (binarize, src/fit-utils.jl:66-72)
+ *   y          host; EVB_F32 [ycols x nobs] (ycols = 1 for a vector target) or EVB_U32 class codes 1..K
+ *   w          host float [nobs], > 0, or NULL for ones       (src/init.jl:173-174)
+ *   pred0      host float [K x nobs] initial predictions (mu + offset), or NULL with mu != NULL
+ *   mu         host float [K] used when pred0 == NULL         (src/init.jl:168-170)
+ *   feattypes  host uint8 [nfeats], 1 = numeric (<=), 0 = categorical (==); NULL = all numeric
+ *   monotone   host int32 [nfeats] in {-1,0,1}; NULL = none   (src/init.jl:184-187)
+ */
+EVB_API int32_t evb_create(evb_handle **out, const evb_params *p, int64_t nobs, int32_t nfeats, const uint8_t *x_bin,
+                   const void *y, int32_t y_dtype, int32_t ycols, const float *w, const float *pred0, const float *mu,
+                   const uint8_t *feattypes, const int32_t *monotone);
+EVB_API void evb_destroy(evb_handle *h);
+
+/*
+ * Row sharding over several GPUs (one handle per GPU, normally one process per GPU).  Rank 0 obtains an
+ * id, the host distributes its 128 bytes (any channel), then every rank calls evb_comm_init.  After that
+ * evb_grow_tree sums the per-level histograms and child row counts over all ranks with NCCL, so every rank
+ * grows the identical tree.  The reference has no counterpart: it is single-GPU
+ * (ext/EvoTreesCUDAExt.jl:7-12).  All ranks must call evb_grow_tree with the same js / update_grads.
+ */
+EVB_API int32_t evb_comm_unique_id(uint8_t id[128]);
+EVB_API int32_t evb_comm_init(evb_handle *h, const uint8_t id[128], int32_t rank, int32_t world);
+
+/*
+ * evb_grow_tree -- replaces one bag iteration of `grow_evotree!(m, cache::CacheGPU, params)`
+ * (ext/EvoTreesKernelAbstractionsExt/fit.jl:1-21): [update_grads!] + subsample + grow_tree! + predict!.
+ *   row_mask     host uint8 [nobs] (the bytes of `rand!(rng, mask)`), rows with mask <= mask_cond are
+ *                sampled (ext/.../subsample.jl:2-8); NULL = all rows
+ *   js           host uint32 [njs], 1-based ascending sampled feature ids (ext/.../fit.jl:8-10)
+ *   update_grads 1 on the first bag of a boosting round (`update_grads!`, ext/.../loss.jl)
+ * Outputs, host, length nn = 2^max_depth - 1, laid out as the fields of `Tree{L,K}` (src/structs.jl:77-84):
+ *   feat int64 (0 = none), cond_bin uint8 (0 = none), w float, gain float, leaf_pred float [K x nn], split uint8.
+ */
+EVB_API int32_t evb_grow_tree(evb_handle *h, const uint8_t *row_mask, uint8_t mask_cond, const uint32_t *js, int32_t njs,
+                      int32_t update_grads, int64_t *feat, uint8_t *cond_bin, float *w_node, float *gain,
+                      float *leaf_pred, uint8_t *split);
+
+/* State read-back for parity checks (each synchronises the handle's stream). */
+EVB_API int32_t evb_get_pred(evb_handle *h, float *pred /* [K x nobs] */);
+EVB_API int32_t evb_get_grads(evb_handle *h, float *grad /* [C x nobs] as cache.∇, src/init.jl:173 */);
+/* node of every row after the last evb_grow_tree: from_partition=1 reads the row lists produced by the
+ * partition kernel (`split_set!`, src/fit-utils.jl:93-312; rows outside the sample get 0), 0 reads the
+ * leaf found by the traversal in the training `predict!` (all rows). */
+EVB_API int32_t evb_get_nidx(evb_handle *h, uint32_t *nidx /* [nobs] */, int32_t from_partition);
+/* histogram of one node of the last tree, double [C x nbins x njs] with feature order = js; only nodes of
+ * depth <= max_depth-2 are retained (deeper ones are consumed by the split scan and not stored). */
+EVB_API int32_t evb_get_hist(evb_handle *h, int32_t node, double *hist);
+EVB_API int32_t evb_get_node_sums(evb_handle *h, double *nsum /* [C x nn] */);
+
+EVB_API int32_t evb_get_timings(evb_handle *h, evb_timings *out);
+EVB_API int32_t evb_reset_timings(evb_handle *h);
+
+/*
+ * evb_predict -- replaces `_predict(m, data, ::Type{<:GPU}; ntree_limit)` and `_predict_leaf_indices`
+ * (ext/EvoTreesKernelAbstractionsExt/predict.jl:115-158) after the host has binarized `data`.
+ * Trees are passed packed: every tree padded to `nn` nodes (the one-node bias tree, src/structs.jl:86-95,
+ * included), tree t at offset t*nn (leaf_pred at t*nn*K).
+ *   out        host float [nobs x K] column-major as the reference returns it (link applied when apply_link)
+ *   leaf_idx   host uint32 [nobs x ntrees] column-major, or NULL (predict_leaf_idx, src/predict.jl:173-185)
+ */
+EVB_API int32_t evb_predict(int32_t device, int32_t loss, int32_t K, int32_t ntrees, int32_t nn, const int64_t *feat,
+                    const uint8_t *cond_bin, const uint8_t *split, const float *leaf_pred, const uint8_t *x_bin,
+                    int64_t nobs, int32_t nfeats, const uint8_t *feattypes, int32_t apply_link, float *out,
+                    uint32_t *leaf_idx);
+
+/*
+ * evb_binarize -- `binarize(X; edges)` (src/fit-utils.jl:66-72) on the device: x_bin[i,j] =
+ * searchsortedfirst(edges[j], x[i,j]).  x host column-major [nobs x nfeats] of dtype EVB_F32 / EVB_F64,
+ * edges host [nedges x nfeats] column-major of the same dtype (ascending per feature), out host uint8.
+ */
+EVB_API int32_t evb_binarize(int32_t device, const void *x, int32_t dtype, int64_t nobs, int32_t nfeats, const void *edges,
+                     int32_t nedges, uint8_t *x_bin);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EVB_H */

@@ -1,0 +1,133 @@
+"""GPU parity tests: the CUDA library (through its C ABI) against the CPU oracle on the same seeded inputs."""
+import numpy as np
+import pytest
+
+from tests.parity import lockstep_check, make_regression
+
+pytestmark = pytest.mark.gpu
+
+
+def _softmax_data(n, f, k, seed=5):
+    rng = np.random.default_rng(seed)
+    x = rng.normal(size=(n, f)).astype(np.float32)
+    W = rng.normal(size=(f, k))
+    logits = x @ W + rng.gumbel(size=(n, k))
+    return x, logits.argmax(axis=1).astype(np.int64)
+
+
+def test_mse_small_config(pkg, orc):
+    """BASELINE config 1 shape (100k x 10, depth 6, 32 bins), a few rounds in lock-step."""
+    x, y = make_regression(100_000, 10, dtype=np.float64)
+    p = pkg.EvoTreeRegressor(loss="mse", nrounds=4, max_depth=6, nbins=32, eta=0.1)
+    s = lockstep_check(pkg, orc, p, x, y, rounds=4)
+    assert s["splits"] > 50 and s["diverged"] == 0, s
+
+
+def test_mse_row_col_sampling(pkg, orc):
+    """Config 2 shape scaled down: 100 features, rowsample / colsample 0.5, 64 bins."""
+    x, y = make_regression(60_000, 100, seed=3, dtype=np.float64)
+    p = pkg.EvoTreeRegressor(loss="mse", nrounds=3, max_depth=6, nbins=64, eta=0.05, rowsample=0.5, colsample=0.5)
+    s = lockstep_check(pkg, orc, p, x, y, rounds=3)
+    assert s["splits"] > 30, s
+
+
+def test_mse_deep_headline_shape(pkg, orc):
+    """Headline shape scaled down in rows: 100 features, depth 11, 64 bins."""
+    x, y = make_regression(200_000, 100, seed=11)
+    p = pkg.EvoTreeRegressor(loss="mse", nrounds=2, max_depth=11, nbins=64)
+    s = lockstep_check(pkg, orc, p, x, y, rounds=2)
+    assert s["splits"] > 500, s
+
+
+def test_logloss(pkg, orc):
+    x, y = make_regression(50_000, 20, seed=9)
+    yb = (y > np.median(y)).astype(np.float32)
+    p = pkg.EvoTreeRegressor(loss="logloss", nrounds=3, max_depth=5, nbins=32, eta=0.3)
+    lockstep_check(pkg, orc, p, x, yb, rounds=3)
+
+
+def test_softmax(pkg, orc):
+    """Config 4 shape scaled down: 28 features, 5 classes, depth 8, 64 bins."""
+    x, y = _softmax_data(80_000, 28, 5)
+    p = pkg.EvoTreeClassifier(nrounds=3, max_depth=8, nbins=64, eta=0.2)
+    s = lockstep_check(pkg, orc, p, x, y, rounds=3)
+    assert s["splits"] > 100, s
+
+
+def test_gaussian_mle(pkg, orc):
+    """Config 5 shape scaled down: 50 features, depth 7, 32 bins, min_weight 8."""
+    rng = np.random.default_rng(17)
+    n, f = 80_000, 50
+    x = rng.random((n, f)).astype(np.float32)
+    y = (x @ rng.normal(size=f) + np.exp(0.5 * x[:, 0]) * rng.normal(size=n)).astype(np.float32)
+    p = pkg.EvoTreeMLE(nrounds=3, max_depth=7, nbins=32, eta=0.2)
+    s = lockstep_check(pkg, orc, p, x, y, rounds=3)
+    assert s["splits"] > 50, s
+
+
+@pytest.mark.parametrize("depth", [1, 2, 3])
+def test_shallow_depths(pkg, orc, depth):
+    x, y = make_regression(5_000, 7, seed=depth)
+    p = pkg.EvoTreeRegressor(nrounds=3, max_depth=depth, nbins=16)
+    lockstep_check(pkg, orc, p, x, y, rounds=3)
+
+
+@pytest.mark.parametrize("nbins,nfeats", [(2, 3), (255, 5), (100, 33), (64, 130), (17, 64)])
+def test_bin_and_feature_edge_sizes(pkg, orc, nbins, nfeats):
+    x, y = make_regression(20_000, nfeats, seed=nbins)
+    p = pkg.EvoTreeRegressor(nrounds=2, max_depth=5, nbins=nbins)
+    lockstep_check(pkg, orc, p, x, y, rounds=2)
+
+
+def test_weights_and_regularisation(pkg, orc):
+    x, y = make_regression(30_000, 12, seed=21)
+    w = np.random.default_rng(1).uniform(0.5, 3.0, size=y.size).astype(np.float32)
+    p = pkg.EvoTreeRegressor(nrounds=3, max_depth=6, nbins=32, lambda_=0.5, L2=2.0, gamma=0.1, min_weight=20.0)
+    lockstep_check(pkg, orc, p, x, y, rounds=3, w=w)
+
+
+def test_monotone_constraints(pkg, orc):
+    x, y = make_regression(30_000, 6, seed=31)
+    p = pkg.EvoTreeRegressor(nrounds=3, max_depth=5, nbins=32, monotone_constraints={1: 1, 2: -1, 4: 1})
+    lockstep_check(pkg, orc, p, x, y, rounds=3)
+
+
+def test_categorical_features(pkg, orc):
+    """feattypes = false uses the `==` rule in the split scan, the partition and the traversal."""
+    rng = np.random.default_rng(41)
+    n, f, nb = 30_000, 6, 12
+    x_bin = np.asfortranarray(rng.integers(1, nb + 1, size=(n, f)).astype(np.uint8))
+    eff = rng.normal(size=(f, nb + 1))
+    y = sum(eff[j][x_bin[:, j]] for j in range(f)).astype(np.float32) + 0.1 * rng.normal(size=n).astype(np.float32)
+    ft = np.array([0, 1, 0, 1, 0, 0], np.uint8)
+    p = pkg.EvoTreeRegressor(nrounds=3, max_depth=5, nbins=nb)
+    lockstep_check(pkg, orc, p, None, y, rounds=3, feattypes=ft, x_bin=x_bin)
+
+
+def test_bagging(pkg, orc):
+    x, y = make_regression(20_000, 9, seed=51)
+    p = pkg.EvoTreeRegressor(nrounds=2, max_depth=4, nbins=32, bagging_size=3, rowsample=0.7)
+    s = lockstep_check(pkg, orc, p, x, y, rounds=2)
+    assert s["trees"] == 6
+
+
+def test_tiny_and_ragged_inputs(pkg, orc):
+    for n in (1, 2, 31, 33, 2049):
+        x, y = make_regression(n, 3, seed=n)
+        p = pkg.EvoTreeRegressor(nrounds=2, max_depth=4, nbins=8, min_weight=0.0)
+        lockstep_check(pkg, orc, p, x, y, rounds=2)
+
+
+def test_empty_subsample_is_an_error(pkg):
+    """`no subsample observation` (src/subsample.jl:36, test/core.jl:510-530)."""
+    x, y = make_regression(50, 3)
+    p = pkg.EvoTreeRegressor(nrounds=1, max_depth=3, nbins=8, rowsample=1e-9)
+    with pytest.raises(pkg.EvbError, match="no subsample"):
+        pkg.fit(p, x_train=x, y_train=y)
+
+
+def test_bad_bins_rejected(pkg):
+    x_bin = np.asfortranarray(np.full((100, 3), 9, np.uint8))
+    p = pkg.EvoTreeRegressor(nrounds=1, max_depth=3, nbins=8)
+    with pytest.raises(pkg.EvbError, match="outside 1..nbins"):
+        pkg.init_core_binned(p, x_bin, np.zeros(100, np.float32), 1, 1, np.zeros(1, np.float32))
