@@ -458,6 +458,12 @@ extern "C" int32_t evb_get_node_sums(evb_handle *h, double *nsum) {
     return EVB_OK;
 }
 
+extern "C" int32_t evb_get_stream(evb_handle *h, void **stream) {
+    if (!h || !stream) { evb_set_error("null argument"); return EVB_ERR_ARG; }
+    *stream = (void *)h->st;
+    return EVB_OK;
+}
+
 extern "C" int32_t evb_get_timings(evb_handle *h, evb_timings *out) {
     EVB_ENTER(h);
     if (!out) { evb_set_error("null output"); return EVB_ERR_ARG; }

@@ -134,6 +134,12 @@ class Cache:
                 "launches": {n: t.launches[i] for i, n in enumerate(_lib.TIMER_NAMES)},
                 "hist_rows": t.hist_rows, "hist_nodes": t.hist_nodes, "trees": t.trees}
 
+    def stream(self) -> int:
+        """cudaStream_t of the handle as an integer (e.g. for torch.cuda.ExternalStream)."""
+        out = C.c_void_p()
+        _lib.check(_lib.lib().evb_get_stream(self.handle, C.byref(out)))
+        return out.value or 0
+
     def reset_timings(self):
         _lib.check(_lib.lib().evb_reset_timings(self.handle))
 

@@ -138,6 +138,9 @@ EVB_API int32_t evb_get_nidx(evb_handle *h, uint32_t *nidx /* [nobs] */, int32_t
 EVB_API int32_t evb_get_hist(evb_handle *h, int32_t node, double *hist);
 EVB_API int32_t evb_get_node_sums(evb_handle *h, double *nsum /* [C x nn] */);
 
+/* The CUDA stream (cudaStream_t) on which the handle enqueues all its work, so that a caller can record
+ * its own events around a sequence of calls. */
+EVB_API int32_t evb_get_stream(evb_handle *h, void **stream);
 EVB_API int32_t evb_get_timings(evb_handle *h, evb_timings *out);
 EVB_API int32_t evb_reset_timings(evb_handle *h);
 

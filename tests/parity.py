@@ -4,7 +4,7 @@ In lock-step mode the oracle restarts every round from the library's own predict
 split that goes the other way cannot compound over rounds: each tree is judged on its own inputs.
 Tolerances (stated once, used everywhere):
   * binning, row->node ids, leaf ids, split feature / bin: bit-exact;
-  * histograms: |gpu - oracle| <= 1e-5 * (upper bound of sum |contribution| of the bin);
+  * histograms: |gpu - oracle| <= 1e-5 * (upper bound of sum |contribution| of the bin at the root);
   * node sums, gains, leaf values, predictions: 1e-5 relative (float32 outputs: plus 1e-6 absolute);
   * a split may differ from the oracle's only if, by the oracle's own histogram, the gain of the library's
     choice is within 1e-5 relative of the oracle's best gain (near tie); descendants of such a node and the
@@ -84,9 +84,12 @@ def compare_tree(op, tg, to, ohist, onsum, feattypes=None):
     return compared, diverged
 
 
-def compare_hist(hg, ho, gmax, wmin):
-    """hg, ho [njs, B, C]; bound of sum|contribution| per bin = gmax[c] * (w_bin / wmin)."""
-    wbin = ho[:, :, -1:]
+def compare_hist(hg, ho, gmax, wmin, wroot):
+    """hg, ho [njs, B, C].  The library accumulates float32 partial sums and gets half of the nodes by
+    parent - sibling subtraction, so its absolute error in a bin is set by the bin's population in the
+    ancestor where the chain of subtractions started (at most the root).  Bound used:
+    sum|contribution| <= gmax[c] * (root w_bin / wmin)."""
+    wbin = wroot[:, :, -1:]
     atol = RTOL * gmax[None, None, :] * (wbin / wmin) + 1e-12
     err = np.abs(hg - ho)
     bad = err > atol
@@ -143,13 +146,15 @@ def lockstep_check(pkg, orc, params, x, y, rounds, w=None, feattypes=None, x_bin
                             if n in dead or (to.w[n - 1] == 0 and n != 1):
                                 continue
                             hg = cache.hist(n, js.size, params.nbins)
-                            stats["hist_worst"] = max(stats["hist_worst"], compare_hist(hg, ohist[n - 1][j0], gmax, wmin))
+                            stats["hist_worst"] = max(stats["hist_worst"], compare_hist(hg, ohist[n - 1][j0], gmax, wmin, ohist[0][j0]))
                 if not div:
                     assert np.array_equal(cache.nidx(from_partition=True), onidx), "row->node ids from the partition differ"
                     leaf = orc.leaf_idx(x_bin, to, feattypes)
                     assert np.array_equal(cache.nidx(from_partition=False), leaf), "leaf ids from the traversal differ"
-                    np.testing.assert_allclose(cache.node_sums()[to.w != 0], onsum[to.w != 0], rtol=RTOL,
-                                               atol=RTOL * float(np.abs(grad).max()) * 4, err_msg="node sums")
+                    # float32 partial sums: the absolute error scales with sum|g| <= gmax * (root rows)
+                    gs, os_ = cache.node_sums()[to.w != 0], onsum[to.w != 0]
+                    atol = RTOL * np.abs(grad).max(axis=0).astype(np.float64) * (onsum[0, -1] / wmin)
+                    assert (np.abs(gs - os_) <= RTOL * np.abs(os_) + atol[None, :]).all(), "node sums"
                 # the library's own tree, applied by the oracle's predict!, must reproduce the library's predictions
                 orc_tree = orc.Tree(tg.feat, tg.cond_bin, tg.w, tg.gain, tg.pred, tg.split.astype(np.uint8))
                 orc.predict_tree(op, x_bin, orc_tree, pred_prev, feattypes)
