@@ -2,6 +2,7 @@
 #include "evb_internal.cuh"
 #include <stdarg.h>
 #include <string.h>
+#include <stdlib.h>
 #include <new>
 
 int32_t evb_launch_check_bins(evb_handle *h);
@@ -94,10 +95,10 @@ static void free_handle(evb_handle *h) {
     cudaSetDevice(h->dev);
     if (h->st) cudaStreamSynchronize(h->st);
     evb_nccl_destroy(h);
-    void *ptrs[] = {h->xT, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
+    void *ptrs[] = {h->xT, h->xC, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
                     h->js_d, h->seg_start, h->seg_cnt, h->gcnt, h->nleft, (h->gnleft != h->nleft) ? h->gnleft : nullptr, h->kind,
                     h->bslot, h->nsum, h->plan /* base of the tree block */, h->cum, h->slot_node, h->item_node, h->item_left,
-                    h->item_lprefix, h->item_bits, h->scan_tmp, h->hist, h->hcomp, h->scratch};
+                    h->item_lprefix, h->item_bits, h->scan_tmp, h->hist, h->hcomp, h->scratch, h->fbest_gain, h->fbest_bin};
     for (void *p : ptrs) if (p) cudaFree(p);
     if (h->h_tree) cudaFreeHost(h->h_tree);
     for (cudaEvent_t e : h->ev) cudaEventDestroy(e);
@@ -113,10 +114,12 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
                            const uint8_t *feattypes, const int32_t *monotone) {
     h->p = *p;
     h->K = p->K; h->C = 2 * p->K + 1; h->B = p->nbins; h->D = p->max_depth; h->nn = (1 << p->max_depth) - 1;
-    h->nfeats = nfeats; h->RS = (nfeats + 31) / 32 * 32; h->GS = (h->C + 3) / 4 * 4; h->n = nobs;
+    h->Ce = (p->loss == EVB_MSE && !getenv("EVB_NO_ELISION")) ? p->K + 1 : h->C;
+    h->nfeats = nfeats; h->RS = (nfeats + 31) / 32 * 32; h->GS = (h->Ce + 3) / 4 * 4; h->n = nobs;
     h->dev = p->device; h->y_dtype = y_dtype; h->ycols = ycols;
     h->timing = (p->flags & EVB_FLAG_TIMING) != 0;
     h->world = 1; h->rank = 0; h->F = nfeats;
+    { const char *e = getenv("EVB_HIST_MODE"); h->hist_mode = e ? atoi(e) : 1; }
     cudaDeviceProp prop;
     EVB_CUDA(cudaGetDeviceProperties(&prop, h->dev));
     if (prop.major < 10) {
@@ -162,6 +165,10 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
     EVB_CUDA(dalloc(&h->item_left, (size_t)h->max_items)); EVB_CUDA(dalloc(&h->item_lprefix, (size_t)h->max_items));
     EVB_CUDA(dalloc(&h->item_bits, (size_t)h->max_items * (EVB_PART_CHUNK / 32)));
     EVB_CUDA(dalloc(&h->scan_tmp, (size_t)(n / 2048 + 2)));
+    {
+        const size_t lv = (size_t)evb_level_nodes(D > 1 ? D - 1 : 1) * nfeats;
+        EVB_CUDA(dalloc(&h->fbest_gain, lv)); EVB_CUDA(dalloc(&h->fbest_bin, lv));
+    }
 
     const bool keep_all = (p->flags & EVB_FLAG_KEEP_ALL_HIST) != 0;
     h->hist_nodes = keep_all ? (1 << (D > 1 ? D - 1 : 0)) : (D >= 2 ? 1 << (D - 2) : 1);
@@ -171,26 +178,12 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
     EVB_CHECK(evb_hist_configure(h));
     EVB_CUDA(dalloc(&h->scratch, h->scratch_floats));
 
-    // ---- uploads: x_bin by blocks of columns, transposed to observation-major rows on the device
+    // ---- uploads: x_bin is kept feature-major (as given) for the row partition and transposed on the device to
+    // observation-major rows for the histogram gathers and the tree traversal
     EVB_CUDA(cudaMemsetAsync(h->xT, 0, (size_t)n * h->RS, h->st));
-    {
-        int njc = (int)((size_t)(256u << 20) / (size_t)(n > 0 ? n : 1));
-        njc = njc / 4 * 4;
-        if (njc < 4) njc = 4;
-        if (njc > nfeats) njc = nfeats;
-        uint8_t *xcol = nullptr;
-        EVB_CUDA(dalloc(&xcol, (size_t)n * njc));
-        int32_t rc = EVB_OK;
-        for (int j0 = 0; j0 < nfeats && rc == EVB_OK; j0 += njc) {
-            const int nj = nfeats - j0 < njc ? nfeats - j0 : njc;
-            cudaError_t e = cudaMemcpyAsync(xcol, x_bin + (size_t)n * j0, (size_t)n * nj, cudaMemcpyHostToDevice, h->st);
-            if (e != cudaSuccess) { evb_set_error("CUDA error %s (x_bin upload)", cudaGetErrorString(e)); rc = EVB_ERR_CUDA; break; }
-            rc = evb_launch_transpose(h, xcol, n, n, j0, nj, h->xT, h->RS, h->st);
-            if (rc == EVB_OK && cudaStreamSynchronize(h->st) != cudaSuccess) { evb_set_error("CUDA error in transpose"); rc = EVB_ERR_CUDA; }
-        }
-        cudaFree(xcol);
-        EVB_CHECK(rc);
-    }
+    EVB_CUDA(dalloc(&h->xC, (size_t)n * nfeats));
+    EVB_CUDA(cudaMemcpyAsync(h->xC, x_bin, (size_t)n * nfeats, cudaMemcpyHostToDevice, h->st));
+    EVB_CHECK(evb_launch_transpose(h, h->xC, n, n, 0, nfeats, h->xT, h->RS, h->st));
     {
         const size_t ybytes = (size_t)n * (y_dtype == EVB_U32 ? 4 : 4 * (size_t)ycols);
         EVB_CUDA(cudaMalloc(&h->y, ybytes ? ybytes : 1));
@@ -402,10 +395,23 @@ extern "C" int32_t evb_get_pred(evb_handle *h, float *pred) {
 extern "C" int32_t evb_get_grads(evb_handle *h, float *grad) {
     EVB_ENTER(h);
     if (!grad) { evb_set_error("null output"); return EVB_ERR_ARG; }
-    // the device keeps padded records of GS floats; the reference layout is [C x nobs]
-    EVB_CUDA(cudaMemcpy2DAsync(grad, sizeof(float) * h->C, h->grad, sizeof(float) * h->GS, sizeof(float) * h->C, (size_t)h->n,
-                               cudaMemcpyDeviceToHost, h->st));
+    // the device keeps padded records of GS floats (channel c at (c / NCH) * 4 + c % NCH); the reference
+    // layout is [C x nobs]
+    std::vector<float> tmp((size_t)h->n * h->GS);
+    EVB_CUDA(cudaMemcpyAsync(tmp.data(), h->grad, sizeof(float) * tmp.size(), cudaMemcpyDeviceToHost, h->st));
     EVB_CUDA(cudaStreamSynchronize(h->st));
+    const int NCH = h->hg.NCH, C = h->C, GS = h->GS, K = h->K;
+    const bool elided = h->Ce != h->C; // mse: records hold g_1..g_K, w; h_k = 2w
+    for (int64_t i = 0; i < h->n; ++i) {
+        const float *rec = tmp.data() + (size_t)i * GS;
+        for (int c = 0; c < C; ++c) {
+            float v;
+            if (!elided) v = rec[(c / NCH) * 4 + (c % NCH)];
+            else if (c < K) v = rec[(c / NCH) * 4 + (c % NCH)];
+            else { const float w = rec[(K / NCH) * 4 + (K % NCH)]; v = c < 2 * K ? 2.0f * w : w; }
+            grad[(size_t)i * C + c] = v;
+        }
+    }
     return EVB_OK;
 }
 

@@ -18,6 +18,7 @@
 //     bit-reproducible from run to run, and transposes them to hcomp[slot][feature][channel][bin].
 //   Every wait on an mbarrier is bounded; on expiry the kernel records an error code and returns.
 #include "evb_internal.cuh"
+#include <stdlib.h>
 
 namespace {
 
@@ -69,20 +70,69 @@ struct HistArgs {
     int *err;
     int RS, GS, F, nbins, C, NFG, U, UB, stages, PG;
     uint32_t img_floats;
+    int mode; // bit 0: stage rows with cp.async (LDGSTS) instead of TMA bulk copies; bit 4: diagnostic, skip the accumulation
 };
 
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive(uint64_t *bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Unit image in shared memory: channels are kept in pairs so that one 64-bit access moves two of them.
+//   NCH = 1: [bin][lane] float            NCH = 2: [bin][lane] float2
+//   NCH = 3: [bin][lane] float2 + [bin][lane] float      NCH = 4: two [bin][lane] float2 regions
+// Lane l touches only addresses whose bank is determined by l, so no access of a warp conflicts.
 template <int BP, int NCH>
-__device__ __forceinline__ void accum_row(float *hl, uint32_t bin, const float4 &g, int nch) {
-    const uint32_t bi = min(bin - 1u, (uint32_t)(BP - 1)) * 32u;
-    hl[bi] += g.x;
-    if (NCH >= 2 && nch >= 2) hl[BP * 32 + bi] += g.y;
-    if (NCH >= 3 && nch >= 3) hl[2 * BP * 32 + bi] += g.z;
-    if (NCH >= 4 && nch >= 4) hl[3 * BP * 32 + bi] += g.w;
+struct Img {
+    static constexpr int W0 = NCH >= 2 ? 2 : 1;
+    static constexpr int W1 = NCH - W0;
+    [[maybe_unused]] static constexpr int P1 = BP * 32 * W0;
+    static constexpr int FLOATS = BP * 32 * NCH;
+    static __device__ __forceinline__ void ld(const float *img, int lane, uint32_t b, float (&v)[NCH]) {
+        if constexpr (W0 == 2) {
+            const float2 t = *reinterpret_cast<const float2 *>(img + (b * 32 + lane) * 2);
+            v[0] = t.x; v[1] = t.y;
+        } else {
+            v[0] = img[b * 32 + lane];
+        }
+        if constexpr (W1 == 2) {
+            const float2 t = *reinterpret_cast<const float2 *>(img + P1 + (b * 32 + lane) * 2);
+            v[2] = t.x; v[3] = t.y;
+        } else if constexpr (W1 == 1) {
+            v[2] = img[P1 + b * 32 + lane];
+        }
+    }
+    static __device__ __forceinline__ void st(float *img, int lane, uint32_t b, const float (&v)[NCH]) {
+        if constexpr (W0 == 2) {
+            *reinterpret_cast<float2 *>(img + (b * 32 + lane) * 2) = make_float2(v[0], v[1]);
+        } else {
+            img[b * 32 + lane] = v[0];
+        }
+        if constexpr (W1 == 2) {
+            *reinterpret_cast<float2 *>(img + P1 + (b * 32 + lane) * 2) = make_float2(v[2], v[3]);
+        } else if constexpr (W1 == 1) {
+            img[P1 + b * 32 + lane] = v[2];
+        }
+    }
+};
+
+template <int BP>
+__device__ __forceinline__ uint32_t bin_index(uint32_t raw) { return min(raw - 1u, (uint32_t)(BP - 1)); }
+
+template <int NCH>
+__device__ __forceinline__ void unpack(const float4 &g, float (&v)[NCH]) {
+    v[0] = g.x;
+    if constexpr (NCH >= 2) v[1] = g.y;
+    if constexpr (NCH >= 3) v[2] = g.z;
+    if constexpr (NCH >= 4) v[3] = g.w;
 }
 
 template <int BP, int NCH>
 __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(HistArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
+    using I = Img<BP, NCH>;
     const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, b = blockIdx.x, ug = blockIdx.y;
     const int nact = min(a.UB, a.U - ug * a.UB);
@@ -90,7 +140,7 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
     const int xbytes = EVB_TILE_ROWS * a.RS, gbytes = EVB_TILE_ROWS * a.GS * 4;
     const int stage_bytes = xbytes + gbytes;
     float *imgs = reinterpret_cast<float *>(smem);
-    unsigned char *stage0 = smem + (size_t)a.UB * 32 * BP * NCH * 4;
+    unsigned char *stage0 = smem + (size_t)a.UB * I::FLOATS * 4;
     uint64_t *full = reinterpret_cast<uint64_t *>(stage0 + (size_t)S * stage_bytes);
     uint64_t *empty = full + S;
 
@@ -98,11 +148,11 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
     const long long lo = R * b / G, hi = R * (b + 1) / G;
     if (lo >= hi) return;
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], nact); }
+        for (int s = 0; s < S; ++s) { mbar_init(&full[s], (a.mode & 1) ? 32 : 1); mbar_init(&empty[s], nact); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    for (int i = tid; i < nact * 32 * BP * NCH; i += blockDim.x) imgs[i] = 0.0f;
+    for (int i = tid; i < nact * I::FLOATS; i += blockDim.x) imgs[i] = 0.0f;
     __syncthreads();
 
     // first build slot that contains row `lo`: largest s with cum[s] <= lo
@@ -116,6 +166,8 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
 
     if (wid == 0) {
         // ---------------- producer: stage tiles of rows with TMA bulk copies -------------------------
+        // Row ids are fetched four tiles (128 rows) at a time and one group ahead, so that the latency
+        // of reading the row list never sits between two tiles.
         uint32_t it = 0;
         long long pos = lo;
         bool ok = true;
@@ -123,21 +175,52 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
             const long long send = min(hi, (long long)a.cum[s + 1]);
             if (send > pos) {
                 const int node = a.slot_node[s];
-                const long long base = (long long)a.seg_start[node] - a.cum[s];
-                for (long long q0 = pos; q0 < send && ok; q0 += EVB_TILE_ROWS, ++it) {
-                    const int st = it % S;
-                    const int nrows = (int)min((long long)EVB_TILE_ROWS, send - q0);
-                    uint32_t row = 0;
-                    if (lane < nrows) row = a.rows[base + q0 + lane];
-                    ok = mbar_wait(&empty[st], ((it / S) & 1u) ^ 1u, a.err, EVB_DERR_WAIT_EMPTY);
-                    if (!ok) break;
-                    if (lane == 0) mbar_expect_tx(&full[st], (uint32_t)nrows * (uint32_t)(a.RS + a.GS * 4));
-                    __syncwarp();
-                    if (lane < nrows) {
-                        unsigned char *sb = stage0 + (size_t)st * stage_bytes;
-                        bulk_g2s(sb + lane * a.RS, a.xT + (size_t)row * a.RS, (uint32_t)a.RS, &full[st]);
-                        bulk_g2s(sb + xbytes + lane * a.GS * 4, a.grad + (size_t)row * a.GS, (uint32_t)a.GS * 4, &full[st]);
+                const uint32_t *rows = a.rows + ((long long)a.seg_start[node] - a.cum[s]);
+                uint32_t cur[4], nxt[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { const long long q = pos + k * 32 + lane; cur[k] = q < send ? rows[q] : 0u; }
+                for (long long q0 = pos; q0 < send && ok; q0 += 4 * EVB_TILE_ROWS) {
+                    const long long qn = q0 + 4 * EVB_TILE_ROWS;
+                    if (qn < send) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) { const long long q = qn + k * 32 + lane; nxt[k] = q < send ? rows[q] : 0u; }
                     }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const long long t0 = q0 + k * EVB_TILE_ROWS;
+                        if (t0 < send && ok) {
+                            const int st = it % S;
+                            const int nrows = (int)min((long long)EVB_TILE_ROWS, send - t0);
+                            ok = mbar_wait(&empty[st], ((it / S) & 1u) ^ 1u, a.err, EVB_DERR_WAIT_EMPTY);
+                            if (ok && (a.mode & 1)) {
+                                unsigned char *sb = stage0 + (size_t)st * stage_bytes;
+                                const int cpr = a.RS >> 4, cprg = a.GS >> 2;
+                                for (int base = 0; base < EVB_TILE_ROWS * cpr; base += 32) {
+                                    const int idx = base + lane, rt = idx / cpr, ch = idx - rt * cpr;
+                                    const uint32_t row = __shfl_sync(0xffffffffu, cur[k], rt & 31);
+                                    if (rt < nrows) cp_async16(sb + rt * a.RS + ch * 16, a.xT + (size_t)row * a.RS + ch * 16);
+                                }
+                                for (int base = 0; base < EVB_TILE_ROWS * cprg; base += 32) {
+                                    const int idx = base + lane, rt = idx / cprg, ch = idx - rt * cprg;
+                                    const uint32_t row = __shfl_sync(0xffffffffu, cur[k], rt & 31);
+                                    if (rt < nrows) cp_async16(sb + xbytes + (rt * a.GS + ch * 4) * 4, a.grad + (size_t)row * a.GS + ch * 4);
+                                }
+                                cp_async_arrive(&full[st]);
+                                ++it;
+                            } else if (ok) {
+                                if (lane == 0) mbar_expect_tx(&full[st], (uint32_t)nrows * (uint32_t)(a.RS + a.GS * 4));
+                                __syncwarp();
+                                if (lane < nrows) {
+                                    unsigned char *sb = stage0 + (size_t)st * stage_bytes;
+                                    bulk_g2s(sb + lane * a.RS, a.xT + (size_t)cur[k] * a.RS, (uint32_t)a.RS, &full[st]);
+                                    bulk_g2s(sb + xbytes + lane * a.GS * 4, a.grad + (size_t)cur[k] * a.GS, (uint32_t)a.GS * 4, &full[st]);
+                                }
+                                ++it;
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) cur[k] = nxt[k];
                 }
             }
             pos = send;
@@ -155,16 +238,15 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
     }
     if (wid - 1 >= nact) return;
 
-    // ---------------- consumers: one unit (32 feature slots x up to NCH channels) per warp ------------
+    // ---------------- consumers: one unit (32 feature slots x NCH channels) per warp ------------------
     const int uw = wid - 1;
     const int u = ug * a.UB + uw;
     const int ct = u / a.NFG, fg = u % a.NFG;
     const int slot = fg * 32 + lane;
     const bool act = slot < a.F;
     const uint32_t foff = act ? a.js0[slot] : 0u;
-    const int nch = min(NCH, a.C - ct * 4);
-    float *img = imgs + (size_t)uw * 32 * BP * NCH;
-    float *hl = img + lane;
+    const int nch = min(NCH, a.C - ct * NCH);
+    float *img = imgs + (size_t)uw * I::FLOATS;
     const int RS = a.RS, GS = a.GS;
 
     uint32_t it = 0;
@@ -178,23 +260,38 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
                 if (!mbar_wait(&full[st], (it / S) & 1u, a.err, EVB_DERR_WAIT_FULL)) return;
                 const unsigned char *xs = stage0 + (size_t)st * stage_bytes + foff;
                 const float *gs = reinterpret_cast<const float *>(stage0 + (size_t)st * stage_bytes + xbytes) + ct * 4;
-                if (act) {
+                if (act && !(a.mode & 16)) {
                     int r = 0;
+                    // Four rows at a time: all loads first, then the adds with forwarding between rows that
+                    // hit the same bin, then the stores in row order.  The result is bit-identical to adding
+                    // the rows one by one, but the four read-modify-write chains overlap.
                     for (; r + 4 <= nrows; r += 4) {
-                        const uint32_t b0 = xs[(r + 0) * RS], b1 = xs[(r + 1) * RS], b2 = xs[(r + 2) * RS], b3 = xs[(r + 3) * RS];
-                        const float4 g0 = *reinterpret_cast<const float4 *>(gs + (r + 0) * GS);
-                        const float4 g1 = *reinterpret_cast<const float4 *>(gs + (r + 1) * GS);
-                        const float4 g2 = *reinterpret_cast<const float4 *>(gs + (r + 2) * GS);
-                        const float4 g3 = *reinterpret_cast<const float4 *>(gs + (r + 3) * GS);
-                        accum_row<BP, NCH>(hl, b0, g0, nch);
-                        accum_row<BP, NCH>(hl, b1, g1, nch);
-                        accum_row<BP, NCH>(hl, b2, g2, nch);
-                        accum_row<BP, NCH>(hl, b3, g3, nch);
+                        const uint32_t b0 = bin_index<BP>(xs[(r + 0) * RS]), b1 = bin_index<BP>(xs[(r + 1) * RS]);
+                        const uint32_t b2 = bin_index<BP>(xs[(r + 2) * RS]), b3 = bin_index<BP>(xs[(r + 3) * RS]);
+                        float g0[NCH], g1[NCH], g2[NCH], g3[NCH], a0[NCH], a1[NCH], a2[NCH], a3[NCH];
+                        unpack<NCH>(*reinterpret_cast<const float4 *>(gs + (r + 0) * GS), g0);
+                        unpack<NCH>(*reinterpret_cast<const float4 *>(gs + (r + 1) * GS), g1);
+                        unpack<NCH>(*reinterpret_cast<const float4 *>(gs + (r + 2) * GS), g2);
+                        unpack<NCH>(*reinterpret_cast<const float4 *>(gs + (r + 3) * GS), g3);
+                        I::ld(img, lane, b0, a0); I::ld(img, lane, b1, a1); I::ld(img, lane, b2, a2); I::ld(img, lane, b3, a3);
+                        const bool e10 = b1 == b0, e20 = b2 == b0, e21 = b2 == b1, e30 = b3 == b0, e31 = b3 == b1, e32 = b3 == b2;
+#pragma unroll
+                        for (int c = 0; c < NCH; ++c) {
+                            a0[c] = a0[c] + g0[c];
+                            a1[c] = (e10 ? a0[c] : a1[c]) + g1[c];
+                            a2[c] = (e21 ? a1[c] : (e20 ? a0[c] : a2[c])) + g2[c];
+                            a3[c] = (e32 ? a2[c] : (e31 ? a1[c] : (e30 ? a0[c] : a3[c]))) + g3[c];
+                        }
+                        I::st(img, lane, b0, a0); I::st(img, lane, b1, a1); I::st(img, lane, b2, a2); I::st(img, lane, b3, a3);
                     }
                     for (; r < nrows; ++r) {
-                        const uint32_t b0 = xs[r * RS];
-                        const float4 g0 = *reinterpret_cast<const float4 *>(gs + r * GS);
-                        accum_row<BP, NCH>(hl, b0, g0, nch);
+                        const uint32_t b0 = bin_index<BP>(xs[r * RS]);
+                        float g0[NCH], a0[NCH];
+                        unpack<NCH>(*reinterpret_cast<const float4 *>(gs + r * GS), g0);
+                        I::ld(img, lane, b0, a0);
+#pragma unroll
+                        for (int c = 0; c < NCH; ++c) a0[c] += g0[c];
+                        I::st(img, lane, b0, a0);
                     }
                 }
                 __syncwarp();
@@ -202,12 +299,15 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
             }
             // flush the piece (CTA b, slot s) and clear the image
             float *dst = a.scratch + ((size_t)(ug * a.PG + b + s) * a.UB + uw) * a.img_floats + lane;
-            for (int c = 0; c < nch; ++c) {
-                for (int bin = 0; bin < a.nbins; ++bin) {
-                    float *p = hl + (c * BP + bin) * 32;
-                    dst[(c * a.nbins + bin) * 32] = *p;
-                    *p = 0.0f;
-                }
+            for (int bin = 0; bin < a.nbins; ++bin) {
+                float v[NCH], z[NCH];
+                I::ld(img, lane, bin, v);
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) z[c] = 0.0f;
+                I::st(img, lane, bin, z);
+#pragma unroll
+                for (int c = 0; c < NCH; ++c)
+                    if (c < nch) dst[(c * a.nbins + bin) * 32] = v[c];
             }
         }
         pos = send;
@@ -220,17 +320,23 @@ struct ReduceArgs {
     double *hcomp;
     const LevelPlan *plan;
     const int32_t *cum;
-    int G, PG, UB, NFG, U, F, C, nbins, NCH;
+    int G, PG, UB, NFG, U, F, C, Ce, K, nbins, NCH; // C: channels of hcomp; Ce: channels accumulated (mse: K + 1)
     uint32_t img_floats;
 };
 
-// grid (max build slots of the level, U, ceil(nbins/16)); 512 threads: warp = bin, lane = feature slot
+// Sums the pieces of every build slot in a fixed order (double precision) and writes
+// hcomp[slot][feature][channel][bin].  grid (max build slots of the level, U * NCH, ceil(nbins / BPB));
+// 512 threads = NPG piece groups x (BPB bins x 32 feature lanes).  Few slots / many pieces per slot (top of
+// the tree) use BPB = 4 with four piece groups; many slots use BPB = 16.
+template <int BPB>
 __global__ void __launch_bounds__(512) k_hist_reduce(ReduceArgs a) {
-    __shared__ double tile[16][33];
-    const int s = blockIdx.x, u = blockIdx.y, bin0 = blockIdx.z * 16;
-    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int NE = BPB * 32, NPG = 512 / NE;
+    __shared__ double part[NPG][NE];
+    __shared__ double tile[BPB][33];
+    const int s = blockIdx.x, u = blockIdx.y / a.NCH, c = blockIdx.y % a.NCH, bin0 = blockIdx.z * BPB;
     const int ug = u / a.UB, uw = u % a.UB, ct = u / a.NFG, fg = u % a.NFG;
-    const int nch = min(a.NCH, a.C - ct * 4);
+    if (c >= min(a.NCH, a.Ce - ct * a.NCH)) return;
+    const int e = threadIdx.x % NE, pg = threadIdx.x / NE, binl = e >> 5, lane = e & 31;
     const int nbuild = a.plan->nbuild;
     const long long R = a.plan->R;
     int bfirst = 0, blast = -1;
@@ -241,23 +347,44 @@ __global__ void __launch_bounds__(512) k_hist_reduce(ReduceArgs a) {
             blast = (int)((c1 * a.G - 1) / R);
         }
     }
-    const int fl = threadIdx.x >> 4, bl = threadIdx.x & 15;
-    for (int c = 0; c < nch; ++c) {
-        double acc = 0.0;
-        const int bin = bin0 + w;
-        if (bin < a.nbins) {
-            const float *src = a.scratch + ((size_t)(ug * a.PG + s) * a.UB + uw) * a.img_floats + (c * a.nbins + bin) * 32 + lane;
-            const size_t bstride = (size_t)a.UB * a.img_floats;
-            // CTAs whose row range is empty (R < G) wrote nothing: skip their slots
-            for (int b = bfirst; b <= blast; ++b)
+    double acc = 0.0;
+    const int bin = bin0 + binl;
+    if (bin < a.nbins) {
+        const float *src = a.scratch + ((size_t)(ug * a.PG + s) * a.UB + uw) * a.img_floats + (c * a.nbins + bin) * 32 + lane;
+        const size_t bstride = (size_t)a.UB * a.img_floats;
+        if (R >= a.G) { // every CTA owns at least one row: all pieces in [bfirst, blast] exist
+#pragma unroll 4
+            for (int b = bfirst + pg; b <= blast; b += NPG) acc += (double)src[(size_t)b * bstride];
+        } else {        // CTAs with an empty row range wrote nothing: skip their slots
+            for (int b = bfirst + pg; b <= blast; b += NPG)
                 if (R * b / a.G < R * (b + 1) / a.G) acc += (double)src[(size_t)b * bstride];
         }
-        tile[w][lane] = acc;
-        __syncthreads();
+    }
+    part[pg][e] = acc;
+    __syncthreads();
+    if (pg == 0) {
+        double t = part[0][e];
+#pragma unroll
+        for (int q = 1; q < NPG; ++q) t += part[q][e];
+        tile[binl][lane] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x < NE) {
+        const int fl = threadIdx.x / BPB, bl = threadIdx.x % BPB;
         const int slotf = fg * 32 + fl, binw = bin0 + bl;
-        if (slotf < a.F && binw < a.nbins)
-            a.hcomp[(((size_t)s * a.F + slotf) * a.C + (ct * 4 + c)) * a.nbins + binw] = tile[bl][fl];
-        __syncthreads();
+        if (slotf < a.F && binw < a.nbins) {
+            double *dst = a.hcomp + ((size_t)s * a.F + slotf) * a.C * a.nbins + binw;
+            const int ce = ct * a.NCH + c;
+            const double v = tile[bl][fl];
+            if (a.Ce == a.C) {
+                dst[(size_t)ce * a.nbins] = v;
+            } else if (ce < a.K) { // mse with elided hessians: accumulated channels are g_1..g_K, w
+                dst[(size_t)ce * a.nbins] = v;
+            } else {
+                dst[(size_t)(2 * a.K) * a.nbins] = v;                                           // w
+                for (int k = 0; k < a.K; ++k) dst[(size_t)(a.K + k) * a.nbins] = 2.0 * v;       // h_k = 2w (src/loss.jl:52)
+            }
+        }
     }
 }
 
@@ -321,11 +448,11 @@ int occupancy(int BP, int NCH, int threads, size_t smem) {
 // Geometry for F feature slots.  Called once at create time with F = nfeats (sizes the scratch buffer)
 // and again per tree when the column sample is smaller.
 int32_t evb_hist_geometry(const evb_handle *h, int F, HistGeom *g) {
-    const int B = h->B, C = h->C;
+    const int B = h->B, C = h->Ce;
     g->BP = B <= 32 ? 32 : B <= 64 ? 64 : B <= 128 ? 128 : 256;
-    g->NCH = C < 4 ? C : 4;
+    g->NCT = (C + 3) / 4;              // channel groups; channels are spread evenly over them
+    g->NCH = (C + g->NCT - 1) / g->NCT;
     g->NFG = (F + 31) / 32;
-    g->NCT = (C + 3) / 4;
     g->U = g->NFG * g->NCT;
     const size_t img = (size_t)32 * g->BP * g->NCH * 4;
     const size_t stage = (size_t)EVB_TILE_ROWS * (h->RS + h->GS * 4);
@@ -339,13 +466,18 @@ int32_t evb_hist_geometry(const evb_handle *h, int F, HistGeom *g) {
     g->UB = UB;
     g->NUG = (g->U + UB - 1) / UB;
     // blocks per SM: as many as fit with >= 3 stages, at most 8
-    int t = (int)(sm_total / (UB * img + 3 * stage + 256 + reserve));
+    int t = (int)(sm_total / (UB * img + 2 * stage + 256 + reserve)); // resident warps matter more than stage depth
+    if (const char *e = getenv("EVB_HIST_BLOCKS_PER_SM")) {           // tuning override
+        const int want = atoi(e);
+        if (want >= 1 && UB * img + 2 * stage + 256 + reserve <= sm_total / want) t = want;
+    }
     if (t < 1) t = 1;
     if (t > 8) t = 8;
     size_t per_block = sm_total / t - reserve;
     if (per_block > blk_max) per_block = blk_max;
     int S = (int)((per_block - UB * img - 256) / stage);
     if (S > 8) S = 8;
+    if (const char *e = getenv("EVB_HIST_STAGES")) { const int want = atoi(e); if (want >= 2 && want < S) S = want; }
     if (S < 2) S = 2;
     g->stages = S;
     g->smem = UB * img + (size_t)S * stage + 2 * S * 8 + 128;
@@ -373,8 +505,9 @@ int32_t evb_launch_hist(evb_handle *h, int level) {
     a.xT = h->xT; a.grad = h->grad; a.rows = h->rows[(level - 1) & 1]; a.js0 = h->js_d;
     a.plan = h->plan + level; a.cum = h->cum; a.slot_node = h->slot_node; a.seg_start = h->seg_start;
     a.scratch = h->scratch; a.err = h->d_err;
-    a.RS = h->RS; a.GS = h->GS; a.F = h->F; a.nbins = h->B; a.C = h->C; a.NFG = g.NFG; a.U = g.U; a.UB = g.UB;
+    a.RS = h->RS; a.GS = h->GS; a.F = h->F; a.nbins = h->B; a.C = h->Ce; a.NFG = g.NFG; a.U = g.U; a.UB = g.UB;
     a.stages = g.stages; a.PG = g.PG; a.img_floats = (uint32_t)g.img_floats;
+    a.mode = h->hist_mode;
     dim3 grid(g.G, g.NUG);
     const int threads = (g.UB + 1) * 32;
     evb_tic(h, EVB_T_HIST);
@@ -394,11 +527,17 @@ int32_t evb_launch_hist_reduce(evb_handle *h, int level) {
     const HistGeom &g = h->hg;
     ReduceArgs a;
     a.scratch = h->scratch; a.hcomp = h->hcomp; a.plan = h->plan + level; a.cum = h->cum;
-    a.G = g.G; a.PG = g.PG; a.UB = g.UB; a.NFG = g.NFG; a.U = g.U; a.F = h->F; a.C = h->C; a.nbins = h->B; a.NCH = g.NCH;
+    a.G = g.G; a.PG = g.PG; a.UB = g.UB; a.NFG = g.NFG; a.U = g.U; a.F = h->F; a.C = h->C; a.Ce = h->Ce; a.K = h->K; a.nbins = h->B; a.NCH = g.NCH;
     a.img_floats = (uint32_t)g.img_floats;
-    dim3 grid(evb_level_slots(level), g.U, (h->B + 15) / 16);
+    const int slots = evb_level_slots(level);
     evb_tic(h, EVB_T_HIST_REDUCE);
-    k_hist_reduce<<<grid, 512, 0, h->st>>>(a);
+    if (slots <= 4) {
+        dim3 grid(slots, g.U * g.NCH, (h->B + 3) / 4);
+        k_hist_reduce<4><<<grid, 512, 0, h->st>>>(a);
+    } else {
+        dim3 grid(slots, g.U * g.NCH, (h->B + 15) / 16);
+        k_hist_reduce<16><<<grid, 512, 0, h->st>>>(a);
+    }
     evb_toc(h, EVB_T_HIST_REDUCE);
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;

@@ -64,6 +64,7 @@ struct HistGeom {
 struct evb_handle {
     evb_params p;
     int K, C, B, D, nn;        // nn = 2^D-1
+    int Ce;                    // channels actually accumulated: C, or K+1 for mse where h = 2w is rebuilt from w
     int nfeats, RS, GS;        // RS: bytes per row of xT (multiple of 32); GS: floats per grad record (multiple of 4)
     int64_t n;                 // local rows
     int dev, num_sms;
@@ -72,6 +73,7 @@ struct evb_handle {
 
     // row data
     uint8_t *xT;       // [n][RS]  observation-major bins (1..B), zero padded
+    uint8_t *xC;       // [nfeats][n] feature-major copy (the layout of the caller's x_bin) read by the row partition
     float *grad;       // [n][GS]  g_1..g_K,h_1..h_K,w,(pad)
     float *pred;       // [n][K]
     void *y;           // float [n][ycols] or uint32 [n]
@@ -105,11 +107,14 @@ struct evb_handle {
     uint32_t *item_bits;   // [max_items][EVB_PART_CHUNK/32]
     int max_items, maxslots;
     int32_t *scan_tmp;     // block counts for the mask compaction
+    double *fbest_gain;    // [nodes of a level][nfeats] per-feature best split of the scan
+    int32_t *fbest_bin;
     int *d_err;            // device error word
     int *h_err;            // pinned mirror
 
     // histograms
     HistGeom hg;
+    int hist_mode;    // EVB_HIST_MODE environment override (kernel variants / diagnostics)
     double *hist;     // [2^(D-2) nodes][F][C][B] retained for the subtraction trick
     int hist_nodes;   // nodes with id < hist_nodes are retained
     double *hcomp;    // [maxslots][F][C][B] freshly built histograms of the level (allreduce buffer)

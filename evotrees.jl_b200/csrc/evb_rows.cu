@@ -13,18 +13,26 @@ constexpr unsigned FULL = 0xffffffffu;
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }             // loss.jl:249-251
 __device__ __forceinline__ float softplusf_(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); } // loss.jl:257-260
 
-// gradient record of one row: rec[0..K) = g*w, rec[K..2K) = h*w, rec[2K] = w (kept)
-__device__ __forceinline__ void grad_row(int loss, int K, const float *p, const void *y, int ycols, long long i, float *rec) {
-    const float w = rec[2 * K];
+// Gradient record of one row.  Channel c (reference order g_1..g_K, h_1..h_K, w) lives at float
+// (c / NCH) * 4 + c % NCH: the channels of one histogram unit start on a 16-byte boundary.
+__device__ __forceinline__ int gpos(int c, int NCH) { return (c / NCH) * 4 + (c % NCH); }
+#define REC(c) rec[gpos((c), NCH)]
+// For mse the hessian channels are not stored (h = 2w is rebuilt when the histogram is reduced): the record is
+// g_1..g_K, w, i.e. `elided` shifts w from channel 2K to channel K.
+__device__ __forceinline__ void grad_row(int loss, int K, int NCH, bool elided, const float *p, const void *y, int ycols, long long i, float *rec) {
+    const float w = REC(elided ? K : 2 * K);
     if (loss == EVB_MSE) {
         const float *yf = (const float *)y + (size_t)i * ycols;
-        for (int k = 0; k < K; ++k) { rec[k] = 2.0f * (p[k] - yf[k]) * w; rec[K + k] = 2.0f * w; }
+        for (int k = 0; k < K; ++k) {
+            REC(k) = 2.0f * (p[k] - yf[k]) * w;
+            if (!elided) REC(K + k) = 2.0f * w;
+        }
     } else if (loss == EVB_LOGLOSS) {
         const float *yf = (const float *)y + (size_t)i * ycols;
         for (int k = 0; k < K; ++k) {
             const float s = sigmoidf_(p[k]);
-            rec[k] = (s - yf[k]) * w;
-            rec[K + k] = s * (1.0f - s) * w;
+            REC(k) = (s - yf[k]) * w;
+            REC(K + k) = s * (1.0f - s) * w;
         }
     } else if (loss == EVB_MLOGLOSS) {
         const uint32_t yi = ((const uint32_t *)y)[i];
@@ -32,8 +40,8 @@ __device__ __forceinline__ void grad_row(int loss, int K, const float *p, const 
         for (int k = 0; k < K; ++k) isum += expf(p[k]);
         for (int k = 0; k < K; ++k) {
             const float prob = expf(p[k]) / isum;
-            rec[k] = (((uint32_t)(k + 1) == yi) ? prob - 1.0f : prob) * w;
-            rec[K + k] = prob * (1.0f - prob) * w;
+            REC(k) = (((uint32_t)(k + 1) == yi) ? prob - 1.0f : prob) * w;
+            REC(K + k) = prob * (1.0f - prob) * w;
         }
     } else { // EVB_GAUSSIAN_MLE
         const int Y = K / 2;
@@ -43,10 +51,10 @@ __device__ __forceinline__ void grad_row(int loss, int K, const float *p, const 
             const float scale = softplusf_(sr), ds = sigmoidf_(sr);
             const float resid = loc - yf[t];
             const float s2 = scale * scale;
-            rec[2 * t] = resid / s2 * w;
-            rec[2 * t + 1] = (1.0f - resid * resid / s2) * ds / scale * w;
-            rec[2 * Y + 2 * t] = 1.0f / s2 * w;
-            rec[2 * Y + 2 * t + 1] = 2.0f * (ds / scale) * (ds / scale) * w;
+            REC(2 * t) = resid / s2 * w;
+            REC(2 * t + 1) = (1.0f - resid * resid / s2) * ds / scale * w;
+            REC(2 * Y + 2 * t) = 1.0f / s2 * w;
+            REC(2 * Y + 2 * t + 1) = 2.0f * (ds / scale) * (ds / scale) * w;
         }
     }
 }
@@ -111,20 +119,21 @@ __global__ void k_check_bins(const uint8_t *xT, long long n, int RS, int nfeats,
     if (bad) atomicCAS(err, 0, EVB_DERR_BIN_RANGE);
 }
 
-__global__ void k_init_state(float *grad, float *pred, const float *w, const float *pred0, const float *mu, long long n, int K, int GS) {
+#undef REC
+__global__ void k_init_state(float *grad, float *pred, const float *w, const float *pred0, const float *mu, long long n, int K, int GS, int NCH, int wch) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float *rec = grad + (size_t)i * GS;
     for (int c = 0; c < GS; ++c) rec[c] = 0.0f;
-    rec[2 * K] = w ? w[i] : 1.0f; // ∇[end, :] .= w (src/init.jl:173-174)
+    rec[gpos(wch, NCH)] = w ? w[i] : 1.0f; // ∇[end, :] .= w (src/init.jl:173-174)
     for (int k = 0; k < K; ++k) pred[(size_t)i * K + k] = pred0 ? pred0[(size_t)i * K + k] : mu[k];
 }
 
 // ---------------------------------------------------------------------------------- gradients
-__global__ void k_grads(int loss, int K, int GS, int ycols, long long n, const float *pred, const void *y, float *grad) {
+__global__ void k_grads(int loss, int K, int GS, int NCH, int elided, int ycols, long long n, const float *pred, const void *y, float *grad) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    grad_row(loss, K, pred + (size_t)i * K, y, ycols, i, grad + (size_t)i * GS);
+    grad_row(loss, K, NCH, elided != 0, pred + (size_t)i * K, y, ycols, i, grad + (size_t)i * GS);
 }
 
 // ---------------------------------------------------------------------------------- row sampling
@@ -215,7 +224,7 @@ struct FinArgs {
     const void *y;
     uint32_t *nidx;
     long long n;
-    int RS, K, GS, loss, nn, ycols, compute_grads, packed_in_smem;
+    int RS, K, GS, NCH, elided, loss, nn, ycols, compute_grads, packed_in_smem;
 };
 __global__ void __launch_bounds__(256) k_finalize(FinArgs a) {
     extern __shared__ uint32_t s_packed[];
@@ -231,7 +240,7 @@ __global__ void __launch_bounds__(256) k_finalize(FinArgs a) {
     a.nidx[i] = (uint32_t)nid;
     float *p = a.pred + (size_t)i * a.K;
     pred_add(a.loss, a.K, p, a.t_pred + (size_t)(nid - 1) * a.K);
-    if (a.compute_grads) grad_row(a.loss, a.K, p, a.y, a.ycols, i, a.grad + (size_t)i * a.GS);
+    if (a.compute_grads) grad_row(a.loss, a.K, a.NCH, a.elided != 0, p, a.y, a.ycols, i, a.grad + (size_t)i * a.GS);
 }
 
 // node of every sampled row from the row lists left by the partition kernels; one CTA per node
@@ -330,14 +339,14 @@ int32_t evb_launch_check_bins(evb_handle *h) {
 }
 
 int32_t evb_launch_init_state(evb_handle *h, const float *w_dev, const float *pred0_dev, const float *mu_dev) {
-    k_init_state<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->grad, h->pred, w_dev, pred0_dev, mu_dev, h->n, h->K, h->GS);
+    k_init_state<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->grad, h->pred, w_dev, pred0_dev, mu_dev, h->n, h->K, h->GS, h->hg.NCH, h->Ce - 1);
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
 }
 
 int32_t evb_launch_grads(evb_handle *h) {
     evb_tic(h, EVB_T_GRADS);
-    k_grads<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->p.loss, h->K, h->GS, h->ycols, h->n, h->pred, h->y, h->grad);
+    k_grads<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->p.loss, h->K, h->GS, h->hg.NCH, h->Ce != h->C, h->ycols, h->n, h->pred, h->y, h->grad);
     evb_toc(h, EVB_T_GRADS);
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
@@ -361,7 +370,7 @@ int32_t evb_launch_rows_init(evb_handle *h, bool use_mask, uint8_t mask_cond) {
 int32_t evb_launch_finalize(evb_handle *h, bool compute_grads) {
     FinArgs a;
     a.xT = h->xT; a.t_packed = h->t_packed; a.t_pred = h->t_pred; a.pred = h->pred; a.grad = h->grad; a.y = h->y;
-    a.nidx = h->nidx; a.n = h->n; a.RS = h->RS; a.K = h->K; a.GS = h->GS; a.loss = h->p.loss; a.nn = h->nn;
+    a.nidx = h->nidx; a.n = h->n; a.RS = h->RS; a.K = h->K; a.GS = h->GS; a.NCH = h->hg.NCH; a.elided = h->Ce != h->C; a.loss = h->p.loss; a.nn = h->nn;
     a.ycols = h->ycols; a.compute_grads = compute_grads ? 1 : 0;
     const size_t smem = (size_t)h->nn * 4;
     a.packed_in_smem = smem <= 40 * 1024 ? 1 : 0;

@@ -105,6 +105,8 @@ struct ScanArgs {
     uint8_t *t_bin, *t_split;
     float *t_gain, *t_w, *t_pred;
     uint32_t *t_packed;
+    double *fbest_gain; // [nodes of the level][F] best gain of each feature
+    int32_t *fbest_bin; // [nodes of the level][F] its bin (0-based) or -1
     int F, C, K, B, level, D, hist_nodes, loss;
     double neb; // -eta / bagging_size
     double lambda, L2, gamma, min_weight;
@@ -128,146 +130,166 @@ __device__ __forceinline__ float leaf_value(const ScanArgs &a, const double *s, 
     return (float)(a.neb * g / fmax(DBL_EPSILON, h + a.lambda * s[C - 1] + a.L2));
 }
 
-// one CTA per node of the level; warps stride over feature slots, lanes over bins
-__global__ void __launch_bounds__(256) k_scan(ScanArgs a) {
-    const int n = (1 << (a.level - 1)) + blockIdx.x;
+// Stage 1: one warp per (node of the level, feature slot), lanes over bins.  Applies the sibling subtraction,
+// stores the node's histogram if its children will need it, scans the bins and records the best split of
+// this feature.  Warps are independent, so even the root level (one node) spreads over many SMs.
+__global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int C = a.C, K = a.K, B = a.B, F = a.F;
+    const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + wid;
+    const int m = 1 << (a.level - 1);
+    const int i = (int)(gw / F), f = (int)(gw % F);
+    __shared__ double s_sum_all[8][72];
+    double *s_sum = s_sum_all[wid];
+    if (i >= m) return;
+    const int n = m + i;
     const int kd = a.kind[n];
     if (kd == EVB_KIND_NONE) return;
-    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
-    const int C = a.C, K = a.K, B = a.B, F = a.F;
     const size_t FCB = (size_t)F * C * B;
-    const double *hc = a.hcomp + (size_t)a.bslot[n] * FCB;
+    const double *__restrict__ hc = a.hcomp + (size_t)a.bslot[n] * FCB;
     const bool sub = kd == EVB_KIND_SUB;
-    const double *hp = a.hist + (size_t)(n >> 1) * FCB;
+    const double *__restrict__ hp = a.hist + (size_t)(n >> 1) * FCB;
     const bool keep = n < a.hist_nodes;
-    double *hn = a.hist + (size_t)n * FCB;
-
-    __shared__ double s_sum[72], s_left[72];
-    __shared__ double s_gain[8];
-    __shared__ int s_slot[8], s_bin[8];
-    __shared__ int s_best_slot, s_best_bin;
-    __shared__ double s_best_gain;
+    double *__restrict__ hn = a.hist + (size_t)n * FCB;
 
     if (n == 1) {
         // root sums = sum over the bins of feature slot 0 (every sampled row has exactly one bin there);
         // the reference sums the gradients of the sampled rows directly (src/fit.jl:66)
-        for (int c = wid; c < C; c += nw) {
+        for (int c = 0; c < C; ++c) {
             double v = 0.0;
-            for (int b = lane; b < B; b += 32) v += hc[(size_t)c * B + b];
+            for (int b = lane; b < B; b += 32) v += __ldg(hc + (size_t)c * B + b);
             v = warp_sum(v);
-            if (lane == 0) a.nsum[(size_t)C + c] = v;
+            if (lane == 0) { s_sum[c] = v; if (f == 0) a.nsum[(size_t)C + c] = v; }
         }
-        __syncthreads();
+    } else {
+        for (int c = lane; c < C; c += 32) s_sum[c] = a.nsum[(size_t)n * C + c];
     }
-    if (tid < C) s_sum[tid] = a.nsum[(size_t)n * C + tid];
-    __syncthreads();
+    __syncwarp();
 
-    const bool can_split = a.level < a.D;
     double gain_p = 0.0;
     const double w_p = s_sum[C - 1];
     for (int k = 0; k < K; ++k) gain_p += term_gh(s_sum[k], s_sum[K + k], w_p, a.lambda, a.L2); // node_gain, split.jl:58-66
 
-    double best_gain = a.gamma; // get_best_split starts at gamma and takes strict improvements (fit-utils.jl:444-450)
-    int best_slot = -1, best_bin = -1;
     const int nchk = (B + 31) >> 5;
-
-    if (can_split) {
-        for (int f = wid; f < F; f += nw) {
-            const uint32_t feat = a.js0[f];
-            const bool numeric = a.feattypes[feat] != 0;
-            const int constraint = a.mono[feat];
-            const int b_max = numeric ? B - 1 : B;
-            const size_t fo = (size_t)f * C * B;
-            auto val = [&](int c, int b) -> double {
-                const size_t o = fo + (size_t)c * B + b;
-                double v = hc[o];
-                if (sub) v = hp[o] - v; // subtract_hist!: parent - sibling (fit-utils.jl:321-332)
-                if (keep) hn[o] = v;
-                return v;
-            };
-            double wl[8], gacc[8];
-            unsigned okmask = 0xffu;
-            {
-                double carry = 0.0;
+    const uint32_t feat = a.js0[f];
+    const bool numeric = a.feattypes[feat] != 0;
+    const int constraint = a.mono[feat];
+    const int b_max = numeric ? B - 1 : B;
+    const size_t fo = (size_t)f * C * B;
+    auto val = [&](int c, int b) -> double {
+        const size_t o = fo + (size_t)c * B + b;
+        double v = __ldg(hc + o);
+        if (sub) v = __ldg(hp + o) - v; // subtract_hist!: parent - sibling (fit-utils.jl:321-332)
+        if (keep) hn[o] = v;
+        return v;
+    };
+    double lg = a.gamma; // get_best_split starts at gamma and takes strict improvements (fit-utils.jl:444-450)
+    int lb = 0x7fffffff;
+    if (a.level < a.D) {
+        double wl[8], gacc[8];
+        unsigned okmask = 0xffu;
+        {
+            double carry = 0.0;
 #pragma unroll
-                for (int ch = 0; ch < 8; ++ch) {
-                    gacc[ch] = 0.0;
-                    wl[ch] = 0.0;
-                    if (ch < nchk) {
-                        const int b = ch * 32 + lane;
-                        double v = b < B ? val(C - 1, b) : 0.0;
-                        if (numeric) { v = warp_incl_scan(v, lane) + carry; carry = __shfl_sync(FULL, v, 31); }
-                        wl[ch] = v;
-                    }
+            for (int ch = 0; ch < 8; ++ch) {
+                gacc[ch] = 0.0;
+                wl[ch] = 0.0;
+                if (ch < nchk) {
+                    const int b = ch * 32 + lane;
+                    double v = b < B ? val(C - 1, b) : 0.0;
+                    if (numeric) { v = warp_incl_scan(v, lane) + carry; carry = __shfl_sync(FULL, v, 31); }
+                    wl[ch] = v;
                 }
             }
-            for (int k = 0; k < K; ++k) {
-                double cg = 0.0, chh = 0.0;
-                const double sg = s_sum[k], sh = s_sum[K + k];
-#pragma unroll
-                for (int ch = 0; ch < 8; ++ch) {
-                    if (ch < nchk) {
-                        const int b = ch * 32 + lane;
-                        double gl = b < B ? val(k, b) : 0.0;
-                        double hl = b < B ? val(K + k, b) : 0.0;
-                        if (numeric) {
-                            gl = warp_incl_scan(gl, lane) + cg; cg = __shfl_sync(FULL, gl, 31);
-                            hl = warp_incl_scan(hl, lane) + chh; chh = __shfl_sync(FULL, hl, 31);
-                        }
-                        const double w_l = wl[ch], w_r = w_p - w_l;
-                        gacc[ch] += term_gh(gl, hl, w_l, a.lambda, a.L2) + term_gh(sg - gl, sh - hl, w_r, a.lambda, a.L2);
-                        if (k == 0 && constraint != 0) {
-                            // pred_scalar on left / right sums (src/predict.jl:205-208, 235-238)
-                            const double pl = a.neb * gl / fmax(DBL_EPSILON, hl + a.lambda * w_l + a.L2);
-                            const double pr = a.neb * (sg - gl) / fmax(DBL_EPSILON, (sh - hl) + a.lambda * w_r + a.L2);
-                            const bool ok = (constraint == -1 && pl > pr) || (constraint == 1 && pl < pr);
-                            if (!ok) okmask &= ~(1u << ch);
-                        }
-                    }
-                }
-            }
-            // candidate of this lane: lowest bin among its strict maxima
-            double lg = a.gamma;
-            int lb = 0x7fffffff;
+        }
+        for (int k = 0; k < K; ++k) {
+            double cg = 0.0, chh = 0.0;
+            const double sg = s_sum[k], sh = s_sum[K + k];
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) {
                 if (ch < nchk) {
                     const int b = ch * 32 + lane;
+                    double gl = b < B ? val(k, b) : 0.0;
+                    double hl = b < B ? val(K + k, b) : 0.0;
+                    if (numeric) {
+                        gl = warp_incl_scan(gl, lane) + cg; cg = __shfl_sync(FULL, gl, 31);
+                        hl = warp_incl_scan(hl, lane) + chh; chh = __shfl_sync(FULL, hl, 31);
+                    }
                     const double w_l = wl[ch], w_r = w_p - w_l;
-                    if (b < b_max && w_l > a.min_weight && w_r > a.min_weight && ((okmask >> ch) & 1u)) {
-                        const double g = gacc[ch] - gain_p;
-                        if (g > lg) { lg = g; lb = b; }
+                    gacc[ch] += term_gh(gl, hl, w_l, a.lambda, a.L2) + term_gh(sg - gl, sh - hl, w_r, a.lambda, a.L2);
+                    if (k == 0 && constraint != 0) {
+                        // pred_scalar on left / right sums (src/predict.jl:205-208, 235-238)
+                        const double pl = a.neb * gl / fmax(DBL_EPSILON, hl + a.lambda * w_l + a.L2);
+                        const double pr = a.neb * (sg - gl) / fmax(DBL_EPSILON, (sh - hl) + a.lambda * w_r + a.L2);
+                        const bool ok = (constraint == -1 && pl > pr) || (constraint == 1 && pl < pr);
+                        if (!ok) okmask &= ~(1u << ch);
                     }
                 }
             }
+        }
+        // candidate of this lane: lowest bin among its strict maxima
 #pragma unroll
-            for (int d = 16; d >= 1; d >>= 1) {
-                const double og = __shfl_xor_sync(FULL, lg, d);
-                const int ob = __shfl_xor_sync(FULL, lb, d);
-                if (og > lg || (og == lg && ob < lb)) { lg = og; lb = ob; }
-            }
-            if (lb != 0x7fffffff && lg > best_gain) { best_gain = lg; best_slot = f; best_bin = lb; }
-        }
-    }
-    if (lane == 0) { s_gain[wid] = best_gain; s_slot[wid] = best_slot; s_bin[wid] = best_bin; }
-    __syncthreads();
-    if (tid == 0) {
-        double bg = a.gamma; int bs = -1, bb = -1;
-        for (int w = 0; w < nw; ++w) {
-            if (s_slot[w] >= 0 && (s_gain[w] > bg || (s_gain[w] == bg && bs >= 0 && s_slot[w] < bs))) {
-                bg = s_gain[w]; bs = s_slot[w]; bb = s_bin[w];
+        for (int ch = 0; ch < 8; ++ch) {
+            if (ch < nchk) {
+                const int b = ch * 32 + lane;
+                const double w_l = wl[ch], w_r = w_p - w_l;
+                if (b < b_max && w_l > a.min_weight && w_r > a.min_weight && ((okmask >> ch) & 1u)) {
+                    const double g = gacc[ch] - gain_p;
+                    if (g > lg) { lg = g; lb = b; }
+                }
             }
         }
-        s_best_gain = bg; s_best_slot = bs; s_best_bin = bb;
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) {
+            const double og = __shfl_xor_sync(FULL, lg, d);
+            const int ob = __shfl_xor_sync(FULL, lb, d);
+            if (og > lg || (og == lg && ob < lb)) { lg = og; lb = ob; }
+        }
     }
-    __syncthreads();
-    const int bs = s_best_slot, bb = s_best_bin;
-    if (bs >= 0) {
-        // _child_sums!: left = bins 1..bin of the winning feature (numeric) or that bin (categorical)
+    if (lane == 0) {
+        a.fbest_gain[(size_t)i * F + f] = lg;
+        a.fbest_bin[(size_t)i * F + f] = lb == 0x7fffffff ? -1 : lb;
+    }
+}
+
+// Stage 2: one warp per node: first strict maximum over the features (ascending feature order), child sums
+// (`_child_sums!`, fit-utils.jl:472-486), tree arrays and leaf values.
+__global__ void __launch_bounds__(256) k_scan_node(ScanArgs a) {
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int C = a.C, K = a.K, B = a.B, F = a.F;
+    const int m = 1 << (a.level - 1);
+    const int i = blockIdx.x * (blockDim.x >> 5) + wid;
+    __shared__ double s_sum_all[8][72], s_left_all[8][72], s_right_all[8][72];
+    double *s_sum = s_sum_all[wid], *s_left = s_left_all[wid], *s_right = s_right_all[wid];
+    if (i >= m) return;
+    const int n = m + i;
+    const int kd = a.kind[n];
+    if (kd == EVB_KIND_NONE) return;
+    const size_t FCB = (size_t)F * C * B;
+    const double *hc = a.hcomp + (size_t)a.bslot[n] * FCB;
+    const bool sub = kd == EVB_KIND_SUB;
+    const double *hp = a.hist + (size_t)(n >> 1) * FCB;
+    for (int c = lane; c < C; c += 32) s_sum[c] = a.nsum[(size_t)n * C + c];
+    __syncwarp();
+
+    double bg = a.gamma;
+    int bs = 0x7fffffff, bb = -1;
+    for (int f = lane; f < F; f += 32) {
+        const double g = a.fbest_gain[(size_t)i * F + f];
+        const int b = a.fbest_bin[(size_t)i * F + f];
+        if (b >= 0 && g > bg) { bg = g; bs = f; bb = b; }
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+        const double og = __shfl_xor_sync(FULL, bg, d);
+        const int os = __shfl_xor_sync(FULL, bs, d), ob = __shfl_xor_sync(FULL, bb, d);
+        if (os != 0x7fffffff && (og > bg || (og == bg && os < bs))) { bg = og; bs = os; bb = ob; }
+    }
+    if (bs != 0x7fffffff) {
         const uint32_t feat = a.js0[bs];
         const bool numeric = a.feattypes[feat] != 0;
         const size_t fo = (size_t)bs * C * B;
-        for (int c = wid; c < C; c += nw) {
+        for (int c = 0; c < C; ++c) {
             double v = 0.0;
             if (numeric) {
                 for (int b = lane; b <= bb; b += 32) {
@@ -279,17 +301,17 @@ __global__ void __launch_bounds__(256) k_scan(ScanArgs a) {
                 const size_t o = fo + (size_t)c * B + bb;
                 v = sub ? hp[o] - hc[o] : hc[o];
             }
-            if (lane == 0) s_left[c] = v;
+            if (lane == 0) { s_left[c] = v; s_right[c] = s_sum[c] - v; }
         }
-        __syncthreads();
+        __syncwarp();
         const int nl = n << 1, nr = nl + 1;
-        if (tid < C) {
-            a.nsum[(size_t)nl * C + tid] = s_left[tid];
-            a.nsum[(size_t)nr * C + tid] = s_sum[tid] - s_left[tid];
+        for (int c = lane; c < C; c += 32) {
+            a.nsum[(size_t)nl * C + c] = s_left[c];
+            a.nsum[(size_t)nr * C + c] = s_right[c];
         }
-        if (tid == 0) {
+        if (lane == 0) {
             a.t_w[n - 1] = (float)s_sum[C - 1];
-            a.t_gain[n - 1] = (float)s_best_gain;
+            a.t_gain[n - 1] = (float)bg;
             a.t_bin[n - 1] = (uint8_t)(bb + 1);
             a.t_feat[n - 1] = (int32_t)feat + 1;
             a.t_split[n - 1] = 1;
@@ -297,24 +319,23 @@ __global__ void __launch_bounds__(256) k_scan(ScanArgs a) {
         }
         if (a.level + 1 == a.D) {
             // children sit at max depth: they are leaves (src/fit.jl:74-82)
-            __shared__ double s_right[72];
-            if (tid < C) s_right[tid] = s_sum[tid] - s_left[tid];
-            __syncthreads();
-            if (tid < K) {
-                a.t_pred[(size_t)(nl - 1) * K + tid] = leaf_value(a, s_left, tid);
-                a.t_pred[(size_t)(nr - 1) * K + tid] = leaf_value(a, s_right, tid);
+            for (int k = lane; k < K; k += 32) {
+                a.t_pred[(size_t)(nl - 1) * K + k] = leaf_value(a, s_left, k);
+                a.t_pred[(size_t)(nr - 1) * K + k] = leaf_value(a, s_right, k);
             }
-            if (tid == 0) { a.t_w[nl - 1] = (float)s_left[C - 1]; a.t_w[nr - 1] = (float)s_right[C - 1]; }
+            if (lane == 0) { a.t_w[nl - 1] = (float)s_left[C - 1]; a.t_w[nr - 1] = (float)s_right[C - 1]; }
         }
     } else {
-        if (tid == 0) a.t_w[n - 1] = (float)s_sum[C - 1];
-        if (tid < K) a.t_pred[(size_t)(n - 1) * K + tid] = leaf_value(a, s_sum, tid);
+        if (lane == 0) a.t_w[n - 1] = (float)s_sum[C - 1];
+        for (int k = lane; k < K; k += 32) a.t_pred[(size_t)(n - 1) * K + k] = leaf_value(a, s_sum, k);
     }
 }
 
 // ------------------------------------------------------------------------------------------ partition
 struct PartArgs {
-    const uint8_t *xT;
+    const uint8_t *xC; // feature-major bins [nfeats][n]: the rows of a node ascend, so its reads of one feature are
+                       // as dense as the node is (whole sectors near the root, one sector per row deep down)
+    long long n;
     const uint32_t *rows_in;
     uint32_t *rows_out;
     const uint8_t *t_split;
@@ -378,7 +399,7 @@ __global__ void __launch_bounds__(EVB_PART_THREADS) k_part_flags(PartArgs a) {
             bool left = false;
             if (pos < cnt) {
                 const uint32_t row = a.rows_in[start + pos];
-                const uint32_t x = a.xT[(size_t)row * a.RS + feat];
+                const uint32_t x = a.xC[(size_t)feat * a.n + row];
                 left = numeric ? (x <= bin) : (x == bin); // split_set! predicate (fit-utils.jl:173, 291)
             }
             const unsigned bal = __ballot_sync(FULL, left);
@@ -504,7 +525,7 @@ __global__ void __launch_bounds__(EVB_PART_THREADS) k_part_scatter(PartArgs a) {
 
 PartArgs make_part_args(evb_handle *h, int level) {
     PartArgs a;
-    a.xT = h->xT; a.rows_in = h->rows[(level - 1) & 1]; a.rows_out = h->rows[level & 1];
+    a.xC = h->xC; a.n = h->n; a.rows_in = h->rows[(level - 1) & 1]; a.rows_out = h->rows[level & 1];
     a.t_split = h->t_split; a.t_packed = h->t_packed;
     a.seg_start = h->seg_start; a.seg_cnt = h->seg_cnt; a.gcnt = h->gcnt; a.nleft = h->nleft; a.gnleft = h->gnleft;
     a.bslot = h->bslot; a.cum = h->cum; a.slot_node = h->slot_node; a.kind = h->kind;
@@ -550,8 +571,14 @@ int32_t evb_launch_scan(evb_handle *h, int level) {
     a.F = h->F; a.C = h->C; a.K = h->K; a.B = h->B; a.level = level; a.D = h->D; a.hist_nodes = h->hist_nodes;
     a.loss = h->p.loss; a.neb = -h->p.eta / (double)h->p.bagging_size;
     a.lambda = h->p.lambda; a.L2 = h->p.L2; a.gamma = h->p.gamma; a.min_weight = h->p.min_weight;
+    a.fbest_gain = h->fbest_gain; a.fbest_bin = h->fbest_bin;
+    const int m = evb_level_nodes(level);
+    const long long warps = (long long)m * h->F;
     evb_tic(h, EVB_T_SCAN);
-    k_scan<<<evb_level_nodes(level), 256, 0, h->st>>>(a);
+    k_scan_feat<<<(unsigned)((warps + 7) / 8), 256, 0, h->st>>>(a);
+    evb_toc(h, EVB_T_SCAN);
+    evb_tic(h, EVB_T_SCAN);
+    k_scan_node<<<(m + 7) / 8, 256, 0, h->st>>>(a);
     evb_toc(h, EVB_T_SCAN);
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
