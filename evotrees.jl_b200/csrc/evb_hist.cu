@@ -542,3 +542,128 @@ int32_t evb_launch_hist_reduce(evb_handle *h, int level) {
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
 }
+
+// =====================================================================================================
+// Stand-alone histogram of one list of rows, for callers that hold their own device buffers.
+// evb_hist_rows allocates its work buffers per call.
+// =====================================================================================================
+namespace {
+
+struct RowsPlan {
+    LevelPlan plan;
+    int32_t cum[2];
+    int32_t slot_node[2];
+    int32_t seg_start[2];
+    int err;
+    int pad;
+};
+
+__global__ void k_rows_plan_fill(RowsPlan *p, uint32_t *js, int nfeats, long long nrows) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < nfeats) js[t] = (uint32_t)t;
+    if (t == 0) {
+        p->plan.nbuild = 1; p->plan.nitems = 0; p->plan.R = nrows; p->plan.n_sel = (int32_t)nrows; p->plan.pad = 0;
+        p->cum[0] = 0; p->cum[1] = (int32_t)nrows;
+        p->slot_node[0] = 1; p->slot_node[1] = 0;
+        p->seg_start[0] = 0; p->seg_start[1] = 0;
+        p->err = 0;
+    }
+}
+
+int32_t rows_hist_check_args(int32_t device, const void *x_rows, int64_t nobs, int32_t nfeats, int32_t row_stride, int32_t nbins,
+                             const void *grad, int32_t nch, const void *rows, int64_t nrows, const void *out) {
+    if (!x_rows || !grad || !rows || !out) { evb_set_error("evb_hist_rows: null pointer"); return EVB_ERR_ARG; }
+    if (nobs < 1 || nobs > 2000000000ll || nrows < 0 || nrows > 2000000000ll) { evb_set_error("evb_hist_rows: nobs / nrows out of range"); return EVB_ERR_ARG; }
+    if (nfeats < 1 || row_stride < nfeats || (row_stride & 15)) { evb_set_error("evb_hist_rows: row_stride must be >= nfeats and a multiple of 16"); return EVB_ERR_ARG; }
+    if (nbins < 2 || nbins > 255 || nch < 1 || nch > 4) { evb_set_error("evb_hist_rows: nbins must be 2..255 and nch 1..4"); return EVB_ERR_ARG; }
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0) { evb_set_error("no CUDA device available (%s): this library has no CPU fallback", cudaGetErrorString(e)); return EVB_ERR_CUDA; }
+    if (device < 0 || device >= ndev || device >= 64) { evb_set_error("evb_hist_rows: device %d out of range", device); return EVB_ERR_ARG; }
+    return EVB_OK;
+}
+
+// Launches hist + reduce for one list of rows with the given work buffers; `max_pieces` bounds the grid.
+int32_t rows_hist_run(int device, cudaStream_t st, const uint8_t *x_rows, int32_t nfeats, int32_t row_stride, int32_t nbins,
+                      const float *grad, int32_t nch, const uint32_t *rows, int64_t nrows, double *out, float *scratch,
+                      size_t scratch_floats, RowsPlan *plan, uint32_t *js, int hist_mode) {
+    evb_handle hh{};
+    hh.B = nbins; hh.C = nch; hh.Ce = nch; hh.K = 1; hh.RS = row_stride; hh.GS = 4; hh.nfeats = nfeats; hh.maxslots = 1;
+    int sms = 0;
+    EVB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    hh.num_sms = sms;
+    HistGeom g;
+    EVB_CHECK(evb_hist_geometry(&hh, nfeats, &g));
+    const size_t per_piece = (size_t)g.NUG * g.UB * g.img_floats;
+    if (2 * per_piece > scratch_floats) {
+        evb_set_error("evb_hist_rows: nfeats x nbins x nch too large for the work buffer (%zu floats per partial image, %zu available)",
+                      per_piece, scratch_floats);
+        return EVB_ERR_LIMIT;
+    }
+    const int gmax = (int)(scratch_floats / per_piece) - 1;
+    if (g.G > gmax) g.G = gmax;
+    g.PG = g.G + 1;
+    k_rows_plan_fill<<<(nfeats + 255) / 256, 256, 0, st>>>(plan, js, nfeats, nrows);
+    EVB_CUDA(cudaGetLastError());
+    HistArgs a;
+    a.xT = x_rows; a.grad = grad; a.rows = rows; a.js0 = js; a.plan = &plan->plan; a.cum = plan->cum; a.slot_node = plan->slot_node;
+    a.seg_start = plan->seg_start; a.scratch = scratch; a.err = &plan->err;
+    a.RS = row_stride; a.GS = 4; a.F = nfeats; a.nbins = nbins; a.C = nch; a.NFG = g.NFG; a.U = g.U; a.UB = g.UB;
+    a.stages = g.stages; a.PG = g.PG; a.img_floats = (uint32_t)g.img_floats; a.mode = hist_mode;
+    dim3 grid(g.G, g.NUG);
+    const int threads = (g.UB + 1) * 32;
+    cudaError_t e;
+    switch (g.BP) {
+    case 32: e = launch_hist_bp<32>(g.NCH, a, grid, threads, g.smem, st); break;
+    case 64: e = launch_hist_bp<64>(g.NCH, a, grid, threads, g.smem, st); break;
+    case 128: e = launch_hist_bp<128>(g.NCH, a, grid, threads, g.smem, st); break;
+    default: e = launch_hist_bp<256>(g.NCH, a, grid, threads, g.smem, st); break;
+    }
+    EVB_CUDA(e);
+    ReduceArgs r;
+    r.scratch = scratch; r.hcomp = out; r.plan = &plan->plan; r.cum = plan->cum;
+    r.G = g.G; r.PG = g.PG; r.UB = g.UB; r.NFG = g.NFG; r.U = g.U; r.F = nfeats; r.C = nch; r.Ce = nch; r.K = 1; r.nbins = nbins; r.NCH = g.NCH;
+    r.img_floats = (uint32_t)g.img_floats;
+    dim3 rgrid(1, g.U * g.NCH, (nbins + 3) / 4);
+    k_hist_reduce<4><<<rgrid, 512, 0, st>>>(r);
+    EVB_CUDA(cudaGetLastError());
+    int derr = 0;
+    EVB_CUDA(cudaMemcpyAsync(&derr, &plan->err, sizeof(int), cudaMemcpyDeviceToHost, st));
+    EVB_CUDA(cudaStreamSynchronize(st));
+    if (derr != 0) { evb_set_error("evb_hist_rows: device self-check failed (code %d)", derr); return EVB_ERR_DEVICE; }
+    return EVB_OK;
+}
+
+} // namespace
+
+extern "C" int32_t evb_hist_rows(int32_t device, void *stream, const uint8_t *x_rows, int64_t nobs, int32_t nfeats, int32_t row_stride,
+                                 int32_t nbins, const float *grad, int32_t nch, const uint32_t *rows, int64_t nrows, double *out) {
+    EVB_CHECK(rows_hist_check_args(device, x_rows, nobs, nfeats, row_stride, nbins, grad, nch, rows, nrows, out));
+    EVB_CUDA(cudaSetDevice(device));
+    cudaStream_t st = (cudaStream_t)stream;
+    evb_handle hh{};
+    hh.B = nbins; hh.C = nch; hh.Ce = nch; hh.RS = row_stride; hh.GS = 4; hh.nfeats = nfeats; hh.maxslots = 1;
+    int sms = 0;
+    EVB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    hh.num_sms = sms;
+    HistGeom g;
+    EVB_CHECK(evb_hist_geometry(&hh, nfeats, &g));
+    const size_t floats = (size_t)g.NUG * g.PG * g.UB * g.img_floats;
+    float *scratch = nullptr;
+    RowsPlan *plan = nullptr;
+    uint32_t *js = nullptr;
+    int32_t rc = EVB_OK;
+    if (cudaMalloc((void **)&scratch, floats * sizeof(float)) != cudaSuccess || cudaMalloc((void **)&plan, sizeof(RowsPlan)) != cudaSuccess ||
+        cudaMalloc((void **)&js, sizeof(uint32_t) * nfeats) != cudaSuccess) {
+        evb_set_error("evb_hist_rows: out of device memory");
+        rc = EVB_ERR_CUDA;
+    } else {
+        const char *e = getenv("EVB_HIST_MODE");
+        rc = rows_hist_run(device, st, x_rows, nfeats, row_stride, nbins, grad, nch, rows, nrows, out, scratch, floats, plan, js, e ? atoi(e) : 1);
+    }
+    cudaStreamSynchronize(st);
+    if (scratch) cudaFree(scratch);
+    if (plan) cudaFree(plan);
+    if (js) cudaFree(js);
+    return rc;
+}

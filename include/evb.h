@@ -165,6 +165,20 @@ EVB_API int32_t evb_predict(int32_t device, int32_t loss, int32_t K, int32_t ntr
 EVB_API int32_t evb_binarize(int32_t device, const void *x, int32_t dtype, int64_t nobs, int32_t nfeats, const void *edges,
                      int32_t nedges, uint8_t *x_bin);
 
+/*
+ * evb_hist_rows -- the histogram kernel on its own: `_hist!` for one node (src/fit-utils.jl:367-394; GPU
+ * counterpart `hist_kernel!`, ext/EvoTreesKernelAbstractionsExt/fit-utils.jl:57-95) on buffers that already live
+ * on the device.  out[f][c][b] = sum over the listed rows of grad[row][c], b = bin of feature f in that row.
+ *   x_rows  device uint8 [nobs][row_stride], observation-major bins 1..nbins (row_stride >= nfeats, multiple of 16)
+ *   grad    device float [nobs][4], channels c < nch are accumulated
+ *   rows    device uint32 [nrows], 0-based row ids (ascending order gives the reference's summation order)
+ *   out     device double [nfeats][nch][nbins]
+ *   stream  cudaStream_t to run on (NULL = default stream); the call returns after the work has finished.
+ * Work buffers are allocated and freed inside the call.
+ */
+EVB_API int32_t evb_hist_rows(int32_t device, void *stream, const uint8_t *x_rows, int64_t nobs, int32_t nfeats, int32_t row_stride,
+                              int32_t nbins, const float *grad, int32_t nch, const uint32_t *rows, int64_t nrows, double *out);
+
 #ifdef __cplusplus
 }
 #endif

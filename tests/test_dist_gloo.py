@@ -1,0 +1,76 @@
+"""Host side of the row-sharded path with two gloo ranks on CPU: shard bounds, bias from sufficient statistics,
+broadcast of edges, and the additivity that the device path relies on (histograms and child row counts of the
+shards sum to those of the whole data set, so every rank takes the same split and build/subtract decisions)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+from tests.conftest import ROOT
+
+
+def _worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    import __graft_entry__ as g
+    g.load_package()
+    from evotrees_b200.dist import Comm, shard_bounds
+    from evotrees_b200.fit import init_target
+    from oracle import evo_oracle as orc
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    comm = Comm(dist)
+    rng = np.random.default_rng(11)
+    n, f, nbins = 5001, 4, 16
+    x = rng.random((n, f))
+    y = (x @ np.array([1.0, -2.0, 0.5, 0.0]) + 0.1 * rng.normal(size=n)).astype(np.float32)
+    lo, hi = shard_bounds(n, world, rank)
+    xs, ys = x[lo:hi], y[lo:hi]
+    # edges come from rank 0 and are identical everywhere
+    edges = orc.get_edges(xs, nbins, np.random.default_rng(1)) if rank == 0 else np.zeros((f, nbins - 1))
+    edges = comm.broadcast_host(edges)
+    out = {"edges": edges}
+    for loss in ("mse", "gaussian_mle", "logloss", "mlogloss"):
+        yy = ys if loss in ("mse", "gaussian_mle") else (ys > 0).astype(np.float32)
+        if loss == "mlogloss":
+            yy = (ys > 0).astype(np.int64) + (ys > 1).astype(np.int64)
+        K, yd, _, mu_local, _, _ = init_target(loss, yy, None)
+        out["mu_" + loss] = comm.allreduce_bias(loss, yd, mu_local, K)
+    # shard histograms of the root sum to the global histogram; so do the child row counts of a split
+    xb = orc.binarize(xs, edges)
+    g = (2 * (ys.mean() - ys)).astype(np.float64)
+    h = np.stack([np.bincount(xb[:, j].astype(np.int64) - 1, weights=g, minlength=nbins) for j in range(f)])
+    out["hist"] = comm.allreduce_sum(h)
+    out["nleft"] = comm.allreduce_sum(np.array([(xb[:, 0] <= 7).sum()]))
+    np.savez(os.path.join(tmp, f"r{rank}.npz"), **out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_host_plumbing(tmp_path, orc, pkg):
+    import torch.multiprocessing as mp
+    from evotrees_b200.fit import init_target
+    port = 29500 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = np.load(tmp_path / "r0.npz"), np.load(tmp_path / "r1.npz")
+    for k in r0.files:
+        assert np.array_equal(r0[k], r1[k]), f"ranks disagree on {k}"
+    rng = np.random.default_rng(11)
+    n, f, nbins = 5001, 4, 16
+    x = rng.random((n, f))
+    y = (x @ np.array([1.0, -2.0, 0.5, 0.0]) + 0.1 * rng.normal(size=n)).astype(np.float32)
+    K, yd, _, mu, _, _ = init_target("mse", y, None)
+    np.testing.assert_allclose(r0["mu_mse"], mu, rtol=1e-6)
+    K, yd, _, mu, _, _ = init_target("gaussian_mle", y, None)
+    np.testing.assert_allclose(r0["mu_gaussian_mle"], mu, rtol=1e-5)
+    K, yd, _, mu, _, _ = init_target("logloss", (y > 0).astype(np.float32), None)
+    np.testing.assert_allclose(r0["mu_logloss"], mu, rtol=1e-5)
+    K, yd, _, mu, _, _ = init_target("mlogloss", (y > 0).astype(np.int64) + (y > 1).astype(np.int64), None)
+    np.testing.assert_allclose(r0["mu_mlogloss"], mu, rtol=1e-5, atol=1e-6)
+    xb = orc.binarize(x, r0["edges"])
+    per = -(-n // 2)
+    gfull = np.concatenate([2 * (y[:per].mean() - y[:per]), 2 * (y[per:].mean() - y[per:])]).astype(np.float64)
+    hfull = np.stack([np.bincount(xb[:, j].astype(np.int64) - 1, weights=gfull, minlength=nbins) for j in range(f)])
+    np.testing.assert_allclose(r0["hist"], hfull, rtol=1e-12, atol=1e-9)
+    assert int(r0["nleft"][0]) == int((xb[:, 0] <= 7).sum())

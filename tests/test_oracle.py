@@ -1,0 +1,264 @@
+"""CPU oracle against everything the reference's own tests pin for this path, plus self-consistency checks.
+
+Known-answer / finite-difference checks follow test/metrics.jl:134-232 (MLE gradients, Fisher information,
+softplus round trip, inverse link, softmax gradient) and test/predict-leaf-idx.jl:25-73 (traversal rule and
+leaf invariants).  Statistical thresholds follow test/core.jl (eval MSE must beat the bias model by > 75 %).
+"""
+import math
+
+import numpy as np
+import pytest
+
+
+def _dbl4(orc, loc, sr, y):
+    import ctypes as C
+    out = (C.c_double * 4)()
+    orc.lib().orc_gaussian_grad_hess64(C.c_double(loc), C.c_double(sr), C.c_double(y), out)
+    return list(out)
+
+
+def gaussian_lpdf(y, loc, scale):
+    return -(math.log(scale) + (y - loc) ** 2 / (2 * scale ** 2))
+
+
+def test_softplus_roundtrip(orc):
+    for scale in (2.0, 0.5, 1.0):
+        sr = orc.lib().orc_invsoftplus64(scale)
+        assert orc.lib().orc_softplus64(sr) == pytest.approx(scale, rel=1e-12)
+
+
+def test_gaussian_mle_gradients_match_finite_differences(orc):
+    loc, scale, h = 0.5, 2.0, 1e-6
+    sr = orc.lib().orc_invsoftplus64(scale)
+    sp = orc.lib().orc_softplus64
+
+    def metric(lc, raw, y):
+        return gaussian_lpdf(y, lc, sp(raw))
+
+    for y in (1.5, 4.0, -3.0):
+        g1, g2, h1, h2 = _dbl4(orc, loc, sr, y)
+        dloc = (metric(loc + h, sr, y) - metric(loc - h, sr, y)) / (2 * h)
+        draw = (metric(loc, sr + h, y) - metric(loc, sr - h, y)) / (2 * h)
+        assert dloc == pytest.approx(-g1, abs=1e-5)
+        assert draw == pytest.approx(-g2, abs=1e-5)
+    # Fisher information: independent of the residual, positive
+    ds = orc.lib().orc_sigmoid64(sr)
+    ref = _dbl4(orc, loc, sr, loc)[2:]
+    assert ref[0] == pytest.approx(1 / scale ** 2)
+    assert ref[1] == pytest.approx(2 * (ds / scale) ** 2)
+    assert ref[0] > 0 and ref[1] > 0
+    for y in (1.5, 4.0, -3.0):
+        assert _dbl4(orc, loc, sr, y)[2:] == ref
+
+
+def test_inverse_link(orc):
+    # Julia: pred = Float32[0.0 1.0; -2.0 0.5] (K x nobs); here rows are observations
+    pred = np.array([[0.0, -2.0], [1.0, 0.5]], np.float32)
+    p = orc.Params(loss="gaussian_mle", K=2)
+    orc.link(p, pred)
+    assert pred[:, 0].tolist() == [0.0, 1.0]
+    sp = np.array([orc.lib().orc_softplus(float(v)) for v in (-2.0, 0.5)], np.float32)
+    np.testing.assert_allclose(pred[:, 1], sp, rtol=1e-6)
+    assert not np.allclose(pred[:, 1], np.exp(np.array([-2.0, 0.5], np.float32)))
+    pl = np.array([[0.3], [-4.0]], np.float32)
+    orc.link(orc.Params(loss="logloss", K=1), pl)
+    np.testing.assert_allclose(pl[:, 0], 1 / (1 + np.exp(-np.array([0.3, -4.0]))), rtol=1e-6)
+    ps = np.array([[2.0, 1.0, 0.0]], np.float32)
+    orc.link(orc.Params(loss="mlogloss", K=3), ps)
+    np.testing.assert_allclose(ps[0], np.exp([2.0, 1.0, 0.0]) / np.exp([2.0, 1.0, 0.0]).sum(), rtol=1e-6)
+
+
+def test_softmax_gradient_and_hessian(orc):
+    import ctypes as C
+
+    def loss(p, k):
+        return math.log(sum(math.exp(v) for v in p)) - p[k]
+
+    target = 1  # the reference's target = 2 (1-based)
+    for p in ([0.0, 0.0, 0.0], [2.0, 1.0, 0.0], [1.0, -0.5, 0.3], [-1.0, -1.0, 2.0]):
+        isum = sum(math.exp(v) for v in p)
+        h = 1e-5
+        for k in range(len(p)):
+            out = (C.c_double * 2)()
+            orc.lib().orc_mlogloss_grad_hess64(C.c_double(p[k]), C.c_double(isum), C.c_int(k == target), out)
+            pp, pm = list(p), list(p)
+            pp[k] += h
+            pm[k] -= h
+            assert out[0] == pytest.approx((loss(pp, target) - loss(pm, target)) / (2 * h), abs=1e-5)
+            assert out[1] == pytest.approx((loss(pp, target) - 2 * loss(p, target) + loss(pm, target)) / h ** 2, abs=1e-4)
+
+
+def test_update_grads_formulas(orc):
+    rng = np.random.default_rng(0)
+    n = 257
+    w = rng.uniform(0.5, 2, n).astype(np.float32)
+    # mse / logloss
+    for loss in ("mse", "logloss"):
+        p = orc.Params(loss=loss, K=1)
+        pred = rng.normal(size=(n, 1)).astype(np.float32)
+        y = rng.random(n).astype(np.float32)
+        g = np.zeros((n, 3), np.float32)
+        g[:, 2] = w
+        orc.update_grads(p, pred, y, g)
+        if loss == "mse":
+            np.testing.assert_array_equal(g[:, 0], (np.float32(2) * (pred[:, 0] - y)) * w)
+            np.testing.assert_array_equal(g[:, 1], np.float32(2) * w)
+        else:
+            s = 1 / (1 + np.exp(-pred[:, 0].astype(np.float64)))
+            np.testing.assert_allclose(g[:, 0], (s - y) * w, rtol=2e-6, atol=1e-7)
+            np.testing.assert_allclose(g[:, 1], s * (1 - s) * w, rtol=2e-6, atol=1e-7)
+    # softmax
+    K = 4
+    p = orc.Params(loss="mlogloss", K=K)
+    pred = rng.normal(size=(n, K)).astype(np.float32)
+    y = rng.integers(1, K + 1, n).astype(np.uint32)
+    g = np.zeros((n, 2 * K + 1), np.float32)
+    g[:, -1] = w
+    orc.update_grads(p, pred, y, g)
+    e = np.exp(pred.astype(np.float64))
+    prob = e / e.sum(axis=1, keepdims=True)
+    onehot = np.eye(K)[y - 1]
+    np.testing.assert_allclose(g[:, :K], (prob - onehot) * w[:, None], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(g[:, K:2 * K], prob * (1 - prob) * w[:, None], rtol=1e-5, atol=1e-6)
+    # gaussian: layout g_mu, g_phi, h_mu, h_phi, w
+    p = orc.Params(loss="gaussian_mle", K=2)
+    pred = rng.normal(size=(n, 2)).astype(np.float32)
+    y = rng.normal(size=n).astype(np.float32)
+    g = np.zeros((n, 5), np.float32)
+    g[:, -1] = w
+    orc.update_grads(p, pred, y, g)
+    for i in range(0, n, 37):
+        ref = _dbl4(orc, float(pred[i, 0]), float(pred[i, 1]), float(y[i]))
+        np.testing.assert_allclose(g[i, :4], np.array(ref) * w[i], rtol=2e-5, atol=1e-6)
+
+
+def _python_traverse(t, xb_row, feattypes=None):
+    nid = 1
+    while t.split[nid - 1]:
+        f = int(t.feat[nid - 1]) - 1
+        num = True if feattypes is None else bool(feattypes[f])
+        cond = xb_row[f] <= t.cond_bin[nid - 1] if num else xb_row[f] == t.cond_bin[nid - 1]
+        nid = (nid << 1) + (0 if cond else 1)
+    return nid
+
+
+def _fit_oracle(orc, loss="mse", n=3000, f=5, depth=4, rounds=5, nbins=16, seed=1, **kw):
+    rng = np.random.default_rng(seed)
+    x = rng.random((n, f))
+    y = (np.sin(x[:, 0] * 6) + x[:, 1] * x[:, 2] + 0.05 * rng.normal(size=n)).astype(np.float32)
+    if loss == "logloss":
+        y = (y > np.median(y)).astype(np.float32)
+    edges = orc.get_edges(x, nbins, rng)
+    xb = orc.binarize(x, edges)
+    p = orc.Params(loss=loss, K=2 if loss == "gaussian_mle" else 1, nbins=nbins, max_depth=depth, **kw)
+    b = orc.Booster(p, xb, y)
+    js = np.arange(1, f + 1, dtype=np.uint32)
+    last = None
+    for _ in range(rounds):
+        last = b.round(None, 255, js, want_hist=True)
+    return b, xb, y, last
+
+
+def test_leaf_index_invariants(orc):
+    b, xb, y, (t, nidx, hist, nsum) = _fit_oracle(orc)
+    leaf = orc.leaf_idx(xb, t)
+    assert np.array_equal(leaf, nidx)                       # partition and traversal agree
+    for i in range(0, xb.shape[0], 97):
+        assert leaf[i] == _python_traverse(t, xb[i])         # independent traversal: nid = nid << 1 + !cond
+    assert not t.split[leaf - 1].any()                       # leaves are non-split nodes
+    pred = np.zeros((xb.shape[0], 1), np.float32)
+    orc.predict_tree(b.p, xb, t, pred)
+    for l in np.unique(leaf):                                # rows of one leaf share one prediction
+        assert np.unique(pred[leaf == l]).size == 1
+    # a stump (max_depth = 1) sends every row to node 1
+    p1 = orc.Params(max_depth=1, nbins=16)
+    b1 = orc.Booster(p1, xb, y)
+    t1, n1, _, _ = b1.round(None, 255, np.arange(1, 6, dtype=np.uint32))
+    assert t1.feat.size == 1 and not t1.split[0] and (n1 == 1).all()
+
+
+def test_histograms_and_subtraction(orc):
+    b, xb, y, (t, nidx, hist, nsum) = _fit_oracle(orc, depth=3, rounds=1)
+    g = b.grad.astype(np.float64)
+    # the gradients that built the tree are the pre-round ones: recompute them from the bias
+    p = b.p
+    pred0 = np.tile(b.mu, (xb.shape[0], 1)).astype(np.float32)
+    g0 = b.grad.copy()
+    orc.update_grads(p, pred0, y, g0)
+    for j in range(xb.shape[1]):
+        for c in range(3):
+            ref = np.bincount(xb[:, j].astype(np.int64) - 1, weights=g0[:, c].astype(np.float64), minlength=p.nbins)
+            np.testing.assert_allclose(hist[0, j, :, c], ref, rtol=1e-12, atol=1e-9)
+    assert t.split[0]
+    np.testing.assert_allclose(hist[0], hist[1] + hist[2], rtol=1e-10, atol=1e-9)   # parent = left + right
+    np.testing.assert_allclose(nsum[0], nsum[1] + nsum[2], rtol=1e-12, atol=1e-9)
+    np.testing.assert_allclose(nsum[0], g0.astype(np.float64).sum(axis=0), rtol=1e-12)
+    # split condition: left child holds exactly the rows with bin <= cond_bin
+    f0, cb = int(t.feat[0]) - 1, int(t.cond_bin[0])
+    assert (xb[:, f0] <= cb).sum() == round(nsum[1, 2])
+
+
+@pytest.mark.parametrize("loss", ["mse", "logloss", "gaussian_mle"])
+def test_training_beats_the_bias_model(orc, loss):
+    b, xb, y, _ = _fit_oracle(orc, loss=loss, n=4000, depth=5, rounds=60, eta=0.2)
+    mu = np.tile(b.mu, (y.size, 1)).astype(np.float32)
+    pred = b.pred.copy()
+    orc.link(b.p, pred)
+    orc.link(b.p, mu)
+    mse0, mse1 = np.mean((mu[:, 0] - y) ** 2), np.mean((pred[:, 0] - y) ** 2)
+    assert mse1 < 0.25 * mse0, (mse0, mse1)
+
+
+def test_softmax_training(orc):
+    rng = np.random.default_rng(3)
+    n, f, K = 3000, 6, 3
+    x = rng.normal(size=(n, f))
+    y = (x[:, :K] + 0.3 * rng.gumbel(size=(n, K))).argmax(axis=1).astype(np.uint32) + 1
+    xb = orc.binarize(x, orc.get_edges(x, 16, rng))
+    p = orc.Params(loss="mlogloss", K=K, nbins=16, max_depth=4, eta=0.3)
+    b = orc.Booster(p, xb, y)
+    for _ in range(30):
+        b.round(None, 255, np.arange(1, f + 1, dtype=np.uint32))
+    assert np.isfinite(b.pred).all() and b.pred.max() <= 0 and b.pred.min() >= -15   # predict! keeps logits in [-15, 0]
+    assert (b.pred.argmax(axis=1) + 1 == y).mean() > 0.8
+
+
+def test_binning(orc):
+    rng = np.random.default_rng(5)
+    for dt in (np.float32, np.float64):
+        x = rng.normal(size=(5000, 4)).astype(dt)
+        e = orc.get_edges(x, 32, rng)
+        assert e.dtype == dt and e.shape == (4, 31) and (np.diff(e, axis=1) >= 0).all()
+        np.testing.assert_allclose(e, np.quantile(x.astype(np.float64), np.arange(1, 32) / 32, axis=0, method="linear").T,
+                                   rtol=1e-5, atol=1e-6)
+        xb = orc.binarize(x, e)
+        ref = np.stack([np.searchsorted(e[j], x[:, j], side="left") for j in range(4)], 1) + 1
+        assert xb.dtype == np.uint8 and np.array_equal(xb, ref) and xb.min() >= 1 and xb.max() <= 32
+    # ties and exact hits: searchsortedfirst puts x == edge into the edge's own bin
+    e = np.array([[1.0, 2.0, 2.0, 3.0]], np.float64)
+    x = np.array([[0.5], [1.0], [2.0], [2.5], [3.0], [9.0]])
+    assert orc.binarize(x, e)[:, 0].tolist() == [1, 1, 2, 4, 4, 5]
+
+
+def test_row_sampling_and_constraints(orc):
+    b, xb, y, _ = _fit_oracle(orc, rounds=1)
+    rng = np.random.default_rng(9)
+    mask = rng.integers(0, 256, xb.shape[0], dtype=np.uint8)
+    t, nidx, _, nsum = b.round(mask, 128, np.array([1, 3, 5], np.uint32))
+    assert ((nidx > 0) == (mask <= 128)).all()                                   # src/subsample.jl:21
+    assert set(np.unique(t.feat)) <= {0, 1, 3, 5}                                # only sampled columns split
+    assert round(nsum[0, 2]) == (mask <= 128).sum()
+    # min_weight is a strict bound on both children (src/fit-utils.jl:419)
+    p = orc.Params(nbins=16, max_depth=6, min_weight=200.0)
+    bb = orc.Booster(p, xb, y)
+    t2, _, _, ns2 = bb.round(None, 255, np.arange(1, 6, dtype=np.uint32))
+    assert (ns2[t2.w != 0][:, 2] > 200).all()
+    # monotone constraint +1 on feature 2: left leaf value < right leaf value wherever feature 2 splits
+    mono = np.array([0, 1, 0, 0, 0], np.int32)
+    bm = orc.Booster(orc.Params(nbins=16, max_depth=5), xb, y, monotone=mono)
+    tm, _, _, nsm = bm.round(None, 255, np.arange(1, 6, dtype=np.uint32))
+    for n in np.nonzero(tm.split)[0] + 1:
+        if tm.feat[n - 1] == 2:
+            pl = -0.1 * nsm[2 * n - 1, 0] / (nsm[2 * n - 1, 1] + 1.0)
+            pr = -0.1 * nsm[2 * n, 0] / (nsm[2 * n, 1] + 1.0)
+            assert pl < pr
