@@ -30,7 +30,7 @@ def call(fn, torch, x, g, rows, nfeats, nbins, nch, device=0):
     dev = torch.device("cuda", device)
     xd = torch.from_numpy(x).to(dev)
     gd = torch.from_numpy(g).to(dev)
-    rd = torch.from_numpy(rows.view(np.int32)).to(dev)
+    rd = torch.from_numpy(rows.view(np.int32)).to(dev) if rows.size else torch.zeros(1, dtype=torch.int32, device=dev)
     out = torch.full((nfeats, nch, nbins), float("nan"), dtype=torch.float64, device=dev)
     torch.cuda.synchronize()
     rc = fn(C.c_int32(device), C.c_void_p(0), C.c_void_p(xd.data_ptr()), C.c_int64(x.shape[0]), C.c_int32(nfeats),
