@@ -545,9 +545,12 @@ int32_t evb_launch_hist_reduce(evb_handle *h, int level) {
 
 // =====================================================================================================
 // Stand-alone histogram of one list of rows, for callers that hold their own device buffers.
-// evb_hist_rows allocates its work buffers per call.
+// evb_hist_rows allocates its work buffers per call; evb_hist_rows_noalloc allocates nothing.
 // =====================================================================================================
 namespace {
+
+constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)2 << 20; // 8 MiB of partial images
+constexpr int NOALLOC_MAX_FEATS = 1024;
 
 struct RowsPlan {
     LevelPlan plan;
@@ -557,6 +560,12 @@ struct RowsPlan {
     int err;
     int pad;
 };
+
+// Work memory of evb_hist_rows_noalloc.  It is part of the loaded library image on every GPU that uses the
+// library and is shared by all calls on that GPU.
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+static __device__ __align__(256) RowsPlan g_noalloc_plan;
+static __device__ __align__(256) uint32_t g_noalloc_js[NOALLOC_MAX_FEATS];
 
 __global__ void k_rows_plan_fill(RowsPlan *p, uint32_t *js, int nfeats, long long nrows) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -569,6 +578,14 @@ __global__ void k_rows_plan_fill(RowsPlan *p, uint32_t *js, int nfeats, long lon
         p->err = 0;
     }
 }
+
+struct NoAllocDev {
+    float *scratch = nullptr;
+    RowsPlan *plan = nullptr;
+    uint32_t *js = nullptr;
+    bool ready = false;
+};
+NoAllocDev g_noalloc_dev[64];
 
 int32_t rows_hist_check_args(int32_t device, const void *x_rows, int64_t nobs, int32_t nfeats, int32_t row_stride, int32_t nbins,
                              const void *grad, int32_t nch, const void *rows, int64_t nrows, const void *out) {
@@ -666,4 +683,27 @@ extern "C" int32_t evb_hist_rows(int32_t device, void *stream, const uint8_t *x_
     if (plan) cudaFree(plan);
     if (js) cudaFree(js);
     return rc;
+}
+
+extern "C" int32_t evb_hist_rows_noalloc(int32_t device, void *stream, const uint8_t *x_rows, int64_t nobs, int32_t nfeats,
+                                         int32_t row_stride, int32_t nbins, const float *grad, int32_t nch, const uint32_t *rows,
+                                         int64_t nrows, double *out) {
+    EVB_CHECK(rows_hist_check_args(device, x_rows, nobs, nfeats, row_stride, nbins, grad, nch, rows, nrows, out));
+    if (nfeats > NOALLOC_MAX_FEATS) {
+        evb_set_error("evb_hist_rows_noalloc: nfeats=%d exceeds the built-in limit of %d features", nfeats, NOALLOC_MAX_FEATS);
+        return EVB_ERR_LIMIT;
+    }
+    EVB_CUDA(cudaSetDevice(device));
+    NoAllocDev &d = g_noalloc_dev[device];
+    if (!d.ready) {
+        // once per device, with that device current: the symbols' names are host-side stand-ins, the kernels need
+        // the device addresses
+        EVB_CUDA(cudaGetSymbolAddress((void **)&d.scratch, g_noalloc_scratch));
+        EVB_CUDA(cudaGetSymbolAddress((void **)&d.plan, g_noalloc_plan));
+        EVB_CUDA(cudaGetSymbolAddress((void **)&d.js, g_noalloc_js));
+        d.ready = true;
+    }
+    const char *e = getenv("EVB_HIST_MODE");
+    return rows_hist_run(device, (cudaStream_t)stream, x_rows, nfeats, row_stride, nbins, grad, nch, rows, nrows, out, d.scratch,
+                         NOALLOC_SCRATCH_FLOATS, d.plan, d.js, e ? atoi(e) : 1);
 }

@@ -179,6 +179,25 @@ EVB_API int32_t evb_binarize(int32_t device, const void *x, int32_t dtype, int64
 EVB_API int32_t evb_hist_rows(int32_t device, void *stream, const uint8_t *x_rows, int64_t nobs, int32_t nfeats, int32_t row_stride,
                               int32_t nbins, const float *grad, int32_t nch, const uint32_t *rows, int64_t nrows, double *out);
 
+/*
+ * evb_hist_rows_noalloc -- same arguments and result as evb_hist_rows, for callers that are not allowed to allocate
+ * device memory while they run: code executing between cudaMalloc-free phases of a real-time or long-running service,
+ * plug-ins that work inside a host framework's memory pool, or anything that must not trigger the implicit
+ * device synchronisation of cudaMalloc / cudaFree.  It has no counterpart in the reference.
+ * It calls no allocator of any kind.  Its work memory is a fixed 8 MiB block that is part of the library image on
+ * every GPU that loads the library (held until the process exits), so:
+ *   - limits: nfeats <= 1024, nbins <= 255, nch <= 4, and two partial images (one per feature group of 32 features:
+ *     32 x nbins x nch floats, per group) must fit in the 8 MiB; larger problems are rejected with EVB_ERR_LIMIT;
+ *   - the first call on a device looks up the device addresses of that block (cudaGetSymbolAddress); make that first
+ *     call outside any stream capture;
+ *   - all calls on one GPU share the block and it keeps the previous call's contents: every value that is read is
+ *     rewritten by the same call first, but two calls that overlap in time on the same GPU race with each other.
+ *     Serialise them (one stream, or events).
+ */
+EVB_API int32_t evb_hist_rows_noalloc(int32_t device, void *stream, const uint8_t *x_rows, int64_t nobs, int32_t nfeats,
+                                      int32_t row_stride, int32_t nbins, const float *grad, int32_t nch, const uint32_t *rows,
+                                      int64_t nrows, double *out);
+
 #ifdef __cplusplus
 }
 #endif
