@@ -70,7 +70,8 @@ struct HistArgs {
     int *err;
     int RS, GS, F, nbins, C, NFG, U, UB, stages, PG;
     uint32_t img_floats;
-    int mode; // bit 0: stage rows with cp.async (LDGSTS) instead of TMA bulk copies; bit 4: diagnostic, skip the accumulation
+    int mode;   // bit 0: stage rows with cp.async (LDGSTS) instead of TMA bulk copies; bit 4: diagnostic, skip the accumulation
+    int contig; // 1 when feature slot s is feature s (no column sample): a lane's FPL bins are adjacent bytes of the row
 };
 
 __device__ __forceinline__ void cp_async16(void *dst, const void *src) {
@@ -80,46 +81,49 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t *bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// Unit image in shared memory: channels are kept in pairs so that one 64-bit access moves two of them.
-//   NCH = 1: [bin][lane] float            NCH = 2: [bin][lane] float2
-//   NCH = 3: [bin][lane] float2 + [bin][lane] float      NCH = 4: two [bin][lane] float2 regions
-// Lane l touches only addresses whose bank is determined by l, so no access of a warp conflicts.
-template <int BP, int NCH>
+// Unit image in shared memory.  A unit is 32 lanes x FPL feature slots per lane x NCH gradient channels.
+// For every feature slot j of the lane there is a sub-image; inside it channels are kept in pairs so that one
+// 64-bit access moves two of them:
+//   region 0: [row 0..BP][lane] float2 (NCH >= 2) or float (NCH == 1)      region 1: the remaining NCH - 2 channels
+// Row v holds bin v (bins are 1-based bytes); row 0 is a guard row that absorbs the zero padding bytes of a
+// row of bins.  Lane l only touches addresses whose bank is determined by l: no access of a warp conflicts and
+// nothing needs an atomic.
+template <int BP, int NCH, int FPL>
 struct Img {
     static constexpr int W0 = NCH >= 2 ? 2 : 1;
     static constexpr int W1 = NCH - W0;
-    [[maybe_unused]] static constexpr int P1 = BP * 32 * W0;
-    static constexpr int FLOATS = BP * 32 * NCH;
-    static __device__ __forceinline__ void ld(const float *img, int lane, uint32_t b, float (&v)[NCH]) {
+    static constexpr int RB0 = 32 * W0 * 4;               // bytes per row, region 0
+    static constexpr int RB1 = 32 * W1 * 4;
+    static constexpr int R1OFF = (BP + 1) * RB0;           // byte offset of region 1 inside a sub-image
+    static constexpr int SUB = (BP + 1) * (RB0 + RB1);     // bytes per sub-image
+    static constexpr int BYTES = FPL * SUB;                // bytes per unit image
+    // o8 = bin << 8 (what one PRMT extracts from the packed bins of a lane); u0 / u1 are 32-bit shared-space
+    // addresses of the lane's column in region 0 / region 1 of the unit
+    static __device__ __forceinline__ void ld(uint32_t u0, uint32_t u1, int j, uint32_t o8, float (&v)[NCH]) {
         if constexpr (W0 == 2) {
-            const float2 t = *reinterpret_cast<const float2 *>(img + (b * 32 + lane) * 2);
-            v[0] = t.x; v[1] = t.y;
+            asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v[0]), "=f"(v[1]) : "r"(u0 + j * SUB + o8));
         } else {
-            v[0] = img[b * 32 + lane];
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[0]) : "r"(u0 + j * SUB + (o8 >> 1)));
         }
         if constexpr (W1 == 2) {
-            const float2 t = *reinterpret_cast<const float2 *>(img + P1 + (b * 32 + lane) * 2);
-            v[2] = t.x; v[3] = t.y;
+            asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v[2]), "=f"(v[3]) : "r"(u1 + j * SUB + o8));
         } else if constexpr (W1 == 1) {
-            v[2] = img[P1 + b * 32 + lane];
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[2]) : "r"(u1 + j * SUB + (o8 >> 1)));
         }
     }
-    static __device__ __forceinline__ void st(float *img, int lane, uint32_t b, const float (&v)[NCH]) {
+    static __device__ __forceinline__ void st(uint32_t u0, uint32_t u1, int j, uint32_t o8, const float (&v)[NCH]) {
         if constexpr (W0 == 2) {
-            *reinterpret_cast<float2 *>(img + (b * 32 + lane) * 2) = make_float2(v[0], v[1]);
+            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(u0 + j * SUB + o8), "f"(v[0]), "f"(v[1]) : "memory");
         } else {
-            img[b * 32 + lane] = v[0];
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(u0 + j * SUB + (o8 >> 1)), "f"(v[0]) : "memory");
         }
         if constexpr (W1 == 2) {
-            *reinterpret_cast<float2 *>(img + P1 + (b * 32 + lane) * 2) = make_float2(v[2], v[3]);
+            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(u1 + j * SUB + o8), "f"(v[2]), "f"(v[3]) : "memory");
         } else if constexpr (W1 == 1) {
-            img[P1 + b * 32 + lane] = v[2];
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(u1 + j * SUB + (o8 >> 1)), "f"(v[2]) : "memory");
         }
     }
 };
-
-template <int BP>
-__device__ __forceinline__ uint32_t bin_index(uint32_t raw) { return min(raw - 1u, (uint32_t)(BP - 1)); }
 
 template <int NCH>
 __device__ __forceinline__ void unpack(const float4 &g, float (&v)[NCH]) {
@@ -129,10 +133,112 @@ __device__ __forceinline__ void unpack(const float4 &g, float (&v)[NCH]) {
     if constexpr (NCH >= 4) v[3] = g.w;
 }
 
-template <int BP, int NCH>
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+// gradient channels of one row for this unit (the record slice of a unit starts on a 16-byte boundary)
+template <int NCH>
+__device__ __forceinline__ void lds_grad(uint32_t addr, float (&v)[NCH]) {
+    if constexpr (NCH == 1) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[0]) : "r"(addr));
+    else if constexpr (NCH == 2) asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v[0]), "=f"(v[1]) : "r"(addr));
+    else if constexpr (NCH == 3) {
+        float w;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(w) : "r"(addr));
+    } else asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(addr));
+}
+
+// packed bins of one row for this lane: byte j = bin of the lane's j-th feature slot
+template <int FPL, bool CONTIG>
+__device__ __forceinline__ uint32_t load_bins(uint32_t row, const uint32_t (&foff)[FPL]) {
+    if constexpr (CONTIG) {
+        if constexpr (FPL == 4) return lds_u32(row + foff[0]);
+        else if constexpr (FPL == 2) return lds_u16(row + foff[0]);
+        else return lds_u8(row + foff[0]);
+    } else {
+        uint32_t v = lds_u8(row + foff[0]);
+#pragma unroll
+        for (int j = 1; j < FPL; ++j) v |= lds_u8(row + foff[j]) << (8 * j);
+        return v;
+    }
+}
+
+// Accumulates the rows of one staged tile into the unit image.  Four rows at a time: all loads first, then the
+// adds with forwarding between rows that hit the same bin of the same feature, then the stores in row order.  The
+// result is bit-identical to adding the rows one by one, but 4 x FPL read-modify-write chains overlap.
+// xs / gs: 32-bit shared-space addresses of the tile's bins and of this unit's slice of the gradient records.
+template <int BP, int NCH, int FPL, bool CONTIG>
+__device__ __forceinline__ void accumulate_tile(uint32_t xs, uint32_t gs, int nrows, int RS, int GSB,
+                                                const uint32_t (&foff)[FPL], uint32_t u0, uint32_t u1) {
+    using I = Img<BP, NCH, FPL>;
+    int r = 0;
+    for (; r + 4 <= nrows; r += 4, xs += 4 * RS, gs += 4 * GSB) {
+        uint32_t raw[4];
+        float g[4][NCH];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            raw[i] = load_bins<FPL, CONTIG>(xs + i * RS, foff);
+            lds_grad<NCH>(gs + i * GSB, g[i]);
+        }
+        uint32_t o[FPL][4];
+        float a[FPL][4][NCH];
+#pragma unroll
+        for (int j = 0; j < FPL; ++j) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                o[j][i] = __byte_perm(raw[i], 0u, 0x4404u | (uint32_t)(j << 4)); // bin << 8
+                I::ld(u0, u1, j, o[j][i], a[j][i]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < FPL; ++j) {
+            const bool e10 = o[j][1] == o[j][0], e20 = o[j][2] == o[j][0], e21 = o[j][2] == o[j][1];
+            const bool e30 = o[j][3] == o[j][0], e31 = o[j][3] == o[j][1], e32 = o[j][3] == o[j][2];
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                a[j][0][c] = a[j][0][c] + g[0][c];
+                a[j][1][c] = (e10 ? a[j][0][c] : a[j][1][c]) + g[1][c];
+                a[j][2][c] = (e21 ? a[j][1][c] : (e20 ? a[j][0][c] : a[j][2][c])) + g[2][c];
+                a[j][3][c] = (e32 ? a[j][2][c] : (e31 ? a[j][1][c] : (e30 ? a[j][0][c] : a[j][3][c]))) + g[3][c];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < FPL; ++j) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) I::st(u0, u1, j, o[j][i], a[j][i]);
+        }
+    }
+    for (; r < nrows; ++r, xs += RS, gs += GSB) {
+        const uint32_t raw = load_bins<FPL, CONTIG>(xs, foff);
+        float g[NCH];
+        lds_grad<NCH>(gs, g);
+#pragma unroll
+        for (int j = 0; j < FPL; ++j) {
+            const uint32_t o = __byte_perm(raw, 0u, 0x4404u | (uint32_t)(j << 4));
+            float a[NCH];
+            I::ld(u0, u1, j, o, a);
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) a[c] += g[c];
+            I::st(u0, u1, j, o, a);
+        }
+    }
+}
+
+template <int BP, int NCH, int FPL>
 __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(HistArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
-    using I = Img<BP, NCH>;
+    using I = Img<BP, NCH, FPL>;
     const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, b = blockIdx.x, ug = blockIdx.y;
     const int nact = min(a.UB, a.U - ug * a.UB);
@@ -140,7 +246,7 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
     const int xbytes = EVB_TILE_ROWS * a.RS, gbytes = EVB_TILE_ROWS * a.GS * 4;
     const int stage_bytes = xbytes + gbytes;
     float *imgs = reinterpret_cast<float *>(smem);
-    unsigned char *stage0 = smem + (size_t)a.UB * I::FLOATS * 4;
+    unsigned char *stage0 = smem + (size_t)a.UB * I::BYTES;
     uint64_t *full = reinterpret_cast<uint64_t *>(stage0 + (size_t)S * stage_bytes);
     uint64_t *empty = full + S;
 
@@ -152,7 +258,7 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    for (int i = tid; i < nact * I::FLOATS; i += blockDim.x) imgs[i] = 0.0f;
+    for (int i = tid; i < nact * (I::BYTES / 4); i += blockDim.x) imgs[i] = 0.0f;
     __syncthreads();
 
     // first build slot that contains row `lo`: largest s with cum[s] <= lo
@@ -238,16 +344,21 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
     }
     if (wid - 1 >= nact) return;
 
-    // ---------------- consumers: one unit (32 feature slots x NCH channels) per warp ------------------
+    // ---------------- consumers: one unit (32 lanes x FPL feature slots x NCH channels) per warp --------
     const int uw = wid - 1;
     const int u = ug * a.UB + uw;
     const int ct = u / a.NFG, fg = u % a.NFG;
-    const int slot = fg * 32 + lane;
-    const bool act = slot < a.F;
-    const uint32_t foff = act ? a.js0[slot] : 0u;
+    const int slot0 = (fg * 32 + lane) * FPL;
+    const bool act = slot0 < a.F;
+    uint32_t foff[FPL];
+#pragma unroll
+    for (int j = 0; j < FPL; ++j) foff[j] = (slot0 + j < a.F) ? a.js0[slot0 + j] : (act ? a.js0[slot0] : 0u);
     const int nch = min(NCH, a.C - ct * NCH);
-    float *img = imgs + (size_t)uw * I::FLOATS;
+    const uint32_t ubase = smem_u32(smem) + (uint32_t)uw * I::BYTES;
+    const uint32_t u0 = ubase + lane * I::W0 * 4;
+    const uint32_t u1 = ubase + I::R1OFF + lane * I::W1 * 4;
     const int RS = a.RS, GS = a.GS;
+    const uint32_t stage0_s = smem_u32(stage0);
 
     uint32_t it = 0;
     long long pos = lo;
@@ -258,56 +369,30 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
                 const int st = it % S;
                 const int nrows = (int)min((long long)EVB_TILE_ROWS, send - q0);
                 if (!mbar_wait(&full[st], (it / S) & 1u, a.err, EVB_DERR_WAIT_FULL)) return;
-                const unsigned char *xs = stage0 + (size_t)st * stage_bytes + foff;
-                const float *gs = reinterpret_cast<const float *>(stage0 + (size_t)st * stage_bytes + xbytes) + ct * 4;
+                const uint32_t xs = stage0_s + (uint32_t)st * stage_bytes;
+                const uint32_t gs = xs + xbytes + ct * 16;
                 if (act && !(a.mode & 16)) {
-                    int r = 0;
-                    // Four rows at a time: all loads first, then the adds with forwarding between rows that
-                    // hit the same bin, then the stores in row order.  The result is bit-identical to adding
-                    // the rows one by one, but the four read-modify-write chains overlap.
-                    for (; r + 4 <= nrows; r += 4) {
-                        const uint32_t b0 = bin_index<BP>(xs[(r + 0) * RS]), b1 = bin_index<BP>(xs[(r + 1) * RS]);
-                        const uint32_t b2 = bin_index<BP>(xs[(r + 2) * RS]), b3 = bin_index<BP>(xs[(r + 3) * RS]);
-                        float g0[NCH], g1[NCH], g2[NCH], g3[NCH], a0[NCH], a1[NCH], a2[NCH], a3[NCH];
-                        unpack<NCH>(*reinterpret_cast<const float4 *>(gs + (r + 0) * GS), g0);
-                        unpack<NCH>(*reinterpret_cast<const float4 *>(gs + (r + 1) * GS), g1);
-                        unpack<NCH>(*reinterpret_cast<const float4 *>(gs + (r + 2) * GS), g2);
-                        unpack<NCH>(*reinterpret_cast<const float4 *>(gs + (r + 3) * GS), g3);
-                        I::ld(img, lane, b0, a0); I::ld(img, lane, b1, a1); I::ld(img, lane, b2, a2); I::ld(img, lane, b3, a3);
-                        const bool e10 = b1 == b0, e20 = b2 == b0, e21 = b2 == b1, e30 = b3 == b0, e31 = b3 == b1, e32 = b3 == b2;
-#pragma unroll
-                        for (int c = 0; c < NCH; ++c) {
-                            a0[c] = a0[c] + g0[c];
-                            a1[c] = (e10 ? a0[c] : a1[c]) + g1[c];
-                            a2[c] = (e21 ? a1[c] : (e20 ? a0[c] : a2[c])) + g2[c];
-                            a3[c] = (e32 ? a2[c] : (e31 ? a1[c] : (e30 ? a0[c] : a3[c]))) + g3[c];
-                        }
-                        I::st(img, lane, b0, a0); I::st(img, lane, b1, a1); I::st(img, lane, b2, a2); I::st(img, lane, b3, a3);
-                    }
-                    for (; r < nrows; ++r) {
-                        const uint32_t b0 = bin_index<BP>(xs[r * RS]);
-                        float g0[NCH], a0[NCH];
-                        unpack<NCH>(*reinterpret_cast<const float4 *>(gs + r * GS), g0);
-                        I::ld(img, lane, b0, a0);
-#pragma unroll
-                        for (int c = 0; c < NCH; ++c) a0[c] += g0[c];
-                        I::st(img, lane, b0, a0);
-                    }
+                    if (a.contig) accumulate_tile<BP, NCH, FPL, true>(xs, gs, nrows, RS, GS * 4, foff, u0, u1);
+                    else accumulate_tile<BP, NCH, FPL, false>(xs, gs, nrows, RS, GS * 4, foff, u0, u1);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[st]);
             }
-            // flush the piece (CTA b, slot s) and clear the image
+            // flush the piece (CTA b, slot s) and clear the image (guard rows included)
             float *dst = a.scratch + ((size_t)(ug * a.PG + b + s) * a.UB + uw) * a.img_floats + lane;
-            for (int bin = 0; bin < a.nbins; ++bin) {
-                float v[NCH], z[NCH];
-                I::ld(img, lane, bin, v);
+            const float zero[NCH] = {};
 #pragma unroll
-                for (int c = 0; c < NCH; ++c) z[c] = 0.0f;
-                I::st(img, lane, bin, z);
+            for (int j = 0; j < FPL; ++j) {
+                I::st(u0, u1, j, 0u, zero);
+                for (int bin = 0; bin < a.nbins; ++bin) {
+                    float v[NCH];
+                    const uint32_t o8 = (uint32_t)(bin + 1) << 8;
+                    I::ld(u0, u1, j, o8, v);
+                    I::st(u0, u1, j, o8, zero);
 #pragma unroll
-                for (int c = 0; c < NCH; ++c)
-                    if (c < nch) dst[(c * a.nbins + bin) * 32] = v[c];
+                    for (int c = 0; c < NCH; ++c)
+                        if (c < nch) dst[((j * NCH + c) * a.nbins + bin) * 32] = v[c];
+                }
             }
         }
         pos = send;
@@ -320,12 +405,12 @@ struct ReduceArgs {
     double *hcomp;
     const LevelPlan *plan;
     const int32_t *cum;
-    int G, PG, UB, NFG, U, F, C, Ce, K, nbins, NCH; // C: channels of hcomp; Ce: channels accumulated (mse: K + 1)
+    int G, PG, UB, NFG, U, F, C, Ce, K, nbins, NCH, FPL; // C: channels of hcomp; Ce: channels accumulated (mse: K + 1)
     uint32_t img_floats;
 };
 
 // Sums the pieces of every build slot in a fixed order (double precision) and writes
-// hcomp[slot][feature][channel][bin].  grid (max build slots of the level, U * NCH, ceil(nbins / BPB));
+// hcomp[slot][feature][channel][bin].  grid (max build slots of the level, U * FPL * NCH, ceil(nbins / BPB));
 // 512 threads = NPG piece groups x (BPB bins x 32 feature lanes).  Few slots / many pieces per slot (top of
 // the tree) use BPB = 4 with four piece groups; many slots use BPB = 16.
 template <int BPB>
@@ -333,7 +418,7 @@ __global__ void __launch_bounds__(512) k_hist_reduce(ReduceArgs a) {
     constexpr int NE = BPB * 32, NPG = 512 / NE;
     __shared__ double part[NPG][NE];
     __shared__ double tile[BPB][33];
-    const int s = blockIdx.x, u = blockIdx.y / a.NCH, c = blockIdx.y % a.NCH, bin0 = blockIdx.z * BPB;
+    const int s = blockIdx.x, u = blockIdx.y / (a.NCH * a.FPL), j = (blockIdx.y / a.NCH) % a.FPL, c = blockIdx.y % a.NCH, bin0 = blockIdx.z * BPB;
     const int ug = u / a.UB, uw = u % a.UB, ct = u / a.NFG, fg = u % a.NFG;
     if (c >= min(a.NCH, a.Ce - ct * a.NCH)) return;
     const int e = threadIdx.x % NE, pg = threadIdx.x / NE, binl = e >> 5, lane = e & 31;
@@ -350,7 +435,7 @@ __global__ void __launch_bounds__(512) k_hist_reduce(ReduceArgs a) {
     double acc = 0.0;
     const int bin = bin0 + binl;
     if (bin < a.nbins) {
-        const float *src = a.scratch + ((size_t)(ug * a.PG + s) * a.UB + uw) * a.img_floats + (c * a.nbins + bin) * 32 + lane;
+        const float *src = a.scratch + ((size_t)(ug * a.PG + s) * a.UB + uw) * a.img_floats + ((j * a.NCH + c) * a.nbins + bin) * 32 + lane;
         const size_t bstride = (size_t)a.UB * a.img_floats;
         if (R >= a.G) { // every CTA owns at least one row: all pieces in [bfirst, blast] exist
 #pragma unroll 4
@@ -371,7 +456,7 @@ __global__ void __launch_bounds__(512) k_hist_reduce(ReduceArgs a) {
     __syncthreads();
     if (threadIdx.x < NE) {
         const int fl = threadIdx.x / BPB, bl = threadIdx.x % BPB;
-        const int slotf = fg * 32 + fl, binw = bin0 + bl;
+        const int slotf = (fg * 32 + fl) * a.FPL + j, binw = bin0 + bl;
         if (slotf < a.F && binw < a.nbins) {
             double *dst = a.hcomp + ((size_t)s * a.F + slotf) * a.C * a.nbins + binw;
             const int ce = ct * a.NCH + c;
@@ -388,59 +473,61 @@ __global__ void __launch_bounds__(512) k_hist_reduce(ReduceArgs a) {
     }
 }
 
-template <int BP, int NCH>
+template <int BP, int NCH, int FPL>
 cudaError_t launch_hist_t(const HistArgs &a, dim3 grid, int threads, size_t smem, cudaStream_t st) {
-    static bool attr_set[16] = {};
+    static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 16 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_hist<BP, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_hist<BP, NCH, FPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    k_hist<BP, NCH><<<grid, threads, smem, st>>>(a);
+    k_hist<BP, NCH, FPL><<<grid, threads, smem, st>>>(a);
     return cudaGetLastError();
 }
-
-template <int BP>
-cudaError_t launch_hist_bp(int NCH, const HistArgs &a, dim3 grid, int threads, size_t smem, cudaStream_t st) {
-    switch (NCH) {
-    case 1: return launch_hist_t<BP, 1>(a, grid, threads, smem, st);
-    case 2: return launch_hist_t<BP, 2>(a, grid, threads, smem, st);
-    case 3: return launch_hist_t<BP, 3>(a, grid, threads, smem, st);
-    default: return launch_hist_t<BP, 4>(a, grid, threads, smem, st);
-    }
-}
-
-template <int BP, int NCH>
+template <int BP, int NCH, int FPL>
 int occupancy_t(int threads, size_t smem) {
-    cudaFuncSetAttribute(k_hist<BP, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(k_hist<BP, NCH, FPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     int nb = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k_hist<BP, NCH>, threads, smem) != cudaSuccess) nb = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k_hist<BP, NCH, FPL>, threads, smem) != cudaSuccess) nb = 0;
     return nb;
 }
-int occupancy(int BP, int NCH, int threads, size_t smem) {
-#define OCC_CASE(bp)                                                    \
-    case bp:                                                            \
-        switch (NCH) {                                                  \
-        case 1: return occupancy_t<bp, 1>(threads, smem);               \
-        case 2: return occupancy_t<bp, 2>(threads, smem);               \
-        case 3: return occupancy_t<bp, 3>(threads, smem);               \
-        default: return occupancy_t<bp, 4>(threads, smem);              \
-        }
-    switch (BP) {
-        OCC_CASE(32)
-        OCC_CASE(64)
-        OCC_CASE(128)
-    default:
-        switch (NCH) {
-        case 1: return occupancy_t<256, 1>(threads, smem);
-        case 2: return occupancy_t<256, 2>(threads, smem);
-        case 3: return occupancy_t<256, 3>(threads, smem);
-        default: return occupancy_t<256, 4>(threads, smem);
-        }
+
+// Runtime (BP, NCH, FPL) -> template instance.  `launch` selects between launching and an occupancy query.
+template <int BP, int NCH>
+int dispatch_fpl(int FPL, bool launch, const HistArgs *a, dim3 grid, int threads, size_t smem, cudaStream_t st) {
+    switch (FPL) {
+    case 1: return launch ? (int)launch_hist_t<BP, NCH, 1>(*a, grid, threads, smem, st) : occupancy_t<BP, NCH, 1>(threads, smem);
+    case 2: return launch ? (int)launch_hist_t<BP, NCH, 2>(*a, grid, threads, smem, st) : occupancy_t<BP, NCH, 2>(threads, smem);
+    default: return launch ? (int)launch_hist_t<BP, NCH, 4>(*a, grid, threads, smem, st) : occupancy_t<BP, NCH, 4>(threads, smem);
     }
-#undef OCC_CASE
+}
+template <int BP>
+int dispatch_nch(int NCH, int FPL, bool launch, const HistArgs *a, dim3 grid, int threads, size_t smem, cudaStream_t st) {
+    switch (NCH) {
+    case 1: return dispatch_fpl<BP, 1>(FPL, launch, a, grid, threads, smem, st);
+    case 2: return dispatch_fpl<BP, 2>(FPL, launch, a, grid, threads, smem, st);
+    case 3: return dispatch_fpl<BP, 3>(FPL, launch, a, grid, threads, smem, st);
+    default: return dispatch_fpl<BP, 4>(FPL, launch, a, grid, threads, smem, st);
+    }
+}
+int dispatch(int BP, int NCH, int FPL, bool launch, const HistArgs *a, dim3 grid, int threads, size_t smem, cudaStream_t st) {
+    switch (BP) {
+    case 32: return dispatch_nch<32>(NCH, FPL, launch, a, grid, threads, smem, st);
+    case 64: return dispatch_nch<64>(NCH, FPL, launch, a, grid, threads, smem, st);
+    case 128: return dispatch_nch<128>(NCH, FPL, launch, a, grid, threads, smem, st);
+    default: return dispatch_nch<256>(NCH, FPL, launch, a, grid, threads, smem, st);
+    }
+}
+cudaError_t launch_hist(const HistGeom &g, const HistArgs &a, dim3 grid, int threads, cudaStream_t st) {
+    return (cudaError_t)dispatch(g.BP, g.NCH, g.FPL, true, &a, grid, threads, g.smem, st);
+}
+int occupancy(const HistGeom &g, int threads) { return dispatch(g.BP, g.NCH, g.FPL, false, nullptr, dim3(), threads, g.smem, 0); }
+
+size_t unit_image_bytes(int BP, int NCH, int FPL) {
+    const int W0 = NCH >= 2 ? 2 : 1, W1 = NCH - W0;
+    return (size_t)FPL * (BP + 1) * (32 * W0 * 4 + 32 * W1 * 4);
 }
 
 } // namespace
@@ -452,9 +539,14 @@ int32_t evb_hist_geometry(const evb_handle *h, int F, HistGeom *g) {
     g->BP = B <= 32 ? 32 : B <= 64 ? 64 : B <= 128 ? 128 : 256;
     g->NCT = (C + 3) / 4;              // channel groups; channels are spread evenly over them
     g->NCH = (C + g->NCT - 1) / g->NCT;
-    g->NFG = (F + 31) / 32;
+    // feature slots per lane: as many as the feature count asks for, as long as a unit image stays <= 64 KB
+    int FPL = 1; // measured on B200: 2 or 4 slots per lane (fewer, fatter warps) are slower than more resident warps
+    if (const char *e = getenv("EVB_HIST_FPL")) { const int want = atoi(e); if (want == 1 || want == 2 || want == 4) FPL = want; }
+    while (FPL > 1 && unit_image_bytes(g->BP, g->NCH, FPL) > 65 * 1024) FPL >>= 1;
+    g->FPL = FPL;
+    g->NFG = (F + 32 * FPL - 1) / (32 * FPL);
     g->U = g->NFG * g->NCT;
-    const size_t img = (size_t)32 * g->BP * g->NCH * 4;
+    const size_t img = unit_image_bytes(g->BP, g->NCH, FPL);
     const size_t stage = (size_t)EVB_TILE_ROWS * (h->RS + h->GS * 4);
     const size_t sm_total = 228 * 1024, blk_max = 227 * 1024, reserve = 1024;
     int UB = g->U < EVB_MAX_UNITS_PER_BLOCK ? g->U : EVB_MAX_UNITS_PER_BLOCK;
@@ -465,8 +557,8 @@ int32_t evb_hist_geometry(const evb_handle *h, int F, HistGeom *g) {
     }
     g->UB = UB;
     g->NUG = (g->U + UB - 1) / UB;
-    // blocks per SM: as many as fit with >= 3 stages, at most 8
-    int t = (int)(sm_total / (UB * img + 2 * stage + 256 + reserve)); // resident warps matter more than stage depth
+    // CTAs per SM: resident warps matter more than stage depth, so take as many CTAs as fit with two stages
+    int t = (int)(sm_total / (UB * img + 2 * stage + 256 + reserve));
     if (const char *e = getenv("EVB_HIST_BLOCKS_PER_SM")) {           // tuning override
         const int want = atoi(e);
         if (want >= 1 && UB * img + 2 * stage + 256 + reserve <= sm_total / want) t = want;
@@ -482,14 +574,14 @@ int32_t evb_hist_geometry(const evb_handle *h, int F, HistGeom *g) {
     g->stages = S;
     g->smem = UB * img + (size_t)S * stage + 2 * S * 8 + 128;
     const int threads = (UB + 1) * 32;
-    int occ = occupancy(g->BP, g->NCH, threads, g->smem);
+    int occ = occupancy(*g, threads);
     if (occ < 1) {
         evb_set_error("histogram kernel cannot be resident (smem=%zu)", g->smem);
         return EVB_ERR_CUDA;
     }
     g->G = occ * h->num_sms;
     g->PG = g->G + h->maxslots;
-    g->img_floats = (size_t)g->NCH * B * 32;
+    g->img_floats = (size_t)FPL * g->NCH * B * 32;
     return EVB_OK;
 }
 
@@ -508,16 +600,11 @@ int32_t evb_launch_hist(evb_handle *h, int level) {
     a.RS = h->RS; a.GS = h->GS; a.F = h->F; a.nbins = h->B; a.C = h->Ce; a.NFG = g.NFG; a.U = g.U; a.UB = g.UB;
     a.stages = g.stages; a.PG = g.PG; a.img_floats = (uint32_t)g.img_floats;
     a.mode = h->hist_mode;
+    a.contig = h->F == h->nfeats ? 1 : 0;
     dim3 grid(g.G, g.NUG);
     const int threads = (g.UB + 1) * 32;
     evb_tic(h, EVB_T_HIST);
-    cudaError_t e;
-    switch (g.BP) {
-    case 32: e = launch_hist_bp<32>(g.NCH, a, grid, threads, g.smem, h->st); break;
-    case 64: e = launch_hist_bp<64>(g.NCH, a, grid, threads, g.smem, h->st); break;
-    case 128: e = launch_hist_bp<128>(g.NCH, a, grid, threads, g.smem, h->st); break;
-    default: e = launch_hist_bp<256>(g.NCH, a, grid, threads, g.smem, h->st); break;
-    }
+    cudaError_t e = launch_hist(g, a, grid, threads, h->st);
     evb_toc(h, EVB_T_HIST);
     EVB_CUDA(e);
     return EVB_OK;
@@ -527,15 +614,15 @@ int32_t evb_launch_hist_reduce(evb_handle *h, int level) {
     const HistGeom &g = h->hg;
     ReduceArgs a;
     a.scratch = h->scratch; a.hcomp = h->hcomp; a.plan = h->plan + level; a.cum = h->cum;
-    a.G = g.G; a.PG = g.PG; a.UB = g.UB; a.NFG = g.NFG; a.U = g.U; a.F = h->F; a.C = h->C; a.Ce = h->Ce; a.K = h->K; a.nbins = h->B; a.NCH = g.NCH;
+    a.G = g.G; a.PG = g.PG; a.UB = g.UB; a.NFG = g.NFG; a.U = g.U; a.F = h->F; a.C = h->C; a.Ce = h->Ce; a.K = h->K; a.nbins = h->B; a.NCH = g.NCH; a.FPL = g.FPL;
     a.img_floats = (uint32_t)g.img_floats;
     const int slots = evb_level_slots(level);
     evb_tic(h, EVB_T_HIST_REDUCE);
     if (slots <= 4) {
-        dim3 grid(slots, g.U * g.NCH, (h->B + 3) / 4);
+        dim3 grid(slots, g.U * g.FPL * g.NCH, (h->B + 3) / 4);
         k_hist_reduce<4><<<grid, 512, 0, h->st>>>(a);
     } else {
-        dim3 grid(slots, g.U * g.NCH, (h->B + 15) / 16);
+        dim3 grid(slots, g.U * g.FPL * g.NCH, (h->B + 15) / 16);
         k_hist_reduce<16><<<grid, 512, 0, h->st>>>(a);
     }
     evb_toc(h, EVB_T_HIST_REDUCE);
@@ -626,22 +713,15 @@ int32_t rows_hist_run(int device, cudaStream_t st, const uint8_t *x_rows, int32_
     a.xT = x_rows; a.grad = grad; a.rows = rows; a.js0 = js; a.plan = &plan->plan; a.cum = plan->cum; a.slot_node = plan->slot_node;
     a.seg_start = plan->seg_start; a.scratch = scratch; a.err = &plan->err;
     a.RS = row_stride; a.GS = 4; a.F = nfeats; a.nbins = nbins; a.C = nch; a.NFG = g.NFG; a.U = g.U; a.UB = g.UB;
-    a.stages = g.stages; a.PG = g.PG; a.img_floats = (uint32_t)g.img_floats; a.mode = hist_mode;
+    a.stages = g.stages; a.PG = g.PG; a.img_floats = (uint32_t)g.img_floats; a.mode = hist_mode; a.contig = 1;
     dim3 grid(g.G, g.NUG);
     const int threads = (g.UB + 1) * 32;
-    cudaError_t e;
-    switch (g.BP) {
-    case 32: e = launch_hist_bp<32>(g.NCH, a, grid, threads, g.smem, st); break;
-    case 64: e = launch_hist_bp<64>(g.NCH, a, grid, threads, g.smem, st); break;
-    case 128: e = launch_hist_bp<128>(g.NCH, a, grid, threads, g.smem, st); break;
-    default: e = launch_hist_bp<256>(g.NCH, a, grid, threads, g.smem, st); break;
-    }
-    EVB_CUDA(e);
+    EVB_CUDA(launch_hist(g, a, grid, threads, st));
     ReduceArgs r;
     r.scratch = scratch; r.hcomp = out; r.plan = &plan->plan; r.cum = plan->cum;
-    r.G = g.G; r.PG = g.PG; r.UB = g.UB; r.NFG = g.NFG; r.U = g.U; r.F = nfeats; r.C = nch; r.Ce = nch; r.K = 1; r.nbins = nbins; r.NCH = g.NCH;
+    r.G = g.G; r.PG = g.PG; r.UB = g.UB; r.NFG = g.NFG; r.U = g.U; r.F = nfeats; r.C = nch; r.Ce = nch; r.K = 1; r.nbins = nbins; r.NCH = g.NCH; r.FPL = g.FPL;
     r.img_floats = (uint32_t)g.img_floats;
-    dim3 rgrid(1, g.U * g.NCH, (nbins + 3) / 4);
+    dim3 rgrid(1, g.U * g.FPL * g.NCH, (nbins + 3) / 4);
     k_hist_reduce<4><<<rgrid, 512, 0, st>>>(r);
     EVB_CUDA(cudaGetLastError());
     int derr = 0;

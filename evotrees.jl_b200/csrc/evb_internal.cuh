@@ -49,7 +49,8 @@ struct LevelPlan {
 struct HistGeom {
     int BP;        // padded bins per image: 32/64/128/256
     int NCH;       // channels per unit image (<= 4)
-    int NFG;       // feature groups of 32 slots
+    int FPL;       // feature slots per lane (1, 2 or 4): a unit covers 32 * FPL feature slots
+    int NFG;       // feature groups of 32 * FPL slots
     int NCT;       // channel groups of 4
     int U;         // units = NFG*NCT
     int UB;        // units (consumer warps) per block
@@ -58,7 +59,7 @@ struct HistGeom {
     int G;         // row-range blocks (grid.x)
     int PG;        // piece slots per unit group = G + max build slots
     size_t smem;   // dynamic shared memory per block
-    size_t img_floats;   // floats per unit image in scratch: NCH*nbins*32
+    size_t img_floats;   // floats per unit image in scratch: FPL*NCH*nbins*32
 };
 
 struct evb_handle {
