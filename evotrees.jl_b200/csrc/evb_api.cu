@@ -90,6 +90,7 @@ static TreeBlockLayout tree_block_layout(int D, int nn, int K) {
     return l;
 }
 
+static void drop_graphs(evb_handle *h);
 static void free_handle(evb_handle *h) {
     if (!h) return;
     cudaSetDevice(h->dev);
@@ -100,7 +101,12 @@ static void free_handle(evb_handle *h) {
                     h->bslot, h->nsum, h->plan /* base of the tree block */, h->cum, h->slot_node, h->item_node, h->item_left,
                     h->item_lprefix, h->item_bits, h->scan_tmp, h->hist, h->hcomp, h->scratch, h->fbest_gain, h->fbest_bin};
     for (void *p : ptrs) if (p) cudaFree(p);
-    if (h->h_tree) cudaFreeHost(h->h_tree);
+    drop_graphs(h);
+    for (int q = 0; q < 2; ++q) {
+        if (h->h_tree[q]) cudaFreeHost(h->h_tree[q]);
+        if (h->h_js[q]) cudaFreeHost(h->h_js[q]);
+        if (h->ev_done[q]) cudaEventDestroy(h->ev_done[q]);
+    }
     for (cudaEvent_t e : h->ev) cudaEventDestroy(e);
     for (cudaEvent_t e : h->ev_tot) if (e) cudaEventDestroy(e);
     if (h->st) cudaStreamDestroy(h->st);
@@ -156,7 +162,13 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
     h->t_feat = (int32_t *)(blk + L.feat); h->t_gain = (float *)(blk + L.gain); h->t_w = (float *)(blk + L.w);
     h->t_pred = (float *)(blk + L.pred); h->t_packed = (uint32_t *)(blk + L.packed); h->t_bin = blk + L.bin; h->t_split = blk + L.split;
     h->h_tree_bytes = L.total;
-    EVB_CUDA(cudaMallocHost(&h->h_tree, L.total));
+    for (int q = 0; q < 2; ++q) {
+        EVB_CUDA(cudaMallocHost(&h->h_tree[q], L.total));
+        EVB_CUDA(cudaMallocHost((void **)&h->h_js[q], sizeof(uint32_t) * nfeats));
+        EVB_CUDA(cudaEventCreateWithFlags(&h->ev_done[q], cudaEventDisableTiming));
+    }
+    { const char *e = getenv("EVB_GRAPH"); h->use_graphs = e ? atoi(e) != 0 : true; }
+    h->graph_mask_cond = -1;
 
     h->maxslots = evb_level_slots(D > 1 ? D - 1 : 1);
     EVB_CUDA(dalloc(&h->cum, (size_t)h->maxslots + 1)); EVB_CUDA(dalloc(&h->slot_node, (size_t)h->maxslots));
@@ -267,66 +279,17 @@ extern "C" int32_t evb_comm_init(evb_handle *h, const uint8_t id[128], int32_t r
     if (h->nccl_comm) { evb_set_error("evb_comm_init: communicator already initialised"); return EVB_ERR_ARG; }
     if (world == 1) return EVB_OK;
     EVB_CHECK(evb_nccl_init(h, id, rank, world));
-    int32_t *g = nullptr;
-    EVB_CUDA(dalloc(&g, (size_t)h->nn + 2));
-    EVB_CUDA(cudaMemset(g, 0, sizeof(int32_t) * (h->nn + 2)));
-    h->gnleft = g;
     return EVB_OK;
 }
 
-extern "C" int32_t evb_grow_tree(evb_handle *h, const uint8_t *row_mask, uint8_t mask_cond, const uint32_t *js, int32_t njs,
-                                 int32_t update_grads, int64_t *feat, uint8_t *cond_bin, float *w_node, float *gain,
-                                 float *leaf_pred, uint8_t *split) {
-    EVB_ENTER(h);
-    if (!js || njs < 1 || njs > h->nfeats || !feat || !cond_bin || !w_node || !gain || !leaf_pred || !split) {
-        evb_set_error("evb_grow_tree: invalid argument");
-        return EVB_ERR_ARG;
-    }
-    std::vector<uint32_t> js0(njs);
-    for (int i = 0; i < njs; ++i) {
-        if (js[i] < 1 || js[i] > (uint32_t)h->nfeats || (i > 0 && js[i] <= js[i - 1])) {
-            evb_set_error("evb_grow_tree: js must be strictly ascending within 1..nfeats");
-            return EVB_ERR_ARG;
-        }
-        js0[i] = js[i] - 1;
-    }
-    if (h->world > 1) EVB_CHECK(evb_nccl_check(h));
+// Everything one tree launches, in stream order.  Runs either directly or under stream capture (then it is
+// replayed as one CUDA graph per tree): it must not synchronise and must not touch pageable host memory.
+static int32_t enqueue_tree(evb_handle *h, bool use_mask, uint8_t mask_cond, bool run_grads, bool fuse, int slot) {
     const int D = h->D;
-    if (h->timing) {
-        if (!h->ev_tot[0]) { EVB_CUDA(cudaEventCreate(&h->ev_tot[0])); EVB_CUDA(cudaEventCreate(&h->ev_tot[1])); }
-        cudaEventRecord(h->ev_tot[0], h->st);
-    }
-    evb_tic(h, EVB_T_H2D);
-    EVB_CUDA(cudaMemcpyAsync(h->js_d, js0.data(), sizeof(uint32_t) * njs, cudaMemcpyHostToDevice, h->st));
-    if (row_mask) EVB_CUDA(cudaMemcpyAsync(h->mask_d, row_mask, (size_t)h->n, cudaMemcpyHostToDevice, h->st));
-    evb_toc(h, EVB_T_H2D);
-    if (njs != h->F || h->hg.NFG != (njs + 31) / 32) {
-        HistGeom g;
-        h->F = njs;
-        EVB_CHECK(evb_hist_geometry(h, njs, &g));
-        const size_t need = (size_t)g.NUG * g.PG * g.UB * g.img_floats;
-        if (need > h->scratch_floats) {
-            EVB_CUDA(cudaStreamSynchronize(h->st));
-            EVB_CUDA(cudaFree(h->scratch));
-            h->scratch = nullptr;
-            EVB_CUDA(dalloc(&h->scratch, need));
-            h->scratch_floats = need;
-        }
-        h->hg = g;
-    }
-    if (update_grads) {
-        h->bag_idx = 0;
-        if (!h->grads_fresh) EVB_CHECK(evb_launch_grads(h));
-    }
-    h->grads_fresh = false;
+    EVB_CUDA(cudaMemcpyAsync(h->js_d, h->h_js[slot], sizeof(uint32_t) * h->F, cudaMemcpyHostToDevice, h->st));
+    if (run_grads) EVB_CHECK(evb_launch_grads(h));
     EVB_CHECK(evb_launch_tree_reset(h));
-    EVB_CHECK(evb_launch_rows_init(h, row_mask != nullptr, mask_cond));
-    if (h->world > 1) {
-        evb_tic(h, EVB_T_ALLREDUCE);
-        int32_t s = evb_nccl_allreduce_i32(h, h->nleft, h->gnleft, 1);
-        evb_toc(h, EVB_T_ALLREDUCE);
-        EVB_CHECK(s);
-    }
+    EVB_CHECK(evb_launch_rows_init(h, use_mask, mask_cond));
     EVB_CHECK(evb_launch_root_plan(h));
     const int last = D > 1 ? D - 1 : 1;
     const bool full_part = (h->p.flags & EVB_FLAG_FULL_PARTITION) != 0;
@@ -342,21 +305,116 @@ extern "C" int32_t evb_grow_tree(evb_handle *h, const uint8_t *row_mask, uint8_t
         EVB_CHECK(evb_launch_scan(h, level));
         if (level < D - 1 || (full_part && level == D - 1)) EVB_CHECK(evb_launch_partition(h, level));
     }
-    const bool fuse = h->bag_idx == h->p.bagging_size - 1;
     EVB_CHECK(evb_launch_finalize(h, fuse));
+    EVB_CUDA(cudaMemcpyAsync(h->h_tree[slot], h->plan, h->h_tree_bytes, cudaMemcpyDeviceToHost, h->st));
+    return EVB_OK;
+}
+
+static void drop_graphs(evb_handle *h) {
+    for (auto &g : h->graph) { if (g) cudaGraphExecDestroy(g); g = nullptr; }
+    for (auto &c : h->graph_calls) c = 0;
+}
+
+extern "C" int32_t evb_grow_tree_begin(evb_handle *h, const uint8_t *row_mask, uint8_t mask_cond, const uint32_t *js, int32_t njs,
+                                       int32_t update_grads) {
+    EVB_ENTER(h);
+    if (!js || njs < 1 || njs > h->nfeats) { evb_set_error("evb_grow_tree: invalid argument"); return EVB_ERR_ARG; }
+    if (h->pending >= 2 || (h->pending >= 1 && h->timing)) {
+        evb_set_error("evb_grow_tree_begin: collect the previous tree with evb_grow_tree_end first");
+        return EVB_ERR_BUSY;
+    }
+    const int slot = h->tree_seq & 1;
+    for (int i = 0; i < njs; ++i) {
+        if (js[i] < 1 || js[i] > (uint32_t)h->nfeats || (i > 0 && js[i] <= js[i - 1])) {
+            evb_set_error("evb_grow_tree: js must be strictly ascending within 1..nfeats");
+            return EVB_ERR_ARG;
+        }
+        h->h_js[slot][i] = js[i] - 1;
+    }
+    if (h->world > 1) EVB_CHECK(evb_nccl_check(h));
+    if (njs != h->F) {
+        HistGeom g;
+        EVB_CUDA(cudaStreamSynchronize(h->st));
+        h->F = njs;
+        EVB_CHECK(evb_hist_geometry(h, njs, &g));
+        const size_t need = (size_t)g.NUG * g.PG * g.UB * g.img_floats;
+        if (need > h->scratch_floats) {
+            EVB_CUDA(cudaFree(h->scratch));
+            h->scratch = nullptr;
+            EVB_CUDA(dalloc(&h->scratch, need));
+            h->scratch_floats = need;
+        }
+        h->hg = g;
+        drop_graphs(h);
+    }
+    if (update_grads) h->bag_idx = 0;
+    const bool run_grads = update_grads && !h->grads_fresh;
+    const bool fuse = h->bag_idx == h->p.bagging_size - 1;
+    const bool use_mask = row_mask != nullptr;
+    if (h->timing) {
+        if (!h->ev_tot[0]) { EVB_CUDA(cudaEventCreate(&h->ev_tot[0])); EVB_CUDA(cudaEventCreate(&h->ev_tot[1])); }
+        cudaEventRecord(h->ev_tot[0], h->st);
+    }
+    if (use_mask) {
+        evb_tic(h, EVB_T_H2D);
+        EVB_CUDA(cudaMemcpyAsync(h->mask_d, row_mask, (size_t)h->n, cudaMemcpyHostToDevice, h->st));
+        evb_toc(h, EVB_T_H2D);
+        h->tm.launches[EVB_T_H2D] -= 1; // a copy, not a kernel
+    }
+    // One CUDA graph per variant of the launch sequence, captured on the second call of a variant (the first
+    // one runs directly: it also sets function attributes).  Per-kernel timing needs the direct path.
+    const int key = (use_mask ? 1 : 0) | (run_grads ? 2 : 0) | (fuse ? 4 : 0) | (slot ? 8 : 0);
+    if (h->graph_mask_cond != (int)mask_cond) { drop_graphs(h); h->graph_mask_cond = mask_cond; }
+    bool launched = false;
+    // Sharded runs stay on direct launches: a run that captured the NCCL collectives into the graph did not
+    // complete on 2 GPUs, so collectives are never captured.
+    if (h->use_graphs && !h->timing && h->world == 1) {
+        if (!h->graph[key] && h->tree_seq >= 1) { // the very first tree of a handle always runs directly
+            int64_t before[EVB_NTIMERS];
+            memcpy(before, h->tm.launches, sizeof(before));
+            cudaGraph_t g = nullptr;
+            cudaError_t e = cudaStreamBeginCapture(h->st, cudaStreamCaptureModeThreadLocal);
+            int32_t rc = e == cudaSuccess ? enqueue_tree(h, use_mask, mask_cond, run_grads, fuse, slot) : EVB_ERR_CUDA;
+            cudaError_t e2 = cudaStreamEndCapture(h->st, &g);
+            for (int i = 0; i < EVB_NTIMERS; ++i) { h->graph_launches[key][i] = h->tm.launches[i] - before[i]; h->tm.launches[i] = before[i]; }
+            if (rc == EVB_OK && e2 == cudaSuccess && g && cudaGraphInstantiate(&h->graph[key], g, 0) == cudaSuccess) {
+                cudaGraphDestroy(g);
+            } else {
+                if (g) cudaGraphDestroy(g);
+                h->graph[key] = nullptr;
+                h->use_graphs = false; // capture is not possible here (e.g. an NCCL build without graph support): stay direct
+                cudaGetLastError();
+            }
+        }
+        if (h->graph[key]) {
+            EVB_CUDA(cudaGraphLaunch(h->graph[key], h->st));
+            for (int i = 0; i < EVB_NTIMERS; ++i) h->tm.launches[i] += h->graph_launches[key][i];
+            launched = true;
+        }
+    }
+    if (!launched) EVB_CHECK(enqueue_tree(h, use_mask, mask_cond, run_grads, fuse, slot));
+    h->graph_calls[key] += 1;
+    if (h->timing) cudaEventRecord(h->ev_tot[1], h->st);
+    EVB_CUDA(cudaEventRecord(h->ev_done[slot], h->st));
     h->grads_fresh = fuse;
     h->bag_idx += 1;
-    evb_tic(h, EVB_T_D2H);
-    EVB_CUDA(cudaMemcpyAsync(h->h_tree, h->plan, h->h_tree_bytes, cudaMemcpyDeviceToHost, h->st));
-    evb_toc(h, EVB_T_D2H);
-    if (h->timing) cudaEventRecord(h->ev_tot[1], h->st);
-    h->tm.launches[EVB_T_H2D] -= 1; // copies, not kernels
-    h->tm.launches[EVB_T_D2H] -= 1;
-    EVB_CUDA(cudaStreamSynchronize(h->st));
-    resolve_timing(h);
+    h->tree_seq += 1;
+    h->pending += 1;
+    return EVB_OK;
+}
 
+extern "C" int32_t evb_grow_tree_end(evb_handle *h, int64_t *feat, uint8_t *cond_bin, float *w_node, float *gain, float *leaf_pred,
+                                     uint8_t *split) {
+    EVB_ENTER(h);
+    if (!feat || !cond_bin || !w_node || !gain || !leaf_pred || !split) { evb_set_error("evb_grow_tree_end: null output"); return EVB_ERR_ARG; }
+    if (h->pending < 1) { evb_set_error("evb_grow_tree_end: no tree in flight"); return EVB_ERR_ARG; }
+    const int slot = (h->tree_seq - h->pending) & 1;
+    EVB_CUDA(cudaEventSynchronize(h->ev_done[slot]));
+    h->pending -= 1;
+    if (h->pending == 0) resolve_timing(h);
+    const int D = h->D, last = D > 1 ? D - 1 : 1;
     const TreeBlockLayout L = tree_block_layout(D, h->nn, h->K);
-    const unsigned char *hb = (const unsigned char *)h->h_tree;
+    const unsigned char *hb = (const unsigned char *)h->h_tree[slot];
     const int derr = *(const int *)(hb + L.err);
     if (derr != EVB_DERR_NONE) {
         evb_set_error("device self-check failed (code %d: %s)", derr,
@@ -381,6 +439,22 @@ extern "C" int32_t evb_grow_tree(evb_handle *h, const uint8_t *row_mask, uint8_t
     memcpy(leaf_pred, hb + L.pred, sizeof(float) * nn * h->K);
     memcpy(cond_bin, hb + L.bin, nn);
     memcpy(split, hb + L.split, nn);
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_grow_tree(evb_handle *h, const uint8_t *row_mask, uint8_t mask_cond, const uint32_t *js, int32_t njs,
+                                 int32_t update_grads, int64_t *feat, uint8_t *cond_bin, float *w_node, float *gain,
+                                 float *leaf_pred, uint8_t *split) {
+    if (!feat || !cond_bin || !w_node || !gain || !leaf_pred || !split) { evb_set_error("evb_grow_tree: invalid argument"); return EVB_ERR_ARG; }
+    if (h && h->pending > 0) { evb_set_error("evb_grow_tree: a tree started with evb_grow_tree_begin is still in flight"); return EVB_ERR_BUSY; }
+    EVB_CHECK(evb_grow_tree_begin(h, row_mask, mask_cond, js, njs, update_grads));
+    return evb_grow_tree_end(h, feat, cond_bin, w_node, gain, leaf_pred, split);
+}
+
+extern "C" int32_t evb_set_timing(evb_handle *h, int32_t on) {
+    EVB_ENTER(h);
+    if (h->pending > 0) { evb_set_error("evb_set_timing: a tree is in flight"); return EVB_ERR_BUSY; }
+    h->timing = on != 0;
     return EVB_OK;
 }
 

@@ -122,9 +122,17 @@ struct evb_handle {
     float *scratch;   // [NUG][PG][UB][NCH][B][32] per-piece partial images
     size_t scratch_floats;
 
-    // pinned host staging for tree outputs
-    void *h_tree; size_t h_tree_bytes;
-    LevelPlan *h_plan;
+    // pinned host staging, double buffered so that tree t+1 can be enqueued before tree t is collected
+    void *h_tree[2]; size_t h_tree_bytes;
+    uint32_t *h_js[2];
+    cudaEvent_t ev_done[2];
+    int tree_seq, pending;          // trees started / started but not yet collected
+    // one CUDA graph per variant of the per-tree launch sequence (mask, gradients first, gradients fused, slot)
+    bool use_graphs;
+    cudaGraphExec_t graph[16];
+    int graph_calls[16];
+    int64_t graph_launches[16][EVB_NTIMERS];
+    int graph_mask_cond;
 
     // multi-GPU
     void *nccl_comm; int rank, world;

@@ -347,6 +347,8 @@ struct PartArgs {
     int32_t *item_left, *item_lprefix;
     uint32_t *item_bits;
     LevelPlan *plan;
+    const double *nsum; // node sums [id][C]; channel C-1 is the sum of weights
+    int C, by_weight;   // by_weight: sharded run, pick the build child by weight sum instead of row count
     int RS, level, D, max_items;
     int *err;
 };
@@ -459,7 +461,13 @@ __global__ void __launch_bounds__(1024) k_level_plan(PartArgs a) {
             a.seg_start[L] = s0; a.seg_cnt[L] = nl; a.gcnt[L] = gl;
             a.seg_start[Rn] = s0 + nl; a.seg_cnt[Rn] = c0 - nl; a.gcnt[Rn] = g0 - gl;
             if (scan_children) {
-                const bool build_left = (g0 - gl) >= gl;
+                // The reference builds the child with fewer rows, ties build the left one (src/fit.jl:123-129).
+                // With rows sharded over GPUs the global row counts would cost one more collective per level, so
+                // there the child with the smaller weight sum is built: every rank knows the sums from the split
+                // scan, and with unit weights it is the same rule.
+                const bool build_left = a.by_weight
+                    ? a.nsum[(size_t)Rn * a.C + a.C - 1] >= a.nsum[(size_t)L * a.C + a.C - 1]
+                    : (g0 - gl) >= gl;
                 a.kind[L] = build_left ? EVB_KIND_BUILD : EVB_KIND_SUB;
                 a.kind[Rn] = build_left ? EVB_KIND_SUB : EVB_KIND_BUILD;
                 build_child = build_left ? L : Rn;
@@ -531,6 +539,7 @@ PartArgs make_part_args(evb_handle *h, int level) {
     a.bslot = h->bslot; a.cum = h->cum; a.slot_node = h->slot_node; a.kind = h->kind;
     a.ibase = h->item_node; a.item_left = h->item_left; a.item_lprefix = h->item_lprefix; a.item_bits = h->item_bits;
     a.plan = h->plan; a.RS = h->RS; a.level = level; a.D = h->D; a.max_items = h->max_items; a.err = h->d_err;
+    a.nsum = h->nsum; a.C = h->C; a.by_weight = h->world > 1 ? 1 : 0;
     return a;
 }
 
@@ -602,12 +611,6 @@ int32_t evb_launch_partition(evb_handle *h, int level) {
     k_part_prefix<<<wblocks, 256, 0, h->st>>>(a);
     evb_toc(h, EVB_T_PLAN);
     EVB_CUDA(cudaGetLastError());
-    if (h->world > 1) {
-        evb_tic(h, EVB_T_ALLREDUCE);
-        int32_t s = evb_nccl_allreduce_i32(h, h->nleft + m, h->gnleft + m, (size_t)m);
-        evb_toc(h, EVB_T_ALLREDUCE);
-        EVB_CHECK(s);
-    }
     evb_tic(h, EVB_T_PLAN);
     k_level_plan<<<1, 1024, 0, h->st>>>(a);
     evb_toc(h, EVB_T_PLAN);

@@ -140,6 +140,9 @@ class Cache:
         _lib.check(_lib.lib().evb_get_stream(self.handle, C.byref(out)))
         return out.value or 0
 
+    def set_timing(self, on: bool):
+        _lib.check(_lib.lib().evb_set_timing(self.handle, C.c_int32(1 if on else 0)))
+
     def reset_timings(self):
         _lib.check(_lib.lib().evb_reset_timings(self.handle))
 
@@ -234,6 +237,41 @@ def grow_tree(cache: Cache, params: EvoTypes, mask, js, update_grads: bool) -> T
     return t
 
 
+def grow_tree_begin(cache: Cache, params: EvoTypes, mask, js, update_grads: bool) -> None:
+    """Enqueues one tree (`evb_grow_tree_begin`); collect it with `grow_tree_end`.  Up to two trees may be in flight,
+    so the host can prepare tree t+1 while the GPU grows tree t."""
+    js = np.ascontiguousarray(js, np.uint32)
+    _lib.check(_lib.lib().evb_grow_tree_begin(cache.handle, _lib.ptr(mask), C.c_uint8(cache.mask_cond), _lib.ptr(js),
+                                              C.c_int32(js.size), C.c_int32(1 if update_grads else 0)))
+
+
+def grow_tree_end(cache: Cache, params: EvoTypes) -> Tree:
+    t = Tree.empty(params.max_depth, cache.K)
+    _lib.check(_lib.lib().evb_grow_tree_end(cache.handle, _lib.ptr(t.feat), _lib.ptr(t.cond_bin), _lib.ptr(t.w), _lib.ptr(t.gain),
+                                            _lib.ptr(t.pred), _lib.ptr(t.split)))
+    return t
+
+
+def grow_rounds(m: EvoTree, cache: Cache, params: EvoTypes, nrounds: int) -> None:
+    """`nrounds` boosting rounds with the host one tree ahead of the GPU (same trees as calling `grow_evotree`
+    `nrounds` times)."""
+    in_flight = 0
+    try:
+        for _ in range(nrounds):
+            for b in range(params.bagging_size):
+                mask, js = sample_round(cache, params)
+                grow_tree_begin(cache, params, mask, js, update_grads=(b == 0))
+                in_flight += 1
+                if in_flight == 2:
+                    m.trees.append(grow_tree_end(cache, params))
+                    in_flight -= 1
+            m.info["nrounds"] += 1
+    finally:
+        while in_flight > 0:
+            m.trees.append(grow_tree_end(cache, params))
+            in_flight -= 1
+
+
 def grow_evotree(m: EvoTree, cache: Cache, params: EvoTypes) -> None:
     """`grow_evotree!(m, cache, params)`: one boosting round = bagging_size trees."""
     for b in range(params.bagging_size):
@@ -249,8 +287,7 @@ def fit(params: EvoTypes, *, x_train, y_train, w_train=None, offset_train=None, 
     if x_eval is not None or y_eval is not None:
         raise NotImplementedError("x_eval / y_eval (eval metric tracking, early stopping) are not built for this device path")
     m, cache = init_core(params, x_train, y_train, w_train, offset_train, feature_names, device, comm=comm)
-    for _ in range(params.nrounds):
-        grow_evotree(m, cache, params)
+    grow_rounds(m, cache, params, params.nrounds)
     if return_cache:
         return m, cache
     cache.close()

@@ -105,8 +105,7 @@ EVB_API void evb_destroy(evb_handle *h);
 /*
  * Row sharding over several GPUs (one handle per GPU, normally one process per GPU).  Rank 0 obtains an
  * id, the host distributes its 128 bytes (any channel), then every rank calls evb_comm_init.  After that
- * evb_grow_tree sums the per-level histograms and child row counts over all ranks with NCCL, so every rank
- * grows the identical tree.  The reference has no counterpart: it is single-GPU
+ * evb_grow_tree sums the per-level histograms over all ranks with NCCL, so every rank grows the identical tree.  The reference has no counterpart: it is single-GPU
  * (ext/EvoTreesCUDAExt.jl:7-12).  All ranks must call evb_grow_tree with the same js / update_grads.
  */
 EVB_API int32_t evb_comm_unique_id(uint8_t id[128]);
@@ -125,6 +124,20 @@ EVB_API int32_t evb_comm_init(evb_handle *h, const uint8_t id[128], int32_t rank
 EVB_API int32_t evb_grow_tree(evb_handle *h, const uint8_t *row_mask, uint8_t mask_cond, const uint32_t *js, int32_t njs,
                       int32_t update_grads, int64_t *feat, uint8_t *cond_bin, float *w_node, float *gain,
                       float *leaf_pred, uint8_t *split);
+
+/*
+ * The same call split in two, so that the host can enqueue tree t+1 while the GPU still works on tree t (the
+ * reference's loop is strictly sequential: ext/.../fit.jl:296-300 reads the tree back before `predict!`).
+ * evb_grow_tree_begin enqueues one tree and returns at once; evb_grow_tree_end waits for the oldest tree in
+ * flight and writes its arrays.  At most two trees may be in flight.  After the first call of a given shape the
+ * launch sequence of a tree is replayed as one CUDA graph (EVB_GRAPH=0 turns that off).
+ */
+EVB_API int32_t evb_grow_tree_begin(evb_handle *h, const uint8_t *row_mask, uint8_t mask_cond, const uint32_t *js, int32_t njs,
+                                    int32_t update_grads);
+EVB_API int32_t evb_grow_tree_end(evb_handle *h, int64_t *feat, uint8_t *cond_bin, float *w_node, float *gain, float *leaf_pred,
+                                  uint8_t *split);
+/* Switches the per-kernel CUDA-event timing of EVB_FLAG_TIMING on or off (timed trees run without graphs). */
+EVB_API int32_t evb_set_timing(evb_handle *h, int32_t on);
 
 /* State read-back for parity checks (each synchronises the handle's stream). */
 EVB_API int32_t evb_get_pred(evb_handle *h, float *pred /* [K x nobs] */);
