@@ -580,6 +580,13 @@ int32_t evb_hist_geometry(const evb_handle *h, int F, HistGeom *g) {
         return EVB_ERR_CUDA;
     }
     g->G = occ * h->num_sms;
+    // Few rows: fewer, longer row ranges (every CTA costs one partial image that the reduce kernel has to read),
+    // but never fewer CTAs than SMs.
+    if (h->n > 0) {
+        long long cap = h->n / 1024;
+        if (cap < h->num_sms) cap = h->num_sms;
+        if ((long long)g->G > cap) g->G = (int)cap;
+    }
     g->PG = g->G + h->maxslots;
     g->img_floats = (size_t)FPL * g->NCH * B * 32;
     return EVB_OK;
@@ -692,7 +699,7 @@ int32_t rows_hist_run(int device, cudaStream_t st, const uint8_t *x_rows, int32_
                       const float *grad, int32_t nch, const uint32_t *rows, int64_t nrows, double *out, float *scratch,
                       size_t scratch_floats, RowsPlan *plan, uint32_t *js, int hist_mode) {
     evb_handle hh{};
-    hh.B = nbins; hh.C = nch; hh.Ce = nch; hh.K = 1; hh.RS = row_stride; hh.GS = 4; hh.nfeats = nfeats; hh.maxslots = 1;
+    hh.B = nbins; hh.C = nch; hh.Ce = nch; hh.K = 1; hh.RS = row_stride; hh.GS = 4; hh.nfeats = nfeats; hh.maxslots = 1; hh.n = nrows;
     int sms = 0;
     EVB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     hh.num_sms = sms;
@@ -739,7 +746,7 @@ extern "C" int32_t evb_hist_rows(int32_t device, void *stream, const uint8_t *x_
     EVB_CUDA(cudaSetDevice(device));
     cudaStream_t st = (cudaStream_t)stream;
     evb_handle hh{};
-    hh.B = nbins; hh.C = nch; hh.Ce = nch; hh.RS = row_stride; hh.GS = 4; hh.nfeats = nfeats; hh.maxslots = 1;
+    hh.B = nbins; hh.C = nch; hh.Ce = nch; hh.RS = row_stride; hh.GS = 4; hh.nfeats = nfeats; hh.maxslots = 1; hh.n = nrows;
     int sms = 0;
     EVB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     hh.num_sms = sms;

@@ -321,6 +321,33 @@ __global__ void __launch_bounds__(256) k_binarize(const T *x, long long ld, long
     }
 }
 
+// binarize a block of rows of the raw matrix straight into observation-major bins xT[row][RS] (what the traversal
+// reads): 256 rows per CTA, staged through shared memory so that both the reads of x and the writes of xT coalesce
+template <typename T>
+__global__ void __launch_bounds__(256) k_binarize_rows(const T *x, long long ld, int row_major, long long n, int nfeats, const T *edges,
+                                                       int nedges, uint8_t *xT, int RS) {
+    extern __shared__ unsigned char s_tile[]; // [256][RS]
+    const long long row0 = (long long)blockIdx.x * 256;
+    const int nr = (int)min((long long)256, n - row0);
+    for (int e = threadIdx.x; e < 256 * RS; e += 256) s_tile[e] = 0;
+    __syncthreads();
+    const int total = nr * nfeats;
+    for (int e = threadIdx.x; e < total; e += 256) {
+        int r, j;
+        T v;
+        if (row_major) { r = e / nfeats; j = e - r * nfeats; v = x[(size_t)(row0 + r) * ld + j]; }
+        else { j = e / nr; r = e - j * nr; v = x[(size_t)j * ld + row0 + r]; }
+        const T *ed = edges + (size_t)j * nedges;
+        int lo = 0, hi = nedges;
+        while (lo < hi) { const int mid = (lo + hi) >> 1; if (__ldg(ed + mid) < v) lo = mid + 1; else hi = mid; }
+        s_tile[r * RS + j] = (uint8_t)(lo + 1);
+    }
+    __syncthreads();
+    const uint4 *src = reinterpret_cast<const uint4 *>(s_tile);
+    uint4 *dst = reinterpret_cast<uint4 *>(xT + (size_t)row0 * RS);
+    for (int e = threadIdx.x; e < nr * (RS / 16); e += 256) dst[e] = src[e];
+}
+
 } // namespace
 
 // =====================================================================================================
@@ -409,13 +436,18 @@ struct DevBuf {
     template <typename T> T *as() { return reinterpret_cast<T *>(p); }
 };
 
-extern "C" int32_t evb_predict(int32_t device, int32_t loss, int32_t K, int32_t ntrees, int32_t nn, const int64_t *feat,
-                               const uint8_t *cond_bin, const uint8_t *split, const float *leaf_pred, const uint8_t *x_bin,
-                               int64_t nobs, int32_t nfeats, const uint8_t *feattypes, int32_t apply_link, float *out,
-                               uint32_t *leaf_idx) {
-    if (!feat || !cond_bin || !split || !leaf_pred || !x_bin || !out || nobs < 0 || nfeats < 1 || nfeats > 65535 ||
+// Common body of evb_predict (binned input) and evb_predict_x (raw input + edges, binarized on the device).
+static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntrees, int32_t nn, const int64_t *feat,
+                            const uint8_t *cond_bin, const uint8_t *split, const float *leaf_pred, const uint8_t *x_bin, const void *x,
+                            int32_t x_dtype, int32_t x_row_major, const void *edges, int32_t nedges, int64_t nobs, int32_t nfeats,
+                            const uint8_t *feattypes, int32_t apply_link, float *out, uint32_t *leaf_idx, double *ms_out) {
+    if (!feat || !cond_bin || !split || !leaf_pred || (!x_bin && !x) || !out || nobs < 0 || nfeats < 1 || nfeats > 65535 ||
         ntrees < 0 || nn < 1 || K < 1 || K > 64 || loss < 0 || loss > 3) {
         evb_set_error("evb_predict: invalid argument");
+        return EVB_ERR_ARG;
+    }
+    if (x && (!edges || nedges < 1 || nedges > 254 || (x_dtype != EVB_F32 && x_dtype != EVB_F64))) {
+        evb_set_error("evb_predict_x: edges / dtype invalid");
         return EVB_ERR_ARG;
     }
     EVB_CHECK(check_device(device));
@@ -423,17 +455,21 @@ extern "C" int32_t evb_predict(int32_t device, int32_t loss, int32_t K, int32_t 
     cudaStream_t st;
     EVB_CUDA(cudaStreamCreate(&st));
     const int RS = (nfeats + 31) / 32 * 32;
+    const size_t es = x_dtype == EVB_F64 ? 8 : 4;
     const long long total = (long long)ntrees * nn;
-    const int64_t chunk = nobs < (int64_t)4 << 20 ? nobs : (int64_t)4 << 20;
-    DevBuf d_feat, d_bin, d_split, d_ft, d_packed, d_leaf, d_xcol, d_xT, d_out, d_lidx;
-    int32_t rc = EVB_OK;
+    const int64_t chunk = nobs < (int64_t)2 << 20 ? nobs : (int64_t)2 << 20;
+    DevBuf d_feat, d_bin, d_split, d_ft, d_packed, d_leaf, d_in, d_xT, d_out, d_lidx, d_edges;
+    cudaEvent_t ev[2] = {nullptr, nullptr};
+    float kernel_ms = 0.f;
     auto body = [&]() -> int32_t {
+        EVB_CUDA(cudaEventCreate(&ev[0])); EVB_CUDA(cudaEventCreate(&ev[1]));
         EVB_CUDA(d_feat.alloc(total * 8)); EVB_CUDA(d_bin.alloc(total)); EVB_CUDA(d_split.alloc(total));
         EVB_CUDA(d_packed.alloc(total * 4)); EVB_CUDA(d_leaf.alloc((size_t)total * K * 4));
-        EVB_CUDA(d_xcol.alloc((size_t)chunk * nfeats)); EVB_CUDA(d_xT.alloc((size_t)chunk * RS));
+        EVB_CUDA(d_in.alloc((size_t)chunk * nfeats * (x ? es : 1))); EVB_CUDA(d_xT.alloc((size_t)chunk * RS));
         EVB_CUDA(d_out.alloc((size_t)nobs * K * 4));
         if (leaf_idx) EVB_CUDA(d_lidx.alloc((size_t)nobs * ntrees * 4));
         if (feattypes) { EVB_CUDA(d_ft.alloc(nfeats)); EVB_CUDA(cudaMemcpyAsync(d_ft.p, feattypes, nfeats, cudaMemcpyHostToDevice, st)); }
+        if (x) { EVB_CUDA(d_edges.alloc((size_t)nedges * nfeats * es)); EVB_CUDA(cudaMemcpyAsync(d_edges.p, edges, (size_t)nedges * nfeats * es, cudaMemcpyHostToDevice, st)); }
         EVB_CUDA(cudaMemcpyAsync(d_feat.p, feat, total * 8, cudaMemcpyHostToDevice, st));
         EVB_CUDA(cudaMemcpyAsync(d_bin.p, cond_bin, total, cudaMemcpyHostToDevice, st));
         EVB_CUDA(cudaMemcpyAsync(d_split.p, split, total, cudaMemcpyHostToDevice, st));
@@ -446,8 +482,28 @@ extern "C" int32_t evb_predict(int32_t device, int32_t loss, int32_t K, int32_t 
         EVB_CUDA(cudaMemsetAsync(d_xT.p, 0, (size_t)chunk * RS, st));
         for (int64_t r0 = 0; r0 < nobs; r0 += chunk) {
             const int64_t nr = nobs - r0 < chunk ? nobs - r0 : chunk;
-            EVB_CUDA(cudaMemcpy2DAsync(d_xcol.p, (size_t)chunk, x_bin + r0, (size_t)nobs, (size_t)nr, (size_t)nfeats, cudaMemcpyHostToDevice, st));
-            EVB_CHECK(evb_launch_transpose(nullptr, d_xcol.as<uint8_t>(), chunk, nr, 0, nfeats, d_xT.as<uint8_t>(), RS, st));
+            if (x) {
+                if (x_row_major) {
+                    EVB_CUDA(cudaMemcpyAsync(d_in.p, (const char *)x + (size_t)r0 * nfeats * es, (size_t)nr * nfeats * es, cudaMemcpyHostToDevice, st));
+                } else {
+                    EVB_CUDA(cudaMemcpy2DAsync(d_in.p, (size_t)chunk * es, (const char *)x + (size_t)r0 * es, (size_t)nobs * es, (size_t)nr * es,
+                                               (size_t)nfeats, cudaMemcpyHostToDevice, st));
+                }
+            } else {
+                EVB_CUDA(cudaMemcpy2DAsync(d_in.p, (size_t)chunk, x_bin + r0, (size_t)nobs, (size_t)nr, (size_t)nfeats, cudaMemcpyHostToDevice, st));
+            }
+            EVB_CUDA(cudaEventRecord(ev[0], st));
+            if (x) {
+                const unsigned blocks = (unsigned)((nr + 255) / 256);
+                const long long ld = x_row_major ? nfeats : chunk;
+                if (x_dtype == EVB_F32)
+                    k_binarize_rows<float><<<blocks, 256, 256 * RS, st>>>(d_in.as<float>(), ld, x_row_major, nr, nfeats, d_edges.as<float>(), nedges, d_xT.as<uint8_t>(), RS);
+                else
+                    k_binarize_rows<double><<<blocks, 256, 256 * RS, st>>>(d_in.as<double>(), ld, x_row_major, nr, nfeats, d_edges.as<double>(), nedges, d_xT.as<uint8_t>(), RS);
+                EVB_CUDA(cudaGetLastError());
+            } else {
+                EVB_CHECK(evb_launch_transpose(nullptr, d_in.as<uint8_t>(), chunk, nr, 0, nfeats, d_xT.as<uint8_t>(), RS, st));
+            }
             PredArgs a;
             a.xT = d_xT.as<uint8_t>(); a.packed = d_packed.as<uint32_t>(); a.leaf = d_leaf.as<float>(); a.out = d_out.as<float>();
             a.leaf_idx = leaf_idx ? d_lidx.as<uint32_t>() : nullptr; a.n = nr; a.row0 = r0; a.nobs_total = nobs; a.RS = RS; a.K = K;
@@ -458,16 +514,41 @@ extern "C" int32_t evb_predict(int32_t device, int32_t loss, int32_t K, int32_t 
             else if (K <= 8) k_predict<8><<<blocks, 256, 0, st>>>(a);
             else k_predict<64><<<blocks, 256, 0, st>>>(a);
             EVB_CUDA(cudaGetLastError());
+            EVB_CUDA(cudaEventRecord(ev[1], st));
+            EVB_CUDA(cudaEventSynchronize(ev[1]));
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, ev[0], ev[1]);
+            kernel_ms += ms;
         }
         EVB_CUDA(cudaMemcpyAsync(out, d_out.p, (size_t)nobs * K * 4, cudaMemcpyDeviceToHost, st));
         if (leaf_idx) EVB_CUDA(cudaMemcpyAsync(leaf_idx, d_lidx.p, (size_t)nobs * ntrees * 4, cudaMemcpyDeviceToHost, st));
         EVB_CUDA(cudaStreamSynchronize(st));
         return EVB_OK;
     };
-    rc = body();
+    int32_t rc = body();
     cudaStreamSynchronize(st);
+    if (ms_out) *ms_out = kernel_ms;
+    for (cudaEvent_t e : ev) if (e) cudaEventDestroy(e);
     cudaStreamDestroy(st);
     return rc;
+}
+
+extern "C" int32_t evb_predict(int32_t device, int32_t loss, int32_t K, int32_t ntrees, int32_t nn, const int64_t *feat,
+                               const uint8_t *cond_bin, const uint8_t *split, const float *leaf_pred, const uint8_t *x_bin,
+                               int64_t nobs, int32_t nfeats, const uint8_t *feattypes, int32_t apply_link, float *out,
+                               uint32_t *leaf_idx) {
+    if (!x_bin) { evb_set_error("evb_predict: x_bin is null"); return EVB_ERR_ARG; }
+    return predict_impl(device, loss, K, ntrees, nn, feat, cond_bin, split, leaf_pred, x_bin, nullptr, 0, 0, nullptr, 0, nobs, nfeats,
+                        feattypes, apply_link, out, leaf_idx, nullptr);
+}
+
+extern "C" int32_t evb_predict_x(int32_t device, int32_t loss, int32_t K, int32_t ntrees, int32_t nn, const int64_t *feat,
+                                 const uint8_t *cond_bin, const uint8_t *split, const float *leaf_pred, const void *x, int32_t x_dtype,
+                                 int32_t x_row_major, const void *edges, int32_t nedges, int64_t nobs, int32_t nfeats,
+                                 const uint8_t *feattypes, int32_t apply_link, float *out, uint32_t *leaf_idx, double *kernel_ms) {
+    if (!x) { evb_set_error("evb_predict_x: x is null"); return EVB_ERR_ARG; }
+    return predict_impl(device, loss, K, ntrees, nn, feat, cond_bin, split, leaf_pred, nullptr, x, x_dtype, x_row_major, edges, nedges,
+                        nobs, nfeats, feattypes, apply_link, out, leaf_idx, kernel_ms);
 }
 
 extern "C" int32_t evb_binarize(int32_t device, const void *x, int32_t dtype, int64_t nobs, int32_t nfeats, const void *edges,

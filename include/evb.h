@@ -171,6 +171,21 @@ EVB_API int32_t evb_predict(int32_t device, int32_t loss, int32_t K, int32_t ntr
                     uint32_t *leaf_idx);
 
 /*
+ * evb_predict_x -- the whole of `_predict(m, data, ::Type{<:GPU})` (ext/EvoTreesKernelAbstractionsExt/predict.jl:115-135),
+ * `binarize` included: the raw feature matrix goes to the device block by block, is binarized there against the
+ * model's edges (`searchsortedfirst`, src/fit-utils.jl:69) straight into observation-major bins, and the trees are
+ * applied.  Same tree arguments and outputs as evb_predict.
+ *   x            host, EVB_F32 / EVB_F64; column-major [nobs x nfeats] (x_row_major = 0, a Julia Matrix) or
+ *                row-major (x_row_major = 1, a C-ordered array)
+ *   edges        host [nedges x nfeats] column-major, same dtype as x
+ *   kernel_ms    optional: receives the summed device time of the binarize + traversal kernels
+ */
+EVB_API int32_t evb_predict_x(int32_t device, int32_t loss, int32_t K, int32_t ntrees, int32_t nn, const int64_t *feat,
+                              const uint8_t *cond_bin, const uint8_t *split, const float *leaf_pred, const void *x, int32_t x_dtype,
+                              int32_t x_row_major, const void *edges, int32_t nedges, int64_t nobs, int32_t nfeats,
+                              const uint8_t *feattypes, int32_t apply_link, float *out, uint32_t *leaf_idx, double *kernel_ms);
+
+/*
  * evb_binarize -- `binarize(X; edges)` (src/fit-utils.jl:66-72) on the device: x_bin[i,j] =
  * searchsortedfirst(edges[j], x[i,j]).  x host column-major [nobs x nfeats] of dtype EVB_F32 / EVB_F64,
  * edges host [nedges x nfeats] column-major of the same dtype (ascending per feature), out host uint8.
