@@ -32,20 +32,23 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// try_wait with a suspend-time hint: the warp sleeps in hardware until the phase completes or the hint (in
+// nanoseconds) runs out, instead of burning issue slots in a polling loop.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.b32 %0, 1, 0, p;\n}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(100000u)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~2^22 polls (or as soon as another warp has flagged an error).
+// Bounded wait: gives up after 2^16 suspended tries of up to 0.1 ms each (or as soon as another warp has flagged an
+// error) and records `code` in the error word.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err, int code) {
-    for (uint32_t i = 0; i < (1u << 22); ++i) {
+    for (uint32_t i = 0; i < (1u << 16); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *(volatile int *)err != 0) return false;
+        if ((i & 15u) == 15u && *(volatile int *)err != 0) return false;
     }
     atomicCAS(err, 0, code);
     return false;
