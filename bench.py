@@ -1,6 +1,6 @@
 """Benchmark of the EvoTrees training hot path on B200.
 
-Metric (BASELINE.json): seconds per 200 boosting rounds, mse, 10M x 100 Float32 features, depth 11, 64 bins,
+Metric: seconds per 200 boosting rounds, mse, 10M x 100 Float32 features, depth 11, 64 bins,
 rows sharded over --gpus GPUs (strong scaling).  A "step" is one boosting round over synthetic data of that
 shape (uniform features, y = x.beta + 0.1 N(0,1); the reference's benchmark data is synthetic too,
 benchmarks/regressor.jl:47-48).

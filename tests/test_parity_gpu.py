@@ -16,7 +16,7 @@ def _softmax_data(n, f, k, seed=5):
 
 
 def test_mse_small_config(pkg, orc):
-    """BASELINE config 1 shape (100k x 10, depth 6, 32 bins), a few rounds in lock-step."""
+    """The reference benchmark's smallest shape (100k x 10, depth 6, 32 bins), a few rounds in lock-step."""
     x, y = make_regression(100_000, 10, dtype=np.float64)
     p = pkg.EvoTreeRegressor(loss="mse", nrounds=4, max_depth=6, nbins=32, eta=0.1)
     s = lockstep_check(pkg, orc, p, x, y, rounds=4)
@@ -24,7 +24,7 @@ def test_mse_small_config(pkg, orc):
 
 
 def test_mse_row_col_sampling(pkg, orc):
-    """Config 2 shape scaled down: 100 features, rowsample / colsample 0.5, 64 bins."""
+    """Regression with 100 features and row / column sampling, scaled down in rows: 100 features, rowsample / colsample 0.5, 64 bins."""
     x, y = make_regression(60_000, 100, seed=3, dtype=np.float64)
     p = pkg.EvoTreeRegressor(loss="mse", nrounds=3, max_depth=6, nbins=64, eta=0.05, rowsample=0.5, colsample=0.5)
     s = lockstep_check(pkg, orc, p, x, y, rounds=3)
@@ -47,7 +47,7 @@ def test_logloss(pkg, orc):
 
 
 def test_softmax(pkg, orc):
-    """Config 4 shape scaled down: 28 features, 5 classes, depth 8, 64 bins."""
+    """Five-class softmax shape scaled down in rows: 28 features, 5 classes, depth 8, 64 bins."""
     x, y = _softmax_data(80_000, 28, 5)
     p = pkg.EvoTreeClassifier(nrounds=3, max_depth=8, nbins=64, eta=0.2)
     s = lockstep_check(pkg, orc, p, x, y, rounds=3)
@@ -55,7 +55,7 @@ def test_softmax(pkg, orc):
 
 
 def test_gaussian_mle(pkg, orc):
-    """Config 5 shape scaled down: 50 features, depth 7, 32 bins, min_weight 8."""
+    """Gaussian maximum-likelihood shape scaled down in rows: 50 features, depth 7, 32 bins, min_weight 8."""
     rng = np.random.default_rng(17)
     n, f = 80_000, 50
     x = rng.random((n, f)).astype(np.float32)
