@@ -96,6 +96,10 @@ static void free_handle(evb_handle *h) {
     cudaSetDevice(h->dev);
     if (h->st) cudaStreamSynchronize(h->st);
     evb_nccl_destroy(h);
+    for (int i = 0; i < h->n_ipc_opened; ++i) cudaIpcCloseMemHandle(h->ipc_opened[i]);
+    if (h->peer_cand[h->rank]) cudaFree(h->peer_cand[h->rank]);
+    if (h->peer_flags[h->rank]) cudaFree(h->peer_flags[h->rank]);
+    if (h->hsum) cudaFree(h->hsum);
     void *ptrs[] = {h->xT, h->xC, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
                     h->js_d, h->seg_start, h->seg_cnt, h->gcnt, h->nleft, (h->gnleft != h->nleft) ? h->gnleft : nullptr, h->kind,
                     h->bslot, h->nsum, h->plan /* base of the tree block */, h->cum, h->slot_node, h->item_node, h->item_left,
@@ -296,7 +300,7 @@ static int32_t enqueue_tree(evb_handle *h, bool use_mask, uint8_t mask_cond, boo
     for (int level = 1; level <= last; ++level) {
         EVB_CHECK(evb_launch_hist(h, level));
         EVB_CHECK(evb_launch_hist_reduce(h, level));
-        if (h->world > 1) {
+        if (h->world > 1 && !h->p2p) { // with peer access the ranks' histograms are summed inside the split scan instead
             evb_tic(h, EVB_T_ALLREDUCE);
             int32_t s = evb_nccl_allreduce_f64(h, h->hcomp, (size_t)evb_level_slots(level) * h->F * h->C * h->B);
             evb_toc(h, EVB_T_ALLREDUCE);
@@ -420,7 +424,8 @@ extern "C" int32_t evb_grow_tree_end(evb_handle *h, int64_t *feat, uint8_t *cond
         evb_set_error("device self-check failed (code %d: %s)", derr,
                       derr == EVB_DERR_WAIT_FULL ? "bounded wait for staged rows expired"
                       : derr == EVB_DERR_WAIT_EMPTY ? "bounded wait for a free stage expired"
-                      : derr == EVB_DERR_PLAN ? "work list overflow" : "unknown");
+                      : derr == EVB_DERR_PLAN ? "work list overflow"
+                      : derr == EVB_DERR_PEER ? "bounded wait for the other ranks expired" : "unknown");
         cudaMemsetAsync(h->d_err, 0, sizeof(int), h->st);
         return EVB_ERR_DEVICE;
     }
@@ -449,6 +454,67 @@ extern "C" int32_t evb_grow_tree(evb_handle *h, const uint8_t *row_mask, uint8_t
     if (h && h->pending > 0) { evb_set_error("evb_grow_tree: a tree started with evb_grow_tree_begin is still in flight"); return EVB_ERR_BUSY; }
     EVB_CHECK(evb_grow_tree_begin(h, row_mask, mask_cond, js, njs, update_grads));
     return evb_grow_tree_end(h, feat, cond_bin, w_node, gain, leaf_pred, split);
+}
+
+// ---- peer access between the ranks' processes (CUDA IPC) -----------------------------------------------------
+struct IpcBlob { cudaIpcMemHandle_t hcomp, cand, flags; };
+static_assert(sizeof(IpcBlob) <= 256, "blob size");
+
+extern "C" int32_t evb_comm_ipc_export(evb_handle *h, uint8_t blob[256]) {
+    EVB_ENTER(h);
+    if (!blob) { evb_set_error("null blob"); return EVB_ERR_ARG; }
+    if (h->world < 2 || h->world > 8) { evb_set_error("evb_comm_ipc_export: needs evb_comm_init with 2..8 ranks first"); return EVB_ERR_ARG; }
+    if (h->p2p || h->peer_cand[h->rank]) { evb_set_error("evb_comm_ipc_export: already exported"); return EVB_ERR_ARG; }
+    EVB_CUDA(cudaStreamSynchronize(h->st));
+    const int D = h->D;
+    // every scanned node keeps the summed histogram of the features this rank owns (children subtract from it)
+    const int keep_nodes = 1 << (D > 1 ? D - 1 : 0);
+    if (keep_nodes > h->hist_nodes) {
+        EVB_CUDA(cudaFree(h->hist));
+        h->hist = nullptr;
+        EVB_CUDA(dalloc(&h->hist, (size_t)keep_nodes * h->nfeats * h->C * h->B));
+        h->hist_nodes = keep_nodes;
+    }
+    EVB_CUDA(dalloc(&h->hsum, (size_t)h->maxslots * h->nfeats * h->C * h->B));
+    double *cand = nullptr;
+    int *flags = nullptr;
+    const size_t ncand = (size_t)keep_nodes * h->world * (3 + h->C);
+    EVB_CUDA(dalloc(&cand, ncand));
+    EVB_CUDA(cudaMemset(cand, 0, ncand * sizeof(double)));
+    EVB_CUDA(dalloc(&flags, (size_t)8));
+    EVB_CUDA(cudaMemset(flags, 0, 8 * sizeof(int)));
+    h->peer_hcomp[h->rank] = h->hcomp; h->peer_cand[h->rank] = cand; h->peer_flags[h->rank] = flags;
+    IpcBlob b;
+    memset(&b, 0, sizeof(b));
+    EVB_CUDA(cudaIpcGetMemHandle(&b.hcomp, h->hcomp));
+    EVB_CUDA(cudaIpcGetMemHandle(&b.cand, cand));
+    EVB_CUDA(cudaIpcGetMemHandle(&b.flags, flags));
+    memset(blob, 0, 256);
+    memcpy(blob, &b, sizeof(b));
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_comm_ipc_import(evb_handle *h, const uint8_t *blobs) {
+    EVB_ENTER(h);
+    if (!blobs || !h->peer_cand[h->rank]) { evb_set_error("evb_comm_ipc_import: call evb_comm_ipc_export first"); return EVB_ERR_ARG; }
+    for (int q = 0; q < h->world; ++q) {
+        if (q == h->rank) continue;
+        IpcBlob b;
+        memcpy(&b, blobs + (size_t)q * 256, sizeof(b));
+        void *p[3] = {nullptr, nullptr, nullptr};
+        const cudaIpcMemHandle_t hs[3] = {b.hcomp, b.cand, b.flags};
+        for (int k = 0; k < 3; ++k) {
+            cudaError_t e = cudaIpcOpenMemHandle(&p[k], hs[k], cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) {
+                evb_set_error("cannot map rank %d's buffers (%s): peer access between the GPUs is required", q, cudaGetErrorString(e));
+                return EVB_ERR_CUDA;
+            }
+            h->ipc_opened[h->n_ipc_opened++] = p[k];
+        }
+        h->peer_hcomp[q] = (double *)p[0]; h->peer_cand[q] = (double *)p[1]; h->peer_flags[q] = (int *)p[2];
+    }
+    h->p2p = true;
+    return EVB_OK;
 }
 
 extern "C" int32_t evb_set_timing(evb_handle *h, int32_t on) {

@@ -26,7 +26,7 @@ void evb_set_error(const char *fmt, ...);
     } while (0)
 
 // device-side error codes written to evb_handle::d_err
-enum { EVB_DERR_NONE = 0, EVB_DERR_WAIT_FULL = 1, EVB_DERR_WAIT_EMPTY = 2, EVB_DERR_BIN_RANGE = 3, EVB_DERR_PLAN = 4 };
+enum { EVB_DERR_NONE = 0, EVB_DERR_WAIT_FULL = 1, EVB_DERR_WAIT_EMPTY = 2, EVB_DERR_BIN_RANGE = 3, EVB_DERR_PLAN = 4, EVB_DERR_PEER = 5 };
 
 // ---- geometry constants ---------------------------------------------------------------------------
 constexpr int EVB_TILE_ROWS = 32;    // rows per staged tile (one per producer lane)
@@ -136,6 +136,12 @@ struct evb_handle {
 
     // multi-GPU
     void *nccl_comm; int rank, world;
+    // peer access between the ranks' processes (CUDA IPC): histograms are summed by peer loads inside the split scan
+    bool p2p;
+    double *peer_hcomp[8]; double *peer_cand[8]; int *peer_flags[8];
+    double *hsum; // sums over the ranks of the owned feature slots of hcomp
+    void *ipc_opened[24]; int n_ipc_opened;
+    int barrier_seq;
 
     // timing
     bool timing;

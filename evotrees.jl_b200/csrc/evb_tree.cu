@@ -93,6 +93,8 @@ __global__ void k_root_plan(RootArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------ split scan
+constexpr int EVB_MAX_PEERS = 8;
+
 struct ScanArgs {
     const double *hcomp;
     double *hist, *nsum;
@@ -107,6 +109,13 @@ struct ScanArgs {
     uint32_t *t_packed;
     double *fbest_gain; // [nodes of the level][F] best gain of each feature
     int32_t *fbest_bin; // [nodes of the level][F] its bin (0-based) or -1
+    const LevelPlan *plan;
+    const int32_t *slot_node;
+    // Row-sharded runs with peer access: every rank scans the feature slots f with f % world == rank (`hcomp` then
+    // points at the sums made by k_peer_reduce) and publishes one candidate per node to every rank.
+    double *peer_cand[EVB_MAX_PEERS];
+    const double *cand_local; // [nodes of the level][world][3 + C]: gain, feature slot, bin, left sums
+    int world, rank;          // world == 1: no peers (single GPU, or histograms already summed by NCCL)
     int F, C, K, B, level, D, hist_nodes, loss;
     double neb; // -eta / bagging_size
     double lambda, L2, gamma, min_weight;
@@ -130,42 +139,55 @@ __device__ __forceinline__ float leaf_value(const ScanArgs &a, const double *s, 
     return (float)(a.neb * g / fmax(DBL_EPSILON, h + a.lambda * s[C - 1] + a.L2));
 }
 
-// Stage 1: one warp per (node of the level, feature slot), lanes over bins.  Applies the sibling subtraction,
-// stores the node's histogram if its children will need it, scans the bins and records the best split of
-// this feature.  Warps are independent, so even the root level (one node) spreads over many SMs.
-__global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
-    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+// Sharded with peer access: sums the ranks' freshly built histograms for the feature slots this rank owns, by
+// loads from the peers' memory past the caches, in rank order (so the result does not depend on timing).  One CTA
+// per (build slot, owned feature); at the root level feature slot 0 is summed on every rank (it gives the root sums).
+struct PeerReduceArgs {
+    const double *peer_hcomp[EVB_MAX_PEERS];
+    double *hsum;
+    const LevelPlan *plan;
+    int world, rank, F, CB, level;
+};
+__global__ void __launch_bounds__(256) k_peer_reduce(PeerReduceArgs a) {
+    const int Fown = (a.F - a.rank + a.world - 1) / a.world;
+    const int per = Fown + 1; // last index of a slot: feature slot 0 (root level only)
+    const int s = blockIdx.x / per, fi = blockIdx.x % per;
+    if (s >= a.plan->nbuild) return;
+    int f;
+    if (fi < Fown) f = fi * a.world + a.rank;
+    else { if (a.level != 1 || a.rank == 0) return; f = 0; }
+    const size_t base = ((size_t)s * a.F + f) * a.CB;
+    for (int idx = threadIdx.x; idx < a.CB; idx += blockDim.x) {
+        double v = 0.0;
+#pragma unroll 8
+        for (int q = 0; q < a.world; ++q) v += __ldcv(a.peer_hcomp[q] + base + idx);
+        a.hsum[base + idx] = v;
+    }
+}
+
+// Scan of one (node, feature): applies the sibling subtraction (`subtract_hist!`, fit-utils.jl:321-332) to the
+// staged histogram `sm` of the build node, stores the node's histogram if its children will need it, scans the
+// bins (`_scan_node!`, fit-utils.jl:403-436) and records the best split of this feature.
+__device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int f, const double *sm, double *s_sum, int lane, bool first_owned) {
     const int C = a.C, K = a.K, B = a.B, F = a.F;
-    const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + wid;
     const int m = 1 << (a.level - 1);
-    const int i = (int)(gw / F), f = (int)(gw % F);
-    __shared__ double s_sum_all[8][72];
-    double *s_sum = s_sum_all[wid];
-    if (i >= m) return;
-    const int n = m + i;
-    const int kd = a.kind[n];
-    if (kd == EVB_KIND_NONE) return;
     const size_t FCB = (size_t)F * C * B;
-    const double *__restrict__ hc = a.hcomp + (size_t)a.bslot[n] * FCB;
-    const bool sub = kd == EVB_KIND_SUB;
     const double *__restrict__ hp = a.hist + (size_t)(n >> 1) * FCB;
     const bool keep = n < a.hist_nodes;
     double *__restrict__ hn = a.hist + (size_t)n * FCB;
-
     if (n == 1) {
         // root sums = sum over the bins of feature slot 0 (every sampled row has exactly one bin there);
         // the reference sums the gradients of the sampled rows directly (src/fit.jl:66)
         for (int c = 0; c < C; ++c) {
             double v = 0.0;
-            for (int b = lane; b < B; b += 32) v += __ldg(hc + (size_t)c * B + b);
+            for (int b = lane; b < B; b += 32) v += __ldg(a.hcomp + (size_t)c * B + b);
             v = warp_sum(v);
-            if (lane == 0) { s_sum[c] = v; if (f == 0) a.nsum[(size_t)C + c] = v; }
+            if (lane == 0) { s_sum[c] = v; if (first_owned) a.nsum[(size_t)C + c] = v; }
         }
     } else {
         for (int c = lane; c < C; c += 32) s_sum[c] = a.nsum[(size_t)n * C + c];
     }
     __syncwarp();
-
     double gain_p = 0.0;
     const double w_p = s_sum[C - 1];
     for (int k = 0; k < K; ++k) gain_p += term_gh(s_sum[k], s_sum[K + k], w_p, a.lambda, a.L2); // node_gain, split.jl:58-66
@@ -177,10 +199,10 @@ __global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
     const int b_max = numeric ? B - 1 : B;
     const size_t fo = (size_t)f * C * B;
     auto val = [&](int c, int b) -> double {
-        const size_t o = fo + (size_t)c * B + b;
-        double v = __ldg(hc + o);
-        if (sub) v = __ldg(hp + o) - v; // subtract_hist!: parent - sibling (fit-utils.jl:321-332)
-        if (keep) hn[o] = v;
+        const int o = c * B + b;
+        double v = sm[o];
+        if (sub) v = __ldg(hp + fo + o) - v;
+        if (keep) hn[fo + o] = v;
         return v;
     };
     double lg = a.gamma; // get_best_split starts at gamma and takes strict improvements (fit-utils.jl:444-450)
@@ -247,62 +269,40 @@ __global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
         }
     }
     if (lane == 0) {
-        a.fbest_gain[(size_t)i * F + f] = lg;
-        a.fbest_bin[(size_t)i * F + f] = lb == 0x7fffffff ? -1 : lb;
+        a.fbest_gain[(size_t)(n - m) * F + f] = lg;
+        a.fbest_bin[(size_t)(n - m) * F + f] = lb == 0x7fffffff ? -1 : lb;
     }
+    __syncwarp();
 }
 
-// Stage 2: one warp per node: first strict maximum over the features (ascending feature order), child sums
-// (`_child_sums!`, fit-utils.jl:472-486), tree arrays and leaf values.
-__global__ void __launch_bounds__(256) k_scan_node(ScanArgs a) {
-    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int C = a.C, K = a.K, B = a.B, F = a.F;
-    const int m = 1 << (a.level - 1);
-    const int i = blockIdx.x * (blockDim.x >> 5) + wid;
-    __shared__ double s_sum_all[8][72], s_left_all[8][72], s_right_all[8][72];
-    double *s_sum = s_sum_all[wid], *s_left = s_left_all[wid], *s_right = s_right_all[wid];
-    if (i >= m) return;
-    const int n = m + i;
-    const int kd = a.kind[n];
-    if (kd == EVB_KIND_NONE) return;
-    const size_t FCB = (size_t)F * C * B;
-    const double *hc = a.hcomp + (size_t)a.bslot[n] * FCB;
-    const bool sub = kd == EVB_KIND_SUB;
-    const double *hp = a.hist + (size_t)(n >> 1) * FCB;
-    for (int c = lane; c < C; c += 32) s_sum[c] = a.nsum[(size_t)n * C + c];
-    __syncwarp();
+// Stage 1: one warp per (node, owned feature slot), lanes over bins.  The nodes of a level come in pairs sharing a
+// build slot: the build node reads the slot's histogram, its sibling subtracts it from the parent's.  Warps are
+// independent, so even the root level (one node) spreads over many SMs.
+__global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
+    __shared__ double s_sum_all[8][72];
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    const int C = a.C, B = a.B, F = a.F;
+    const int Fown = (F - a.rank + a.world - 1) / a.world;
+    if (Fown <= 0) return;
+    long long gw = (long long)blockIdx.x * wpb + wid;
+    const int which = a.level > 1 ? (int)(gw & 1) : 0;
+    if (a.level > 1) gw >>= 1;
+    const int s = (int)(gw / Fown), fi = (int)(gw % Fown);
+    if (s >= a.plan->nbuild) return;
+    const int f = fi * a.world + a.rank;
+    const int nb = a.slot_node[s];
+    scan_one(a, which ? nb ^ 1 : nb, which != 0, f, a.hcomp + ((size_t)s * F + f) * C * B, s_sum_all[wid], lane, fi == 0);
+}
 
-    double bg = a.gamma;
-    int bs = 0x7fffffff, bb = -1;
-    for (int f = lane; f < F; f += 32) {
-        const double g = a.fbest_gain[(size_t)i * F + f];
-        const int b = a.fbest_bin[(size_t)i * F + f];
-        if (b >= 0 && g > bg) { bg = g; bs = f; bb = b; }
-    }
-#pragma unroll
-    for (int d = 16; d >= 1; d >>= 1) {
-        const double og = __shfl_xor_sync(FULL, bg, d);
-        const int os = __shfl_xor_sync(FULL, bs, d), ob = __shfl_xor_sync(FULL, bb, d);
-        if (os != 0x7fffffff && (og > bg || (og == bg && os < bs))) { bg = og; bs = os; bb = ob; }
-    }
-    if (bs != 0x7fffffff) {
-        const uint32_t feat = a.js0[bs];
+// Writes everything that follows from the split decision of node n: child sums, tree arrays, leaf values
+// (`_child_sums!` result, src/fit.jl:90-98, 120-121, 74-82, 131-135).  One warp; s_left holds the left sums.
+__device__ __forceinline__ void apply_split(const ScanArgs &a, int n, bool has, double gain, int slot, int bin, const double *s_sum,
+                                            double *s_left, double *s_right, int lane) {
+    const int C = a.C, K = a.K;
+    if (has) {
+        const uint32_t feat = a.js0[slot];
         const bool numeric = a.feattypes[feat] != 0;
-        const size_t fo = (size_t)bs * C * B;
-        for (int c = 0; c < C; ++c) {
-            double v = 0.0;
-            if (numeric) {
-                for (int b = lane; b <= bb; b += 32) {
-                    const size_t o = fo + (size_t)c * B + b;
-                    v += sub ? hp[o] - hc[o] : hc[o];
-                }
-                v = warp_sum(v);
-            } else {
-                const size_t o = fo + (size_t)c * B + bb;
-                v = sub ? hp[o] - hc[o] : hc[o];
-            }
-            if (lane == 0) { s_left[c] = v; s_right[c] = s_sum[c] - v; }
-        }
+        for (int c = lane; c < C; c += 32) s_right[c] = s_sum[c] - s_left[c];
         __syncwarp();
         const int nl = n << 1, nr = nl + 1;
         for (int c = lane; c < C; c += 32) {
@@ -311,11 +311,11 @@ __global__ void __launch_bounds__(256) k_scan_node(ScanArgs a) {
         }
         if (lane == 0) {
             a.t_w[n - 1] = (float)s_sum[C - 1];
-            a.t_gain[n - 1] = (float)bg;
-            a.t_bin[n - 1] = (uint8_t)(bb + 1);
+            a.t_gain[n - 1] = (float)gain;
+            a.t_bin[n - 1] = (uint8_t)(bin + 1);
             a.t_feat[n - 1] = (int32_t)feat + 1;
             a.t_split[n - 1] = 1;
-            a.t_packed[n - 1] = feat | ((uint32_t)(bb + 1) << 16) | (1u << 24) | ((numeric ? 1u : 0u) << 25);
+            a.t_packed[n - 1] = feat | ((uint32_t)(bin + 1) << 16) | (1u << 24) | ((numeric ? 1u : 0u) << 25);
         }
         if (a.level + 1 == a.D) {
             // children sit at max depth: they are leaves (src/fit.jl:74-82)
@@ -329,6 +329,132 @@ __global__ void __launch_bounds__(256) k_scan_node(ScanArgs a) {
         if (lane == 0) a.t_w[n - 1] = (float)s_sum[C - 1];
         for (int k = lane; k < K; k += 32) a.t_pred[(size_t)(n - 1) * K + k] = leaf_value(a, s_sum, k);
     }
+}
+
+// Stage 2: one warp per node: first strict maximum over the (owned) features in ascending feature order and the
+// left-child sums of the winner (`_child_sums!`, fit-utils.jl:472-486).  Single GPU: the split is applied at once.
+// Sharded with peer access: the rank's candidate is written into every rank's candidate table instead.
+__global__ void __launch_bounds__(256) k_scan_node(ScanArgs a) {
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int C = a.C, B = a.B, F = a.F;
+    const int m = 1 << (a.level - 1);
+    const int i = blockIdx.x * (blockDim.x >> 5) + wid;
+    __shared__ double s_sum_all[8][72], s_left_all[8][72], s_right_all[8][72];
+    double *s_sum = s_sum_all[wid], *s_left = s_left_all[wid], *s_right = s_right_all[wid];
+    if (i >= m) return;
+    const int n = m + i;
+    const int kd = a.kind[n];
+    if (kd == EVB_KIND_NONE) return;
+    const size_t FCB = (size_t)F * C * B;
+    const double *hc = a.hcomp + (size_t)a.bslot[n] * FCB;
+    const bool sub = kd == EVB_KIND_SUB;
+    const double *hp = a.hist + (size_t)(n >> 1) * FCB;
+    const double *hn = a.hist + (size_t)n * FCB;
+    for (int c = lane; c < C; c += 32) s_sum[c] = a.nsum[(size_t)n * C + c];
+    __syncwarp();
+
+    double bg = a.gamma;
+    int bs = 0x7fffffff, bb = -1;
+    const int Fown = (F - a.rank + a.world - 1) / a.world;
+    for (int fi = lane; fi < Fown; fi += 32) {
+        const int f = fi * a.world + a.rank;
+        const double g = a.fbest_gain[(size_t)i * F + f];
+        const int b = a.fbest_bin[(size_t)i * F + f];
+        if (b >= 0 && g > bg) { bg = g; bs = f; bb = b; }
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+        const double og = __shfl_xor_sync(FULL, bg, d);
+        const int os = __shfl_xor_sync(FULL, bs, d), ob = __shfl_xor_sync(FULL, bb, d);
+        if (os != 0x7fffffff && (og > bg || (og == bg && os < bs))) { bg = og; bs = os; bb = ob; }
+    }
+    const bool has = bs != 0x7fffffff;
+    if (has) {
+        const bool numeric = a.feattypes[a.js0[bs]] != 0;
+        const size_t fo = (size_t)bs * C * B;
+        for (int c = 0; c < C; ++c) {
+            double v = 0.0;
+            const int b0 = numeric ? lane : bb, b1 = bb;
+            for (int b = b0; b <= b1; b += 32) {
+                const size_t o = fo + (size_t)c * B + b;
+                // sharded: the summed histogram of every scanned node is retained locally for the owned features
+                v += a.world > 1 ? hn[o] : (sub ? hp[o] - hc[o] : hc[o]);
+                if (!numeric) break;
+            }
+            if (numeric) v = warp_sum(v);
+            if (lane == 0) s_left[c] = v;
+        }
+        __syncwarp();
+    }
+    if (a.world == 1) {
+        apply_split(a, n, has, bg, bs, bb, s_sum, s_left, s_right, lane);
+        return;
+    }
+    const int RC = 3 + C;
+    for (int q = 0; q < a.world; ++q) {
+        double *rec = a.peer_cand[q] + ((size_t)i * a.world + a.rank) * RC;
+        if (lane == 0) { rec[0] = bg; rec[1] = has ? (double)bs : -1.0; rec[2] = (double)bb; }
+        if (has) for (int c = lane; c < C; c += 32) rec[3 + c] = s_left[c];
+    }
+}
+
+// Stage 3 (sharded with peer access only): every rank picks, for every node, the best of the ranks' candidates
+// (ties: lowest feature slot, as in the single-GPU order) and applies it.  All ranks read identical tables.
+__global__ void __launch_bounds__(256) k_scan_final(ScanArgs a) {
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int C = a.C;
+    const int m = 1 << (a.level - 1);
+    const int i = blockIdx.x * (blockDim.x >> 5) + wid;
+    __shared__ double s_sum_all[8][72], s_left_all[8][72], s_right_all[8][72];
+    double *s_sum = s_sum_all[wid], *s_left = s_left_all[wid], *s_right = s_right_all[wid];
+    if (i >= m) return;
+    const int n = m + i;
+    if (a.kind[n] == EVB_KIND_NONE) return;
+    for (int c = lane; c < C; c += 32) s_sum[c] = a.nsum[(size_t)n * C + c];
+    const int RC = 3 + C;
+    double bg = a.gamma;
+    int bs = 0x7fffffff, bb = -1, bq = -1;
+    if (lane < a.world) {
+        const double *rec = a.cand_local + ((size_t)i * a.world + lane) * RC;
+        const double g = __ldcv(rec), sl = __ldcv(rec + 1), bn = __ldcv(rec + 2);
+        if (sl >= 0.0 && g > bg) { bg = g; bs = (int)sl; bb = (int)bn; bq = lane; }
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+        const double og = __shfl_xor_sync(FULL, bg, d);
+        const int os = __shfl_xor_sync(FULL, bs, d), ob = __shfl_xor_sync(FULL, bb, d), oq = __shfl_xor_sync(FULL, bq, d);
+        if (os != 0x7fffffff && (og > bg || (og == bg && os < bs))) { bg = og; bs = os; bb = ob; bq = oq; }
+    }
+    const bool has = bs != 0x7fffffff;
+    if (has) {
+        const double *rec = a.cand_local + ((size_t)i * a.world + bq) * RC;
+        for (int c = lane; c < C; c += 32) s_left[c] = __ldcv(rec + 3 + c);
+    }
+    __syncwarp();
+    apply_split(a, n, has, bg, bs, bb, s_sum, s_left, s_right, lane);
+}
+
+// Cross-GPU barrier for the peer-access path: every rank writes the sequence number into its slot of every
+// rank's flag array and waits (bounded, ~2 s) until all slots of its own array have reached it.
+struct BarrierArgs {
+    int *peer_flags[EVB_MAX_PEERS];
+    int *flags_local;
+    int *err;
+    int world, rank, seq;
+};
+__global__ void k_peer_barrier(BarrierArgs a) {
+    const int t = threadIdx.x;
+    if (t >= a.world) return;
+    __threadfence_system();
+    *(volatile int *)(a.peer_flags[t] + a.rank) = a.seq;
+    __threadfence_system();
+    volatile int *mine = a.flags_local + t;
+    for (unsigned it = 0; it < 20000000u; ++it) {
+        if (*mine - a.seq >= 0) { __threadfence_system(); return; }
+        if ((it & 1023u) == 1023u && *(volatile int *)a.err != 0) return;
+        __nanosleep(100);
+    }
+    atomicCAS(a.err, 0, EVB_DERR_PEER);
 }
 
 // ------------------------------------------------------------------------------------------ partition
@@ -572,6 +698,15 @@ int32_t evb_launch_root_plan(evb_handle *h) {
     return EVB_OK;
 }
 
+static int32_t launch_peer_barrier(evb_handle *h) {
+    BarrierArgs b;
+    for (int q = 0; q < EVB_MAX_PEERS; ++q) b.peer_flags[q] = q < h->world ? h->peer_flags[q] : nullptr;
+    b.flags_local = h->peer_flags[h->rank]; b.err = h->d_err; b.world = h->world; b.rank = h->rank; b.seq = ++h->barrier_seq;
+    k_peer_barrier<<<1, 32, 0, h->st>>>(b);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
 int32_t evb_launch_scan(evb_handle *h, int level) {
     ScanArgs a;
     a.hcomp = h->hcomp; a.hist = h->hist; a.nsum = h->nsum; a.kind = h->kind; a.bslot = h->bslot; a.js0 = h->js_d;
@@ -581,14 +716,39 @@ int32_t evb_launch_scan(evb_handle *h, int level) {
     a.loss = h->p.loss; a.neb = -h->p.eta / (double)h->p.bagging_size;
     a.lambda = h->p.lambda; a.L2 = h->p.L2; a.gamma = h->p.gamma; a.min_weight = h->p.min_weight;
     a.fbest_gain = h->fbest_gain; a.fbest_bin = h->fbest_bin;
+    a.plan = h->plan + level; a.slot_node = h->slot_node;
+    const bool p2p = h->p2p && h->world > 1;
+    a.world = p2p ? h->world : 1; a.rank = p2p ? h->rank : 0;
+    for (int q = 0; q < EVB_MAX_PEERS; ++q) a.peer_cand[q] = p2p && q < h->world ? h->peer_cand[q] : nullptr;
+    a.cand_local = p2p ? h->peer_cand[h->rank] : nullptr;
     const int m = evb_level_nodes(level);
-    const long long warps = (long long)m * h->F;
+    const int slots = evb_level_slots(level);
+    const int Fown = (h->F - a.rank + a.world - 1) / a.world;
+    if (p2p) {
+        // all ranks' histograms of this level are complete -> sum the owned feature slots from the peers' memory
+        evb_tic(h, EVB_T_ALLREDUCE);
+        int32_t rc = launch_peer_barrier(h);
+        PeerReduceArgs r;
+        for (int q = 0; q < EVB_MAX_PEERS; ++q) r.peer_hcomp[q] = q < h->world ? h->peer_hcomp[q] : nullptr;
+        r.hsum = h->hsum; r.plan = h->plan + level; r.world = h->world; r.rank = h->rank; r.F = h->F; r.CB = h->C * h->B; r.level = level;
+        if (rc == EVB_OK) k_peer_reduce<<<slots * (Fown + 1), 256, 0, h->st>>>(r);
+        evb_toc(h, EVB_T_ALLREDUCE);
+        EVB_CHECK(rc);
+        a.hcomp = h->hsum;
+    }
+    const long long warps = (long long)slots * Fown * (level > 1 ? 2 : 1);
     evb_tic(h, EVB_T_SCAN);
-    k_scan_feat<<<(unsigned)((warps + 7) / 8), 256, 0, h->st>>>(a);
+    if (warps > 0) k_scan_feat<<<(unsigned)((warps + 7) / 8), 256, 0, h->st>>>(a);
     evb_toc(h, EVB_T_SCAN);
     evb_tic(h, EVB_T_SCAN);
     k_scan_node<<<(m + 7) / 8, 256, 0, h->st>>>(a);
     evb_toc(h, EVB_T_SCAN);
+    if (p2p) {
+        evb_tic(h, EVB_T_ALLREDUCE); int32_t rc = launch_peer_barrier(h); evb_toc(h, EVB_T_ALLREDUCE); EVB_CHECK(rc);
+        evb_tic(h, EVB_T_SCAN);
+        k_scan_final<<<(m + 7) / 8, 256, 0, h->st>>>(a);
+        evb_toc(h, EVB_T_SCAN);
+    }
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
 }

@@ -28,6 +28,8 @@ class Comm:
         self.rank = dist.get_rank()
         self.world = dist.get_world_size()
         self.device = device  # torch device for collectives (None = CPU tensors, gloo)
+        import os
+        self.p2p = os.environ.get("EVB_P2P", "1") != "0"
 
     def _tensor(self, a: np.ndarray):
         import torch
@@ -38,6 +40,14 @@ class Comm:
         t = self._tensor(a)
         self.dist.broadcast(t, src=src)
         return t.cpu().numpy()
+
+    def allgather_host(self, a: np.ndarray) -> np.ndarray:
+        """[world, *a.shape] with rank q's array in row q."""
+        import torch
+        t = self._tensor(a)
+        out = [torch.empty_like(t) for _ in range(self.world)]
+        self.dist.all_gather(out, t)
+        return np.stack([o.cpu().numpy() for o in out])
 
     def allreduce_sum(self, a: np.ndarray) -> np.ndarray:
         t = self._tensor(np.asarray(a, np.float64))
@@ -76,3 +86,10 @@ class Comm:
             _lib.check(_lib.lib().evb_comm_unique_id(_lib.ptr(ident)))
         ident = self.broadcast_host(ident)
         _lib.check(_lib.lib().evb_comm_init(cache.handle, _lib.ptr(ident), C.c_int32(self.rank), C.c_int32(self.world)))
+        if self.p2p and 2 <= self.world <= 8:
+            # peer access: exchange the CUDA IPC handles so that the split scan can read the other ranks' histograms
+            blob = np.zeros(256, np.uint8)
+            _lib.check(_lib.lib().evb_comm_ipc_export(cache.handle, _lib.ptr(blob)))
+            blobs = np.ascontiguousarray(self.allgather_host(blob))
+            _lib.check(_lib.lib().evb_comm_ipc_import(cache.handle, _lib.ptr(blobs)))
+            self.dist.barrier()

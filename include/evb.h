@@ -110,6 +110,16 @@ EVB_API void evb_destroy(evb_handle *h);
  */
 EVB_API int32_t evb_comm_unique_id(uint8_t id[128]);
 EVB_API int32_t evb_comm_init(evb_handle *h, const uint8_t id[128], int32_t rank, int32_t world);
+/*
+ * Optional second step for ranks that are separate processes on one NVLink / NVSwitch node (2..8 ranks): every
+ * rank exports a 256-byte blob (CUDA IPC handles of its per-level histogram buffer, candidate table and barrier
+ * flags), the host gathers the blobs of all ranks in rank order, every rank imports them.  From then on the NCCL
+ * all-reduce per level is replaced by peer loads inside the split scan: rank r scans the feature slots
+ * f % world == r, summing the ranks' histograms straight from their memory in rank order, and writes its best
+ * candidate per node into every rank's table; bounded flag barriers separate the phases.
+ */
+EVB_API int32_t evb_comm_ipc_export(evb_handle *h, uint8_t blob[256]);
+EVB_API int32_t evb_comm_ipc_import(evb_handle *h, const uint8_t *blobs /* world x 256 bytes */);
 
 /*
  * evb_grow_tree -- replaces one bag iteration of `grow_evotree!(m, cache::CacheGPU, params)`
