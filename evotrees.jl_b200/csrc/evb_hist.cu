@@ -476,6 +476,61 @@ __global__ void __launch_bounds__(512) k_hist_reduce(ReduceArgs a) {
     }
 }
 
+// Variant for levels with many build slots (each with few pieces): one CTA per (build slot, unit, feature slot
+// of the lane) sums all channels and bins of that sub-image, so that deep levels launch a thousand CTAs with real
+// work each instead of many thousands of tiny ones.  Same fixed summation order as k_hist_reduce.
+__global__ void __launch_bounds__(256) k_hist_reduce_unit(ReduceArgs a) {
+    __shared__ double tile[64][33];
+    const int s = blockIdx.x, u = blockIdx.y / a.FPL, j = blockIdx.y % a.FPL;
+    const int ug = u / a.UB, uw = u % a.UB, ct = u / a.NFG, fg = u % a.NFG;
+    const int nch = min(a.NCH, a.Ce - ct * a.NCH);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int nbuild = a.plan->nbuild;
+    const long long R = a.plan->R;
+    int bfirst = 0, blast = -1;
+    if (s < nbuild && R > 0) {
+        const long long c0 = a.cum[s], c1 = a.cum[s + 1];
+        if (c1 > c0) {
+            bfirst = (int)(((c0 + 1) * a.G - 1) / R);
+            blast = (int)((c1 * a.G - 1) / R);
+        }
+    }
+    const bool all_exist = R >= a.G;
+    const size_t bstride = (size_t)a.UB * a.img_floats;
+    const float *src0 = a.scratch + ((size_t)(ug * a.PG + s) * a.UB + uw) * a.img_floats + lane;
+    for (int c = 0; c < nch; ++c) {
+        for (int bin0 = 0; bin0 < a.nbins; bin0 += 64) {
+            for (int bl = w; bl < 64; bl += 8) {
+                const int bin = bin0 + bl;
+                double acc = 0.0;
+                if (bin < a.nbins) {
+                    const float *src = src0 + ((j * a.NCH + c) * a.nbins + bin) * 32;
+                    for (int b = bfirst; b <= blast; ++b)
+                        if (all_exist || R * b / a.G < R * (b + 1) / a.G) acc += (double)src[(size_t)b * bstride];
+                }
+                tile[bl][lane] = acc;
+            }
+            __syncthreads();
+            for (int e = threadIdx.x; e < 64 * 32; e += 256) {
+                const int fl = e >> 6, bl = e & 63;
+                const int slotf = (fg * 32 + fl) * a.FPL + j, binw = bin0 + bl;
+                if (slotf < a.F && binw < a.nbins) {
+                    double *dst = a.hcomp + ((size_t)s * a.F + slotf) * a.C * a.nbins + binw;
+                    const int ce = ct * a.NCH + c;
+                    const double v = tile[bl][fl];
+                    if (a.Ce == a.C || ce < a.K) {
+                        dst[(size_t)ce * a.nbins] = v;
+                    } else { // mse with elided hessians: w, and h_k = 2w
+                        dst[(size_t)(2 * a.K) * a.nbins] = v;
+                        for (int k = 0; k < a.K; ++k) dst[(size_t)(a.K + k) * a.nbins] = 2.0 * v;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
 template <int BP, int NCH, int FPL>
 cudaError_t launch_hist_t(const HistArgs &a, dim3 grid, int threads, size_t smem, cudaStream_t st) {
     static bool attr_set[64] = {};
@@ -628,12 +683,18 @@ int32_t evb_launch_hist_reduce(evb_handle *h, int level) {
     a.img_floats = (uint32_t)g.img_floats;
     const int slots = evb_level_slots(level);
     evb_tic(h, EVB_T_HIST_REDUCE);
-    if (slots <= 4) {
+    if (slots <= 2) {           // top of the tree: hundreds of pieces per slot -> 16 piece groups per CTA
+        dim3 grid(slots, g.U * g.FPL * g.NCH, h->B);
+        k_hist_reduce<1><<<grid, 512, 0, h->st>>>(a);
+    } else if (slots <= 8) {
         dim3 grid(slots, g.U * g.FPL * g.NCH, (h->B + 3) / 4);
         k_hist_reduce<4><<<grid, 512, 0, h->st>>>(a);
-    } else {
+    } else if (slots <= 32) {
         dim3 grid(slots, g.U * g.FPL * g.NCH, (h->B + 15) / 16);
         k_hist_reduce<16><<<grid, 512, 0, h->st>>>(a);
+    } else {                    // deep levels: few pieces per slot -> one CTA per sub-image
+        dim3 grid(slots, g.U * g.FPL);
+        k_hist_reduce_unit<<<grid, 256, 0, h->st>>>(a);
     }
     evb_toc(h, EVB_T_HIST_REDUCE);
     EVB_CUDA(cudaGetLastError());

@@ -547,31 +547,55 @@ __global__ void __launch_bounds__(EVB_PART_THREADS) k_part_flags(PartArgs a) {
     }
 }
 
-// warp per node: exclusive prefix of the left counts of the node's items, and the node's left total
-__global__ void k_part_prefix(PartArgs a) {
+// Exclusive prefix of the left counts of every split node's work items and the node's left total.  Runs inside the
+// single-CTA plan kernel: levels with few nodes (many items per node) scan each node with the whole CTA, deeper
+// levels give every node to one warp.
+__device__ void part_prefix(const PartArgs &a, int *sm) {
     const int lo = 1 << (a.level - 1), m = lo;
-    const int lane = threadIdx.x & 31;
-    const int wglobal = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
-    for (int i = wglobal; i < m; i += nwarps) {
-        const int n = lo + i;
-        int running = 0;
-        if (a.t_split[n - 1]) {
-            const int j0 = a.ibase[i], j1 = a.ibase[i + 1];
-            for (int j = j0; j < j1; j += 32) {
-                const int v = (j + lane < j1) ? a.item_left[j + lane] : 0;
-                const int incl = warp_incl_scan_i(v, lane);
-                if (j + lane < j1) a.item_lprefix[j + lane] = running + incl - v;
-                running += __shfl_sync(FULL, incl, 31);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (m <= 16) {
+        for (int i = 0; i < m; ++i) {
+            const int n = lo + i;
+            int running = 0;
+            if (a.t_split[n - 1]) {
+                const int j0 = a.ibase[i], j1 = a.ibase[i + 1];
+                for (int j = j0; j < j1; j += blockDim.x) {
+                    const int idx = j + threadIdx.x;
+                    const int v = idx < j1 ? a.item_left[idx] : 0;
+                    int total;
+                    const int ex = block_excl_scan(v, sm, &total);
+                    if (idx < j1) a.item_lprefix[idx] = running + ex;
+                    running += total;
+                    __syncthreads();
+                }
             }
+            if (threadIdx.x == 0) a.nleft[n] = running;
         }
-        if (lane == 0) a.nleft[n] = running;
+    } else {
+        for (int i = wid; i < m; i += nw) {
+            const int n = lo + i;
+            int running = 0;
+            if (a.t_split[n - 1]) {
+                const int j0 = a.ibase[i], j1 = a.ibase[i + 1];
+                for (int j = j0; j < j1; j += 32) {
+                    const int v = (j + lane < j1) ? a.item_left[j + lane] : 0;
+                    const int incl = warp_incl_scan_i(v, lane);
+                    if (j + lane < j1) a.item_lprefix[j + lane] = running + incl - v;
+                    running += __shfl_sync(FULL, incl, 31);
+                }
+            }
+            if (lane == 0) a.nleft[n] = running;
+        }
     }
+    __threadfence_block();
+    __syncthreads();
 }
 
 // children segments / counts, build-or-subtract choice (src/fit.jl:123-129: the child with fewer rows is
 // built, ties build the left child), build slots and the histogram plan of the next level
 __global__ void __launch_bounds__(1024) k_level_plan(PartArgs a) {
     __shared__ int sm[33];
+    part_prefix(a, sm);
     const int lo = 1 << (a.level - 1), m = lo;
     const bool scan_children = a.level + 1 < a.D;
     int carry_slot = 0, carry_rows = 0;
@@ -765,12 +789,6 @@ int32_t evb_launch_partition(evb_handle *h, int level) {
     evb_tic(h, EVB_T_PARTITION);
     k_part_flags<<<pgrid, EVB_PART_THREADS, 0, h->st>>>(a);
     evb_toc(h, EVB_T_PARTITION);
-    evb_tic(h, EVB_T_PLAN);
-    int wblocks = (m * 32 + 255) / 256;
-    if (wblocks > h->num_sms * 4) wblocks = h->num_sms * 4;
-    k_part_prefix<<<wblocks, 256, 0, h->st>>>(a);
-    evb_toc(h, EVB_T_PLAN);
-    EVB_CUDA(cudaGetLastError());
     evb_tic(h, EVB_T_PLAN);
     k_level_plan<<<1, 1024, 0, h->st>>>(a);
     evb_toc(h, EVB_T_PLAN);

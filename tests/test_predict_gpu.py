@@ -75,3 +75,32 @@ def test_training_predictions_equal_inference(pkg):
     finally:
         cache.close()
     assert np.mean((pkg.predict(m, x) - y) ** 2) < 0.5 * np.var(y)
+
+
+def test_pipelined_rounds_equal_sequential_rounds(pkg):
+    """`grow_rounds` (host one tree ahead, per-tree CUDA graph replay) grows exactly the trees that one
+    `grow_evotree` call per round grows."""
+    x, y = make_regression(40_000, 15, seed=13)
+    params = pkg.EvoTreeRegressor(nrounds=8, max_depth=6, nbins=32, eta=0.2, rowsample=0.8, colsample=0.8)
+    m1, c1 = pkg.init_core(params, x, y)
+    m2, c2 = pkg.init_core(params, x, y)
+    try:
+        pkg.grow_rounds(m1, c1, params, 8)
+        for _ in range(8):
+            pkg.grow_evotree(m2, c2, params)
+        assert len(m1.trees) == len(m2.trees) == 9
+        for t1, t2 in zip(m1.trees, m2.trees):
+            assert np.array_equal(t1.feat, t2.feat) and np.array_equal(t1.cond_bin, t2.cond_bin)
+            assert np.array_equal(t1.pred, t2.pred) and np.array_equal(t1.gain, t2.gain)
+        assert np.array_equal(c1.pred(), c2.pred())
+        # a third tree cannot be started while two are in flight
+        mask, js = pkg.sample_round(c1, params)
+        pkg.grow_tree_begin(c1, params, mask, js, True)
+        pkg.grow_tree_begin(c1, params, mask, js, True)
+        with pytest.raises(pkg.EvbError):
+            pkg.grow_tree_begin(c1, params, mask, js, True)
+        pkg.grow_tree_end(c1, params)
+        pkg.grow_tree_end(c1, params)
+    finally:
+        c1.close()
+        c2.close()
