@@ -168,6 +168,7 @@ __global__ void __launch_bounds__(256) k_peer_reduce(PeerReduceArgs a) {
 // Scan of one (node, feature): applies the sibling subtraction (`subtract_hist!`, fit-utils.jl:321-332) to the
 // staged histogram `sm` of the build node, stores the node's histogram if its children will need it, scans the
 // bins (`_scan_node!`, fit-utils.jl:403-436) and records the best split of this feature.
+template <int MAXCHK>
 __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int f, const double *sm, double *s_sum, int lane, bool first_owned) {
     const int C = a.C, K = a.K, B = a.B, F = a.F;
     const int m = 1 << (a.level - 1);
@@ -208,12 +209,12 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
     double lg = a.gamma; // get_best_split starts at gamma and takes strict improvements (fit-utils.jl:444-450)
     int lb = 0x7fffffff;
     if (a.level < a.D) {
-        double wl[8], gacc[8];
+        double wl[MAXCHK], gacc[MAXCHK];
         unsigned okmask = 0xffu;
         {
             double carry = 0.0;
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
+            for (int ch = 0; ch < MAXCHK; ++ch) {
                 gacc[ch] = 0.0;
                 wl[ch] = 0.0;
                 if (ch < nchk) {
@@ -228,7 +229,7 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
             double cg = 0.0, chh = 0.0;
             const double sg = s_sum[k], sh = s_sum[K + k];
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
+            for (int ch = 0; ch < MAXCHK; ++ch) {
                 if (ch < nchk) {
                     const int b = ch * 32 + lane;
                     double gl = b < B ? val(k, b) : 0.0;
@@ -251,7 +252,7 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
         }
         // candidate of this lane: lowest bin among its strict maxima
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
+        for (int ch = 0; ch < MAXCHK; ++ch) {
             if (ch < nchk) {
                 const int b = ch * 32 + lane;
                 const double w_l = wl[ch], w_r = w_p - w_l;
@@ -278,6 +279,7 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
 // Stage 1: one warp per (node, owned feature slot), lanes over bins.  The nodes of a level come in pairs sharing a
 // build slot: the build node reads the slot's histogram, its sibling subtracts it from the parent's.  Warps are
 // independent, so even the root level (one node) spreads over many SMs.
+template <int MAXCHK>
 __global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
     __shared__ double s_sum_all[8][72];
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
@@ -291,7 +293,8 @@ __global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
     if (s >= a.plan->nbuild) return;
     const int f = fi * a.world + a.rank;
     const int nb = a.slot_node[s];
-    scan_one(a, which ? nb ^ 1 : nb, which != 0, f, a.hcomp + ((size_t)s * F + f) * C * B, s_sum_all[wid], lane, fi == 0);
+    const double *src = a.hcomp + ((size_t)s * F + f) * C * B;
+    scan_one<MAXCHK>(a, which ? nb ^ 1 : nb, which != 0, f, src, s_sum_all[wid], lane, fi == 0);
 }
 
 // Writes everything that follows from the split decision of node n: child sums, tree arrays, leaf values
@@ -553,7 +556,7 @@ __global__ void __launch_bounds__(EVB_PART_THREADS) k_part_flags(PartArgs a) {
 __device__ void part_prefix(const PartArgs &a, int *sm) {
     const int lo = 1 << (a.level - 1), m = lo;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    if (m <= 16) {
+    if (m <= 2) {
         for (int i = 0; i < m; ++i) {
             const int n = lo + i;
             int running = 0;
@@ -762,7 +765,10 @@ int32_t evb_launch_scan(evb_handle *h, int level) {
     }
     const long long warps = (long long)slots * Fown * (level > 1 ? 2 : 1);
     evb_tic(h, EVB_T_SCAN);
-    if (warps > 0) k_scan_feat<<<(unsigned)((warps + 7) / 8), 256, 0, h->st>>>(a);
+    if (warps > 0) {
+        if (h->B <= 64) k_scan_feat<2><<<(unsigned)((warps + 7) / 8), 256, 0, h->st>>>(a);
+        else k_scan_feat<8><<<(unsigned)((warps + 7) / 8), 256, 0, h->st>>>(a);
+    }
     evb_toc(h, EVB_T_SCAN);
     evb_tic(h, EVB_T_SCAN);
     k_scan_node<<<(m + 7) / 8, 256, 0, h->st>>>(a);
