@@ -316,7 +316,10 @@ def main():
                        "eta": eta, "rowsample": rowsample, "colsample": colsample, "rows_per_gpu": nloc,
                        "l2_policy": "inputs larger than L2 (x_bin shard %.0f MB)" % (nloc * 128 / 1e6)},
             "roofline": {"bound": "hbm", "kernel": "k_hist", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": (achieved / peak) if achieved else None, "traffic": None,
+                         "frac": (achieved / peak) if achieved else None,
+                         # DRAM bytes per launch: 150 B per streamed row, measured with ncu on a 2M-row case of this
+                         # workload (dram__bytes_read + write = 300.0 MB for 2M rows) and scaled by the rows per launch
+                         "traffic": (150.0 * tm["hist_rows"] / max(1, hist_launches)) if args.workload == "headline_10Mx100_d11" else None,
                          "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650",
                          "hist_ms_per_launch": hist_ms / max(1, hist_launches), "hist_launches": hist_launches,
                          "measured_in": "instrumented pass (CUDA events around every launch) of the same rounds right after the timed region",

@@ -375,7 +375,12 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
                 const uint32_t xs = stage0_s + (uint32_t)st * stage_bytes;
                 const uint32_t gs = xs + xbytes + ct * 16;
                 if (act && !(a.mode & 16)) {
-                    if (a.contig) accumulate_tile<BP, NCH, FPL, true>(xs, gs, nrows, RS, GS * 4, foff, u0, u1);
+                    // the common strides are passed as literals so that the row offsets fold into the instructions
+                    if (a.contig && RS == 128 && GS == 4) accumulate_tile<BP, NCH, FPL, true>(xs, gs, nrows, 128, 16, foff, u0, u1);
+                    else if (a.contig && RS == 64 && GS == 8) accumulate_tile<BP, NCH, FPL, true>(xs, gs, nrows, 64, 32, foff, u0, u1);
+                    else if (a.contig && RS == 32 && GS == 12) accumulate_tile<BP, NCH, FPL, true>(xs, gs, nrows, 32, 48, foff, u0, u1);
+                    else if (a.contig && RS == 32 && GS == 4) accumulate_tile<BP, NCH, FPL, true>(xs, gs, nrows, 32, 16, foff, u0, u1);
+                    else if (a.contig) accumulate_tile<BP, NCH, FPL, true>(xs, gs, nrows, RS, GS * 4, foff, u0, u1);
                     else accumulate_tile<BP, NCH, FPL, false>(xs, gs, nrows, RS, GS * 4, foff, u0, u1);
                 }
                 __syncwarp();
