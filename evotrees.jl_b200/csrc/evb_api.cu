@@ -496,7 +496,8 @@ extern "C" int32_t evb_comm_ipc_export(evb_handle *h, uint8_t blob[256]) {
 
 extern "C" int32_t evb_comm_ipc_import(evb_handle *h, const uint8_t *blobs) {
     EVB_ENTER(h);
-    if (!blobs || !h->peer_cand[h->rank]) { evb_set_error("evb_comm_ipc_import: call evb_comm_ipc_export first"); return EVB_ERR_ARG; }
+    if (!blobs) { h->p2p = false; return EVB_OK; } // the ranks agreed not to use peer access: stay on the NCCL path
+    if (!h->peer_cand[h->rank]) { evb_set_error("evb_comm_ipc_import: call evb_comm_ipc_export first"); return EVB_ERR_ARG; }
     for (int q = 0; q < h->world; ++q) {
         if (q == h->rank) continue;
         IpcBlob b;

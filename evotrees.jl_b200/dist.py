@@ -87,9 +87,20 @@ class Comm:
         ident = self.broadcast_host(ident)
         _lib.check(_lib.lib().evb_comm_init(cache.handle, _lib.ptr(ident), C.c_int32(self.rank), C.c_int32(self.world)))
         if self.p2p and 2 <= self.world <= 8:
-            # peer access: exchange the CUDA IPC handles so that the split scan can read the other ranks' histograms
+            # peer access: exchange the CUDA IPC handles so that the split scan can read the other ranks' histograms;
+            # it is used only if every rank could map every other rank, otherwise all ranks stay on NCCL
             blob = np.zeros(256, np.uint8)
-            _lib.check(_lib.lib().evb_comm_ipc_export(cache.handle, _lib.ptr(blob)))
+            ok = 1.0
+            try:
+                _lib.check(_lib.lib().evb_comm_ipc_export(cache.handle, _lib.ptr(blob)))
+            except _lib.EvbError:
+                ok = 0.0
             blobs = np.ascontiguousarray(self.allgather_host(blob))
-            _lib.check(_lib.lib().evb_comm_ipc_import(cache.handle, _lib.ptr(blobs)))
+            if ok:
+                try:
+                    _lib.check(_lib.lib().evb_comm_ipc_import(cache.handle, _lib.ptr(blobs)))
+                except _lib.EvbError:
+                    ok = 0.0
+            if self.allreduce_sum(np.array([ok]))[0] < self.world:
+                _lib.check(_lib.lib().evb_comm_ipc_import(cache.handle, None))
             self.dist.barrier()

@@ -119,7 +119,7 @@ EVB_API int32_t evb_comm_init(evb_handle *h, const uint8_t id[128], int32_t rank
  * candidate per node into every rank's table; bounded flag barriers separate the phases.
  */
 EVB_API int32_t evb_comm_ipc_export(evb_handle *h, uint8_t blob[256]);
-EVB_API int32_t evb_comm_ipc_import(evb_handle *h, const uint8_t *blobs /* world x 256 bytes */);
+EVB_API int32_t evb_comm_ipc_import(evb_handle *h, const uint8_t *blobs /* world x 256 bytes; NULL = do not use peer access */);
 
 /*
  * evb_grow_tree -- replaces one bag iteration of `grow_evotree!(m, cache::CacheGPU, params)`
