@@ -131,3 +131,32 @@ def test_bad_bins_rejected(pkg):
     p = pkg.EvoTreeRegressor(nrounds=1, max_depth=3, nbins=8)
     with pytest.raises(pkg.EvbError, match="outside 1..nbins"):
         pkg.init_core_binned(p, x_bin, np.zeros(100, np.float32), 1, 1, np.zeros(1, np.float32))
+
+
+def test_multi_target_mse(pkg, orc):
+    """Matrix target (K = 3): for mse only g_1..g_K and w are accumulated, the hessians are rebuilt from w."""
+    x, y = make_regression(30_000, 11, seed=61)
+    rng = np.random.default_rng(2)
+    Y = np.stack([y, -0.5 * y + 0.1 * rng.normal(size=y.size), np.sin(3 * x[:, 0])], axis=1).astype(np.float32)
+    p = pkg.EvoTreeRegressor(nrounds=3, max_depth=5, nbins=32, eta=0.3)
+    s = lockstep_check(pkg, orc, p, x, Y, rounds=3)
+    assert s["splits"] > 30, s
+
+
+def test_multi_target_logloss(pkg, orc):
+    """K = 2 logistic targets: five channels in two channel groups."""
+    x, y = make_regression(30_000, 40, seed=62)
+    Y = np.stack([(y > np.median(y)), (x[:, 1] + x[:, 2] > 1.0)], axis=1).astype(np.float32)
+    p = pkg.EvoTreeRegressor(loss="logloss", nrounds=3, max_depth=5, nbins=64, eta=0.3)
+    lockstep_check(pkg, orc, p, x, Y, rounds=3)
+
+
+def test_softmax_many_classes(pkg, orc):
+    """12 classes: 25 channels in seven channel groups, several unit groups per CTA."""
+    rng = np.random.default_rng(63)
+    n, f, k = 40_000, 20, 12
+    x = rng.normal(size=(n, f)).astype(np.float32)
+    y = (x @ rng.normal(size=(f, k)) + rng.gumbel(size=(n, k))).argmax(axis=1).astype(np.int64)
+    p = pkg.EvoTreeClassifier(nrounds=2, max_depth=5, nbins=32, eta=0.3)
+    s = lockstep_check(pkg, orc, p, x, y, rounds=2)
+    assert s["splits"] > 20, s
