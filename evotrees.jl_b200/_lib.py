@@ -15,13 +15,14 @@ LIB_PATH = os.path.join(HERE, "libevotrees_b200.so")
 
 EVB_F32, EVB_U32, EVB_F64 = 0, 1, 2
 LOSS_CODES = {"mse": 0, "logloss": 1, "mlogloss": 2, "gaussian_mle": 3}
+METRIC_CODES = {"mse": 0, "rmse": 0, "mae": 1, "logloss": 2, "mlogloss": 3, "gaussian_mle": 4}  # rmse = sqrt of the mse sums
 FLAG_TIMING, FLAG_FULL_PARTITION, FLAG_KEEP_ALL_HIST = 1, 2, 4
 NTIMERS = 12
 TIMER_NAMES = ["grads", "rows_init", "hist", "hist_reduce", "allreduce", "scan", "partition", "plan", "finalize",
                "d2h", "h2d", "tree_total"]
 
 EXPORTS = ["evb_last_error", "evb_version", "evb_create", "evb_destroy", "evb_comm_unique_id", "evb_comm_init", "evb_comm_ipc_export", "evb_comm_ipc_import",
-           "evb_grow_tree", "evb_grow_tree_begin", "evb_grow_tree_end", "evb_set_timing", "evb_get_pred", "evb_get_grads", "evb_get_nidx", "evb_get_hist", "evb_get_node_sums",
+           "evb_grow_tree", "evb_grow_tree_begin", "evb_grow_tree_end", "evb_eval_attach", "evb_eval_sums", "evb_eval_get_pred", "evb_eval_detach", "evb_set_timing", "evb_get_pred", "evb_get_grads", "evb_get_nidx", "evb_get_hist", "evb_get_node_sums",
            "evb_get_stream", "evb_get_timings", "evb_reset_timings", "evb_predict", "evb_predict_x", "evb_binarize", "evb_hist_rows", "evb_hist_rows_noalloc"]
 
 

@@ -4,6 +4,7 @@
 #include <string.h>
 #include <stdlib.h>
 #include <new>
+#include <algorithm>
 
 int32_t evb_launch_check_bins(evb_handle *h);
 int32_t evb_launch_init_state(evb_handle *h, const float *w_dev, const float *pred0_dev, const float *mu_dev);
@@ -70,15 +71,16 @@ static cudaError_t dalloc(T **p, size_t count) { return cudaMalloc((void **)p, (
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Device block that travels to the host once per tree: [plan][err][feat][gain][w][pred][packed][bin][split]
+// Device block that travels to the host once per tree: [plan][err][eval sums][feat][gain][w][pred][packed][bin][split]
 struct TreeBlockLayout {
-    size_t plan, err, feat, gain, w, pred, packed, bin, split, total;
+    size_t plan, err, evsum, feat, gain, w, pred, packed, bin, split, total;
 };
 static TreeBlockLayout tree_block_layout(int D, int nn, int K) {
     TreeBlockLayout l;
     size_t o = 0;
     l.plan = o; o += align_up(sizeof(LevelPlan) * (D + 2), 16);
     l.err = o; o += 16;
+    l.evsum = o; o += 16;
     l.feat = o; o += align_up(sizeof(int32_t) * nn, 16);
     l.gain = o; o += align_up(sizeof(float) * nn, 16);
     l.w = o; o += align_up(sizeof(float) * nn, 16);
@@ -91,6 +93,12 @@ static TreeBlockLayout tree_block_layout(int D, int nn, int K) {
 }
 
 static void drop_graphs(evb_handle *h);
+static void free_eval(evb_handle *h) {
+    void *ptrs[] = {h->ev_xT, h->ev_y, h->ev_w, h->ev_pred, h->ev_part};
+    for (void *p : ptrs) if (p) cudaFree(p);
+    h->ev_xT = nullptr; h->ev_y = nullptr; h->ev_w = nullptr; h->ev_pred = nullptr; h->ev_part = nullptr;
+    h->ev_n = 0;
+}
 static void free_handle(evb_handle *h) {
     if (!h) return;
     cudaSetDevice(h->dev);
@@ -100,6 +108,7 @@ static void free_handle(evb_handle *h) {
     if (h->peer_cand[h->rank]) cudaFree(h->peer_cand[h->rank]);
     if (h->peer_flags[h->rank]) cudaFree(h->peer_flags[h->rank]);
     if (h->hsum) cudaFree(h->hsum);
+    free_eval(h);
     void *ptrs[] = {h->xT, h->xC, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
                     h->js_d, h->seg_start, h->seg_cnt, h->gcnt, h->nleft, (h->gnleft != h->nleft) ? h->gnleft : nullptr, h->kind,
                     h->bslot, h->nsum, h->plan /* base of the tree block */, h->cum, h->slot_node, h->item_node, h->item_left,
@@ -162,7 +171,7 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
     unsigned char *blk = nullptr;
     EVB_CUDA(dalloc(&blk, L.total));
     EVB_CUDA(cudaMemset(blk, 0, L.total));
-    h->plan = (LevelPlan *)(blk + L.plan); h->d_err = (int *)(blk + L.err);
+    h->plan = (LevelPlan *)(blk + L.plan); h->d_err = (int *)(blk + L.err); h->d_evsum = (double *)(blk + L.evsum);
     h->t_feat = (int32_t *)(blk + L.feat); h->t_gain = (float *)(blk + L.gain); h->t_w = (float *)(blk + L.w);
     h->t_pred = (float *)(blk + L.pred); h->t_packed = (uint32_t *)(blk + L.packed); h->t_bin = blk + L.bin; h->t_split = blk + L.split;
     h->h_tree_bytes = L.total;
@@ -310,6 +319,7 @@ static int32_t enqueue_tree(evb_handle *h, bool use_mask, uint8_t mask_cond, boo
         if (level < D - 1 || (full_part && level == D - 1)) EVB_CHECK(evb_launch_partition(h, level));
     }
     EVB_CHECK(evb_launch_finalize(h, fuse));
+    if (h->ev_n > 0) EVB_CHECK(evb_launch_eval(h, nullptr));
     EVB_CUDA(cudaMemcpyAsync(h->h_tree[slot], h->plan, h->h_tree_bytes, cudaMemcpyDeviceToHost, h->st));
     return EVB_OK;
 }
@@ -429,6 +439,7 @@ extern "C" int32_t evb_grow_tree_end(evb_handle *h, int64_t *feat, uint8_t *cond
         cudaMemsetAsync(h->d_err, 0, sizeof(int), h->st);
         return EVB_ERR_DEVICE;
     }
+    memcpy(h->last_eval, hb + L.evsum, sizeof(h->last_eval));
     const LevelPlan *hp = (const LevelPlan *)(hb + L.plan);
     if (hp[1].n_sel == 0 && h->world == 1) {
         evb_set_error("no subsample observation - choose larger rowsample");
@@ -454,6 +465,99 @@ extern "C" int32_t evb_grow_tree(evb_handle *h, const uint8_t *row_mask, uint8_t
     if (h && h->pending > 0) { evb_set_error("evb_grow_tree: a tree started with evb_grow_tree_begin is still in flight"); return EVB_ERR_BUSY; }
     EVB_CHECK(evb_grow_tree_begin(h, row_mask, mask_cond, js, njs, update_grads));
     return evb_grow_tree_end(h, feat, cond_bin, w_node, gain, leaf_pred, split);
+}
+
+// ---- evaluation data on the device ---------------------------------------------------------------------------
+static int32_t eval_attach_impl(evb_handle *h, int64_t nobs, const uint8_t *x_bin, const void *y, const float *w, const float *pred0,
+                                const float *bias, int32_t metric, double sums[2]) {
+    const int K = h->K;
+    h->ev_metric = metric;
+    h->ev_blocks = (int)std::min<int64_t>((nobs + 255) / 256, (int64_t)h->num_sms * 8);
+    EVB_CUDA(dalloc(&h->ev_xT, (size_t)nobs * h->RS));
+    EVB_CUDA(dalloc(&h->ev_pred, (size_t)nobs * K));
+    EVB_CUDA(dalloc(&h->ev_part, (size_t)h->ev_blocks * 2));
+    const size_t ybytes = (size_t)nobs * (h->y_dtype == EVB_U32 ? 4 : 4 * (size_t)h->ycols);
+    EVB_CUDA(cudaMalloc(&h->ev_y, ybytes));
+    EVB_CUDA(cudaMemcpyAsync(h->ev_y, y, ybytes, cudaMemcpyHostToDevice, h->st));
+    if (w) {
+        EVB_CUDA(dalloc(&h->ev_w, (size_t)nobs));
+        EVB_CUDA(cudaMemcpyAsync(h->ev_w, w, sizeof(float) * nobs, cudaMemcpyHostToDevice, h->st));
+    }
+    if (pred0) EVB_CUDA(cudaMemcpyAsync(h->ev_pred, pred0, sizeof(float) * nobs * K, cudaMemcpyHostToDevice, h->st));
+    else EVB_CUDA(cudaMemsetAsync(h->ev_pred, 0, sizeof(float) * nobs * K, h->st));
+    // feature-major upload -> observation-major rows, column block by column block through a bounded staging buffer
+    EVB_CUDA(cudaMemsetAsync(h->ev_xT, 0, (size_t)nobs * h->RS, h->st));
+    uint8_t *stage = nullptr;
+    float *leaf_d = nullptr;
+    const int jb = (int)std::max<int64_t>(1, std::min<int64_t>(h->nfeats, ((int64_t)256 << 20) / nobs));
+    EVB_CUDA(dalloc(&stage, (size_t)jb * nobs));
+    int32_t rc = EVB_OK;
+    for (int j0 = 0; j0 < h->nfeats && rc == EVB_OK; j0 += jb) {
+        const int nj = std::min(jb, h->nfeats - j0);
+        if (cudaMemcpyAsync(stage, x_bin + (size_t)j0 * nobs, (size_t)nj * nobs, cudaMemcpyHostToDevice, h->st) != cudaSuccess) rc = EVB_ERR_CUDA;
+        if (rc == EVB_OK) rc = evb_launch_transpose(h, stage, nobs, nobs, j0, nj, h->ev_xT, h->RS, h->st);
+    }
+    h->ev_n = nobs;
+    if (rc == EVB_OK) {
+        // iteration 0: `cb(logger, 0, m.trees[end])` applies the bias tree (src/fit.jl:416); a model without one adds zeros
+        std::vector<float> leaf(K, 0.0f);
+        if (bias) memcpy(leaf.data(), bias, sizeof(float) * K);
+        if (dalloc(&leaf_d, (size_t)K) != cudaSuccess || cudaMemcpyAsync(leaf_d, leaf.data(), sizeof(float) * K, cudaMemcpyHostToDevice, h->st) != cudaSuccess) rc = EVB_ERR_CUDA;
+        if (rc == EVB_OK) rc = evb_launch_eval(h, leaf_d);
+        if (rc == EVB_OK && cudaMemcpyAsync(h->last_eval, h->d_evsum, sizeof(h->last_eval), cudaMemcpyDeviceToHost, h->st) != cudaSuccess) rc = EVB_ERR_CUDA;
+    }
+    cudaError_t e = cudaStreamSynchronize(h->st);
+    if (stage) cudaFree(stage);
+    if (leaf_d) cudaFree(leaf_d);
+    if (rc == EVB_ERR_CUDA || e != cudaSuccess) {
+        evb_set_error("evb_eval_attach: CUDA error %s", cudaGetErrorString(e != cudaSuccess ? e : cudaGetLastError()));
+        return EVB_ERR_CUDA;
+    }
+    EVB_CHECK(rc);
+    sums[0] = h->last_eval[0]; sums[1] = h->last_eval[1];
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_eval_attach(evb_handle *h, int64_t nobs, const uint8_t *x_bin, const void *y, const float *w, const float *pred0,
+                                   const float *bias, int32_t metric, double sums[2]) {
+    EVB_ENTER(h);
+    if (!x_bin || !y || !sums || nobs < 1 || nobs > 2000000000ll) { evb_set_error("evb_eval_attach: invalid argument"); return EVB_ERR_ARG; }
+    if (h->pending > 0) { evb_set_error("evb_eval_attach: a tree is still in flight"); return EVB_ERR_BUSY; }
+    if (h->ev_n > 0) { evb_set_error("evb_eval_attach: evaluation data already attached (evb_eval_detach first)"); return EVB_ERR_ARG; }
+    const int loss = h->p.loss;
+    const bool ok = (loss == EVB_MLOGLOSS) ? metric == EVB_METRIC_MLOGLOSS
+                    : (loss == EVB_GAUSSIAN_MLE) ? metric == EVB_METRIC_GAUSSIAN_MLE
+                    : (metric == EVB_METRIC_MSE || metric == EVB_METRIC_MAE || metric == EVB_METRIC_LOGLOSS);
+    if (!ok) { evb_set_error("evb_eval_attach: metric %d is not defined for loss %d", metric, loss); return EVB_ERR_ARG; }
+    drop_graphs(h); // the launch sequence of a tree changes
+    int32_t rc = eval_attach_impl(h, nobs, x_bin, y, w, pred0, bias, metric, sums);
+    if (rc != EVB_OK) free_eval(h);
+    return rc;
+}
+
+extern "C" int32_t evb_eval_sums(evb_handle *h, double sums[2]) {
+    EVB_ENTER(h);
+    if (!sums) { evb_set_error("evb_eval_sums: null output"); return EVB_ERR_ARG; }
+    if (h->ev_n == 0) { evb_set_error("evb_eval_sums: no evaluation data attached"); return EVB_ERR_ARG; }
+    sums[0] = h->last_eval[0]; sums[1] = h->last_eval[1];
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_eval_get_pred(evb_handle *h, float *pred) {
+    EVB_ENTER(h);
+    if (!pred || h->ev_n == 0) { evb_set_error("evb_eval_get_pred: no evaluation data attached or null output"); return EVB_ERR_ARG; }
+    EVB_CUDA(cudaMemcpyAsync(pred, h->ev_pred, sizeof(float) * h->ev_n * h->K, cudaMemcpyDeviceToHost, h->st));
+    EVB_CUDA(cudaStreamSynchronize(h->st));
+    return EVB_OK;
+}
+
+extern "C" int32_t evb_eval_detach(evb_handle *h) {
+    EVB_ENTER(h);
+    if (h->pending > 0) { evb_set_error("evb_eval_detach: a tree is still in flight"); return EVB_ERR_BUSY; }
+    EVB_CUDA(cudaStreamSynchronize(h->st));
+    drop_graphs(h);
+    free_eval(h);
+    return EVB_OK;
 }
 
 // ---- peer access between the ranks' processes (CUDA IPC) -----------------------------------------------------

@@ -113,6 +113,15 @@ struct evb_handle {
     int *d_err;            // device error word
     int *h_err;            // pinned mirror
 
+    // evaluation shard (evb_eval_attach): every grown tree is applied to ev_pred and the metric sums go to d_evsum
+    int64_t ev_n;      // 0 = none attached
+    uint8_t *ev_xT;    // [ev_n][RS]
+    void *ev_y; float *ev_w; float *ev_pred;
+    double *ev_part;   // [ev_blocks][2] per-block partial sums
+    double *d_evsum;   // [2] inside the tree block: sum w*value, sum w
+    int ev_metric, ev_blocks;
+    double last_eval[2]; // sums of the tree collected last
+
     // histograms
     HistGeom hg;
     int hist_mode;    // EVB_HIST_MODE environment override (kernel variants / diagnostics)
@@ -159,6 +168,7 @@ int32_t evb_launch_grads(evb_handle *h);
 int32_t evb_launch_rows_init(evb_handle *h, bool use_mask, uint8_t mask_cond);
 int32_t evb_launch_finalize(evb_handle *h, bool compute_grads);
 int32_t evb_launch_nidx_from_partition(evb_handle *h, uint32_t *out_dev);
+int32_t evb_launch_eval(evb_handle *h, const float *fixed_leaf_dev);
 // evb_hist.cu
 int32_t evb_hist_configure(evb_handle *h);   // fills h->hg from p / nfeats (uses max F = nfeats)
 int32_t evb_launch_hist(evb_handle *h, int level);

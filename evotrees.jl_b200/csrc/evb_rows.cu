@@ -348,6 +348,91 @@ __global__ void __launch_bounds__(256) k_binarize_rows(const T *x, long long ld,
     for (int e = threadIdx.x; e < nr * (RS / 16); e += 256) dst[e] = src[e];
 }
 
+// ---------------------------------------------------------------------------------- evaluation data
+// Per-row metric value in float, as `_metric_value` / `_mle2p_metric_value` / `mlogloss` compute it
+// (src/metrics.jl:1-110): the caller multiplies by w and accumulates in double.
+__device__ __forceinline__ float metric_row(int metric, int K, const float *p, const void *y, int ycols, long long i, float w) {
+    if (metric == EVB_METRIC_MLOGLOSS) {
+        const uint32_t yi = ((const uint32_t *)y)[i];
+        float isum = 0.0f;
+        for (int k = 0; k < K; ++k) isum += expf(p[k]);
+        return w * (logf(isum) - p[yi - 1]);
+    }
+    const float *yf = (const float *)y + (size_t)i * ycols;
+    if (metric == EVB_METRIC_GAUSSIAN_MLE) {
+        const int Y = K / 2;
+        float acc = 0.0f;
+        for (int t = 0; t < Y; ++t) {
+            const float scale = softplusf_(p[2 * t + 1]), d = yf[t] - p[2 * t];
+            acc += -(logf(scale) + d * d / (2.0f * scale * scale));
+        }
+        return w * acc / (float)Y;
+    }
+    float acc = 0.0f;
+    for (int k = 0; k < K; ++k) {
+        const float pk = p[k], yk = yf[k];
+        if (metric == EVB_METRIC_MSE) acc += (pk - yk) * (pk - yk);
+        else if (metric == EVB_METRIC_MAE) acc += fabsf(pk - yk);
+        else { const float s = sigmoidf_(pk); acc += -yk * logf(s) + (yk - 1.0f) * logf(1.0f - s); }
+    }
+    return w * acc / (float)K;
+}
+
+struct EvalArgs {
+    const uint8_t *xT;
+    const uint32_t *t_packed;
+    const float *t_pred;
+    const float *fixed_leaf; // non-null: every row receives this leaf (the one-node bias tree), no traversal
+    float *pred;
+    const void *y;
+    const float *w;
+    double *part; // [gridDim.x][2]
+    long long n;
+    int RS, K, loss, metric, nn, ycols, packed_in_smem;
+};
+// `predict!(cb.p, tree, cb.x_bin, cb.feattypes)` followed by the per-row metric (src/callback.jl:123-128).  Every
+// block owns a fixed set of rows and sums them in a fixed order, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256) k_eval_tree(EvalArgs a) {
+    extern __shared__ uint32_t s_packed[];
+    __shared__ double s_red[2][8];
+    const uint32_t *packed = a.t_packed;
+    if (a.packed_in_smem && !a.fixed_leaf) {
+        for (int i = threadIdx.x; i < a.nn; i += blockDim.x) s_packed[i] = a.t_packed[i];
+        __syncthreads();
+        packed = s_packed;
+    }
+    double sv = 0.0, sw = 0.0;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (long long)gridDim.x * blockDim.x) {
+        float *p = a.pred + (size_t)i * a.K;
+        const float *leaf = a.fixed_leaf ? a.fixed_leaf : a.t_pred + (size_t)(traverse(packed, a.xT + (size_t)i * a.RS) - 1) * a.K;
+        pred_add(a.loss, a.K, p, leaf);
+        const float w = a.w ? a.w[i] : 1.0f;
+        sv += (double)metric_row(a.metric, a.K, p, a.y, a.ycols, i, w);
+        sw += (double)w;
+    }
+    for (int o = 16; o > 0; o >>= 1) { sv += __shfl_down_sync(FULL, sv, o); sw += __shfl_down_sync(FULL, sw, o); }
+    if ((threadIdx.x & 31) == 0) { s_red[0][threadIdx.x >> 5] = sv; s_red[1][threadIdx.x >> 5] = sw; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double tv = 0.0, tw = 0.0;
+        for (int q = 0; q < 8; ++q) { tv += s_red[0][q]; tw += s_red[1][q]; }
+        a.part[2 * blockIdx.x] = tv;
+        a.part[2 * blockIdx.x + 1] = tw;
+    }
+}
+__global__ void __launch_bounds__(256) k_eval_sum(const double *part, int nblocks, double *out) {
+    __shared__ double s_red[2][256];
+    double tv = 0.0, tw = 0.0;
+    for (int b = threadIdx.x; b < nblocks; b += 256) { tv += part[2 * b]; tw += part[2 * b + 1]; }
+    s_red[0][threadIdx.x] = tv; s_red[1][threadIdx.x] = tw;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if ((int)threadIdx.x < o) { s_red[0][threadIdx.x] += s_red[0][threadIdx.x + o]; s_red[1][threadIdx.x] += s_red[1][threadIdx.x + o]; }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) { out[0] = s_red[0][0]; out[1] = s_red[1][0]; }
+}
+
 } // namespace
 
 // =====================================================================================================
@@ -404,6 +489,24 @@ int32_t evb_launch_finalize(evb_handle *h, bool compute_grads) {
     evb_tic(h, EVB_T_FINALIZE);
     k_finalize<<<(unsigned)((h->n + 255) / 256), 256, a.packed_in_smem ? smem : 0, h->st>>>(a);
     evb_toc(h, EVB_T_FINALIZE);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+// applies the current tree (or, with `fixed_leaf_dev`, one leaf for every row) to the evaluation predictions and
+// leaves the metric sums in h->d_evsum
+int32_t evb_launch_eval(evb_handle *h, const float *fixed_leaf_dev) {
+    EvalArgs a;
+    a.xT = h->ev_xT; a.t_packed = h->t_packed; a.t_pred = h->t_pred; a.fixed_leaf = fixed_leaf_dev; a.pred = h->ev_pred;
+    a.y = h->ev_y; a.w = h->ev_w; a.part = h->ev_part; a.n = h->ev_n; a.RS = h->RS; a.K = h->K; a.loss = h->p.loss;
+    a.metric = h->ev_metric; a.nn = h->nn; a.ycols = h->ycols;
+    const size_t smem = (size_t)h->nn * 4;
+    a.packed_in_smem = smem <= 40 * 1024 ? 1 : 0;
+    evb_tic(h, EVB_T_FINALIZE);
+    k_eval_tree<<<h->ev_blocks, 256, (a.packed_in_smem && !fixed_leaf_dev) ? smem : 0, h->st>>>(a);
+    k_eval_sum<<<1, 256, 0, h->st>>>(h->ev_part, h->ev_blocks, h->d_evsum);
+    evb_toc(h, EVB_T_FINALIZE);
+    h->tm.launches[EVB_T_FINALIZE] += 1; // two kernels inside one timed bracket
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
 }

@@ -252,10 +252,19 @@ def grow_tree_end(cache: Cache, params: EvoTypes) -> Tree:
     return t
 
 
-def grow_rounds(m: EvoTree, cache: Cache, params: EvoTypes, nrounds: int) -> None:
+def grow_rounds(m: EvoTree, cache: Cache, params: EvoTypes, nrounds: int, on_tree=None) -> None:
     """`nrounds` boosting rounds with the host one tree ahead of the GPU (same trees as calling `grow_evotree`
-    `nrounds` times)."""
-    in_flight = 0
+    `nrounds` times).  `on_tree(i)` is called after the i-th tree of this call has been collected."""
+    in_flight = collected = 0
+
+    def collect():
+        nonlocal in_flight, collected
+        m.trees.append(grow_tree_end(cache, params))
+        in_flight -= 1
+        collected += 1
+        if on_tree is not None:
+            on_tree(collected)
+
     try:
         for _ in range(nrounds):
             for b in range(params.bagging_size):
@@ -263,13 +272,11 @@ def grow_rounds(m: EvoTree, cache: Cache, params: EvoTypes, nrounds: int) -> Non
                 grow_tree_begin(cache, params, mask, js, update_grads=(b == 0))
                 in_flight += 1
                 if in_flight == 2:
-                    m.trees.append(grow_tree_end(cache, params))
-                    in_flight -= 1
+                    collect()
             m.info["nrounds"] += 1
     finally:
         while in_flight > 0:
-            m.trees.append(grow_tree_end(cache, params))
-            in_flight -= 1
+            collect()
 
 
 def grow_evotree(m: EvoTree, cache: Cache, params: EvoTypes) -> None:
@@ -280,14 +287,146 @@ def grow_evotree(m: EvoTree, cache: Cache, params: EvoTypes) -> None:
     m.info["nrounds"] += 1
 
 
-def fit(params: EvoTypes, *, x_train, y_train, w_train=None, offset_train=None, x_eval=None, y_eval=None,
-        feature_names=None, device: int = 0, return_cache: bool = False, comm=None, **_ignored):
-    """`fit(params; x_train, y_train, w_train, offset_train, feature_names)` (src/fit.jl:388-437).
-    Evaluation data / early stopping are not part of this device path yet and are rejected."""
-    if x_eval is not None or y_eval is not None:
-        raise NotImplementedError("x_eval / y_eval (eval metric tracking, early stopping) are not built for this device path")
+IS_MAXIMISE = {"mse": False, "rmse": False, "mae": False, "logloss": False, "mlogloss": False,
+               "gaussian_mle": True}   # src/metrics.jl:194-205
+
+
+def init_logger(metric: str, maximise: bool, early_stopping_rounds: int, early_stopping_tolerance: float = 0.0) -> dict:
+    """`init_logger` (src/callback.jl:130-144)."""
+    return {"name": str(metric), "maximise": maximise, "early_stopping_rounds": early_stopping_rounds,
+            "early_stopping_tolerance": early_stopping_tolerance, "nrounds": 0, "iter": [], "metrics": [],
+            "iter_since_best": 0, "best_iter": 0, "best_metric": 0.0}
+
+
+def update_logger(logger: dict, it: int, metric: float) -> None:
+    """`update_logger!` (src/callback.jl:146-164)."""
+    logger["nrounds"] = it
+    logger["iter"].append(it)
+    logger["metrics"].append(metric)
+    if it == 0:
+        logger["best_metric"] = metric
+        return
+    tol = logger["early_stopping_tolerance"]
+    improved = metric > logger["best_metric"] + tol if logger["maximise"] else metric < logger["best_metric"] - tol
+    if improved:
+        logger["best_metric"] = metric
+        logger["best_iter"] = it
+        logger["iter_since_best"] = 0
+    else:
+        logger["iter_since_best"] += logger["iter"][-1] - logger["iter"][-2]
+
+
+def eval_levelcode(y_eval, target_levels) -> np.ndarray:
+    """Class codes 1..K of `y_eval` against the levels the model was trained on (src/callback.jl:11-19)."""
+    y_eval = np.asarray(y_eval)
+    levels = np.asarray(target_levels)
+    pos = np.searchsorted(levels, y_eval)
+    pos = np.clip(pos, 0, levels.size - 1)
+    bad = levels[pos] != y_eval
+    if bad.any():
+        raise ValueError(f"`y_eval` contains levels absent from `y_train`: {np.unique(y_eval[bad]).tolist()}. "
+                         f"Training levels are {levels.tolist()}.")
+    return (pos + 1).astype(np.uint32)
+
+
+class CallBack:
+    """`CallBack(params, m, x_eval, y_eval, device; w_eval, offset_eval)` (src/callback.jl:82-121): the evaluation
+    data is binarized with the model's edges and handed to the training handle (`evb_eval_attach`), which from then
+    on applies every grown tree to the evaluation predictions and re-evaluates the metric on the device.  Calling
+    the object after a tree has been collected logs that tree's metric (`(cb::CallBack)(logger, iter, tree)`,
+    src/callback.jl:123-128).  With `comm` every rank holds a shard of the evaluation rows and the sums are added
+    over the ranks.  Deviation: with bagging_size > 1 the reference adds only the last tree of a round to the
+    evaluation predictions; here all trees of the round are added, so they equal `m(x_eval)` in link space."""
+
+    def __init__(self, params: EvoTypes, m: EvoTree, cache: Cache, x_eval, y_eval, w_eval=None, offset_eval=None,
+                 device: int = 0, comm=None):
+        x_eval = np.asarray(x_eval)
+        if x_eval.dtype not in (np.float32, np.float64):
+            x_eval = x_eval.astype(np.float64)
+        nobs = x_eval.shape[0]
+        if x_eval.ndim != 2 or x_eval.shape[1] != cache.nfeats:
+            raise ValueError("x_eval must have the columns of x_train")
+        edges = m.info["edges"]
+        x_bin = binarize(x_eval.astype(edges.dtype, copy=False), edges, device)
+        loss, K = params.loss, m.K
+        if loss == "mlogloss":
+            y = eval_levelcode(y_eval, m.info["target_levels"])
+        else:
+            y = np.ascontiguousarray(y_eval, np.float32)
+        if y.shape[0] != nobs:
+            raise ValueError("y_eval must have one entry per row of x_eval")
+        w = None if w_eval is None else np.ascontiguousarray(w_eval, np.float32)
+        pred0 = None
+        if offset_eval is not None:                                  # src/callback.jl:110-118
+            off = np.array(offset_eval, np.float32, copy=True).reshape(nobs, -1)
+            if loss == "logloss":
+                off = _logit(off)
+            elif loss == "mlogloss":
+                off = np.log(off)
+            elif loss == "gaussian_mle":
+                off[:, 1::2] = [[_invsoftplus(float(v)) for v in row] for row in off[:, 1::2]]
+            pred0 = np.ascontiguousarray(np.broadcast_to(off, (nobs, K)), np.float32)
+        self.metric = params.metric
+        self.cache, self.comm = cache, comm
+        bias = np.ascontiguousarray(m.trees[-1].pred[0], np.float32)  # cb(logger, 0, m.trees[end]), src/fit.jl:416
+        sums = (C.c_double * 2)()
+        _lib.check(_lib.lib().evb_eval_attach(cache.handle, C.c_int64(nobs), _lib.ptr(x_bin), _lib.ptr(y), _lib.ptr(w),
+                                              _lib.ptr(pred0), _lib.ptr(bias), C.c_int32(_lib.METRIC_CODES[self.metric]), sums))
+        self.nobs = nobs
+        self.initial = self._metric(sums)
+
+    def _metric(self, sums) -> float:
+        s = np.array([sums[0], sums[1]], np.float64)
+        if self.comm is not None:
+            s = self.comm.allreduce_sum(s)
+        v = float(s[0] / s[1])
+        return math.sqrt(v) if self.metric == "rmse" else v
+
+    def last(self) -> float:
+        """Metric after the tree collected last by `grow_tree` / `grow_tree_end`."""
+        sums = (C.c_double * 2)()
+        _lib.check(_lib.lib().evb_eval_sums(self.cache.handle, sums))
+        return self._metric(sums)
+
+    def pred(self) -> np.ndarray:
+        out = np.empty((self.nobs, self.cache.K), np.float32)
+        _lib.check(_lib.lib().evb_eval_get_pred(self.cache.handle, _lib.ptr(out)))
+        return out
+
+    def __call__(self, logger: dict, it: int) -> None:
+        update_logger(logger, it, self.initial if it == 0 else self.last())
+
+    def detach(self) -> None:
+        _lib.check(_lib.lib().evb_eval_detach(self.cache.handle))
+
+
+def fit(params: EvoTypes, *, x_train, y_train, w_train=None, offset_train=None, x_eval=None, y_eval=None, w_eval=None,
+        offset_eval=None, feature_names=None, device: int = 0, return_cache: bool = False, comm=None, **_ignored):
+    """`fit(params; x_train, y_train, w_train, offset_train, x_eval, y_eval, w_eval, offset_eval, feature_names)`
+    (src/fit.jl:388-437).  With evaluation data the metric of every round is logged in `m.info["logger"]` and
+    boosting stops once `early_stopping_rounds` rounds passed without improvement."""
     m, cache = init_core(params, x_train, y_train, w_train, offset_train, feature_names, device, comm=comm)
-    grow_rounds(m, cache, params, params.nrounds)
+    if (x_eval is None) != (y_eval is None):
+        import warnings
+        warnings.warn("To track eval metric in logger, both `x_eval` and `y_eval` must be provided.")
+    logger = cb = None
+    if x_eval is not None and y_eval is not None:
+        cb = CallBack(params, m, cache, x_eval, y_eval, w_eval, offset_eval, device, comm)
+        logger = init_logger(params.metric, IS_MAXIMISE[params.metric], params.early_stopping_rounds,
+                             params.early_stopping_tolerance)
+        cb(logger, 0)
+    if logger is None:
+        grow_rounds(m, cache, params, params.nrounds)
+    elif params.early_stopping_rounds > params.nrounds and params.bagging_size == 1:
+        # early stopping cannot trigger: keep the host one tree ahead and log each tree as it is collected
+        grow_rounds(m, cache, params, params.nrounds, on_tree=lambda i: cb(logger, i))
+    else:
+        for i in range(1, params.nrounds + 1):
+            grow_evotree(m, cache, params)
+            cb(logger, i)
+            if logger["iter_since_best"] >= logger["early_stopping_rounds"]:
+                break
+    m.info["logger"] = logger
     if return_cache:
         return m, cache
     cache.close()

@@ -147,4 +147,52 @@ function EvoTrees._predict_leaf_indices(m::EvoTree{L,K}, data, ::Type{<:GPU}; nt
     return leaf
 end
 
+# ---- evaluation data on the device: replaces CallBack(...) + (cb::CallBack)(logger, iter, tree), src/callback.jl:82-128
+# `fit` builds the callback without handing it the cache (src/fit.jl:414), so `init_core` above has to remember the
+# cache it created last (e.g. `LAST_CACHE[] = cache`); the reference's `fit` then works unchanged.
+const LAST_CACHE = Ref{Union{Nothing,B200Cache}}(nothing)
+const METRIC_CODE = Dict(:mse => 0, :rmse => 0, :mae => 1, :logloss => 2, :mlogloss => 3, :gaussian_mle => 4, :gaussian => 4)
+
+struct B200CallBack
+    cache::B200Cache
+    metric::Symbol
+    initial::Float64
+end
+
+metric_value(metric::Symbol, sums) = metric == :rmse ? sqrt(sums[1] / sums[2]) : sums[1] / sums[2]
+
+function EvoTrees.CallBack(params::EvoTypes, m::EvoTree{L,K}, x_eval::AbstractMatrix, y_eval, ::Type{<:GPU};
+    w_eval=nothing, offset_eval=nothing) where {L,K}
+    cache = LAST_CACHE[]
+    x_bin = binarize(x_eval; feature_names=m.info[:feature_names], edges=m.info[:edges])
+    y = L == EvoTrees.MLogLoss ? EvoTrees.eval_levelcode(y_eval, m.info[:target_levels]) : Float32.(y_eval)
+    w = isnothing(w_eval) ? C_NULL : Float32.(w_eval)
+    p0 = C_NULL
+    if !isnothing(offset_eval)                     # same link transforms as src/callback.jl:110-118
+        off = Float32.(offset_eval)
+        L == EvoTrees.LogLoss && (off .= EvoTrees.logit.(off))
+        L == EvoTrees.MLogLoss && (off .= log.(off))
+        L == EvoTrees.GaussianMLE && EvoTrees.unconstrain_mle_scale!(off)
+        p0 = Matrix{Float32}(reshape(off, size(x_eval, 1), :)')   # K x nobs
+    end
+    bias = Float32.(m.trees[end].pred[:, 1])
+    sums = zeros(Float64, 2)
+    GC.@preserve x_bin y w p0 bias check(ccall((:evb_eval_attach, LIB), Int32,
+        (Ptr{Cvoid}, Int64, Ptr{UInt8}, Ptr{Cvoid}, Ptr{Float32}, Ptr{Float32}, Ptr{Float32}, Int32, Ptr{Float64}),
+        cache.handle, size(x_eval, 1), x_bin, y, w, p0, bias, METRIC_CODE[params.metric], sums))
+    return B200CallBack(cache, params.metric, metric_value(params.metric, sums))
+end
+EvoTrees.is_maximise(cb::B200CallBack) = cb.metric in (:gaussian_mle, :gaussian)   # `fit` asks is_maximise(cb.feval)
+
+function (cb::B200CallBack)(logger, iter, tree)
+    if iter == 0
+        EvoTrees.update_logger!(logger, iter, cb.initial)
+    else
+        sums = zeros(Float64, 2)
+        check(ccall((:evb_eval_sums, LIB), Int32, (Ptr{Cvoid}, Ptr{Float64}), cb.cache.handle, sums))
+        EvoTrees.update_logger!(logger, iter, metric_value(cb.metric, sums))
+    end
+    return nothing
+end
+
 end # module

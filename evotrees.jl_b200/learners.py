@@ -36,9 +36,11 @@ class EvoTypes:
     seed: int = 123
     device: str = "gpu"
     early_stopping_rounds: int = 2 ** 62
+    early_stopping_tolerance: float = 0.0
     metric: str | None = None
 
     _losses = ()
+    _metrics = ()
 
     def __post_init__(self):
         self.loss = str(self.loss)
@@ -50,6 +52,12 @@ class EvoTypes:
             self.loss = "gaussian_mle"
         if self.loss not in self._losses:
             raise ValueError(f"Invalid loss. Must be one of: {list(self._losses)}")
+        # metric defaults to the loss (src/learners.jl:75-87, 260, 352-365)
+        self.metric = self.loss if self.metric is None else str(self.metric)
+        if self.metric == "gaussian":
+            self.metric = "gaussian_mle"
+        if self.metric not in self._metrics:
+            raise ValueError(f"Invalid metric. Must be one of: {list(self._metrics)}")
         self.check_args()
 
     def check_args(self):
@@ -63,6 +71,7 @@ class EvoTypes:
         _check("colsample", self.colsample, 2.220446049250313e-16, 1.0)
         _check("eta", self.eta, 0.0, float("inf"))
         _check("bagging_size", self.bagging_size, 1, 2 ** 31)
+        _check("early_stopping_tolerance", self.early_stopping_tolerance, 0.0, float("inf"))
         if self.tree_type != "binary":
             raise ValueError("Invalid input for `tree_type` parameter: only `binary` trees are built by this device path")
         if self.device not in ("gpu", "cuda"):
@@ -72,12 +81,14 @@ class EvoTypes:
 @dataclass
 class EvoTreeRegressor(EvoTypes):
     _losses = _REG_LOSSES
+    _metrics = ("mse", "rmse", "mae", "logloss")
 
 
 @dataclass
 class EvoTreeClassifier(EvoTypes):
     loss: str = "mlogloss"
     _losses = ("mlogloss",)
+    _metrics = ("mlogloss",)
 
 
 @dataclass
@@ -85,3 +96,4 @@ class EvoTreeMLE(EvoTypes):
     loss: str = "gaussian_mle"
     min_weight: float = 8.0
     _losses = _MLE_LOSSES
+    _metrics = ("gaussian_mle",)

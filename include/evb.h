@@ -146,6 +146,31 @@ EVB_API int32_t evb_grow_tree_begin(evb_handle *h, const uint8_t *row_mask, uint
                                     int32_t update_grads);
 EVB_API int32_t evb_grow_tree_end(evb_handle *h, int64_t *feat, uint8_t *cond_bin, float *w_node, float *gain, float *leaf_pred,
                                   uint8_t *split);
+/*
+ * Evaluation data tracked on the device -- replaces `CallBack(params, m, x_eval, y_eval, device; w_eval, offset_eval)`
+ * and `(cb::CallBack)(logger, iter, tree)` (src/callback.jl:82-128) with the metric kernels of
+ * ext/EvoTreesKernelAbstractionsExt/metrics.jl (`eval_metric_kernel!`, `eval_mlogloss_kernel!`, `eval_mle2p_kernel!`).
+ * evb_eval_attach uploads one evaluation shard, sets its predictions to pred0 (or zeros), adds the bias leaf with
+ * the clamps of `predict!` (src/predict.jl:1-62) and returns the metric sums of iteration 0.  From then on every
+ * tree grown by the handle is also applied to the evaluation predictions and the metric is re-evaluated, inside the
+ * same launch sequence; evb_eval_sums returns the sums that belong to the tree collected last.
+ *   x_bin    host uint8 [nobs x nfeats] column-major, binarized with the model's edges (src/callback.jl:93)
+ *   y        host, same dtype / ycols as the training target (class codes 1..K for mlogloss)
+ *   w        host float [nobs] or NULL for ones
+ *   pred0    host float [K x nobs] offsets in link space, or NULL for zeros (src/callback.jl:94, 110-118)
+ *   bias     host float [K]: leaf of the bias tree (`m.trees[1].pred`), or NULL when the model has none
+ *   sums     [0] = sum_i w_i * value_i in double, value_i the per-row metric of src/metrics.jl:1-110 rounded to
+ *            float as there; [1] = sum_i w_i.  The metric is sums[0] / sums[1] (its square root for :rmse); a
+ *            caller that shards the evaluation rows over several handles adds the sums first.
+ * Metrics: mse / mae / logloss for the mse and logloss losses, mlogloss for mlogloss, gaussian_mle for gaussian_mle.
+ */
+enum evb_metric { EVB_METRIC_MSE = 0, EVB_METRIC_MAE = 1, EVB_METRIC_LOGLOSS = 2, EVB_METRIC_MLOGLOSS = 3, EVB_METRIC_GAUSSIAN_MLE = 4 };
+EVB_API int32_t evb_eval_attach(evb_handle *h, int64_t nobs, const uint8_t *x_bin, const void *y, const float *w, const float *pred0,
+                                const float *bias, int32_t metric, double sums[2]);
+EVB_API int32_t evb_eval_sums(evb_handle *h, double sums[2]);
+EVB_API int32_t evb_eval_get_pred(evb_handle *h, float *pred /* [K x nobs_eval] */);
+EVB_API int32_t evb_eval_detach(evb_handle *h);
+
 /* Switches the per-kernel CUDA-event timing of EVB_FLAG_TIMING on or off (timed trees run without graphs). */
 EVB_API int32_t evb_set_timing(evb_handle *h, int32_t on);
 

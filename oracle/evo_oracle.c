@@ -451,6 +451,51 @@ void orc_link(int32_t loss, int32_t K, int64_t nobs, float *pred) {
     }
 }
 
+/* Evaluation metrics: `_eval_metric` (src/metrics.jl:31-49) for mse / mae / logloss, `mlogloss` (:60-76) and
+ * `_eval_mle2p_metric` for gaussian_mle (:89-116).  eval[i] = w[i] * acc / K in float, then
+ * sum(Float64, eval) / sum(Float64, w); out[0] and out[1] are the two sums (the caller divides; rmse takes the
+ * square root of the mse ratio, :53-54).  Unpinned, like the rest of this file: the reference's own tests compare
+ * the logged metric with a metric recomputed from `predict` (test/metrics.jl:71-123), which tests/ repeats. */
+enum { ORC_METRIC_MSE = 0, ORC_METRIC_MAE = 1, ORC_METRIC_LOGLOSS = 2, ORC_METRIC_MLOGLOSS = 3, ORC_METRIC_GAUSSIAN_MLE = 4 };
+void orc_eval_metric(int32_t metric, int32_t K, int64_t nobs, const float *pred, const void *yv, int32_t ycols,
+                     const float *w, float *eval, double out[2]) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < nobs; i++) {
+        const float *p = pred + (size_t)K * i;
+        const float wi = w ? w[i] : 1.0f;
+        if (metric == ORC_METRIC_MLOGLOSS) {
+            const uint32_t yi = ((const uint32_t *)yv)[i];
+            float isum = 0.0f;
+            for (int k = 0; k < K; k++) isum += expf(p[k]);
+            eval[i] = wi * (logf(isum) - p[yi - 1]);
+        } else if (metric == ORC_METRIC_GAUSSIAN_MLE) {
+            const float *y = (const float *)yv + (size_t)ycols * i;
+            const int Y = K / 2;
+            float acc = 0.0f;
+            for (int t = 0; t < Y; t++) {
+                const float scale = orc_softplusf(p[2 * t + 1]);
+                const float d = y[t] - p[2 * t];
+                acc += -(logf(scale) + d * d / (2.0f * scale * scale));
+            }
+            eval[i] = wi * acc / (float)Y;
+        } else {
+            const float *y = (const float *)yv + (size_t)ycols * i;
+            float acc = 0.0f;
+            for (int k = 0; k < K; k++) {
+                const float pk = p[k], yk = ycols == 1 ? y[0] : y[k]; /* _target(y, k, i), src/loss.jl:49-50 */
+                if (metric == ORC_METRIC_MSE) acc += (pk - yk) * (pk - yk);
+                else if (metric == ORC_METRIC_MAE) acc += fabsf(pk - yk);
+                else { const float s = orc_sigmoidf(pk); acc += -yk * logf(s) + (yk - 1.0f) * logf(1.0f - s); }
+            }
+            eval[i] = wi * acc / (float)K;
+        }
+    }
+    double sv = 0.0, sw = 0.0;
+    for (int64_t i = 0; i < nobs; i++) { sv += (double)eval[i]; sw += (double)(w ? w[i] : 1.0f); }
+    out[0] = sv;
+    out[1] = sw;
+}
+
 /* binarize: x_bin[i,j] = searchsortedfirst(edges[j], x[i,j])  (src/fit-utils.jl:66-72).
  * edges are passed flattened with a fixed count per feature (the Matrix method of get_edges never
  * de-duplicates, src/fit-utils.jl:16).  NaN is not handled: the reference rejects missings earlier. */

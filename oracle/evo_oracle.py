@@ -215,6 +215,50 @@ def init_pred(p: Params, y: np.ndarray) -> np.ndarray:
     raise ValueError(p.loss)
 
 
+METRICS = {"mse": 0, "rmse": 0, "mae": 1, "logloss": 2, "mlogloss": 3, "gaussian_mle": 4}
+IS_MAXIMISE = {"mse": False, "rmse": False, "mae": False, "logloss": False, "mlogloss": False, "gaussian_mle": True}
+
+
+def eval_metric(metric: str, pred: np.ndarray, y: np.ndarray, w: np.ndarray | None = None) -> float:
+    """Metric functions of src/metrics.jl:31-116 on link-space predictions `pred` [nobs, K] (float32)."""
+    pred = np.ascontiguousarray(pred, np.float32)
+    nobs, K = pred.shape
+    y = np.ascontiguousarray(y, np.uint32 if metric == "mlogloss" else np.float32)
+    ycols = 1 if y.ndim == 1 else y.shape[1]
+    w32 = None if w is None else np.ascontiguousarray(w, np.float32)
+    ev = np.empty(nobs, np.float32)
+    out = (C.c_double * 2)()
+    lib().orc_eval_metric(C.c_int32(METRICS[metric]), C.c_int32(K), C.c_int64(nobs), _p(pred), _p(y), C.c_int32(ycols),
+                          _p(w32), _p(ev), out)
+    v = out[0] / out[1]
+    return float(np.sqrt(v)) if metric == "rmse" else float(v)
+
+
+class Logger:
+    """`init_logger` / `update_logger!` (src/callback.jl:130-164) and the stopping rule of `fit` (src/fit.jl:429)."""
+
+    def __init__(self, metric: str, early_stopping_rounds: int, early_stopping_tolerance: float = 0.0):
+        self.maximise = IS_MAXIMISE[metric]
+        self.rounds, self.tol = early_stopping_rounds, early_stopping_tolerance
+        self.iter, self.metrics = [], []
+        self.iter_since_best = self.best_iter = 0
+        self.best_metric = 0.0
+
+    def update(self, it: int, metric: float) -> bool:
+        """Logs one iteration; True when boosting has to stop."""
+        self.iter.append(it)
+        self.metrics.append(metric)
+        if it == 0:
+            self.best_metric = metric
+            return False
+        better = metric > self.best_metric + self.tol if self.maximise else metric < self.best_metric - self.tol
+        if better:
+            self.best_metric, self.best_iter, self.iter_since_best = metric, it, 0
+        else:
+            self.iter_since_best += self.iter[-1] - self.iter[-2]
+        return self.iter_since_best >= self.rounds
+
+
 def num_threads() -> int:
     return lib().orc_num_threads()
 

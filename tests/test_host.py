@@ -105,9 +105,52 @@ def test_shard_bounds(pkg):
         assert b[0][0] == 0 and b[-1][1] == n and all(b[i][1] == b[i + 1][0] for i in range(w - 1))
 
 
-def test_eval_data_is_rejected(pkg):
-    with pytest.raises(NotImplementedError):
-        pkg.fit(pkg.EvoTreeRegressor(nrounds=1), x_train=np.zeros((4, 2)), y_train=np.zeros(4), x_eval=np.zeros((4, 2)), y_eval=np.zeros(4))
+def test_logger_matches_oracle_rule(pkg, orc):
+    """`update_logger!` + the stopping rule (src/callback.jl:146-164, src/fit.jl:429) on random metric sequences."""
+    F = pkg
+    rng = np.random.default_rng(5)
+    for metric in ("mse", "gaussian_mle"):
+        for tol in (0.0, 0.05):
+            seq = np.cumsum(rng.normal(0.0 if metric == "mse" else 0.01, 0.1, 60))
+            lg = F.init_logger(metric, F.IS_MAXIMISE[metric], 4, tol)
+            ol = orc.Logger(metric, 4, tol)
+            for it, v in enumerate(seq):
+                F.update_logger(lg, it, float(v))
+                stop = ol.update(it, float(v))
+                assert (lg["iter_since_best"] >= lg["early_stopping_rounds"]) == stop
+                assert (lg["best_iter"], lg["best_metric"], lg["iter_since_best"]) == (ol.best_iter, ol.best_metric, ol.iter_since_best)
+                if stop:
+                    break
+            assert lg["nrounds"] == lg["iter"][-1] and lg["metrics"] == ol.metrics
+
+
+def test_logger_hand_case(pkg):
+    F = pkg
+    lg = F.init_logger("mse", False, 2, 0.1)
+    for it, v in enumerate([1.0, 0.8, 0.75, 0.72, 0.5]):   # 0.75 and 0.72 do not beat 0.8 - 0.1
+        F.update_logger(lg, it, v)
+        if lg["iter_since_best"] >= 2:
+            break
+    assert lg["best_iter"] == 1 and lg["best_metric"] == 0.8 and lg["iter"] == [0, 1, 2, 3] and lg["iter_since_best"] == 2
+
+
+def test_eval_levelcode(pkg):
+    F = pkg
+    lv = np.array([2, 5, 9])
+    assert F.eval_levelcode(np.array([9, 2, 2, 5]), lv).tolist() == [3, 1, 1, 2]
+    assert F.eval_levelcode(np.array([9, 9]), lv).tolist() == [3, 3]          # an eval fold without some classes
+    with pytest.raises(ValueError, match="absent from `y_train`"):
+        F.eval_levelcode(np.array([2, 7, 11]), lv)
+
+
+def test_metric_defaults_and_validation(pkg):
+    assert pkg.EvoTreeRegressor().metric == "mse" and pkg.EvoTreeRegressor(loss="logloss").metric == "logloss"
+    assert pkg.EvoTreeRegressor(metric="rmse").metric == "rmse"
+    assert pkg.EvoTreeClassifier().metric == "mlogloss" and pkg.EvoTreeMLE().metric == "gaussian_mle"
+    with pytest.raises(ValueError, match="Invalid metric"):
+        pkg.EvoTreeClassifier(metric="mse")
+    with pytest.raises(ValueError, match="early_stopping_tolerance"):
+        pkg.EvoTreeRegressor(early_stopping_tolerance=-1.0)
 
 
 @pytest.mark.skipif(has_gpu(), reason="checks the behaviour of a machine without a GPU")

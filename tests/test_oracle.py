@@ -262,3 +262,32 @@ def test_row_sampling_and_constraints(orc):
             pl = -0.1 * nsm[2 * n - 1, 0] / (nsm[2 * n - 1, 1] + 1.0)
             pr = -0.1 * nsm[2 * n, 0] / (nsm[2 * n, 1] + 1.0)
             assert pl < pr
+
+
+def test_eval_metrics_against_float64_formulas(orc):
+    """The metric restatement against the closed forms of src/metrics.jl:1-110 evaluated in float64."""
+    rng = np.random.default_rng(11)
+    n = 5000
+    w = rng.uniform(0.5, 2.0, n).astype(np.float32)
+    p = rng.normal(0, 1.5, (n, 1)).astype(np.float32)
+    y = rng.normal(0, 1, n).astype(np.float32)
+    p64, y64, w64 = p[:, 0].astype(np.float64), y.astype(np.float64), w.astype(np.float64)
+    assert np.isclose(orc.eval_metric("mse", p, y, w), np.sum(w64 * (p64 - y64) ** 2) / w64.sum(), rtol=1e-6)
+    assert np.isclose(orc.eval_metric("rmse", p, y, w), np.sqrt(np.sum(w64 * (p64 - y64) ** 2) / w64.sum()), rtol=1e-6)
+    assert np.isclose(orc.eval_metric("mae", p, y), np.mean(np.abs(p64 - y64)), rtol=1e-6)
+    yb = (rng.random(n) < 0.3).astype(np.float32)
+    s = 1 / (1 + np.exp(-p64))
+    assert np.isclose(orc.eval_metric("logloss", p, yb, w), np.sum(w64 * -(yb * np.log(s) + (1 - yb) * np.log(1 - s))) / w64.sum(), rtol=1e-5)
+    K = 4
+    pm = rng.normal(0, 1, (n, K)).astype(np.float32)
+    yc = rng.integers(1, K + 1, n).astype(np.uint32)
+    lse = np.log(np.exp(pm.astype(np.float64)).sum(axis=1))
+    assert np.isclose(orc.eval_metric("mlogloss", pm, yc, w), np.sum(w64 * (lse - pm[np.arange(n), yc - 1])) / w64.sum(), rtol=1e-5)
+    pg = np.stack([rng.normal(0, 1, n), rng.normal(0, 1, n)], axis=1).astype(np.float32)
+    sc = np.log1p(np.exp(pg[:, 1].astype(np.float64)))
+    ref = np.sum(w64 * -(np.log(sc) + (y64 - pg[:, 0]) ** 2 / (2 * sc ** 2))) / w64.sum()
+    assert np.isclose(orc.eval_metric("gaussian_mle", pg, y, w), ref, rtol=1e-5)
+    # matrix target: mean over the K columns (src/metrics.jl:43-47)
+    p2 = rng.normal(0, 1, (n, 3)).astype(np.float32)
+    y2 = rng.normal(0, 1, (n, 3)).astype(np.float32)
+    assert np.isclose(orc.eval_metric("mse", p2, y2), np.mean((p2.astype(np.float64) - y2) ** 2), rtol=1e-6)
