@@ -87,6 +87,7 @@ function EvoTrees.init_core(params::EvoTypes, ::Type{<:GPU}, data, feature_names
     js = zeros(UInt32, ceil(Int, params.colsample * nfeats))
     cache = B200Cache(handle[], rng, K, nobs, zeros(UInt8, nobs), round(UInt8, 255 * params.rowsample),
         collect(UInt32(1):UInt32(nfeats)), js, feature_names, feattypes)
+    LAST_CACHE[] = cache   # read by the CallBack constructor below
     return m, cache
 end
 
@@ -154,6 +155,7 @@ const LAST_CACHE = Ref{Union{Nothing,B200Cache}}(nothing)
 const METRIC_CODE = Dict(:mse => 0, :rmse => 0, :mae => 1, :logloss => 2, :mlogloss => 3, :gaussian_mle => 4, :gaussian => 4)
 
 struct B200CallBack
+    feval::Function        # only read by `fit` for is_maximise(cb.feval), src/fit.jl:415
     cache::B200Cache
     metric::Symbol
     initial::Float64
@@ -180,9 +182,8 @@ function EvoTrees.CallBack(params::EvoTypes, m::EvoTree{L,K}, x_eval::AbstractMa
     GC.@preserve x_bin y w p0 bias check(ccall((:evb_eval_attach, LIB), Int32,
         (Ptr{Cvoid}, Int64, Ptr{UInt8}, Ptr{Cvoid}, Ptr{Float32}, Ptr{Float32}, Ptr{Float32}, Int32, Ptr{Float64}),
         cache.handle, size(x_eval, 1), x_bin, y, w, p0, bias, METRIC_CODE[params.metric], sums))
-    return B200CallBack(cache, params.metric, metric_value(params.metric, sums))
+    return B200CallBack(EvoTrees.metric_dict[params.metric], cache, params.metric, metric_value(params.metric, sums))
 end
-EvoTrees.is_maximise(cb::B200CallBack) = cb.metric in (:gaussian_mle, :gaussian)   # `fit` asks is_maximise(cb.feval)
 
 function (cb::B200CallBack)(logger, iter, tree)
     if iter == 0
