@@ -109,7 +109,7 @@ static void free_handle(evb_handle *h) {
     if (h->peer_flags[h->rank]) cudaFree(h->peer_flags[h->rank]);
     if (h->hsum) cudaFree(h->hsum);
     free_eval(h);
-    void *ptrs[] = {h->xT, h->xC, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
+    void *ptrs[] = {h->gradq, h->d_gmax, h->d_qinv, h->xT, h->xC, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
                     h->js_d, h->seg_start, h->seg_cnt, h->gcnt, h->nleft, (h->gnleft != h->nleft) ? h->gnleft : nullptr, h->kind,
                     h->bslot, h->nsum, h->plan /* base of the tree block */, h->cum, h->slot_node, h->item_node, h->item_left,
                     h->item_lprefix, h->item_bits, h->scan_tmp, h->hist, h->hcomp, h->scratch, h->fbest_gain, h->fbest_bin};
@@ -135,6 +135,21 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
     h->K = p->K; h->C = 2 * p->K + 1; h->B = p->nbins; h->D = p->max_depth; h->nn = (1 << p->max_depth) - 1;
     h->Ce = (p->loss == EVB_MSE && !getenv("EVB_NO_ELISION")) ? p->K + 1 : h->C;
     h->nfeats = nfeats; h->RS = (nfeats + 31) / 32 * 32; h->GS = (h->Ce + 3) / 4 * 4; h->n = nobs;
+    { const int nct = (h->Ce + 3) / 4; h->rec_nch = (h->Ce + nct - 1) / nct; }
+    // mse with one target runs the fixed-point histogram kernel (EVB_HIST_Q=0: the float kernel)
+    { const char *e = getenv("EVB_HIST_Q"); h->use_q = p->loss == EVB_MSE && p->K == 1 && h->Ce == 2 && !(e && atoi(e) == 0); }
+    h->unit_w = w == nullptr;
+    h->wscale = 1.0f; h->winv = 1.0;
+    if (h->use_q && w) {
+        float wmax = 0.0f;
+        for (int64_t i = 0; i < nobs; ++i) wmax = w[i] > wmax ? w[i] : wmax;
+        if (wmax > 0.0f && wmax < INFINITY) {
+            int e;
+            frexpf(wmax, &e);
+            h->wscale = ldexpf(1.0f, 29 - e);
+            h->winv = ldexp(1.0, e - 29);
+        }
+    }
     h->dev = p->device; h->y_dtype = y_dtype; h->ycols = ycols;
     h->timing = (p->flags & EVB_FLAG_TIMING) != 0;
     h->world = 1; h->rank = 0; h->F = nfeats;
@@ -152,6 +167,12 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
 
     EVB_CUDA(dalloc(&h->xT, (size_t)n * h->RS));
     EVB_CUDA(dalloc(&h->grad, (size_t)n * h->GS));
+    if (h->use_q) {
+        EVB_CUDA(dalloc(&h->gradq, (size_t)n * (h->unit_w ? 1 : 2)));
+        EVB_CUDA(dalloc(&h->d_gmax, (size_t)1));
+        EVB_CUDA(dalloc(&h->d_qinv, (size_t)2));
+        EVB_CUDA(cudaMemset(h->d_gmax, 0, sizeof(unsigned)));
+    }
     EVB_CUDA(dalloc(&h->pred, (size_t)n * K));
     EVB_CUDA(dalloc(&h->nidx, (size_t)n));
     EVB_CUDA(dalloc(&h->rows[0], (size_t)n));
@@ -297,10 +318,11 @@ extern "C" int32_t evb_comm_init(evb_handle *h, const uint8_t id[128], int32_t r
 
 // Everything one tree launches, in stream order.  Runs either directly or under stream capture (then it is
 // replayed as one CUDA graph per tree): it must not synchronise and must not touch pageable host memory.
-static int32_t enqueue_tree(evb_handle *h, bool use_mask, uint8_t mask_cond, bool run_grads, bool fuse, int slot) {
+static int32_t enqueue_tree(evb_handle *h, bool use_mask, uint8_t mask_cond, bool run_grads, bool quantize, bool fuse, int slot) {
     const int D = h->D;
     EVB_CUDA(cudaMemcpyAsync(h->js_d, h->h_js[slot], sizeof(uint32_t) * h->F, cudaMemcpyHostToDevice, h->st));
     if (run_grads) EVB_CHECK(evb_launch_grads(h));
+    if (quantize) EVB_CHECK(evb_launch_quantize(h)); // fixed-point histogram kernel: the gradients changed since the last tree
     EVB_CHECK(evb_launch_tree_reset(h));
     EVB_CHECK(evb_launch_rows_init(h, use_mask, mask_cond));
     EVB_CHECK(evb_launch_root_plan(h));
@@ -359,6 +381,7 @@ extern "C" int32_t evb_grow_tree_begin(evb_handle *h, const uint8_t *row_mask, u
             h->scratch_floats = need;
         }
         h->hg = g;
+        h->q_active = g.q;
         drop_graphs(h);
     }
     if (update_grads) h->bag_idx = 0;
@@ -377,7 +400,10 @@ extern "C" int32_t evb_grow_tree_begin(evb_handle *h, const uint8_t *row_mask, u
     }
     // One CUDA graph per variant of the launch sequence, captured on the second call of a variant (the first
     // one runs directly: it also sets function attributes).  Per-kernel timing needs the direct path.
-    const int key = (use_mask ? 1 : 0) | (run_grads ? 2 : 0) | (fuse ? 4 : 0) | (slot ? 8 : 0);
+    if (update_grads) h->gradq_valid = false;
+    const bool quantize = h->q_active && !h->gradq_valid;
+    if (quantize) h->gradq_valid = true;
+    const int key = (use_mask ? 1 : 0) | (run_grads ? 2 : 0) | (fuse ? 4 : 0) | (slot ? 8 : 0) | (quantize ? 16 : 0);
     if (h->graph_mask_cond != (int)mask_cond) { drop_graphs(h); h->graph_mask_cond = mask_cond; }
     bool launched = false;
     // Sharded runs stay on direct launches: a run that captured the NCCL collectives into the graph did not
@@ -388,7 +414,7 @@ extern "C" int32_t evb_grow_tree_begin(evb_handle *h, const uint8_t *row_mask, u
             memcpy(before, h->tm.launches, sizeof(before));
             cudaGraph_t g = nullptr;
             cudaError_t e = cudaStreamBeginCapture(h->st, cudaStreamCaptureModeThreadLocal);
-            int32_t rc = e == cudaSuccess ? enqueue_tree(h, use_mask, mask_cond, run_grads, fuse, slot) : EVB_ERR_CUDA;
+            int32_t rc = e == cudaSuccess ? enqueue_tree(h, use_mask, mask_cond, run_grads, quantize, fuse, slot) : EVB_ERR_CUDA;
             cudaError_t e2 = cudaStreamEndCapture(h->st, &g);
             for (int i = 0; i < EVB_NTIMERS; ++i) { h->graph_launches[key][i] = h->tm.launches[i] - before[i]; h->tm.launches[i] = before[i]; }
             if (rc == EVB_OK && e2 == cudaSuccess && g && cudaGraphInstantiate(&h->graph[key], g, 0) == cudaSuccess) {
@@ -406,7 +432,7 @@ extern "C" int32_t evb_grow_tree_begin(evb_handle *h, const uint8_t *row_mask, u
             launched = true;
         }
     }
-    if (!launched) EVB_CHECK(enqueue_tree(h, use_mask, mask_cond, run_grads, fuse, slot));
+    if (!launched) EVB_CHECK(enqueue_tree(h, use_mask, mask_cond, run_grads, quantize, fuse, slot));
     h->graph_calls[key] += 1;
     if (h->timing) cudaEventRecord(h->ev_tot[1], h->st);
     EVB_CUDA(cudaEventRecord(h->ev_done[slot], h->st));
@@ -645,7 +671,7 @@ extern "C" int32_t evb_get_grads(evb_handle *h, float *grad) {
     std::vector<float> tmp((size_t)h->n * h->GS);
     EVB_CUDA(cudaMemcpyAsync(tmp.data(), h->grad, sizeof(float) * tmp.size(), cudaMemcpyDeviceToHost, h->st));
     EVB_CUDA(cudaStreamSynchronize(h->st));
-    const int NCH = h->hg.NCH, C = h->C, GS = h->GS, K = h->K;
+    const int NCH = h->rec_nch, C = h->C, GS = h->GS, K = h->K;
     const bool elided = h->Ce != h->C; // mse: records hold g_1..g_K, w; h_k = 2w
     for (int64_t i = 0; i < h->n; ++i) {
         const float *rec = tmp.data() + (size_t)i * GS;

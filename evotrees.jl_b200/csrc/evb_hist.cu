@@ -84,6 +84,79 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t *bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// Producer warp of the histogram kernels: stages tiles of 32 rows (bins + gradient record of every row) for the
+// consumer warps of the CTA.  Row ids are fetched four tiles (128 rows) at a time and one group ahead, so that the
+// latency of reading the row list never sits between two tiles.
+__device__ __forceinline__ void produce_tiles(const HistArgs &a, long long lo, long long hi, int s, uint64_t *full, uint64_t *empty,
+                                              unsigned char *stage0, int S, int stage_bytes, int xbytes, int lane) {
+    uint32_t it = 0;
+    long long pos = lo;
+    bool ok = true;
+    while (pos < hi && ok) {
+        const long long send = min(hi, (long long)a.cum[s + 1]);
+        if (send > pos) {
+            const int node = a.slot_node[s];
+            const uint32_t *rows = a.rows + ((long long)a.seg_start[node] - a.cum[s]);
+            uint32_t cur[4], nxt[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { const long long q = pos + k * 32 + lane; cur[k] = q < send ? rows[q] : 0u; }
+            for (long long q0 = pos; q0 < send && ok; q0 += 4 * EVB_TILE_ROWS) {
+                const long long qn = q0 + 4 * EVB_TILE_ROWS;
+                if (qn < send) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) { const long long q = qn + k * 32 + lane; nxt[k] = q < send ? rows[q] : 0u; }
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const long long t0 = q0 + k * EVB_TILE_ROWS;
+                    if (t0 < send && ok) {
+                        const int st = it % S;
+                        const int nrows = (int)min((long long)EVB_TILE_ROWS, send - t0);
+                        ok = mbar_wait(&empty[st], ((it / S) & 1u) ^ 1u, a.err, EVB_DERR_WAIT_EMPTY);
+                        if (ok && (a.mode & 1)) {
+                            unsigned char *sb = stage0 + (size_t)st * stage_bytes;
+                            const int cpr = a.RS >> 4, cprg = a.GS >> 2;
+                            for (int base = 0; base < EVB_TILE_ROWS * cpr; base += 32) {
+                                const int idx = base + lane, rt = idx / cpr, ch = idx - rt * cpr;
+                                const uint32_t row = __shfl_sync(0xffffffffu, cur[k], rt & 31);
+                                if (rt < nrows) cp_async16(sb + rt * a.RS + ch * 16, a.xT + (size_t)row * a.RS + ch * 16);
+                            }
+                            for (int base = 0; base < EVB_TILE_ROWS * cprg; base += 32) {
+                                const int idx = base + lane, rt = idx / cprg, ch = idx - rt * cprg;
+                                const uint32_t row = __shfl_sync(0xffffffffu, cur[k], rt & 31);
+                                if (rt < nrows) cp_async16(sb + xbytes + (rt * a.GS + ch * 4) * 4, a.grad + (size_t)row * a.GS + ch * 4);
+                            }
+                            cp_async_arrive(&full[st]);
+                            ++it;
+                        } else if (ok) {
+                            if (lane == 0) mbar_expect_tx(&full[st], (uint32_t)nrows * (uint32_t)(a.RS + a.GS * 4));
+                            __syncwarp();
+                            if (lane < nrows) {
+                                unsigned char *sb = stage0 + (size_t)st * stage_bytes;
+                                bulk_g2s(sb + lane * a.RS, a.xT + (size_t)cur[k] * a.RS, (uint32_t)a.RS, &full[st]);
+                                bulk_g2s(sb + xbytes + lane * a.GS * 4, a.grad + (size_t)cur[k] * a.GS, (uint32_t)a.GS * 4, &full[st]);
+                            }
+                            ++it;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) cur[k] = nxt[k];
+            }
+        }
+        pos = send;
+        ++s;
+    }
+    if (!ok) {
+        // error path: let the copies already issued land before the CTA's shared memory is released
+        const uint32_t first = it > (uint32_t)S ? it - S : 0;
+        for (uint32_t j = first; j < it; ++j) {
+            for (uint32_t i = 0; i < (1u << 16); ++i)
+                if (mbar_try_wait(&full[j % S], (j / S) & 1u)) break;
+        }
+    }
+}
+
 // Unit image in shared memory.  A unit is 32 lanes x FPL feature slots per lane x NCH gradient channels.
 // For every feature slot j of the lane there is a sub-image; inside it channels are kept in pairs so that one
 // 64-bit access moves two of them:
@@ -274,75 +347,7 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
     }
 
     if (wid == 0) {
-        // ---------------- producer: stage tiles of rows with TMA bulk copies -------------------------
-        // Row ids are fetched four tiles (128 rows) at a time and one group ahead, so that the latency
-        // of reading the row list never sits between two tiles.
-        uint32_t it = 0;
-        long long pos = lo;
-        bool ok = true;
-        while (pos < hi && ok) {
-            const long long send = min(hi, (long long)a.cum[s + 1]);
-            if (send > pos) {
-                const int node = a.slot_node[s];
-                const uint32_t *rows = a.rows + ((long long)a.seg_start[node] - a.cum[s]);
-                uint32_t cur[4], nxt[4] = {0, 0, 0, 0};
-#pragma unroll
-                for (int k = 0; k < 4; ++k) { const long long q = pos + k * 32 + lane; cur[k] = q < send ? rows[q] : 0u; }
-                for (long long q0 = pos; q0 < send && ok; q0 += 4 * EVB_TILE_ROWS) {
-                    const long long qn = q0 + 4 * EVB_TILE_ROWS;
-                    if (qn < send) {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) { const long long q = qn + k * 32 + lane; nxt[k] = q < send ? rows[q] : 0u; }
-                    }
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const long long t0 = q0 + k * EVB_TILE_ROWS;
-                        if (t0 < send && ok) {
-                            const int st = it % S;
-                            const int nrows = (int)min((long long)EVB_TILE_ROWS, send - t0);
-                            ok = mbar_wait(&empty[st], ((it / S) & 1u) ^ 1u, a.err, EVB_DERR_WAIT_EMPTY);
-                            if (ok && (a.mode & 1)) {
-                                unsigned char *sb = stage0 + (size_t)st * stage_bytes;
-                                const int cpr = a.RS >> 4, cprg = a.GS >> 2;
-                                for (int base = 0; base < EVB_TILE_ROWS * cpr; base += 32) {
-                                    const int idx = base + lane, rt = idx / cpr, ch = idx - rt * cpr;
-                                    const uint32_t row = __shfl_sync(0xffffffffu, cur[k], rt & 31);
-                                    if (rt < nrows) cp_async16(sb + rt * a.RS + ch * 16, a.xT + (size_t)row * a.RS + ch * 16);
-                                }
-                                for (int base = 0; base < EVB_TILE_ROWS * cprg; base += 32) {
-                                    const int idx = base + lane, rt = idx / cprg, ch = idx - rt * cprg;
-                                    const uint32_t row = __shfl_sync(0xffffffffu, cur[k], rt & 31);
-                                    if (rt < nrows) cp_async16(sb + xbytes + (rt * a.GS + ch * 4) * 4, a.grad + (size_t)row * a.GS + ch * 4);
-                                }
-                                cp_async_arrive(&full[st]);
-                                ++it;
-                            } else if (ok) {
-                                if (lane == 0) mbar_expect_tx(&full[st], (uint32_t)nrows * (uint32_t)(a.RS + a.GS * 4));
-                                __syncwarp();
-                                if (lane < nrows) {
-                                    unsigned char *sb = stage0 + (size_t)st * stage_bytes;
-                                    bulk_g2s(sb + lane * a.RS, a.xT + (size_t)cur[k] * a.RS, (uint32_t)a.RS, &full[st]);
-                                    bulk_g2s(sb + xbytes + lane * a.GS * 4, a.grad + (size_t)cur[k] * a.GS, (uint32_t)a.GS * 4, &full[st]);
-                                }
-                                ++it;
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) cur[k] = nxt[k];
-                }
-            }
-            pos = send;
-            ++s;
-        }
-        if (!ok) {
-            // error path: let the copies already issued land before the CTA's shared memory is released
-            const uint32_t first = it > (uint32_t)S ? it - S : 0;
-            for (uint32_t j = first; j < it; ++j) {
-                for (uint32_t i = 0; i < (1u << 16); ++i)
-                    if (mbar_try_wait(&full[j % S], (j / S) & 1u)) break;
-            }
-        }
+        produce_tiles(a, lo, hi, s, full, empty, stage0, S, stage_bytes, xbytes, lane);
         return;
     }
     if (wid - 1 >= nact) return;
@@ -405,6 +410,324 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
         }
         pos = send;
         ++s;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Fixed-point variant for mse with one target.  The quantisation kernel turns the gradient of every row into a
+// fixed-point number q = rint(g * 2^s), |q| < 2^29 (and the weight likewise, unless no weights were given: the w
+// channel is then a row count).  The kernel splits q into hi = q >> 15 (signed) and lo = q & 0x7fff and adds the
+// NW words (hi, lo, 1) or (hi, lo, w_hi, w_lo) into the image [word][bin][lane] of the unit with
+// `red.shared.add.u32`: one shared-memory pass per word and row, no read-modify-write chain.  Integer sums do not
+// depend on the order of the rows, so
+//   * several warps share one image: a CTA (one per SM) keeps a single image per unit of 32 feature slots and
+//     QWPU warps per unit take the 32-row tiles of the CTA's row range in turn;
+//   * the shared memory that the float variant spends on one image per warp holds row data in flight instead:
+//     there is no producer warp and no mbarrier -- every warp stages the 32-byte slice of bins of its unit and the
+//     4 (8) bytes of q of the rows of its own tiles with cp.async into a private ring, QDR tiles deep, and waits
+//     with cp.async.wait_group.
+// A piece covers at most 2^17 rows, so neither the sum of the lo words (< 2^32) nor of the hi words (|.| < 2^31)
+// can overflow.  The reduce kernel recombines hi * 2^15 + lo in 64-bit integers and scales by 2^-s: every
+// histogram entry is the exact sum of the quantised gradients, whatever the order and the number of pieces.
+// Needs feature slot s == feature s (no column sample): the unit's bins are then 32 adjacent bytes of a row.
+constexpr int QWPU = 4;                 // warps per unit
+constexpr int QDR = 6;                  // tiles in flight per warp
+constexpr int QSPLIT = 15;              // q = hi * 2^15 + lo: a piece may hold 2^17 rows (|q| < 2^29)
+__host__ __device__ constexpr int q_tile_bytes(int NW) { return EVB_TILE_ROWS * (32 + (NW == 3 ? 4 : 8)); } // bins + q (+ q of w)
+
+template <uint32_t OFF>
+__device__ __forceinline__ void red_off(uint32_t addr, uint32_t v) {
+    asm volatile("red.shared.add.u32 [%0+%2], %1;" ::"r"(addr), "r"(v), "n"(OFF) : "memory");
+}
+// adds one row into the word planes of the image (plane k starts k * WSZ bytes further): hi and lo part of the
+// fixed-point gradient, then the row count (NW == 3) or hi and lo part of the fixed-point weight (NW == 4)
+template <int NW, uint32_t WSZ>
+__device__ __forceinline__ void red_row(uint32_t addr, uint32_t qg, uint32_t qw) {
+    red_off<0>(addr, (uint32_t)((int32_t)qg >> QSPLIT));
+    red_off<WSZ>(addr, qg & ((1u << QSPLIT) - 1));
+    if constexpr (NW == 3) red_off<2 * WSZ>(addr, 1u);
+    else {
+        red_off<2 * WSZ>(addr, qw >> QSPLIT);
+        red_off<3 * WSZ>(addr, qw & ((1u << QSPLIT) - 1));
+    }
+}
+__device__ __forceinline__ void lds_v4(uint32_t addr, uint32_t (&w)[4]) {
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
+}
+// All rows of one staged tile.  Four rows at a time: lane (k = lane & 7, rr = lane >> 3) loads the 32-bit word with
+// the bins of features 4k .. 4k+3 of row r + rr -- one conflict-free load brings the 128 bins of four rows -- and the
+// fixed-point words of that row.  In step j = 0..3 the lane adds its row into feature 4k + ((j + rr) & 3): the four
+// lanes that share k work on four different features, so the 32 lanes of every reduction hit 32 different banks.
+//   tb: shared-space address of the tile's bins + k * 4 + rr * 32, tw: of its words + rr * (4 or 8),
+//   col[j]: image column of the lane's feature of step j, sel[j]: PRMT selector of that feature's byte.
+template <int NW, uint32_t WSZ>
+__device__ __forceinline__ void q_tile(uint32_t tb, uint32_t tw, int nrows, int rr, const uint32_t (&col)[4], const uint32_t (&sel)[4]) {
+    constexpr int RW = NW == 3 ? 1 : 2;
+    constexpr int NB = EVB_TILE_ROWS / 4;
+    uint32_t bins = lds_u32(tb), qg = lds_u32(tw), qw = RW == 2 ? lds_u32(tw + 4) : 0u;
+#pragma unroll
+    for (int bt = 0; bt < NB; ++bt) {
+        uint32_t nbins = 0, nqg = 0, nqw = 0;
+        if (bt + 1 < NB) { // loads of the next four rows before the reductions of these
+            nbins = lds_u32(tb + (bt + 1) * 128);
+            nqg = lds_u32(tw + (bt + 1) * 16 * RW);
+            if constexpr (RW == 2) nqw = lds_u32(tw + (bt + 1) * 32 + 4);
+        }
+        if (bt * 4 + rr < nrows) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) red_row<NW, WSZ>(col[j] + __byte_perm(bins, 0u, sel[j]) * 128u, qg, qw);
+        }
+        bins = nbins; qg = nqg; qw = nqw;
+    }
+}
+
+template <int BP, int NW>
+__global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QWPU * 32) k_histq(HistArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr uint32_t WSZ = (BP + 1) * 128;    // bytes of one word plane [bin 0..BP][lane]
+    constexpr uint32_t IMG = NW * WSZ;
+    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+    const int G = gridDim.x, b = blockIdx.x, ug = blockIdx.y;
+    const int nact = min(a.UB, a.U - ug * a.UB);
+    const long long R = a.plan->R;
+    const long long lo = R * b / G, hi = R * (b + 1) / G;
+    if (lo >= hi) return;
+    uint32_t *imgs = reinterpret_cast<uint32_t *>(smem);
+    for (int i = tid; i < a.UB * (int)(IMG / 4); i += blockDim.x) imgs[i] = 0u;
+    __syncthreads();
+    const int uw = wid / QWPU, j = wid % QWPU;
+    if (uw >= nact) return;
+
+    const int nbuild = a.plan->nbuild;
+    int s;
+    {
+        int l = 0, r = nbuild - 1;
+        while (l < r) { int m = (l + r + 1) >> 1; if ((long long)a.cum[m] <= lo) l = m; else r = m - 1; }
+        s = l;
+    }
+    const int fg = ug * a.UB + uw;          // the unit: feature slots fg*32 .. fg*32+31
+    const uint32_t u0 = smem_u32(smem) + (uint32_t)uw * IMG + lane * 4; // column of feature slot `lane` (flush)
+    const int k = lane & 7, rr = lane >> 3;
+    uint32_t col[4], sel[4];
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+        const int sh = (jj + rr) & 3;
+        col[jj] = smem_u32(smem) + (uint32_t)uw * IMG + (uint32_t)(4 * k + sh) * 4;
+        sel[jj] = 0x4440u | (uint32_t)sh;
+    }
+    constexpr int QTILE = q_tile_bytes(NW), RW = NW == 3 ? 1 : 2;
+    unsigned char *ring = smem + (size_t)a.UB * IMG + (size_t)wid * (QDR * QTILE);
+    const uint32_t ring_s = smem_u32(ring);
+    const uint8_t *xsl = a.xT + fg * 32;    // the unit's slice of every row of bins
+    const int32_t *gq = reinterpret_cast<const int32_t *>(a.grad);
+    const size_t RS = a.RS;
+
+    long long pos = lo;
+    while (pos < hi) {
+        const long long send = min(hi, (long long)a.cum[s + 1]);
+        if (send > pos) {
+            const uint32_t *rows = a.rows + ((long long)a.seg_start[a.slot_node[s]] - a.cum[s]);
+            const long long ntiles = (send - pos + EVB_TILE_ROWS - 1) / EVB_TILE_ROWS;
+            const int nmine = ntiles > j ? (int)((ntiles - j + QWPU - 1) / QWPU) : 0; // tiles j, j + QWPU, ...
+            // row id of this lane in my k-th tile (0 beyond the end of the segment: never copied)
+            auto rid_of = [&](int k) -> uint32_t {
+                const long long q = pos + ((long long)k * QWPU + j) * EVB_TILE_ROWS + lane;
+                return (k < nmine && q < send) ? rows[q] : 0u;
+            };
+            uint32_t r0 = rid_of(0), r1 = rid_of(1);
+            for (int i = 0; i < nmine + QDR - 1; ++i) {
+                const uint32_t r2 = rid_of(i + 2);
+                if (i < nmine) { // stage my tile i: lane = row of the tile
+                    const long long q = pos + ((long long)i * QWPU + j) * EVB_TILE_ROWS + lane;
+                    if (q < send) {
+                        unsigned char *dst = ring + (i % QDR) * QTILE;
+                        const uint8_t *src = xsl + (size_t)r0 * RS;
+                        cp_async16(dst + lane * 32, src);
+                        cp_async16(dst + lane * 32 + 16, src + 16);
+                        if constexpr (RW == 1) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst + EVB_TILE_ROWS * 32 + lane * 4)), "l"(gq + r0) : "memory");
+                        else asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst + EVB_TILE_ROWS * 32 + lane * 8)), "l"(gq + (size_t)r0 * 2) : "memory");
+                    }
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                r0 = r1; r1 = r2;
+                if (i >= QDR - 1) { // consume my tile c: lane = feature slot of the unit
+                    const int c = i - (QDR - 1);
+                    asm volatile("cp.async.wait_group %0;" ::"n"(QDR - 1) : "memory");
+                    __syncwarp();
+                    const long long q0 = pos + ((long long)c * QWPU + j) * EVB_TILE_ROWS;
+                    const int nrows = (int)min((long long)EVB_TILE_ROWS, send - q0);
+                    const uint32_t ts = ring_s + (c % QDR) * QTILE;
+                    if (!(a.mode & 16)) q_tile<NW, WSZ>(ts + k * 4 + rr * 32, ts + EVB_TILE_ROWS * 32 + rr * 4 * RW, nrows, rr, col, sel);
+                    __syncwarp(); // the slot is staged again in the next iteration
+                }
+            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            // all warps of the unit are done with the segment: flush the piece (CTA b, slot s), clear the image
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + uw), "r"(QWPU * 32) : "memory");
+            uint32_t *dst = reinterpret_cast<uint32_t *>(a.scratch) + ((size_t)(ug * a.PG + b + s) * a.UB + uw) * a.img_floats + lane;
+#pragma unroll
+            for (int q = 0; q < NW; ++q) {
+                if (j == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(u0 + q * WSZ), "r"(0u) : "memory"); // guard row
+                for (int bin = j; bin < a.nbins; bin += QWPU) {
+                    const uint32_t ai = u0 + q * WSZ + (uint32_t)(bin + 1) * 128u;
+                    const uint32_t v = lds_u32(ai);
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(ai), "r"(0u) : "memory");
+                    dst[(q * a.nbins + bin) * 32] = v;
+                }
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + uw), "r"(QWPU * 32) : "memory");
+        }
+        pos = send;
+        ++s;
+    }
+}
+
+struct ReduceQArgs {
+    const uint32_t *scratch;
+    double *hcomp;
+    const LevelPlan *plan;
+    const int32_t *cum;
+    const double *qinv; // [2]: 2^-s of the g words, and of the w words (1 when w is a row count)
+    int G, PG, UB, NFG, F, nbins, NW;
+    uint32_t img_words;
+};
+
+// pieces of build slot s: CTAs bfirst..blast (the CTAs whose row range intersects the slot's rows)
+__device__ __forceinline__ void slot_pieces(const LevelPlan *plan, const int32_t *cum, int s, int G, int &bfirst, int &blast, long long &R) {
+    const int nbuild = plan->nbuild;
+    R = plan->R;
+    bfirst = 0; blast = -1;
+    if (s < nbuild && R > 0) {
+        const long long c0 = cum[s], c1 = cum[s + 1];
+        if (c1 > c0) {
+            bfirst = (int)(((c0 + 1) * G - 1) / R);
+            blast = (int)((c1 * G - 1) / R);
+        }
+    }
+}
+// hcomp[slot][feature][g, h = 2w, w][bin] from the exact integer sums (K = 1; h: src/loss.jl:52)
+__device__ __forceinline__ void store_q(double *hcomp, int s, int F, int nbins, int slotf, int bin, int ch, double v) {
+    double *dst = hcomp + ((size_t)s * F + slotf) * 3 * nbins + bin;
+    if (ch == 0) dst[0] = v;
+    else { dst[(size_t)2 * nbins] = v; dst[nbins] = 2.0 * v; }
+}
+
+// Sums the pieces of every build slot of the fixed-point variant: grid (build slots of the level, NFG * 2 channels,
+// ceil(nbins / BPB)), 512 threads = NPG piece groups x (BPB bins x 32 feature lanes).
+template <int BPB>
+__global__ void __launch_bounds__(512) k_histq_reduce(ReduceQArgs a) {
+    constexpr int NE = BPB * 32, NPG = 512 / NE;
+    __shared__ long long part_hi[NPG][NE], part_lo[NPG][NE];
+    __shared__ double tile[BPB][33];
+    const int s = blockIdx.x, fg = blockIdx.y >> 1, ch = blockIdx.y & 1, bin0 = blockIdx.z * BPB;
+    const int ug = fg / a.UB, uw = fg % a.UB;
+    const int e = threadIdx.x % NE, pg = threadIdx.x / NE, binl = e >> 5, lane = e & 31;
+    int bfirst, blast;
+    long long R;
+    slot_pieces(a.plan, a.cum, s, a.G, bfirst, blast, R);
+    const bool two = ch == 0 || a.NW == 4;   // hi + lo words, or a single count word
+    const int w0 = ch == 0 ? 0 : 2;
+    long long hi = 0, lo = 0;
+    const int bin = bin0 + binl;
+    if (bin < a.nbins) {
+        const uint32_t *src = a.scratch + ((size_t)(ug * a.PG + s) * a.UB + uw) * a.img_words + (w0 * a.nbins + bin) * 32 + lane;
+        const size_t bstride = (size_t)a.UB * a.img_words, wstride = (size_t)a.nbins * 32;
+        const bool all = R >= a.G;
+        for (int b = bfirst + pg; b <= blast; b += NPG) {
+            if (all || R * b / a.G < R * (b + 1) / a.G) {
+                if (two) { hi += (long long)(int32_t)src[(size_t)b * bstride]; lo += (long long)src[(size_t)b * bstride + wstride]; }
+                else lo += (long long)src[(size_t)b * bstride];
+            }
+        }
+    }
+    part_hi[pg][e] = hi; part_lo[pg][e] = lo;
+    __syncthreads();
+    if (pg == 0) {
+        long long th = 0, tl = 0;
+#pragma unroll
+        for (int q = 0; q < NPG; ++q) { th += part_hi[q][e]; tl += part_lo[q][e]; }
+        tile[binl][lane] = (double)(th * (1ll << QSPLIT) + tl) * a.qinv[ch];
+    }
+    __syncthreads();
+    if (threadIdx.x < NE) {
+        const int fl = threadIdx.x / BPB, bl = threadIdx.x % BPB;
+        const int slotf = fg * 32 + fl, binw = bin0 + bl;
+        if (slotf < a.F && binw < a.nbins) store_q(a.hcomp, s, a.F, a.nbins, slotf, binw, ch, tile[bl][fl]);
+    }
+}
+
+// deep levels (many build slots, few pieces each): one CTA per (build slot, unit)
+__global__ void __launch_bounds__(256) k_histq_reduce_unit(ReduceQArgs a) {
+    __shared__ double tile[64][33];
+    const int s = blockIdx.x, fg = blockIdx.y;
+    const int ug = fg / a.UB, uw = fg % a.UB;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int bfirst, blast;
+    long long R;
+    slot_pieces(a.plan, a.cum, s, a.G, bfirst, blast, R);
+    const bool all = R >= a.G;
+    const size_t bstride = (size_t)a.UB * a.img_words, wstride = (size_t)a.nbins * 32;
+    const uint32_t *src0 = a.scratch + ((size_t)(ug * a.PG + s) * a.UB + uw) * a.img_words + lane;
+    for (int ch = 0; ch < 2; ++ch) {
+        const bool two = ch == 0 || a.NW == 4;
+        const int w0 = ch == 0 ? 0 : 2;
+        for (int bin0 = 0; bin0 < a.nbins; bin0 += 64) {
+            for (int bl = w; bl < 64; bl += 8) {
+                const int bin = bin0 + bl;
+                long long hi = 0, lo = 0;
+                if (bin < a.nbins) {
+                    const uint32_t *src = src0 + (w0 * a.nbins + bin) * 32;
+                    for (int b = bfirst; b <= blast; ++b) {
+                        if (all || R * b / a.G < R * (b + 1) / a.G) {
+                            if (two) { hi += (long long)(int32_t)src[(size_t)b * bstride]; lo += (long long)src[(size_t)b * bstride + wstride]; }
+                            else lo += (long long)src[(size_t)b * bstride];
+                        }
+                    }
+                }
+                tile[bl][lane] = (double)(hi * (1ll << QSPLIT) + lo) * a.qinv[ch];
+            }
+            __syncthreads();
+            for (int e = threadIdx.x; e < 64 * 32; e += 256) {
+                const int fl = e >> 6, bl = e & 63;
+                const int slotf = fg * 32 + fl, binw = bin0 + bl;
+                if (slotf < a.F && binw < a.nbins) store_q(a.hcomp, s, a.F, a.nbins, slotf, binw, ch, tile[bl][fl]);
+            }
+            __syncthreads();
+        }
+    }
+}
+
+template <int BP, int NW>
+cudaError_t launch_histq_t(const HistArgs &a, dim3 grid, int threads, size_t smem, cudaStream_t st) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_histq<BP, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    k_histq<BP, NW><<<grid, threads, smem, st>>>(a);
+    return cudaGetLastError();
+}
+template <int BP, int NW>
+int occupancy_q_t(int threads, size_t smem) {
+    cudaFuncSetAttribute(k_histq<BP, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    int nb = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k_histq<BP, NW>, threads, smem) != cudaSuccess) nb = 0;
+    return nb;
+}
+template <int BP>
+int dispatch_q_nw(int NW, bool launch, const HistArgs *a, dim3 grid, int threads, size_t smem, cudaStream_t st) {
+    if (NW == 3) return launch ? (int)launch_histq_t<BP, 3>(*a, grid, threads, smem, st) : occupancy_q_t<BP, 3>(threads, smem);
+    return launch ? (int)launch_histq_t<BP, 4>(*a, grid, threads, smem, st) : occupancy_q_t<BP, 4>(threads, smem);
+}
+int dispatch_q(int BP, int NW, bool launch, const HistArgs *a, dim3 grid, int threads, size_t smem, cudaStream_t st) {
+    switch (BP) {
+    case 32: return dispatch_q_nw<32>(NW, launch, a, grid, threads, smem, st);
+    case 64: return dispatch_q_nw<64>(NW, launch, a, grid, threads, smem, st);
+    case 128: return dispatch_q_nw<128>(NW, launch, a, grid, threads, smem, st);
+    default: return dispatch_q_nw<256>(NW, launch, a, grid, threads, smem, st);
     }
 }
 
@@ -597,8 +920,37 @@ size_t unit_image_bytes(int BP, int NCH, int FPL) {
 
 // Geometry for F feature slots.  Called once at create time with F = nfeats (sizes the scratch buffer)
 // and again per tree when the column sample is smaller.
+// fixed-point variant: one unit per 32 feature slots, NCH = words per row, one CTA per SM
+static int32_t histq_geometry(const evb_handle *h, int F, HistGeom *g) {
+    const int B = h->B;
+    g->BP = B <= 32 ? 32 : B <= 64 ? 64 : B <= 128 ? 128 : 256;
+    g->q = true;
+    g->NCT = 1; g->NCH = h->unit_w ? 3 : 4; g->FPL = 1;
+    g->NFG = (F + 31) / 32;
+    g->U = g->NFG;
+    const size_t img = (size_t)g->NCH * (g->BP + 1) * 128, rings = (size_t)QWPU * QDR * q_tile_bytes(g->NCH);
+    int UB = g->U < EVB_MAX_UNITS_PER_BLOCK ? g->U : EVB_MAX_UNITS_PER_BLOCK;
+    while (UB > 1 && UB * (img + rings) > 227 * 1024) --UB;
+    if (UB * (img + rings) > 227 * 1024) return EVB_ERR_LIMIT; // 256 bins with weights: the caller falls back to the float kernel
+    g->UB = UB; g->NUG = (g->U + UB - 1) / UB; g->stages = QDR;
+    g->smem = UB * (img + rings);
+    const int occ = dispatch_q(g->BP, g->NCH, false, nullptr, dim3(), UB * QWPU * 32, g->smem, 0);
+    if (occ < 1) { evb_set_error("histogram kernel cannot be resident (smem=%zu)", g->smem); return EVB_ERR_CUDA; }
+    g->G = occ * h->num_sms;
+    // the 32-bit partial sums of a piece hold at most 2^17 rows: more (equal) row ranges than resident CTAs if needed
+    if ((long long)g->G * 130000 < h->n) g->G = (int)((h->n + 129999) / 130000 + g->G - 1) / g->G * g->G;
+    g->PG = g->G + h->maxslots;
+    g->img_floats = (size_t)g->NCH * B * 32;
+    return EVB_OK;
+}
+
 int32_t evb_hist_geometry(const evb_handle *h, int F, HistGeom *g) {
+    if (h->use_q && F == h->nfeats) {
+        const int32_t rc = histq_geometry(h, F, g);
+        if (rc != EVB_ERR_LIMIT) return rc;
+    }
     const int B = h->B, C = h->Ce;
+    g->q = false;
     g->BP = B <= 32 ? 32 : B <= 64 ? 64 : B <= 128 ? 128 : 256;
     g->NCT = (C + 3) / 4;              // channel groups; channels are spread evenly over them
     g->NCH = (C + g->NCT - 1) / g->NCT;
@@ -657,6 +1009,7 @@ int32_t evb_hist_geometry(const evb_handle *h, int F, HistGeom *g) {
 
 int32_t evb_hist_configure(evb_handle *h) {
     EVB_CHECK(evb_hist_geometry(h, h->nfeats, &h->hg));
+    h->q_active = h->hg.q;
     h->scratch_floats = (size_t)h->hg.NUG * h->hg.PG * h->hg.UB * h->hg.img_floats;
     return EVB_OK;
 }
@@ -664,7 +1017,7 @@ int32_t evb_hist_configure(evb_handle *h) {
 int32_t evb_launch_hist(evb_handle *h, int level) {
     const HistGeom &g = h->hg;
     HistArgs a;
-    a.xT = h->xT; a.grad = h->grad; a.rows = h->rows[(level - 1) & 1]; a.js0 = h->js_d;
+    a.xT = h->xT; a.grad = h->q_active ? reinterpret_cast<const float *>(h->gradq) : h->grad; a.rows = h->rows[(level - 1) & 1]; a.js0 = h->js_d;
     a.plan = h->plan + level; a.cum = h->cum; a.slot_node = h->slot_node; a.seg_start = h->seg_start;
     a.scratch = h->scratch; a.err = h->d_err;
     a.RS = h->RS; a.GS = h->GS; a.F = h->F; a.nbins = h->B; a.C = h->Ce; a.NFG = g.NFG; a.U = g.U; a.UB = g.UB;
@@ -672,9 +1025,9 @@ int32_t evb_launch_hist(evb_handle *h, int level) {
     a.mode = h->hist_mode;
     a.contig = h->F == h->nfeats ? 1 : 0;
     dim3 grid(g.G, g.NUG);
-    const int threads = (g.UB + 1) * 32;
+    const int threads = h->q_active ? g.UB * QWPU * 32 : (g.UB + 1) * 32;
     evb_tic(h, EVB_T_HIST);
-    cudaError_t e = launch_hist(g, a, grid, threads, h->st);
+    cudaError_t e = h->q_active ? (cudaError_t)dispatch_q(g.BP, g.NCH, true, &a, grid, threads, g.smem, h->st) : launch_hist(g, a, grid, threads, h->st);
     evb_toc(h, EVB_T_HIST);
     EVB_CUDA(e);
     return EVB_OK;
@@ -682,6 +1035,21 @@ int32_t evb_launch_hist(evb_handle *h, int level) {
 
 int32_t evb_launch_hist_reduce(evb_handle *h, int level) {
     const HistGeom &g = h->hg;
+    if (h->q_active) {
+        ReduceQArgs a;
+        a.scratch = reinterpret_cast<const uint32_t *>(h->scratch); a.hcomp = h->hcomp; a.plan = h->plan + level; a.cum = h->cum;
+        a.qinv = h->d_qinv; a.G = g.G; a.PG = g.PG; a.UB = g.UB; a.NFG = g.NFG; a.F = h->F; a.nbins = h->B; a.NW = g.NCH;
+        a.img_words = (uint32_t)g.img_floats;
+        const int slots = evb_level_slots(level);
+        evb_tic(h, EVB_T_HIST_REDUCE);
+        if (slots <= 2) k_histq_reduce<1><<<dim3(slots, g.NFG * 2, h->B), 512, 0, h->st>>>(a);
+        else if (slots <= 8) k_histq_reduce<4><<<dim3(slots, g.NFG * 2, (h->B + 3) / 4), 512, 0, h->st>>>(a);
+        else if (slots <= 32) k_histq_reduce<16><<<dim3(slots, g.NFG * 2, (h->B + 15) / 16), 512, 0, h->st>>>(a);
+        else k_histq_reduce_unit<<<dim3(slots, g.NFG), 256, 0, h->st>>>(a);
+        evb_toc(h, EVB_T_HIST_REDUCE);
+        EVB_CUDA(cudaGetLastError());
+        return EVB_OK;
+    }
     ReduceArgs a;
     a.scratch = h->scratch; a.hcomp = h->hcomp; a.plan = h->plan + level; a.cum = h->cum;
     a.G = g.G; a.PG = g.PG; a.UB = g.UB; a.NFG = g.NFG; a.U = g.U; a.F = h->F; a.C = h->C; a.Ce = h->Ce; a.K = h->K; a.nbins = h->B; a.NCH = g.NCH; a.FPL = g.FPL;

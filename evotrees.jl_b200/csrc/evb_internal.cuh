@@ -57,6 +57,7 @@ struct HistGeom {
     int NUG;       // unit groups = ceil(U/UB)
     int stages;    // staged tiles in flight
     int G;         // row-range blocks (grid.x)
+    bool q;        // geometry of the fixed-point kernel
     int PG;        // piece slots per unit group = G + max build slots
     size_t smem;   // dynamic shared memory per block
     size_t img_floats;   // floats per unit image in scratch: FPL*NCH*nbins*32
@@ -66,6 +67,7 @@ struct evb_handle {
     evb_params p;
     int K, C, B, D, nn;        // nn = 2^D-1
     int Ce;                    // channels actually accumulated: C, or K+1 for mse where h = 2w is rebuilt from w
+    int rec_nch;               // channels per 16-byte group of the float gradient record (see gpos)
     int nfeats, RS, GS;        // RS: bytes per row of xT (multiple of 32); GS: floats per grad record (multiple of 4)
     int64_t n;                 // local rows
     int dev, num_sms;
@@ -122,6 +124,15 @@ struct evb_handle {
     int ev_metric, ev_blocks;
     double last_eval[2]; // sums of the tree collected last
 
+    // fixed-point histogram variant (mse, one target): gradq holds the integer words of every row
+    bool use_q, unit_w;   // unit_w: no weights were given, the w channel is a row count
+    bool q_active;        // the current geometry is the fixed-point one (no column sample)
+    bool gradq_valid;     // gradq holds the words of the current gradients
+    int32_t *gradq;       // [n] fixed-point g, or [n][2] fixed-point g and w when weights were given
+    unsigned *d_gmax;     // bits of max |g| over the rows, filled by the gradient kernels
+    double *d_qinv;       // [2] 2^-s of the g words / of the w words
+    float wscale; double winv;
+
     // histograms
     HistGeom hg;
     int hist_mode;    // EVB_HIST_MODE environment override (kernel variants / diagnostics)
@@ -138,9 +149,9 @@ struct evb_handle {
     int tree_seq, pending;          // trees started / started but not yet collected
     // one CUDA graph per variant of the per-tree launch sequence (mask, gradients first, gradients fused, slot)
     bool use_graphs;
-    cudaGraphExec_t graph[16];
-    int graph_calls[16];
-    int64_t graph_launches[16][EVB_NTIMERS];
+    cudaGraphExec_t graph[32];
+    int graph_calls[32];
+    int64_t graph_launches[32][EVB_NTIMERS];
     int graph_mask_cond;
 
     // multi-GPU
@@ -165,6 +176,7 @@ struct evb_handle {
 // evb_rows.cu
 int32_t evb_launch_transpose(evb_handle *h, const uint8_t *xcol_dev, int64_t ld, int64_t nrows, int j0, int nj, uint8_t *xT, int RS, cudaStream_t st);
 int32_t evb_launch_grads(evb_handle *h);
+int32_t evb_launch_quantize(evb_handle *h);
 int32_t evb_launch_rows_init(evb_handle *h, bool use_mask, uint8_t mask_cond);
 int32_t evb_launch_finalize(evb_handle *h, bool compute_grads);
 int32_t evb_launch_nidx_from_partition(evb_handle *h, uint32_t *out_dev);

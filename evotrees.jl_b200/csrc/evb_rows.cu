@@ -130,10 +130,48 @@ __global__ void k_init_state(float *grad, float *pred, const float *w, const flo
 }
 
 // ---------------------------------------------------------------------------------- gradients
-__global__ void k_grads(int loss, int K, int GS, int NCH, int elided, int ycols, long long n, const float *pred, const void *y, float *grad) {
+// max |g| over the rows of a 256-thread block -> global maximum (bit pattern of a non-negative float, which orders
+// like an unsigned integer).  Every thread of the block must call it.
+__device__ __forceinline__ void block_absmax(float v, unsigned *gmax) {
+    __shared__ unsigned s_max[8];
+    unsigned m = __reduce_max_sync(FULL, __float_as_uint(fabsf(v)));
+    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int q = 1; q < 8; ++q) m = max(m, s_max[q]);
+        if (m > *(volatile unsigned *)gmax) atomicMax(gmax, m);
+    }
+}
+__global__ void __launch_bounds__(256) k_grads(int loss, int K, int GS, int NCH, int elided, int ycols, long long n, const float *pred, const void *y, float *grad, unsigned *gmax) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    float g0 = 0.0f;
+    if (i < n) {
+        grad_row(loss, K, NCH, elided != 0, pred + (size_t)i * K, y, ycols, i, grad + (size_t)i * GS);
+        g0 = grad[(size_t)i * GS];
+    }
+    if (gmax) block_absmax(g0, gmax);
+}
+// Fixed-point gradient of every row for the integer histogram kernel: q = rint(g * 2^s) with 2^s the largest power
+// of two that keeps max |g| * 2^s below 2^29; the weight likewise with its own scale (nothing when no weights were
+// given: the kernel counts rows).  2^-s goes to qinv for the reduce kernel.
+__global__ void __launch_bounds__(256) k_quantize(const float *grad, int32_t *gradq, long long n, const unsigned *gmax, double *qinv,
+                                                   float wscale, double winv, int unit_w) {
+    const float m = __uint_as_float(*gmax);
+    float sc = 1.0f;
+    double inv = 1.0;
+    if (m > 0.0f && m < INFINITY) {
+        int e;
+        frexpf(m, &e); // m = f * 2^e, f in [0.5, 1)
+        sc = ldexpf(1.0f, 29 - e);
+        inv = ldexp(1.0, e - 29);
+    }
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i == 0) { qinv[0] = inv; qinv[1] = unit_w ? 1.0 : winv; }
     if (i >= n) return;
-    grad_row(loss, K, NCH, elided != 0, pred + (size_t)i * K, y, ycols, i, grad + (size_t)i * GS);
+    const float2 gw = reinterpret_cast<const float2 *>(grad)[i * 2]; // record = g, w, pad, pad
+    const int q = __float2int_rn(gw.x * sc);
+    if (unit_w) gradq[i] = q;
+    else reinterpret_cast<int2 *>(gradq)[i] = make_int2(q, __float2int_rn(gw.y * wscale));
 }
 
 // ---------------------------------------------------------------------------------- row sampling
@@ -223,6 +261,7 @@ struct FinArgs {
     float *pred, *grad;
     const void *y;
     uint32_t *nidx;
+    unsigned *gmax; // non-null: track max |g| of the gradients computed here (fixed-point histogram variant)
     long long n;
     int RS, K, GS, NCH, elided, loss, nn, ycols, compute_grads, packed_in_smem;
 };
@@ -235,12 +274,18 @@ __global__ void __launch_bounds__(256) k_finalize(FinArgs a) {
         packed = s_packed;
     }
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= a.n) return;
-    const int nid = traverse(packed, a.xT + (size_t)i * a.RS);
-    a.nidx[i] = (uint32_t)nid;
-    float *p = a.pred + (size_t)i * a.K;
-    pred_add(a.loss, a.K, p, a.t_pred + (size_t)(nid - 1) * a.K);
-    if (a.compute_grads) grad_row(a.loss, a.K, a.NCH, a.elided != 0, p, a.y, a.ycols, i, a.grad + (size_t)i * a.GS);
+    float g0 = 0.0f;
+    if (i < a.n) {
+        const int nid = traverse(packed, a.xT + (size_t)i * a.RS);
+        a.nidx[i] = (uint32_t)nid;
+        float *p = a.pred + (size_t)i * a.K;
+        pred_add(a.loss, a.K, p, a.t_pred + (size_t)(nid - 1) * a.K);
+        if (a.compute_grads) {
+            grad_row(a.loss, a.K, a.NCH, a.elided != 0, p, a.y, a.ycols, i, a.grad + (size_t)i * a.GS);
+            g0 = a.grad[(size_t)i * a.GS];
+        }
+    }
+    if (a.gmax && a.compute_grads) block_absmax(g0, a.gmax);
 }
 
 // node of every sampled row from the row lists left by the partition kernels; one CTA per node
@@ -451,14 +496,24 @@ int32_t evb_launch_check_bins(evb_handle *h) {
 }
 
 int32_t evb_launch_init_state(evb_handle *h, const float *w_dev, const float *pred0_dev, const float *mu_dev) {
-    k_init_state<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->grad, h->pred, w_dev, pred0_dev, mu_dev, h->n, h->K, h->GS, h->hg.NCH, h->Ce - 1);
+    k_init_state<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->grad, h->pred, w_dev, pred0_dev, mu_dev, h->n, h->K, h->GS, h->rec_nch, h->Ce - 1);
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
 }
 
 int32_t evb_launch_grads(evb_handle *h) {
+    if (h->use_q) EVB_CUDA(cudaMemsetAsync(h->d_gmax, 0, sizeof(unsigned), h->st));
     evb_tic(h, EVB_T_GRADS);
-    k_grads<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->p.loss, h->K, h->GS, h->hg.NCH, h->Ce != h->C, h->ycols, h->n, h->pred, h->y, h->grad);
+    k_grads<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->p.loss, h->K, h->GS, h->rec_nch, h->Ce != h->C, h->ycols, h->n, h->pred, h->y, h->grad,
+                                                                h->use_q ? h->d_gmax : nullptr);
+    evb_toc(h, EVB_T_GRADS);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+int32_t evb_launch_quantize(evb_handle *h) {
+    evb_tic(h, EVB_T_GRADS);
+    k_quantize<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->grad, h->gradq, h->n, h->d_gmax, h->d_qinv, h->wscale, h->winv, h->unit_w ? 1 : 0);
     evb_toc(h, EVB_T_GRADS);
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
@@ -482,7 +537,9 @@ int32_t evb_launch_rows_init(evb_handle *h, bool use_mask, uint8_t mask_cond) {
 int32_t evb_launch_finalize(evb_handle *h, bool compute_grads) {
     FinArgs a;
     a.xT = h->xT; a.t_packed = h->t_packed; a.t_pred = h->t_pred; a.pred = h->pred; a.grad = h->grad; a.y = h->y;
-    a.nidx = h->nidx; a.n = h->n; a.RS = h->RS; a.K = h->K; a.GS = h->GS; a.NCH = h->hg.NCH; a.elided = h->Ce != h->C; a.loss = h->p.loss; a.nn = h->nn;
+    a.nidx = h->nidx; a.n = h->n; a.RS = h->RS; a.K = h->K; a.GS = h->GS; a.NCH = h->rec_nch; a.elided = h->Ce != h->C; a.loss = h->p.loss; a.nn = h->nn;
+    a.gmax = h->use_q ? h->d_gmax : nullptr;
+    if (h->use_q && compute_grads) EVB_CUDA(cudaMemsetAsync(h->d_gmax, 0, sizeof(unsigned), h->st));
     a.ycols = h->ycols; a.compute_grads = compute_grads ? 1 : 0;
     const size_t smem = (size_t)h->nn * 4;
     a.packed_in_smem = smem <= 40 * 1024 ? 1 : 0;
