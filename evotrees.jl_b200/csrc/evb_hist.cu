@@ -420,20 +420,23 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
 // NW words (hi, lo, 1) or (hi, lo, w_hi, w_lo) into the image [word][bin][lane] of the unit with
 // `red.shared.add.u32`: one shared-memory pass per word and row, no read-modify-write chain.  Integer sums do not
 // depend on the order of the rows, so
-//   * several warps share one image: a CTA (one per SM) keeps a single image per unit of 32 feature slots and
-//     QWPU warps per unit take the 32-row tiles of the CTA's row range in turn;
-//   * the shared memory that the float variant spends on one image per warp holds row data in flight instead:
-//     there is no producer warp and no mbarrier -- every warp stages the 32-byte slice of bins of its unit and the
-//     4 (8) bytes of q of the rows of its own tiles with cp.async into a private ring, QDR tiles deep, and waits
-//     with cp.async.wait_group.
+//   * several warps share one image: a CTA (one per SM) keeps a single image per unit of 32 feature slots;
+//   * the shared memory that the float variant spends on one image per warp holds row data in flight instead.
+//     The warps form QT teams with one warp per unit.  The teams take the 32-row tiles of the CTA's row range in
+//     turn; a team stages its tile together with cp.async -- eight adjacent lanes copy the 128 bytes of one row,
+//     so a copy instruction touches 4 lines instead of 32 -- into a ring QDR tiles deep (+1 slot so that one
+//     named barrier per tile is enough), waits with cp.async.wait_group and the team barrier, and then every warp
+//     adds the tile into the image of its unit.  There is no producer warp and no mbarrier.
+//     Row r of a tile is stored rotated by 32 * (r & 3) bytes inside its 128 bytes, so that the four rows which
+//     the consumers read with one load fall into different banks.
 // A piece covers at most 2^17 rows, so neither the sum of the lo words (< 2^32) nor of the hi words (|.| < 2^31)
 // can overflow.  The reduce kernel recombines hi * 2^15 + lo in 64-bit integers and scales by 2^-s: every
 // histogram entry is the exact sum of the quantised gradients, whatever the order and the number of pieces.
 // Needs feature slot s == feature s (no column sample): the unit's bins are then 32 adjacent bytes of a row.
-constexpr int QWPU = 4;                 // warps per unit
-constexpr int QDR = 6;                  // tiles in flight per warp
+constexpr int QT = 4;                   // teams per CTA
+constexpr int QDR = 5;                  // tiles in flight per team
 constexpr int QSPLIT = 15;              // q = hi * 2^15 + lo: a piece may hold 2^17 rows (|q| < 2^29)
-__host__ __device__ constexpr int q_tile_bytes(int NW) { return EVB_TILE_ROWS * (32 + (NW == 3 ? 4 : 8)); } // bins + q (+ q of w)
+__host__ __device__ constexpr int q_tile_bytes(int NW) { return EVB_TILE_ROWS * (128 + (NW == 3 ? 4 : 8)); } // bins + q (+ q of w)
 
 template <uint32_t OFF>
 __device__ __forceinline__ void red_off(uint32_t addr, uint32_t v) {
@@ -454,26 +457,29 @@ __device__ __forceinline__ void red_row(uint32_t addr, uint32_t qg, uint32_t qw)
 __device__ __forceinline__ void lds_v4(uint32_t addr, uint32_t (&w)[4]) {
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
 }
-// All rows of one staged tile.  Four rows at a time: lane (k = lane & 7, rr = lane >> 3) loads the 32-bit word with
-// the bins of features 4k .. 4k+3 of row r + rr -- one conflict-free load brings the 128 bins of four rows -- and the
-// fixed-point words of that row.  In step j = 0..3 the lane adds its row into feature 4k + ((j + rr) & 3): the four
-// lanes that share k work on four different features, so the 32 lanes of every reduction hit 32 different banks.
-//   tb: shared-space address of the tile's bins + k * 4 + rr * 32, tw: of its words + rr * (4 or 8),
+// All rows of one staged tile.  4 * REP rows at a time.  With REP = 1 lane (k = lane & 7, rr = lane >> 3) loads the
+// 32-bit word with the bins of features 4k .. 4k+3 of row r + rr -- one conflict-free load brings the 128 bins of
+// four rows -- and the fixed-point words of that row.  In step j = 0..3 the lane adds its row into feature
+// 4k + ((j + rr) & 3): the four lanes that share k work on four different features, so the 32 lanes of every
+// reduction hit 32 different banks.  A unit with few features (the last one: 8 / REP groups of four features or
+// fewer) keeps REP replicas of its columns instead, k = lane % (8 / REP), rr = lane / (8 / REP), replica rr >> 2,
+// and takes 4 * REP rows per step; the replicas are added when the image is flushed.
+//   tb: shared-space address of the lane's word of row rr of the tile, tw: of the tile's words + rr * (4 or 8),
 //   col[j]: image column of the lane's feature of step j, sel[j]: PRMT selector of that feature's byte.
-template <int NW, uint32_t WSZ>
+template <int NW, uint32_t WSZ, int REP>
 __device__ __forceinline__ void q_tile(uint32_t tb, uint32_t tw, int nrows, int rr, const uint32_t (&col)[4], const uint32_t (&sel)[4]) {
     constexpr int RW = NW == 3 ? 1 : 2;
-    constexpr int NB = EVB_TILE_ROWS / 4;
+    constexpr int RB = 4 * REP, NB = EVB_TILE_ROWS / RB;
     uint32_t bins = lds_u32(tb), qg = lds_u32(tw), qw = RW == 2 ? lds_u32(tw + 4) : 0u;
 #pragma unroll
     for (int bt = 0; bt < NB; ++bt) {
         uint32_t nbins = 0, nqg = 0, nqw = 0;
-        if (bt + 1 < NB) { // loads of the next four rows before the reductions of these
-            nbins = lds_u32(tb + (bt + 1) * 128);
-            nqg = lds_u32(tw + (bt + 1) * 16 * RW);
-            if constexpr (RW == 2) nqw = lds_u32(tw + (bt + 1) * 32 + 4);
+        if (bt + 1 < NB) { // loads of the next rows before the reductions of these
+            nbins = lds_u32(tb + (bt + 1) * RB * 128);
+            nqg = lds_u32(tw + (bt + 1) * RB * 4 * RW);
+            if constexpr (RW == 2) nqw = lds_u32(tw + (bt + 1) * RB * 8 + 4);
         }
-        if (bt * 4 + rr < nrows) {
+        if (bt * RB + rr < nrows) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) red_row<NW, WSZ>(col[j] + __byte_perm(bins, 0u, sel[j]) * 128u, qg, qw);
         }
@@ -482,10 +488,11 @@ __device__ __forceinline__ void q_tile(uint32_t tb, uint32_t tw, int nrows, int 
 }
 
 template <int BP, int NW>
-__global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QWPU * 32) k_histq(HistArgs a) {
+__global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QT * 32) k_histq(HistArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr uint32_t WSZ = (BP + 1) * 128;    // bytes of one word plane [bin 0..BP][lane]
     constexpr uint32_t IMG = NW * WSZ;
+    constexpr int QTILE = q_tile_bytes(NW), RW = NW == 3 ? 1 : 2, NSLOT = QDR + 1;
     const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, b = blockIdx.x, ug = blockIdx.y;
     const int nact = min(a.UB, a.U - ug * a.UB);
@@ -495,7 +502,7 @@ __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QWPU * 32) k_histq(H
     uint32_t *imgs = reinterpret_cast<uint32_t *>(smem);
     for (int i = tid; i < a.UB * (int)(IMG / 4); i += blockDim.x) imgs[i] = 0u;
     __syncthreads();
-    const int uw = wid / QWPU, j = wid % QWPU;
+    const int team = wid / a.UB, uw = wid % a.UB;
     if (uw >= nact) return;
 
     const int nbuild = a.plan->nbuild;
@@ -507,20 +514,36 @@ __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QWPU * 32) k_histq(H
     }
     const int fg = ug * a.UB + uw;          // the unit: feature slots fg*32 .. fg*32+31
     const uint32_t u0 = smem_u32(smem) + (uint32_t)uw * IMG + lane * 4; // column of feature slot `lane` (flush)
-    const int k = lane & 7, rr = lane >> 3;
+    // groups of four features in this unit -> replicas of its columns (see q_tile)
+    const int nq = min(8, (a.F - fg * 32 + 3) / 4);
+    const int rep = nq <= 1 ? 8 : nq <= 2 ? 4 : nq <= 4 ? 2 : 1, nqp = 8 / rep;
+    const int k = lane % nqp, rr = lane / nqp;
     uint32_t col[4], sel[4];
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
         const int sh = (jj + rr) & 3;
-        col[jj] = smem_u32(smem) + (uint32_t)uw * IMG + (uint32_t)(4 * k + sh) * 4;
+        col[jj] = smem_u32(smem) + (uint32_t)uw * IMG + (uint32_t)((rr >> 2) * nqp * 4 + 4 * k + sh) * 4;
         sel[jj] = 0x4440u | (uint32_t)sh;
     }
-    constexpr int QTILE = q_tile_bytes(NW), RW = NW == 3 ? 1 : 2;
-    unsigned char *ring = smem + (size_t)a.UB * IMG + (size_t)wid * (QDR * QTILE);
+    unsigned char *ring = smem + (size_t)a.UB * IMG + (size_t)team * (NSLOT * QTILE);
     const uint32_t ring_s = smem_u32(ring);
-    const uint8_t *xsl = a.xT + fg * 32;    // the unit's slice of every row of bins
+    // the lane's word of row rr inside a tile (rows are rotated by 32 * (row & 3) bytes)
+    const uint32_t rd_off = (uint32_t)rr * 128u + ((uint32_t)(uw * 32 + k * 4 + 32 * (rr & 3)) & 127u);
+    // staging: the team copies 32 rows x nact * 32 bytes of bins as 16-byte chunks, two per lane
+    const int cpr = 2 * nact;               // chunks per row
+    int st_row[2], st_src[2], st_dst[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int c = t * nact * 32 + uw * 32 + lane;
+        st_row[t] = c / cpr;
+        const int pch = c % cpr;
+        st_src[t] = pch * 16;
+        st_dst[t] = st_row[t] * 128 + ((pch + 2 * (st_row[t] & 3)) & 7) * 16;
+    }
+    const uint8_t *xsl = a.xT + (size_t)ug * a.UB * 32;  // the CTA's slice of every row of bins
     const int32_t *gq = reinterpret_cast<const int32_t *>(a.grad);
     const size_t RS = a.RS;
+    const uint32_t team_bar = 1 + team, unit_bar = 1 + QT + uw;
 
     long long pos = lo;
     while (pos < hi) {
@@ -528,54 +551,65 @@ __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QWPU * 32) k_histq(H
         if (send > pos) {
             const uint32_t *rows = a.rows + ((long long)a.seg_start[a.slot_node[s]] - a.cum[s]);
             const long long ntiles = (send - pos + EVB_TILE_ROWS - 1) / EVB_TILE_ROWS;
-            const int nmine = ntiles > j ? (int)((ntiles - j + QWPU - 1) / QWPU) : 0; // tiles j, j + QWPU, ...
-            // row id of this lane in my k-th tile (0 beyond the end of the segment: never copied)
-            auto rid_of = [&](int k) -> uint32_t {
-                const long long q = pos + ((long long)k * QWPU + j) * EVB_TILE_ROWS + lane;
-                return (k < nmine && q < send) ? rows[q] : 0u;
+            const int nmine = ntiles > team ? (int)((ntiles - team + QT - 1) / QT) : 0; // tiles team, team + QT, ...
+            // row id of row `lane` of the team's k-th tile (0 beyond the end of the segment: never copied)
+            auto rid_of = [&](int kk) -> uint32_t {
+                const long long q = pos + ((long long)kk * QT + team) * EVB_TILE_ROWS + lane;
+                return (kk < nmine && q < send) ? rows[q] : 0u;
             };
             uint32_t r0 = rid_of(0), r1 = rid_of(1);
             for (int i = 0; i < nmine + QDR - 1; ++i) {
                 const uint32_t r2 = rid_of(i + 2);
-                if (i < nmine) { // stage my tile i: lane = row of the tile
-                    const long long q = pos + ((long long)i * QWPU + j) * EVB_TILE_ROWS + lane;
-                    if (q < send) {
-                        unsigned char *dst = ring + (i % QDR) * QTILE;
-                        const uint8_t *src = xsl + (size_t)r0 * RS;
-                        cp_async16(dst + lane * 32, src);
-                        cp_async16(dst + lane * 32 + 16, src + 16);
-                        if constexpr (RW == 1) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst + EVB_TILE_ROWS * 32 + lane * 4)), "l"(gq + r0) : "memory");
-                        else asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst + EVB_TILE_ROWS * 32 + lane * 8)), "l"(gq + (size_t)r0 * 2) : "memory");
+                if (i < nmine) { // stage the team's tile i
+                    const long long q0 = pos + ((long long)i * QT + team) * EVB_TILE_ROWS;
+                    const int nrows = (int)min((long long)EVB_TILE_ROWS, send - q0);
+                    unsigned char *dst = ring + (i % NSLOT) * QTILE;
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        const uint32_t rid = __shfl_sync(0xffffffffu, r0, st_row[t]);
+                        if (st_row[t] < nrows) cp_async16(dst + st_dst[t], xsl + (size_t)rid * RS + st_src[t]);
+                    }
+                    if (uw == 0 && lane < nrows) {
+                        if constexpr (RW == 1) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst + EVB_TILE_ROWS * 128 + lane * 4)), "l"(gq + r0) : "memory");
+                        else asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst + EVB_TILE_ROWS * 128 + lane * 8)), "l"(gq + (size_t)r0 * 2) : "memory");
                     }
                 }
                 asm volatile("cp.async.commit_group;" ::: "memory");
                 r0 = r1; r1 = r2;
-                if (i >= QDR - 1) { // consume my tile c: lane = feature slot of the unit
+                if (i >= QDR - 1) { // consume the team's tile c
                     const int c = i - (QDR - 1);
                     asm volatile("cp.async.wait_group %0;" ::"n"(QDR - 1) : "memory");
-                    __syncwarp();
-                    const long long q0 = pos + ((long long)c * QWPU + j) * EVB_TILE_ROWS;
+                    // the copies of all warps of the team have landed, and everybody is done with tile c - 1
+                    asm volatile("bar.sync %0, %1;" ::"r"(team_bar), "r"(nact * 32) : "memory");
+                    const long long q0 = pos + ((long long)c * QT + team) * EVB_TILE_ROWS;
                     const int nrows = (int)min((long long)EVB_TILE_ROWS, send - q0);
-                    const uint32_t ts = ring_s + (c % QDR) * QTILE;
-                    if (!(a.mode & 16)) q_tile<NW, WSZ>(ts + k * 4 + rr * 32, ts + EVB_TILE_ROWS * 32 + rr * 4 * RW, nrows, rr, col, sel);
-                    __syncwarp(); // the slot is staged again in the next iteration
+                    const uint32_t ts = ring_s + (c % NSLOT) * QTILE;
+                    if (!(a.mode & 16)) {
+                        const uint32_t tb = ts + rd_off, tw = ts + EVB_TILE_ROWS * 128 + rr * 4 * RW;
+                        if (rep == 1) q_tile<NW, WSZ, 1>(tb, tw, nrows, rr, col, sel);
+                        else if (rep == 2) q_tile<NW, WSZ, 2>(tb, tw, nrows, rr, col, sel);
+                        else if (rep == 4) q_tile<NW, WSZ, 4>(tb, tw, nrows, rr, col, sel);
+                        else q_tile<NW, WSZ, 8>(tb, tw, nrows, rr, col, sel);
+                    }
                 }
             }
             asm volatile("cp.async.wait_group 0;" ::: "memory");
+            asm volatile("bar.sync %0, %1;" ::"r"(team_bar), "r"(nact * 32) : "memory"); // ring free for the next segment
             // all warps of the unit are done with the segment: flush the piece (CTA b, slot s), clear the image
-            asm volatile("bar.sync %0, %1;" ::"r"(1 + uw), "r"(QWPU * 32) : "memory");
+            asm volatile("bar.sync %0, %1;" ::"r"(unit_bar), "r"(QT * 32) : "memory");
             uint32_t *dst = reinterpret_cast<uint32_t *>(a.scratch) + ((size_t)(ug * a.PG + b + s) * a.UB + uw) * a.img_floats + lane;
 #pragma unroll
             for (int q = 0; q < NW; ++q) {
-                if (j == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(u0 + q * WSZ), "r"(0u) : "memory"); // guard row
-                for (int bin = j; bin < a.nbins; bin += QWPU) {
+                if (team == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(u0 + q * WSZ), "r"(0u) : "memory"); // guard row
+                for (int bin = team; bin < a.nbins; bin += QT) {
                     const uint32_t ai = u0 + q * WSZ + (uint32_t)(bin + 1) * 128u;
-                    const uint32_t v = lds_u32(ai);
+                    uint32_t v = lds_u32(ai);
                     asm volatile("st.shared.u32 [%0], %1;" ::"r"(ai), "r"(0u) : "memory");
+                    for (int o = 32 / rep; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o); // add the replicas
                     dst[(q * a.nbins + bin) * 32] = v;
                 }
             }
-            asm volatile("bar.sync %0, %1;" ::"r"(1 + uw), "r"(QWPU * 32) : "memory");
+            asm volatile("bar.sync %0, %1;" ::"r"(unit_bar), "r"(QT * 32) : "memory");
         }
         pos = send;
         ++s;
@@ -928,13 +962,13 @@ static int32_t histq_geometry(const evb_handle *h, int F, HistGeom *g) {
     g->NCT = 1; g->NCH = h->unit_w ? 3 : 4; g->FPL = 1;
     g->NFG = (F + 31) / 32;
     g->U = g->NFG;
-    const size_t img = (size_t)g->NCH * (g->BP + 1) * 128, rings = (size_t)QWPU * QDR * q_tile_bytes(g->NCH);
+    const size_t img = (size_t)g->NCH * (g->BP + 1) * 128, rings = (size_t)QT * (QDR + 1) * q_tile_bytes(g->NCH); // rings: per CTA
     int UB = g->U < EVB_MAX_UNITS_PER_BLOCK ? g->U : EVB_MAX_UNITS_PER_BLOCK;
-    while (UB > 1 && UB * (img + rings) > 227 * 1024) --UB;
-    if (UB * (img + rings) > 227 * 1024) return EVB_ERR_LIMIT; // 256 bins with weights: the caller falls back to the float kernel
+    while (UB > 1 && UB * img + rings > 227 * 1024) --UB;
+    if (UB * img + rings > 227 * 1024) return EVB_ERR_LIMIT; // 256 bins with weights: the caller falls back to the float kernel
     g->UB = UB; g->NUG = (g->U + UB - 1) / UB; g->stages = QDR;
-    g->smem = UB * (img + rings);
-    const int occ = dispatch_q(g->BP, g->NCH, false, nullptr, dim3(), UB * QWPU * 32, g->smem, 0);
+    g->smem = UB * img + rings;
+    const int occ = dispatch_q(g->BP, g->NCH, false, nullptr, dim3(), UB * QT * 32, g->smem, 0);
     if (occ < 1) { evb_set_error("histogram kernel cannot be resident (smem=%zu)", g->smem); return EVB_ERR_CUDA; }
     g->G = occ * h->num_sms;
     // the 32-bit partial sums of a piece hold at most 2^17 rows: more (equal) row ranges than resident CTAs if needed
@@ -1025,7 +1059,7 @@ int32_t evb_launch_hist(evb_handle *h, int level) {
     a.mode = h->hist_mode;
     a.contig = h->F == h->nfeats ? 1 : 0;
     dim3 grid(g.G, g.NUG);
-    const int threads = h->q_active ? g.UB * QWPU * 32 : (g.UB + 1) * 32;
+    const int threads = h->q_active ? g.UB * QT * 32 : (g.UB + 1) * 32;
     evb_tic(h, EVB_T_HIST);
     cudaError_t e = h->q_active ? (cudaError_t)dispatch_q(g.BP, g.NCH, true, &a, grid, threads, g.smem, h->st) : launch_hist(g, a, grid, threads, h->st);
     evb_toc(h, EVB_T_HIST);
