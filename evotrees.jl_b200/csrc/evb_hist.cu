@@ -434,22 +434,29 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
 // histogram entry is the exact sum of the quantised gradients, whatever the order and the number of pieces.
 // Needs feature slot s == feature s (no column sample): the unit's bins are then 32 adjacent bytes of a row.
 constexpr int QT = 4;                   // teams per CTA
-constexpr int QDR = 5;                  // tiles in flight per team
-constexpr int QSPLIT = 15;              // q = hi * 2^15 + lo: a piece may hold 2^17 rows (|q| < 2^29)
+constexpr int QDR = 7;                  // tiles in flight per team
+constexpr int QSPLIT = 15;              // scratch words: sum = hi * 2^15 + lo, a piece may hold 2^17 rows (|q| < 2^29)
+// Unit weights (NW == 3): the image has two planes only.  q (|q| < 2^26) is split at bit 8 and the row count rides in
+// the upper 12 bits of the lo word: plane 0 += q >> 8, plane 1 += (q & 0xff) | 1 << 20.  That holds QSUB * QT tiles
+// (3968 rows: lo sum < 2^20, count < 2^12, |hi sum| < 2^30); then the image is flushed into the piece's scratch
+// words (hi, lo, count as above), which are private to the CTA (first flush: stores, later ones: red.global.add).
+constexpr int QSUB = 31;                // tiles per team between two flushes
+__host__ __device__ constexpr int q_planes(int NW) { return NW == 3 ? 2 : 4; }
 __host__ __device__ constexpr int q_tile_bytes(int NW) { return EVB_TILE_ROWS * (128 + (NW == 3 ? 4 : 8)); } // bins + q (+ q of w)
 
 template <uint32_t OFF>
 __device__ __forceinline__ void red_off(uint32_t addr, uint32_t v) {
     asm volatile("red.shared.add.u32 [%0+%2], %1;" ::"r"(addr), "r"(v), "n"(OFF) : "memory");
 }
-// adds one row into the word planes of the image (plane k starts k * WSZ bytes further): hi and lo part of the
-// fixed-point gradient, then the row count (NW == 3) or hi and lo part of the fixed-point weight (NW == 4)
+// adds one row into the word planes of the image (plane k starts k * WSZ bytes further)
 template <int NW, uint32_t WSZ>
 __device__ __forceinline__ void red_row(uint32_t addr, uint32_t qg, uint32_t qw) {
-    red_off<0>(addr, (uint32_t)((int32_t)qg >> QSPLIT));
-    red_off<WSZ>(addr, qg & ((1u << QSPLIT) - 1));
-    if constexpr (NW == 3) red_off<2 * WSZ>(addr, 1u);
-    else {
+    if constexpr (NW == 3) {
+        red_off<0>(addr, (uint32_t)((int32_t)qg >> 8));
+        red_off<WSZ>(addr, (qg & 0xffu) | (1u << 20));
+    } else {
+        red_off<0>(addr, (uint32_t)((int32_t)qg >> QSPLIT));
+        red_off<WSZ>(addr, qg & ((1u << QSPLIT) - 1));
         red_off<2 * WSZ>(addr, qw >> QSPLIT);
         red_off<3 * WSZ>(addr, qw & ((1u << QSPLIT) - 1));
     }
@@ -491,7 +498,7 @@ template <int BP, int NW>
 __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QT * 32) k_histq(HistArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr uint32_t WSZ = (BP + 1) * 128;    // bytes of one word plane [bin 0..BP][lane]
-    constexpr uint32_t IMG = NW * WSZ;
+    constexpr uint32_t IMG = q_planes(NW) * WSZ;
     constexpr int QTILE = q_tile_bytes(NW), RW = NW == 3 ? 1 : 2, NSLOT = QDR + 1;
     const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, b = blockIdx.x, ug = blockIdx.y;
@@ -552,6 +559,49 @@ __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QT * 32) k_histq(His
             const uint32_t *rows = a.rows + ((long long)a.seg_start[a.slot_node[s]] - a.cum[s]);
             const long long ntiles = (send - pos + EVB_TILE_ROWS - 1) / EVB_TILE_ROWS;
             const int nmine = ntiles > team ? (int)((ntiles - team + QT - 1) / QT) : 0; // tiles team, team + QT, ...
+            // All warps of the unit are done with the rows so far: move the image into the scratch words of the piece
+            // (CTA b, slot s) and clear it.  `first`: the piece has no contents yet (store instead of add).
+            bool started = false;
+            auto flush = [&](bool first) {
+                asm volatile("bar.sync %0, %1;" ::"r"(unit_bar), "r"(QT * 32) : "memory");
+                uint32_t *dst = reinterpret_cast<uint32_t *>(a.scratch) + ((size_t)(ug * a.PG + b + s) * a.UB + uw) * a.img_floats + lane;
+                const int pl = a.nbins * 32; // words per scratch plane
+                if constexpr (NW == 3) {
+                    if (team == 0) { // guard rows
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(u0), "r"(0u) : "memory");
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(u0 + WSZ), "r"(0u) : "memory");
+                    }
+                    for (int bin = team; bin < a.nbins; bin += QT) {
+                        const uint32_t ai = u0 + (uint32_t)(bin + 1) * 128u;
+                        uint32_t vh = lds_u32(ai), vp = lds_u32(ai + WSZ);
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(ai), "r"(0u) : "memory");
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(ai + WSZ), "r"(0u) : "memory");
+                        for (int o = 32 / rep; o < 32; o <<= 1) { vh += __shfl_xor_sync(0xffffffffu, vh, o); vp += __shfl_xor_sync(0xffffffffu, vp, o); }
+                        const long long sum = (long long)(int32_t)vh * 256 + (long long)(vp & 0xfffffu);
+                        uint32_t h = (uint32_t)(int32_t)(sum >> QSPLIT), l = (uint32_t)(sum & ((1 << QSPLIT) - 1)), c = vp >> 20;
+                        uint32_t *d = dst + bin * 32;
+                        if (first) { d[0] = h; d[pl] = l; d[2 * pl] = c; }
+                        else { // nothing waits for the result: reductions into words that only this thread touches
+                            asm volatile("red.global.add.u32 [%0], %1;" ::"l"(d), "r"(h) : "memory");
+                            asm volatile("red.global.add.u32 [%0], %1;" ::"l"(d + pl), "r"(l) : "memory");
+                            asm volatile("red.global.add.u32 [%0], %1;" ::"l"(d + 2 * pl), "r"(c) : "memory");
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < NW; ++q) {
+                        if (team == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(u0 + q * WSZ), "r"(0u) : "memory"); // guard row
+                        for (int bin = team; bin < a.nbins; bin += QT) {
+                            const uint32_t ai = u0 + q * WSZ + (uint32_t)(bin + 1) * 128u;
+                            uint32_t v = lds_u32(ai);
+                            asm volatile("st.shared.u32 [%0], %1;" ::"r"(ai), "r"(0u) : "memory");
+                            for (int o = 32 / rep; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o); // add the replicas
+                            dst[(q * a.nbins + bin) * 32] = v;
+                        }
+                    }
+                }
+                asm volatile("bar.sync %0, %1;" ::"r"(unit_bar), "r"(QT * 32) : "memory");
+            };
             // row id of row `lane` of the team's k-th tile (0 beyond the end of the segment: never copied)
             auto rid_of = [&](int kk) -> uint32_t {
                 const long long q = pos + ((long long)kk * QT + team) * EVB_TILE_ROWS + lane;
@@ -591,25 +641,14 @@ __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QT * 32) k_histq(His
                         else if (rep == 4) q_tile<NW, WSZ, 4>(tb, tw, nrows, rr, col, sel);
                         else q_tile<NW, WSZ, 8>(tb, tw, nrows, rr, col, sel);
                     }
+                    if constexpr (NW == 3) { // the packed counters are full after QSUB tiles of every team
+                        if ((c + 1) % QSUB == 0 && ntiles > (long long)(c + 1) * QT) { flush(!started); started = true; }
+                    }
                 }
             }
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             asm volatile("bar.sync %0, %1;" ::"r"(team_bar), "r"(nact * 32) : "memory"); // ring free for the next segment
-            // all warps of the unit are done with the segment: flush the piece (CTA b, slot s), clear the image
-            asm volatile("bar.sync %0, %1;" ::"r"(unit_bar), "r"(QT * 32) : "memory");
-            uint32_t *dst = reinterpret_cast<uint32_t *>(a.scratch) + ((size_t)(ug * a.PG + b + s) * a.UB + uw) * a.img_floats + lane;
-#pragma unroll
-            for (int q = 0; q < NW; ++q) {
-                if (team == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(u0 + q * WSZ), "r"(0u) : "memory"); // guard row
-                for (int bin = team; bin < a.nbins; bin += QT) {
-                    const uint32_t ai = u0 + q * WSZ + (uint32_t)(bin + 1) * 128u;
-                    uint32_t v = lds_u32(ai);
-                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(ai), "r"(0u) : "memory");
-                    for (int o = 32 / rep; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o); // add the replicas
-                    dst[(q * a.nbins + bin) * 32] = v;
-                }
-            }
-            asm volatile("bar.sync %0, %1;" ::"r"(unit_bar), "r"(QT * 32) : "memory");
+            flush(!started);
         }
         pos = send;
         ++s;
@@ -962,7 +1001,7 @@ static int32_t histq_geometry(const evb_handle *h, int F, HistGeom *g) {
     g->NCT = 1; g->NCH = h->unit_w ? 3 : 4; g->FPL = 1;
     g->NFG = (F + 31) / 32;
     g->U = g->NFG;
-    const size_t img = (size_t)g->NCH * (g->BP + 1) * 128, rings = (size_t)QT * (QDR + 1) * q_tile_bytes(g->NCH); // rings: per CTA
+    const size_t img = (size_t)q_planes(g->NCH) * (g->BP + 1) * 128, rings = (size_t)QT * (QDR + 1) * q_tile_bytes(g->NCH); // rings: per CTA
     int UB = g->U < EVB_MAX_UNITS_PER_BLOCK ? g->U : EVB_MAX_UNITS_PER_BLOCK;
     while (UB > 1 && UB * img + rings > 227 * 1024) --UB;
     if (UB * img + rings > 227 * 1024) return EVB_ERR_LIMIT; // 256 bins with weights: the caller falls back to the float kernel

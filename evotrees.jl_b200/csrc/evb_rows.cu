@@ -152,18 +152,19 @@ __global__ void __launch_bounds__(256) k_grads(int loss, int K, int GS, int NCH,
     if (gmax) block_absmax(g0, gmax);
 }
 // Fixed-point gradient of every row for the integer histogram kernel: q = rint(g * 2^s) with 2^s the largest power
-// of two that keeps max |g| * 2^s below 2^29; the weight likewise with its own scale (nothing when no weights were
-// given: the kernel counts rows).  2^-s goes to qinv for the reduce kernel.
+// of two that keeps max |g| * 2^s below 2^qbits (26 when no weights were given and the kernel counts rows inside the
+// low word, else 29); the weight likewise with its own scale.  2^-s goes to qinv for the reduce kernel.
 __global__ void __launch_bounds__(256) k_quantize(const float *grad, int32_t *gradq, long long n, const unsigned *gmax, double *qinv,
                                                    float wscale, double winv, int unit_w) {
+    const int qbits = unit_w ? 26 : 29;
     const float m = __uint_as_float(*gmax);
     float sc = 1.0f;
     double inv = 1.0;
     if (m > 0.0f && m < INFINITY) {
         int e;
         frexpf(m, &e); // m = f * 2^e, f in [0.5, 1)
-        sc = ldexpf(1.0f, 29 - e);
-        inv = ldexp(1.0, e - 29);
+        sc = ldexpf(1.0f, qbits - e);
+        inv = ldexp(1.0, e - qbits);
     }
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i == 0) { qinv[0] = inv; qinv[1] = unit_w ? 1.0 : winv; }
