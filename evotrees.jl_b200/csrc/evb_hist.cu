@@ -433,14 +433,14 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
 // can overflow.  The reduce kernel recombines hi * 2^15 + lo in 64-bit integers and scales by 2^-s: every
 // histogram entry is the exact sum of the quantised gradients, whatever the order and the number of pieces.
 // Needs feature slot s == feature s (no column sample): the unit's bins are then 32 adjacent bytes of a row.
-constexpr int QT = 4;                   // teams per CTA
-constexpr int QDR = 7;                  // tiles in flight per team
+constexpr int QT = 6;                   // teams per CTA
+constexpr int QDR = 5;                  // tiles in flight per team
 constexpr int QSPLIT = 15;              // scratch words: sum = hi * 2^15 + lo, a piece may hold 2^17 rows (|q| < 2^29)
 // Unit weights (NW == 3): the image has two planes only.  q (|q| < 2^26) is split at bit 8 and the row count rides in
 // the upper 12 bits of the lo word: plane 0 += q >> 8, plane 1 += (q & 0xff) | 1 << 20.  That holds QSUB * QT tiles
-// (3968 rows: lo sum < 2^20, count < 2^12, |hi sum| < 2^30); then the image is flushed into the piece's scratch
+// (at most 4095 rows: lo sum < 2^20, count < 2^12, |hi sum| < 2^30); then the image is flushed into the piece's scratch
 // words (hi, lo, count as above), which are private to the CTA (first flush: stores, later ones: red.global.add).
-constexpr int QSUB = 31;                // tiles per team between two flushes
+constexpr int QSUB = 4095 / (QT * EVB_TILE_ROWS); // tiles per team between two flushes
 __host__ __device__ constexpr int q_planes(int NW) { return NW == 3 ? 2 : 4; }
 __host__ __device__ constexpr int q_tile_bytes(int NW) { return EVB_TILE_ROWS * (128 + (NW == 3 ? 4 : 8)); } // bins + q (+ q of w)
 
