@@ -311,15 +311,17 @@ def main():
             "metric": "train_seconds_per_200_rounds", "value": ms_step * ROUNDS_PER_JOB / 1e3, "unit": "s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32 gradients / shared-memory partials, f64 histograms and split scan", "data": "synthetic",
+            "dtype": "f32 gradients, exact 32-bit fixed-point partial sums in shared memory, f64 histograms and split scan", "data": "synthetic",
             "config": {"workload": args.workload, "rows": rows, "feats": feats, "max_depth": depth, "nbins": nbins, "loss": "mse",
                        "eta": eta, "rowsample": rowsample, "colsample": colsample, "rows_per_gpu": nloc,
                        "l2_policy": "inputs larger than L2 (x_bin shard %.0f MB)" % (nloc * 128 / 1e6)},
-            "roofline": {"bound": "hbm", "kernel": "k_hist", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": "k_histq", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": (achieved / peak) if achieved else None,
-                         # DRAM bytes per launch: 150 B per streamed row, measured with ncu on a 2M-row case of this
-                         # workload (dram__bytes_read + write = 300.0 MB for 2M rows) and scaled by the rows per launch
-                         "traffic": (150.0 * tm["hist_rows"] / max(1, hist_launches)) if args.workload == "headline_10Mx100_d11" else None,
+                         # DRAM bytes per launch: 145 B per streamed row, measured with ncu on a 2M-row case of this
+                         # workload (dram__bytes_read + write: 306.5 MB for the 2M rows of the root launch = 153 B per
+                         # row, 127.0 MB for the 0.98M rows of the level-2 launch = 130 B per row) and scaled by the
+                         # rows per launch
+                         "traffic": (145.0 * tm["hist_rows"] / max(1, hist_launches)) if args.workload == "headline_10Mx100_d11" else None,
                          "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650",
                          "hist_ms_per_launch": hist_ms / max(1, hist_launches), "hist_launches": hist_launches,
                          "measured_in": "instrumented pass (CUDA events around every launch) of the same rounds right after the timed region",
