@@ -25,7 +25,11 @@ def _depth(n):
 
 
 @pytest.mark.parametrize("weighted", [False, True])
-@pytest.mark.parametrize("nobs,nfeats,nbins,depth", [(60_000, 100, 64, 6), (300_000, 37, 32, 5), (5_000, 9, 255, 4)])
+# shapes: the headline's 3 full units + a 4-feature unit; two units with a short second one and several sub-piece flushes per
+# CTA; one short unit with 255 bins; more than 128 features (several CTA groups per row range); more rows than 148 pieces of
+# 2^17 rows can hold (the row ranges are doubled)
+@pytest.mark.parametrize("nobs,nfeats,nbins,depth", [(60_000, 100, 64, 6), (300_000, 37, 32, 5), (5_000, 9, 255, 4),
+                                                     (40_000, 150, 16, 4), (20_000_000, 4, 8, 3)])
 def test_histograms_are_exact_sums_of_quantised_gradients(pkg, nobs, nfeats, nbins, depth, weighted):
     from evotrees_b200 import _lib
     from evotrees_b200.fit import init_target
@@ -61,7 +65,7 @@ def test_histograms_are_exact_sums_of_quantised_gradients(pkg, nobs, nfeats, nbi
             if rows.size == 0:
                 continue
             hg = cache.hist(n, nfeats, nbins)              # [feature, bin, (g, h, w)]
-            for f in (0, nfeats // 2, nfeats - 1):
+            for f in sorted({0, nfeats // 2, nfeats - 1}):
                 b = x_bin[rows, f].astype(np.int64) - 1
                 sg = np.zeros(nbins, np.int64); np.add.at(sg, b, qg[rows])
                 sw = np.zeros(nbins, np.int64); np.add.at(sw, b, qw[rows])
