@@ -448,18 +448,22 @@ template <uint32_t OFF>
 __device__ __forceinline__ void red_off(uint32_t addr, uint32_t v) {
     asm volatile("red.shared.add.u32 [%0+%2], %1;" ::"r"(addr), "r"(v), "n"(OFF) : "memory");
 }
-// adds one row into the word planes of the image (plane k starts k * WSZ bytes further)
-template <int NW, uint32_t WSZ>
-__device__ __forceinline__ void red_row(uint32_t addr, uint32_t qg, uint32_t qw) {
+// the words that one row adds to the image: (q >> 8, (q & 0xff) | 1 << 20) without weights, else hi / lo of g and w
+template <int NW>
+__device__ __forceinline__ void row_words(uint32_t qg, uint32_t qw, uint32_t (&w)[4]) {
     if constexpr (NW == 3) {
-        red_off<0>(addr, (uint32_t)((int32_t)qg >> 8));
-        red_off<WSZ>(addr, (qg & 0xffu) | (1u << 20));
+        w[0] = (uint32_t)((int32_t)qg >> 8); w[1] = (qg & 0xffu) | (1u << 20); w[2] = 0u; w[3] = 0u;
     } else {
-        red_off<0>(addr, (uint32_t)((int32_t)qg >> QSPLIT));
-        red_off<WSZ>(addr, qg & ((1u << QSPLIT) - 1));
-        red_off<2 * WSZ>(addr, qw >> QSPLIT);
-        red_off<3 * WSZ>(addr, qw & ((1u << QSPLIT) - 1));
+        w[0] = (uint32_t)((int32_t)qg >> QSPLIT); w[1] = qg & ((1u << QSPLIT) - 1);
+        w[2] = qw >> QSPLIT; w[3] = qw & ((1u << QSPLIT) - 1);
     }
+}
+// adds them into the word planes of the image (plane k starts k * WSZ bytes further)
+template <int NW, uint32_t WSZ>
+__device__ __forceinline__ void red_row(uint32_t addr, const uint32_t (&w)[4]) {
+    red_off<0>(addr, w[0]);
+    red_off<WSZ>(addr, w[1]);
+    if constexpr (NW == 4) { red_off<2 * WSZ>(addr, w[2]); red_off<3 * WSZ>(addr, w[3]); }
 }
 __device__ __forceinline__ void lds_v4(uint32_t addr, uint32_t (&w)[4]) {
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
@@ -473,7 +477,7 @@ __device__ __forceinline__ void lds_v4(uint32_t addr, uint32_t (&w)[4]) {
 // and takes 4 * REP rows per step; the replicas are added when the image is flushed.
 //   tb: shared-space address of the lane's word of row rr of the tile, tw: of the tile's words + rr * (4 or 8),
 //   col[j]: image column of the lane's feature of step j, sel[j]: PRMT selector of that feature's byte.
-template <int NW, uint32_t WSZ, int REP>
+template <int NW, uint32_t WSZ, int REP, bool FULL>
 __device__ __forceinline__ void q_tile(uint32_t tb, uint32_t tw, int nrows, int rr, const uint32_t (&col)[4], const uint32_t (&sel)[4]) {
     constexpr int RW = NW == 3 ? 1 : 2;
     constexpr int RB = 4 * REP, NB = EVB_TILE_ROWS / RB;
@@ -486,9 +490,11 @@ __device__ __forceinline__ void q_tile(uint32_t tb, uint32_t tw, int nrows, int 
             nqg = lds_u32(tw + (bt + 1) * RB * 4 * RW);
             if constexpr (RW == 2) nqw = lds_u32(tw + (bt + 1) * RB * 8 + 4);
         }
-        if (bt * RB + rr < nrows) {
+        if (FULL || bt * RB + rr < nrows) { // FULL: a whole tile of 32 rows, nothing to test
+            uint32_t w[4];
+            row_words<NW>(qg, qw, w);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) red_row<NW, WSZ>(col[j] + __byte_perm(bins, 0u, sel[j]) * 128u, qg, qw);
+            for (int j = 0; j < 4; ++j) red_row<NW, WSZ>(col[j] + __byte_perm(bins, 0u, sel[j]) * 128u, w);
         }
         bins = nbins; qg = nqg; qw = nqw;
     }
@@ -551,6 +557,8 @@ __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QT * 32) k_histq(His
     const int32_t *gq = reinterpret_cast<const int32_t *>(a.grad);
     const size_t RS = a.RS;
     const uint32_t team_bar = 1 + team, unit_bar = 1 + QT + uw;
+    const bool skip_acc = (a.mode & 16) != 0; // diagnostic: stage only
+    const int team_threads = nact * 32;
 
     long long pos = lo;
     while (pos < hi) {
@@ -630,16 +638,16 @@ __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QT * 32) k_histq(His
                     const int c = i - (QDR - 1);
                     asm volatile("cp.async.wait_group %0;" ::"n"(QDR - 1) : "memory");
                     // the copies of all warps of the team have landed, and everybody is done with tile c - 1
-                    asm volatile("bar.sync %0, %1;" ::"r"(team_bar), "r"(nact * 32) : "memory");
+                    asm volatile("bar.sync %0, %1;" ::"r"(team_bar), "r"(team_threads) : "memory");
                     const long long q0 = pos + ((long long)c * QT + team) * EVB_TILE_ROWS;
                     const int nrows = (int)min((long long)EVB_TILE_ROWS, send - q0);
                     const uint32_t ts = ring_s + (c % NSLOT) * QTILE;
-                    if (!(a.mode & 16)) {
+                    if (!skip_acc) {
                         const uint32_t tb = ts + rd_off, tw = ts + EVB_TILE_ROWS * 128 + rr * 4 * RW;
-                        if (rep == 1) q_tile<NW, WSZ, 1>(tb, tw, nrows, rr, col, sel);
-                        else if (rep == 2) q_tile<NW, WSZ, 2>(tb, tw, nrows, rr, col, sel);
-                        else if (rep == 4) q_tile<NW, WSZ, 4>(tb, tw, nrows, rr, col, sel);
-                        else q_tile<NW, WSZ, 8>(tb, tw, nrows, rr, col, sel);
+                        if (rep == 1) { if (nrows == EVB_TILE_ROWS) q_tile<NW, WSZ, 1, true>(tb, tw, nrows, rr, col, sel); else q_tile<NW, WSZ, 1, false>(tb, tw, nrows, rr, col, sel); }
+                        else if (rep == 2) q_tile<NW, WSZ, 2, false>(tb, tw, nrows, rr, col, sel);
+                        else if (rep == 4) q_tile<NW, WSZ, 4, false>(tb, tw, nrows, rr, col, sel);
+                        else q_tile<NW, WSZ, 8, false>(tb, tw, nrows, rr, col, sel);
                     }
                     if constexpr (NW == 3) { // the packed counters are full after QSUB tiles of every team
                         if ((c + 1) % QSUB == 0 && ntiles > (long long)(c + 1) * QT) { flush(!started); started = true; }
@@ -647,7 +655,7 @@ __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QT * 32) k_histq(His
                 }
             }
             asm volatile("cp.async.wait_group 0;" ::: "memory");
-            asm volatile("bar.sync %0, %1;" ::"r"(team_bar), "r"(nact * 32) : "memory"); // ring free for the next segment
+            asm volatile("bar.sync %0, %1;" ::"r"(team_bar), "r"(team_threads) : "memory"); // ring free for the next segment
             flush(!started);
         }
         pos = send;
