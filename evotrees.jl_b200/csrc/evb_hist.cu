@@ -610,18 +610,21 @@ __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QT * 32) k_histq(His
                 }
                 asm volatile("bar.sync %0, %1;" ::"r"(unit_bar), "r"(QT * 32) : "memory");
             };
-            // row id of row `lane` of the team's k-th tile (0 beyond the end of the segment: never copied)
-            auto rid_of = [&](int kk) -> uint32_t {
-                const long long q = pos + ((long long)kk * QT + team) * EVB_TILE_ROWS + lane;
-                return (kk < nmine && q < send) ? rows[q] : 0u;
-            };
-            uint32_t r0 = rid_of(0), r1 = rid_of(1);
+            // Everything below counts in 32-bit offsets from the start of the segment (a row range of a CTA is short).
+            const int seglen = (int)(send - pos), ntl = (int)ntiles;
+            const uint32_t *rows_seg = rows + pos;
+            // row id of row `lane` of the tile at offset o (0 beyond the end of the segment: never copied)
+            auto rid_at = [&](int o) -> uint32_t { return o + lane < seglen ? rows_seg[o + lane] : 0u; };
+            const int step = QT * EVB_TILE_ROWS;
+            int so = team * EVB_TILE_ROWS;       // offset of the tile staged next
+            int co = so;                          // offset of the tile consumed next
+            uint32_t r0 = rid_at(so), r1 = rid_at(so + step);
+            int sslot = 0, cslot = 0, c = 0, until_flush = QSUB;
             for (int i = 0; i < nmine + QDR - 1; ++i) {
-                const uint32_t r2 = rid_of(i + 2);
+                const uint32_t r2 = rid_at(so + 2 * step);
                 if (i < nmine) { // stage the team's tile i
-                    const long long q0 = pos + ((long long)i * QT + team) * EVB_TILE_ROWS;
-                    const int nrows = (int)min((long long)EVB_TILE_ROWS, send - q0);
-                    unsigned char *dst = ring + (i % NSLOT) * QTILE;
+                    const int nrows = min(EVB_TILE_ROWS, seglen - so);
+                    unsigned char *dst = ring + sslot * QTILE;
 #pragma unroll
                     for (int t = 0; t < 2; ++t) {
                         const uint32_t rid = __shfl_sync(0xffffffffu, r0, st_row[t]);
@@ -631,17 +634,17 @@ __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QT * 32) k_histq(His
                         if constexpr (RW == 1) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst + EVB_TILE_ROWS * 128 + lane * 4)), "l"(gq + r0) : "memory");
                         else asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst + EVB_TILE_ROWS * 128 + lane * 8)), "l"(gq + (size_t)r0 * 2) : "memory");
                     }
+                    sslot = sslot + 1 == NSLOT ? 0 : sslot + 1;
                 }
+                so += step;
                 asm volatile("cp.async.commit_group;" ::: "memory");
                 r0 = r1; r1 = r2;
                 if (i >= QDR - 1) { // consume the team's tile c
-                    const int c = i - (QDR - 1);
                     asm volatile("cp.async.wait_group %0;" ::"n"(QDR - 1) : "memory");
                     // the copies of all warps of the team have landed, and everybody is done with tile c - 1
                     asm volatile("bar.sync %0, %1;" ::"r"(team_bar), "r"(team_threads) : "memory");
-                    const long long q0 = pos + ((long long)c * QT + team) * EVB_TILE_ROWS;
-                    const int nrows = (int)min((long long)EVB_TILE_ROWS, send - q0);
-                    const uint32_t ts = ring_s + (c % NSLOT) * QTILE;
+                    const int nrows = min(EVB_TILE_ROWS, seglen - co);
+                    const uint32_t ts = ring_s + cslot * QTILE;
                     if (!skip_acc) {
                         const uint32_t tb = ts + rd_off, tw = ts + EVB_TILE_ROWS * 128 + rr * 4 * RW;
                         if (rep == 1) { if (nrows == EVB_TILE_ROWS) q_tile<NW, WSZ, 1, true>(tb, tw, nrows, rr, col, sel); else q_tile<NW, WSZ, 1, false>(tb, tw, nrows, rr, col, sel); }
@@ -649,8 +652,14 @@ __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QT * 32) k_histq(His
                         else if (rep == 4) q_tile<NW, WSZ, 4, false>(tb, tw, nrows, rr, col, sel);
                         else q_tile<NW, WSZ, 8, false>(tb, tw, nrows, rr, col, sel);
                     }
+                    cslot = cslot + 1 == NSLOT ? 0 : cslot + 1;
+                    co += step;
+                    ++c;
                     if constexpr (NW == 3) { // the packed counters are full after QSUB tiles of every team
-                        if ((c + 1) % QSUB == 0 && ntiles > (long long)(c + 1) * QT) { flush(!started); started = true; }
+                        if (--until_flush == 0) {
+                            until_flush = QSUB;
+                            if (ntl > c * QT) { flush(!started); started = true; }
+                        }
                     }
                 }
             }
