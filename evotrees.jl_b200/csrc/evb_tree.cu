@@ -147,6 +147,7 @@ struct PeerReduceArgs {
     double *hsum;
     const LevelPlan *plan;
     int world, rank, F, CB, level;
+    int K, elided; // elided: mse, every rank's hessian channels are exactly 2 x its weight channel -- they are not fetched
 };
 __global__ void __launch_bounds__(256) k_peer_reduce(PeerReduceArgs a) {
     const int Fown = (a.F - a.rank + a.world - 1) / a.world;
@@ -157,11 +158,16 @@ __global__ void __launch_bounds__(256) k_peer_reduce(PeerReduceArgs a) {
     if (fi < Fown) f = fi * a.world + a.rank;
     else { if (a.level != 1 || a.rank == 0) return; f = 0; }
     const size_t base = ((size_t)s * a.F + f) * a.CB;
+    const int B = a.CB / (2 * a.K + 1);
     for (int idx = threadIdx.x; idx < a.CB; idx += blockDim.x) {
+        const int c = idx / B;
+        if (a.elided && c >= a.K && c < 2 * a.K) continue;
         double v = 0.0;
 #pragma unroll 8
         for (int q = 0; q < a.world; ++q) v += __ldcv(a.peer_hcomp[q] + base + idx);
         a.hsum[base + idx] = v;
+        if (a.elided && c == 2 * a.K) // h_k = 2w (src/loss.jl:52): doubling commutes with the rounding of the sum
+            for (int k = 0; k < a.K; ++k) a.hsum[base + (size_t)(a.K + k) * B + (idx - c * B)] = 2.0 * v;
     }
 }
 
@@ -758,6 +764,7 @@ int32_t evb_launch_scan(evb_handle *h, int level) {
         PeerReduceArgs r;
         for (int q = 0; q < EVB_MAX_PEERS; ++q) r.peer_hcomp[q] = q < h->world ? h->peer_hcomp[q] : nullptr;
         r.hsum = h->hsum; r.plan = h->plan + level; r.world = h->world; r.rank = h->rank; r.F = h->F; r.CB = h->C * h->B; r.level = level;
+        r.K = h->K; r.elided = h->Ce != h->C ? 1 : 0;
         if (rc == EVB_OK) k_peer_reduce<<<slots * (Fown + 1), 256, 0, h->st>>>(r);
         evb_toc(h, EVB_T_ALLREDUCE);
         EVB_CHECK(rc);
