@@ -289,6 +289,42 @@ __global__ void __launch_bounds__(256) k_finalize(FinArgs a) {
     if (a.gmax && a.compute_grads) block_absmax(g0, a.gmax);
 }
 
+// The same update with the rows of bins staged through shared memory: the CTA copies its 256 rows with fully
+// coalesced 16-byte loads (one memory round trip instead of one per tree level and sector), then every thread walks
+// the tree on its own row out of shared memory.  Rows are padded by one word so that equal byte offsets of different
+// rows fall into different banks.  Used when a row is at most 256 bytes.
+__global__ void __launch_bounds__(256) k_finalize_staged(FinArgs a) {
+    extern __shared__ uint32_t s_fin[]; // [nn] packed tree, then [256][RS / 4 + 1] words of bins
+    uint32_t *s_tree = s_fin;
+    uint32_t *s_rows = s_fin + a.nn;
+    const int rw = a.RS >> 2, rwp = rw + 1; // words per row, padded
+    for (int i = threadIdx.x; i < a.nn; i += 256) s_tree[i] = a.t_packed[i];
+    const long long row0 = (long long)blockIdx.x * 256;
+    const int nr = (int)min((long long)256, a.n - row0);
+    const uint4 *src = reinterpret_cast<const uint4 *>(a.xT + (size_t)row0 * a.RS);
+    const int cpr = a.RS >> 4, nchunk = nr * cpr;
+    for (int c = threadIdx.x; c < nchunk; c += 256) {
+        const uint4 v = src[c];
+        const int r = c / cpr, part = c - r * cpr;
+        uint32_t *d = s_rows + r * rwp + part * 4;
+        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+    }
+    __syncthreads();
+    const long long i = row0 + threadIdx.x;
+    float g0 = 0.0f;
+    if (i < a.n) {
+        const int nid = traverse(s_tree, reinterpret_cast<const uint8_t *>(s_rows + threadIdx.x * rwp));
+        a.nidx[i] = (uint32_t)nid;
+        float *p = a.pred + (size_t)i * a.K;
+        pred_add(a.loss, a.K, p, a.t_pred + (size_t)(nid - 1) * a.K);
+        if (a.compute_grads) {
+            grad_row(a.loss, a.K, a.NCH, a.elided != 0, p, a.y, a.ycols, i, a.grad + (size_t)i * a.GS);
+            g0 = a.grad[(size_t)i * a.GS];
+        }
+    }
+    if (a.gmax && a.compute_grads) block_absmax(g0, a.gmax);
+}
+
 // node of every sampled row from the row lists left by the partition kernels; one CTA per node
 __global__ void k_nidx_from_partition(const uint32_t *rows0, const uint32_t *rows1, const int32_t *seg_start,
                                       const int32_t *seg_cnt, const uint8_t *t_split, int nn, uint32_t *out) {
@@ -544,8 +580,16 @@ int32_t evb_launch_finalize(evb_handle *h, bool compute_grads) {
     a.ycols = h->ycols; a.compute_grads = compute_grads ? 1 : 0;
     const size_t smem = (size_t)h->nn * 4;
     a.packed_in_smem = smem <= 40 * 1024 ? 1 : 0;
+    const size_t staged = smem + (size_t)256 * (h->RS + 4);
+    static bool attr_set[64] = {};
+    static const bool direct = getenv("EVB_FINALIZE_DIRECT") != nullptr;
     evb_tic(h, EVB_T_FINALIZE);
-    k_finalize<<<(unsigned)((h->n + 255) / 256), 256, a.packed_in_smem ? smem : 0, h->st>>>(a);
+    if (h->RS <= 256 && staged <= 100 * 1024 && !direct && h->dev < 64) {
+        if (!attr_set[h->dev]) { cudaFuncSetAttribute(k_finalize_staged, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); attr_set[h->dev] = true; }
+        k_finalize_staged<<<(unsigned)((h->n + 255) / 256), 256, staged, h->st>>>(a);
+    } else {
+        k_finalize<<<(unsigned)((h->n + 255) / 256), 256, a.packed_in_smem ? smem : 0, h->st>>>(a);
+    }
     evb_toc(h, EVB_T_FINALIZE);
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
