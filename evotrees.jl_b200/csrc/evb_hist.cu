@@ -477,27 +477,52 @@ __device__ __forceinline__ void lds_v4(uint32_t addr, uint32_t (&w)[4]) {
 // and takes 4 * REP rows per step; the replicas are added when the image is flushed.
 //   tb: shared-space address of the lane's word of row rr of the tile, tw: of the tile's words + rr * (4 or 8),
 //   col[j]: image column of the lane's feature of step j, sel[j]: PRMT selector of that feature's byte.
-template <int NW, uint32_t WSZ, int REP, bool FULL>
-__device__ __forceinline__ void q_tile(uint32_t tb, uint32_t tw, int nrows, int rr, const uint32_t (&col)[4], const uint32_t (&sel)[4]) {
+template <uint32_t OFF>
+__device__ __forceinline__ uint32_t lds_u32_at(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+    return v;
+}
+// batch BT of a tile (see q_tile): loads of batch BT + 1 first, then the reductions of batch BT
+template <int NW, uint32_t WSZ, int REP, bool FULL, int BT>
+__device__ __forceinline__ void q_batch(uint32_t tb, uint32_t tw, int nrows, int rr, const uint32_t (&col)[4], const uint32_t (&sel)[4],
+                                        uint32_t bins, uint32_t qg, uint32_t qw) {
     constexpr int RW = NW == 3 ? 1 : 2;
     constexpr int RB = 4 * REP, NB = EVB_TILE_ROWS / RB;
-    uint32_t bins = lds_u32(tb), qg = lds_u32(tw), qw = RW == 2 ? lds_u32(tw + 4) : 0u;
-#pragma unroll
-    for (int bt = 0; bt < NB; ++bt) {
-        uint32_t nbins = 0, nqg = 0, nqw = 0;
-        if (bt + 1 < NB) { // loads of the next rows before the reductions of these
-            nbins = lds_u32(tb + (bt + 1) * RB * 128);
-            nqg = lds_u32(tw + (bt + 1) * RB * 4 * RW);
-            if constexpr (RW == 2) nqw = lds_u32(tw + (bt + 1) * RB * 8 + 4);
-        }
-        if (FULL || bt * RB + rr < nrows) { // FULL: a whole tile of 32 rows, nothing to test
-            uint32_t w[4];
-            row_words<NW>(qg, qw, w);
+    uint32_t nbins = 0, nqg = 0, nqw = 0;
+    if constexpr (BT + 1 < NB) {
+        nbins = lds_u32_at<(BT + 1) * RB * 128>(tb);
+        nqg = lds_u32_at<(BT + 1) * RB * 4 * RW>(tw);
+        if constexpr (RW == 2) nqw = lds_u32_at<(BT + 1) * RB * 8 + 4>(tw);
+    }
+    if (FULL || BT * RB + rr < nrows) { // FULL: a whole tile of 32 rows, nothing to test
+        uint32_t w[4];
+        row_words<NW>(qg, qw, w);
+        if constexpr (NW == 3) {
+            // the four steps of the lane's row as one block: byte select, image address, two reductions each
+            asm volatile(
+                "{\n .reg .u32 b0, b1, b2, b3, a0, a1, a2, a3;\n"
+                " prmt.b32 b0, %0, 0, %1;\n prmt.b32 b1, %0, 0, %2;\n prmt.b32 b2, %0, 0, %3;\n prmt.b32 b3, %0, 0, %4;\n"
+                " mad.lo.u32 a0, b0, 128, %5;\n mad.lo.u32 a1, b1, 128, %6;\n mad.lo.u32 a2, b2, 128, %7;\n mad.lo.u32 a3, b3, 128, %8;\n"
+                " red.shared.add.u32 [a0], %9;\n red.shared.add.u32 [a0+%11], %10;\n"
+                " red.shared.add.u32 [a1], %9;\n red.shared.add.u32 [a1+%11], %10;\n"
+                " red.shared.add.u32 [a2], %9;\n red.shared.add.u32 [a2+%11], %10;\n"
+                " red.shared.add.u32 [a3], %9;\n red.shared.add.u32 [a3+%11], %10;\n}\n"
+                ::"r"(bins), "r"(sel[0]), "r"(sel[1]), "r"(sel[2]), "r"(sel[3]), "r"(col[0]), "r"(col[1]), "r"(col[2]), "r"(col[3]),
+                  "r"(w[0]), "r"(w[1]), "n"(WSZ)
+                : "memory");
+        } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j) red_row<NW, WSZ>(col[j] + __byte_perm(bins, 0u, sel[j]) * 128u, w);
         }
-        bins = nbins; qg = nqg; qw = nqw;
     }
+    if constexpr (BT + 1 < NB) q_batch<NW, WSZ, REP, FULL, BT + 1>(tb, tw, nrows, rr, col, sel, nbins, nqg, nqw);
+}
+template <int NW, uint32_t WSZ, int REP, bool FULL>
+__device__ __forceinline__ void q_tile(uint32_t tb, uint32_t tw, int nrows, int rr, const uint32_t (&col)[4], const uint32_t (&sel)[4]) {
+    constexpr int RW = NW == 3 ? 1 : 2;
+    const uint32_t bins = lds_u32(tb), qg = lds_u32(tw), qw = RW == 2 ? lds_u32(tw + 4) : 0u;
+    q_batch<NW, WSZ, REP, FULL, 0>(tb, tw, nrows, rr, col, sel, bins, qg, qw);
 }
 
 template <int BP, int NW>
