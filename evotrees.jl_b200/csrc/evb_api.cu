@@ -271,10 +271,11 @@ extern "C" int32_t evb_create(evb_handle **out, const evb_params *p, int64_t nob
     *out = nullptr;
     if (!p || !x_bin || !y || (!pred0 && !mu)) { evb_set_error("evb_create: null argument"); return EVB_ERR_ARG; }
     if (nobs < 1 || nobs > 2000000000ll || nfeats < 1 || nfeats > 65535) { evb_set_error("evb_create: nobs/nfeats out of range"); return EVB_ERR_ARG; }
-    if (p->loss < 0 || p->loss > 3) { evb_set_error("evb_create: unknown loss %d", p->loss); return EVB_ERR_ARG; }
+    if (p->loss < 0 || p->loss > EVB_LOGISTIC_MLE) { evb_set_error("evb_create: unknown loss %d", p->loss); return EVB_ERR_ARG; }
     if (p->K < 1 || p->K > 32) { evb_set_error("evb_create: K=%d outside 1..32", p->K); return EVB_ERR_ARG; }
-    if ((p->loss == EVB_GAUSSIAN_MLE && (p->K % 2 != 0 || ycols != p->K / 2)) ||
-        ((p->loss == EVB_MSE || p->loss == EVB_LOGLOSS) && ycols != p->K) || (p->loss == EVB_MLOGLOSS && p->K < 2)) {
+    const bool mle = p->loss == EVB_GAUSSIAN_MLE || p->loss == EVB_LOGISTIC_MLE;
+    if ((mle && (p->K % 2 != 0 || ycols != p->K / 2)) || (!mle && p->loss != EVB_MLOGLOSS && ycols != p->K) ||
+        (p->loss == EVB_MLOGLOSS && p->K < 2)) {
         evb_set_error("evb_create: K=%d / ycols=%d inconsistent with the loss", p->K, ycols);
         return EVB_ERR_ARG;
     }
@@ -552,8 +553,9 @@ extern "C" int32_t evb_eval_attach(evb_handle *h, int64_t nobs, const uint8_t *x
     if (h->ev_n > 0) { evb_set_error("evb_eval_attach: evaluation data already attached (evb_eval_detach first)"); return EVB_ERR_ARG; }
     const int loss = h->p.loss;
     const bool ok = (loss == EVB_MLOGLOSS) ? metric == EVB_METRIC_MLOGLOSS
-                    : (loss == EVB_GAUSSIAN_MLE) ? metric == EVB_METRIC_GAUSSIAN_MLE
-                    : (metric == EVB_METRIC_MSE || metric == EVB_METRIC_MAE || metric == EVB_METRIC_LOGLOSS);
+                    : (loss == EVB_GAUSSIAN_MLE || loss == EVB_LOGISTIC_MLE) ? (metric == EVB_METRIC_GAUSSIAN_MLE || metric == EVB_METRIC_LOGISTIC_MLE)
+                    : (metric == EVB_METRIC_MSE || metric == EVB_METRIC_MAE || metric == EVB_METRIC_LOGLOSS ||
+                       metric == EVB_METRIC_POISSON || metric == EVB_METRIC_GAMMA || metric == EVB_METRIC_TWEEDIE);
     if (!ok) { evb_set_error("evb_eval_attach: metric %d is not defined for loss %d", metric, loss); return EVB_ERR_ARG; }
     drop_graphs(h); // the launch sequence of a tree changes
     int32_t rc = eval_attach_impl(h, nobs, x_bin, y, w, pred0, bias, metric, sums);

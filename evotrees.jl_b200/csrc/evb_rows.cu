@@ -43,6 +43,33 @@ __device__ __forceinline__ void grad_row(int loss, int K, int NCH, bool elided, 
             REC(k) = (((uint32_t)(k + 1) == yi) ? prob - 1.0f : prob) * w;
             REC(K + k) = prob * (1.0f - prob) * w;
         }
+    } else if (loss == EVB_POISSON || loss == EVB_GAMMA || loss == EVB_TWEEDIE) { // src/loss.jl:65-84
+        const float *yf = (const float *)y + (size_t)i * ycols;
+        for (int k = 0; k < K; ++k) {
+            const float pr = expf(p[k]), yk = yf[k];
+            float g, h;
+            if (loss == EVB_POISSON) { g = pr - yk; h = pr; }
+            else if (loss == EVB_GAMMA) { g = 2.0f * (1.0f - yk / pr); h = 2.0f * yk / pr; }
+            else { // rho = 1.5: pred^(2-rho) = sqrt(pred), pred^(1-rho) = 1 / sqrt(pred)
+                const float a = sqrtf(pr), b = 1.0f / a;
+                g = 2.0f * (a - yk * b);
+                h = 2.0f * (0.5f * a + 0.5f * yk * b);
+            }
+            REC(k) = g * w;
+            REC(K + k) = h * w;
+        }
+    } else if (loss == EVB_LOGISTIC_MLE) { // src/loss.jl:207-217
+        const int Y = K / 2;
+        const float *yf = (const float *)y + (size_t)i * ycols;
+        for (int t = 0; t < Y; ++t) {
+            const float loc = p[2 * t], sr = p[2 * t + 1];
+            const float scale = softplusf_(sr), ds = sigmoidf_(sr);
+            const float z = (yf[t] - loc) / scale, th = tanhf(z / 2.0f);
+            REC(2 * t) = -th / scale * w;
+            REC(2 * t + 1) = (1.0f - z * th) * ds / scale * w;
+            REC(2 * Y + 2 * t) = 1.0f / (3.0f * scale * scale) * w;
+            REC(2 * Y + 2 * t + 1) = (3.14159274f * 3.14159274f + 3.0f) / 9.0f * (ds / scale) * (ds / scale) * w;
+        }
     } else { // EVB_GAUSSIAN_MLE
         const int Y = K / 2;
         const float *yf = (const float *)y + (size_t)i * ycols;
@@ -63,7 +90,7 @@ __device__ __forceinline__ void grad_row(int loss, int K, int NCH, bool elided, 
 __device__ __forceinline__ void pred_add(int loss, int K, float *p, const float *leaf) {
     if (loss == EVB_LOGLOSS) {
         for (int k = 0; k < K; ++k) p[k] = fminf(fmaxf(p[k] + leaf[k], -15.0f), 15.0f);
-    } else if (loss == EVB_GAUSSIAN_MLE) {
+    } else if (loss == EVB_GAUSSIAN_MLE || loss == EVB_LOGISTIC_MLE) {
         for (int t = 0; t < K / 2; ++t) {
             p[2 * t] += leaf[2 * t];
             p[2 * t + 1] = fmaxf(-15.0f, p[2 * t + 1] + leaf[2 * t + 1]);
@@ -364,7 +391,8 @@ __global__ void __launch_bounds__(256) k_predict(PredArgs a) {
     }
     if (a.apply_link) { // apply_prediction_link! (src/predict.jl:105-116)
         if (a.loss == EVB_LOGLOSS) { for (int k = 0; k < K; ++k) p[k] = sigmoidf_(p[k]); }
-        else if (a.loss == EVB_GAUSSIAN_MLE) { for (int k = 1; k < K; k += 2) p[k] = softplusf_(p[k]); }
+        else if (a.loss == EVB_GAUSSIAN_MLE || a.loss == EVB_LOGISTIC_MLE) { for (int k = 1; k < K; k += 2) p[k] = softplusf_(p[k]); }
+        else if (a.loss == EVB_POISSON || a.loss == EVB_GAMMA || a.loss == EVB_TWEEDIE) { for (int k = 0; k < K; ++k) p[k] = expf(p[k]); }
         else if (a.loss == EVB_MLOGLOSS) {
             float s = 0.0f;
             for (int k = 0; k < K; ++k) { p[k] = expf(p[k]); s += p[k]; }
@@ -441,12 +469,13 @@ __device__ __forceinline__ float metric_row(int metric, int K, const float *p, c
         return w * (logf(isum) - p[yi - 1]);
     }
     const float *yf = (const float *)y + (size_t)i * ycols;
-    if (metric == EVB_METRIC_GAUSSIAN_MLE) {
+    if (metric == EVB_METRIC_GAUSSIAN_MLE || metric == EVB_METRIC_LOGISTIC_MLE) {
         const int Y = K / 2;
         float acc = 0.0f;
         for (int t = 0; t < Y; ++t) {
             const float scale = softplusf_(p[2 * t + 1]), d = yf[t] - p[2 * t];
-            acc += -(logf(scale) + d * d / (2.0f * scale * scale));
+            if (metric == EVB_METRIC_GAUSSIAN_MLE) acc += -(logf(scale) + d * d / (2.0f * scale * scale));
+            else { const float az = fabsf(d / scale); acc += -logf(scale) - az - 2.0f * log1pf(expf(-az)); } // src/metrics.jl:84-89
         }
         return w * acc / (float)Y;
     }
@@ -455,7 +484,15 @@ __device__ __forceinline__ float metric_row(int metric, int K, const float *p, c
         const float pk = p[k], yk = yf[k];
         if (metric == EVB_METRIC_MSE) acc += (pk - yk) * (pk - yk);
         else if (metric == EVB_METRIC_MAE) acc += fabsf(pk - yk);
-        else { const float s = sigmoidf_(pk); acc += -yk * logf(s) + (yk - 1.0f) * logf(1.0f - s); }
+        else if (metric == EVB_METRIC_LOGLOSS) { const float s = sigmoidf_(pk); acc += -yk * logf(s) + (yk - 1.0f) * logf(1.0f - s); }
+        else if (metric == EVB_METRIC_POISSON) { // src/metrics.jl:13-17; eps(1f-7)
+            const float pr = expf(pk);
+            acc += 2.0f * (yk * logf(yk / pr + 7.1054274e-15f) + pr - yk);
+        } else if (metric == EVB_METRIC_GAMMA) { const float pr = expf(pk); acc += 2.0f * (logf(pr / yk) + yk / pr - 1.0f); }
+        else { // tweedie, rho = 1.5 (src/metrics.jl:24-28)
+            const float pr = expf(pk), a = sqrtf(pr);
+            acc += 2.0f * (sqrtf(yk) / -0.5f / 0.5f - yk * (1.0f / a) / -0.5f + a / 0.5f);
+        }
     }
     return w * acc / (float)K;
 }
@@ -647,7 +684,7 @@ static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntr
                             int32_t x_dtype, int32_t x_row_major, const void *edges, int32_t nedges, int64_t nobs, int32_t nfeats,
                             const uint8_t *feattypes, int32_t apply_link, float *out, uint32_t *leaf_idx, double *ms_out) {
     if (!feat || !cond_bin || !split || !leaf_pred || (!x_bin && !x) || !out || nobs < 0 || nfeats < 1 || nfeats > 65535 ||
-        ntrees < 0 || nn < 1 || K < 1 || K > 64 || loss < 0 || loss > 3) {
+        ntrees < 0 || nn < 1 || K < 1 || K > 64 || loss < 0 || loss > EVB_LOGISTIC_MLE) {
         evb_set_error("evb_predict: invalid argument");
         return EVB_ERR_ARG;
     }

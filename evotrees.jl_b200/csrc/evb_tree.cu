@@ -128,7 +128,7 @@ __device__ __forceinline__ double term_gh(double g, double h, double w, double l
 __device__ __forceinline__ float leaf_value(const ScanArgs &a, const double *s, int k) {
     const int K = a.K, C = a.C;
     double g, h;
-    if (a.loss == EVB_GAUSSIAN_MLE) {
+    if (a.loss == EVB_GAUSSIAN_MLE || a.loss == EVB_LOGISTIC_MLE) {
         const int Y = K / 2, t = k >> 1, j = k & 1;
         g = s[2 * t + j];
         h = s[2 * Y + 2 * t + j];

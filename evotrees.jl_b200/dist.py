@@ -58,16 +58,16 @@ class Comm:
         """Initial bias of the whole data set from per-shard sufficient statistics
         (same formulas as `_init_target`, src/init.jl:19-145)."""
         from .fit import _invsoftplus, _logit
-        if loss in ("mse", "logloss"):
+        if loss in ("mse", "logloss", "poisson", "gamma", "tweedie"):
             y2 = y.reshape(y.shape[0], -1).astype(np.float64)
             s = self.allreduce_sum(np.concatenate([y2.sum(axis=0), [y2.shape[0]]]))
             m = s[:-1] / s[-1]
-            return (m if loss == "mse" else _logit(m)).astype(np.float32)
+            return (m if loss == "mse" else _logit(m) if loss == "logloss" else np.log(m)).astype(np.float32)
         if loss == "mlogloss":
             cnt = self.allreduce_sum(np.bincount(y.astype(np.int64) - 1, minlength=K))
             mu = np.log(cnt / cnt.sum()).astype(np.float32)
             return mu - mu.max()
-        if loss == "gaussian_mle":
+        if loss in ("gaussian_mle", "logistic_mle"):
             y2 = y.reshape(y.shape[0], -1).astype(np.float64)
             s = self.allreduce_sum(np.concatenate([y2.sum(axis=0), (y2 ** 2).sum(axis=0), [y2.shape[0]]]))
             n, Y = s[-1], y2.shape[1]
@@ -75,7 +75,8 @@ class Comm:
             var = (s[Y:2 * Y] - n * mean ** 2) / (n - 1)
             mu = np.empty(2 * Y, np.float32)
             mu[0::2] = mean
-            mu[1::2] = [_invsoftplus(float(np.sqrt(v))) for v in var]
+            f = np.sqrt(3.0) / np.pi if loss == "logistic_mle" else 1.0
+            mu[1::2] = [_invsoftplus(float(np.sqrt(v)) * f) for v in var]
             return mu
         raise ValueError(loss)
 

@@ -29,7 +29,7 @@ def init_target(loss: str, y_train: np.ndarray, offset):
     """`_init_target` (src/init.jl:10-146) for the four losses of this path.
     Returns K, y (device dtype), ycols, mu float32 [K], target_levels, offset (link space)."""
     levels = None
-    if loss in ("mse", "logloss"):
+    if loss in ("mse", "logloss", "poisson", "gamma", "tweedie"):
         y = np.ascontiguousarray(y_train, np.float32)
         ycols = 1 if y.ndim == 1 else y.shape[1]
         K = ycols
@@ -40,6 +40,10 @@ def init_target(loss: str, y_train: np.ndarray, offset):
             mu = _logit(m).astype(np.float32)
             if offset is not None:
                 offset = _logit(offset)
+        elif loss != "mse":                                   # log link (src/init.jl:31-42)
+            mu = np.log(m).astype(np.float32)
+            if offset is not None:
+                offset = np.log(offset)
         else:
             mu = m.astype(np.float32)
     elif loss == "mlogloss":
@@ -57,15 +61,16 @@ def init_target(loss: str, y_train: np.ndarray, offset):
         mu -= mu.max()
         if offset is not None:
             offset = np.log(offset)
-    elif loss == "gaussian_mle":
+    elif loss in ("gaussian_mle", "logistic_mle"):
         y = np.ascontiguousarray(y_train, np.float32)
         ycols = 1 if y.ndim == 1 else y.shape[1]
         K = 2 * ycols
         y2 = y.reshape(y.shape[0], -1)
         mu = np.empty(K, np.float32)
+        sd_factor = math.sqrt(3.0) / math.pi if loss == "logistic_mle" else 1.0   # src/init.jl:86, 95
         for t in range(ycols):
             mu[2 * t] = y2[:, t].mean(dtype=np.float32)
-            mu[2 * t + 1] = _invsoftplus(float(np.std(y2[:, t].astype(np.float64), ddof=1)))
+            mu[2 * t + 1] = _invsoftplus(float(np.std(y2[:, t].astype(np.float64), ddof=1)) * sd_factor)
         if offset is not None:
             offset = np.array(offset, np.float32, copy=True)
             offset[:, 1::2] = [[_invsoftplus(float(v)) for v in row] for row in offset[:, 1::2]]
@@ -287,8 +292,8 @@ def grow_evotree(m: EvoTree, cache: Cache, params: EvoTypes) -> None:
     m.info["nrounds"] += 1
 
 
-IS_MAXIMISE = {"mse": False, "rmse": False, "mae": False, "logloss": False, "mlogloss": False,
-               "gaussian_mle": True}   # src/metrics.jl:194-205
+IS_MAXIMISE = {"mse": False, "rmse": False, "mae": False, "logloss": False, "mlogloss": False, "poisson": False,
+               "gamma": False, "tweedie": False, "gaussian_mle": True, "logistic_mle": True}   # src/metrics.jl:194-205
 
 
 def init_logger(metric: str, maximise: bool, early_stopping_rounds: int, early_stopping_tolerance: float = 0.0) -> dict:
@@ -361,9 +366,9 @@ class CallBack:
             off = np.array(offset_eval, np.float32, copy=True).reshape(nobs, -1)
             if loss == "logloss":
                 off = _logit(off)
-            elif loss == "mlogloss":
+            elif loss in ("mlogloss", "poisson", "gamma", "tweedie"):
                 off = np.log(off)
-            elif loss == "gaussian_mle":
+            elif loss in ("gaussian_mle", "logistic_mle"):
                 off[:, 1::2] = [[_invsoftplus(float(v)) for v in row] for row in off[:, 1::2]]
             pred0 = np.ascontiguousarray(np.broadcast_to(off, (nobs, K)), np.float32)
         self.metric = params.metric

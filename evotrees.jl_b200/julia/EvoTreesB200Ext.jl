@@ -23,7 +23,7 @@ struct EvbParams
     device::Int32; flags::UInt32
 end
 
-const LOSS_CODE = Dict(:mse => 0, :logloss => 1, :mlogloss => 2, :gaussian_mle => 3)
+const LOSS_CODE = Dict(:mse => 0, :logloss => 1, :mlogloss => 2, :gaussian_mle => 3, :poisson => 4, :gamma => 5, :tweedie => 6, :logistic_mle => 7)
 
 function check(rc::Int32)
     rc == 0 && return nothing
@@ -152,7 +152,8 @@ end
 # `fit` builds the callback without handing it the cache (src/fit.jl:414), so `init_core` above has to remember the
 # cache it created last (e.g. `LAST_CACHE[] = cache`); the reference's `fit` then works unchanged.
 const LAST_CACHE = Ref{Union{Nothing,B200Cache}}(nothing)
-const METRIC_CODE = Dict(:mse => 0, :rmse => 0, :mae => 1, :logloss => 2, :mlogloss => 3, :gaussian_mle => 4, :gaussian => 4)
+const METRIC_CODE = Dict(:mse => 0, :rmse => 0, :mae => 1, :logloss => 2, :mlogloss => 3, :gaussian_mle => 4, :gaussian => 4,
+    :poisson => 5, :poisson_deviance => 5, :gamma => 6, :gamma_deviance => 6, :tweedie => 7, :tweedie_deviance => 7, :logistic_mle => 8)
 
 struct B200CallBack
     feval::Function        # only read by `fit` for is_maximise(cb.feval), src/fit.jl:415

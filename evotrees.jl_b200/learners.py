@@ -8,8 +8,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-_REG_LOSSES = ("mse", "logloss")
-_MLE_LOSSES = ("gaussian_mle",)
+_REG_LOSSES = ("mse", "logloss", "poisson", "gamma", "tweedie")
+_MLE_LOSSES = ("gaussian_mle", "logistic_mle")
 
 
 def _check(name, value, lo, hi):
@@ -46,8 +46,8 @@ class EvoTypes:
         self.loss = str(self.loss)
         if self.loss == "linear":
             self.loss = "mse"
-        if self.loss == "logistic":
-            self.loss = "logloss"
+        if self.loss == "logistic":   # EvoTreeMLE: :logistic_mle; EvoTreeRegressor: the old name of :logloss
+            self.loss = "logistic_mle" if "logistic_mle" in self._losses else "logloss"
         if self.loss == "gaussian":
             self.loss = "gaussian_mle"
         if self.loss not in self._losses:
@@ -56,6 +56,8 @@ class EvoTypes:
         self.metric = self.loss if self.metric is None else str(self.metric)
         if self.metric == "gaussian":
             self.metric = "gaussian_mle"
+        if self.metric == "logistic":
+            self.metric = "logistic_mle"
         if self.metric not in self._metrics:
             raise ValueError(f"Invalid metric. Must be one of: {list(self._metrics)}")
         self.check_args()
@@ -81,7 +83,7 @@ class EvoTypes:
 @dataclass
 class EvoTreeRegressor(EvoTypes):
     _losses = _REG_LOSSES
-    _metrics = ("mse", "rmse", "mae", "logloss")
+    _metrics = ("mse", "rmse", "mae", "logloss", "poisson", "gamma", "tweedie")
 
 
 @dataclass
@@ -96,4 +98,12 @@ class EvoTreeMLE(EvoTypes):
     loss: str = "gaussian_mle"
     min_weight: float = 8.0
     _losses = _MLE_LOSSES
-    _metrics = ("gaussian_mle",)
+    _metrics = ("gaussian_mle", "logistic_mle")
+
+
+@dataclass
+class EvoTreeCount(EvoTypes):
+    """`EvoTreeCount` (src/learners.jl:122-200): poisson loss and metric."""
+    loss: str = "poisson"
+    _losses = ("poisson",)
+    _metrics = ("poisson",)

@@ -44,7 +44,10 @@ enum evb_status {
     EVB_ERR_LIMIT = -7     /* size beyond a documented limit                     */
 };
 
-enum evb_loss { EVB_MSE = 0, EVB_LOGLOSS = 1, EVB_MLOGLOSS = 2, EVB_GAUSSIAN_MLE = 3 };
+/* 0..3: the losses of the reference's GPU benchmark configurations; 4..7: the other gradient-regression and two-parameter
+ * likelihood losses of src/loss.jl:65-84, 207-217 (poisson, gamma, tweedie with rho = 1.5: log link; logistic_mle) */
+enum evb_loss { EVB_MSE = 0, EVB_LOGLOSS = 1, EVB_MLOGLOSS = 2, EVB_GAUSSIAN_MLE = 3,
+                EVB_POISSON = 4, EVB_GAMMA = 5, EVB_TWEEDIE = 6, EVB_LOGISTIC_MLE = 7 };
 enum evb_dtype { EVB_F32 = 0, EVB_U32 = 1, EVB_F64 = 2 };
 
 /* flags of evb_params.flags */
@@ -53,8 +56,8 @@ enum evb_dtype { EVB_F32 = 0, EVB_U32 = 1, EVB_F64 = 2 };
 #define EVB_FLAG_KEEP_ALL_HIST 4u  /* retain the histograms of the last split level too (for evb_get_hist)               */
 
 /* Learner hyper-parameters needed on the device; filled by the glue from the reference's learner
- * struct (src/learners.jl:1-23).  K is the number of prediction rows (1 mse/logloss, #classes for
- * mlogloss, 2 for gaussian_mle); histogram channels are C = 2K+1 (g_1..g_K, h_1..h_K, w). */
+ * struct (src/learners.jl:1-23).  K is the number of prediction rows (1 mse/logloss/poisson/gamma/tweedie, #classes for
+ * mlogloss, 2 for gaussian_mle / logistic_mle); histogram channels are C = 2K+1 (g_1..g_K, h_1..h_K, w). */
 typedef struct {
     int32_t loss;          /* enum evb_loss */
     int32_t K;
@@ -162,9 +165,11 @@ EVB_API int32_t evb_grow_tree_end(evb_handle *h, int64_t *feat, uint8_t *cond_bi
  *   sums     [0] = sum_i w_i * value_i in double, value_i the per-row metric of src/metrics.jl:1-110 rounded to
  *            float as there; [1] = sum_i w_i.  The metric is sums[0] / sums[1] (its square root for :rmse); a
  *            caller that shards the evaluation rows over several handles adds the sums first.
- * Metrics: mse / mae / logloss for the mse and logloss losses, mlogloss for mlogloss, gaussian_mle for gaussian_mle.
+ * Metrics: mse / mae / logloss / poisson / gamma / tweedie for the regression losses (mse, logloss, poisson, gamma, tweedie),
+ * mlogloss for mlogloss, gaussian_mle / logistic_mle for the two likelihood losses (src/learners.jl:75, 352).
  */
-enum evb_metric { EVB_METRIC_MSE = 0, EVB_METRIC_MAE = 1, EVB_METRIC_LOGLOSS = 2, EVB_METRIC_MLOGLOSS = 3, EVB_METRIC_GAUSSIAN_MLE = 4 };
+enum evb_metric { EVB_METRIC_MSE = 0, EVB_METRIC_MAE = 1, EVB_METRIC_LOGLOSS = 2, EVB_METRIC_MLOGLOSS = 3, EVB_METRIC_GAUSSIAN_MLE = 4,
+                  EVB_METRIC_POISSON = 5, EVB_METRIC_GAMMA = 6, EVB_METRIC_TWEEDIE = 7, EVB_METRIC_LOGISTIC_MLE = 8 };
 EVB_API int32_t evb_eval_attach(evb_handle *h, int64_t nobs, const uint8_t *x_bin, const void *y, const float *w, const float *pred0,
                                 const float *bias, int32_t metric, double sums[2]);
 EVB_API int32_t evb_eval_sums(evb_handle *h, double sums[2]);

@@ -34,7 +34,8 @@
 #include <omp.h>
 #endif
 
-enum { ORC_MSE = 0, ORC_LOGLOSS = 1, ORC_MLOGLOSS = 2, ORC_GAUSSIAN_MLE = 3 };
+enum { ORC_MSE = 0, ORC_LOGLOSS = 1, ORC_MLOGLOSS = 2, ORC_GAUSSIAN_MLE = 3, ORC_POISSON = 4, ORC_GAMMA = 5, ORC_TWEEDIE = 6, ORC_LOGISTIC_MLE = 7 };
+static inline int orc_is_mle(int loss) { return loss == ORC_GAUSSIAN_MLE || loss == ORC_LOGISTIC_MLE; }
 
 typedef struct {
     int32_t loss, K, nbins, max_depth, bagging_size, tree_type;
@@ -74,7 +75,7 @@ void orc_mlogloss_grad_hess64(double pk, double isum, int is_target, double out[
 /* ---- update_grads!: src/loss.jl:100-128, 219-236 (Float32 arithmetic like the reference) */
 void orc_update_grads(const orc_params *p, int64_t nobs, const float *pred, const void *yv, float *grad) {
     const int K = p->K, C = 2 * K + 1;
-    if (p->loss == ORC_MSE || p->loss == ORC_LOGLOSS) {
+    if (p->loss == ORC_MSE || p->loss == ORC_LOGLOSS || p->loss == ORC_POISSON || p->loss == ORC_GAMMA || p->loss == ORC_TWEEDIE) {
         const float *y = (const float *)yv; /* [nobs] or [K x nobs] */
 #pragma omp parallel for schedule(static)
         for (int64_t i = 0; i < nobs; i++) {
@@ -83,7 +84,14 @@ void orc_update_grads(const orc_params *p, int64_t nobs, const float *pred, cons
                 float pk = pred[k + K * i], yk = y[k + K * i];
                 float g, h;
                 if (p->loss == ORC_MSE) { g = 2.0f * (pk - yk); h = 2.0f; }          /* loss.jl:52 */
-                else { float s = orc_sigmoidf(pk); g = s - yk; h = s * (1.0f - s); } /* loss.jl:54-57 */
+                else if (p->loss == ORC_LOGLOSS) { float s = orc_sigmoidf(pk); g = s - yk; h = s * (1.0f - s); } /* loss.jl:54-57 */
+                else if (p->loss == ORC_POISSON) { float pr = expf(pk); g = pr - yk; h = pr; }                     /* loss.jl:59-62 */
+                else if (p->loss == ORC_GAMMA) { float pr = expf(pk); g = 2.0f * (1.0f - yk / pr); h = 2.0f * yk / pr; } /* loss.jl:64-67 */
+                else { /* tweedie, rho = 1.5: loss.jl:69-76 */
+                    float rho = 1.5f, pr = expf(pk);
+                    g = 2.0f * (powf(pr, 2.0f - rho) - yk * powf(pr, 1.0f - rho));
+                    h = 2.0f * ((2.0f - rho) * powf(pr, 2.0f - rho) - (1.0f - rho) * yk * powf(pr, 1.0f - rho));
+                }
                 grad[k + C * i] = g * w;
                 grad[K + k + C * i] = h * w;
             }
@@ -101,6 +109,23 @@ void orc_update_grads(const orc_params *p, int64_t nobs, const float *pred, cons
                 float h = prob * (1.0f - prob);
                 grad[k + C * i] = g * w;
                 grad[K + k + C * i] = h * w;
+            }
+        }
+    } else if (p->loss == ORC_LOGISTIC_MLE) { /* mle2p_grad_hess, loss.jl:207-217 */
+        const float *y = (const float *)yv;
+        const int Y = K / 2;
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < nobs; i++) {
+            float w = grad[(C - 1) + C * i];
+            for (int t = 0; t < Y; t++) {
+                int gb = 2 * t, hb = 2 * Y + 2 * t;
+                float loc = pred[2 * t + K * i], sr = pred[2 * t + 1 + K * i];
+                float scale = orc_softplusf(sr), ds = orc_sigmoidf(sr);
+                float z = (y[t + Y * i] - loc) / scale, th = tanhf(z / 2.0f);
+                grad[gb + C * i] = -th / scale * w;
+                grad[gb + 1 + C * i] = (1.0f - z * th) * ds / scale * w;
+                grad[hb + C * i] = 1.0f / (3.0f * scale * scale) * w;
+                grad[hb + 1 + C * i] = (3.14159274f * 3.14159274f + 3.0f) / 9.0f * (ds / scale) * (ds / scale) * w;
             }
         }
     } else if (p->loss == ORC_GAUSSIAN_MLE) {
@@ -151,7 +176,7 @@ static double split_gain(const double *s, const double *sl, int C, double w_l, d
 /* pred_scalar: src/predict.jl:205-208 (gradient regression), :235-238 (MLE2P) */
 static double pred_scalar(const double *s, const orc_params *p) {
     const double eps = DBL_EPSILON;
-    if (p->loss == ORC_GAUSSIAN_MLE)
+    if (orc_is_mle(p->loss))
         return -p->eta / p->bagging_size * s[0] / fmax(eps, s[2] + p->lambda * s[4] + p->L2);
     return -p->eta / p->bagging_size * s[0] / fmax(eps, s[1] + p->lambda * s[2] + p->L2);
 }
@@ -159,7 +184,7 @@ static double pred_scalar(const double *s, const orc_params *p) {
 static void pred_leaf(float *tpred, int n0, const double *s, const orc_params *p) {
     const double eps = DBL_EPSILON;
     const int K = p->K, C = 2 * K + 1;
-    if (p->loss == ORC_GAUSSIAN_MLE) {
+    if (orc_is_mle(p->loss)) {
         int Y = K / 2;
         double wsum = s[C - 1];
         for (int t = 0; t < Y; t++) {
@@ -414,7 +439,7 @@ void orc_predict_tree(int32_t loss, int32_t K, int64_t nobs, const uint8_t *x_bi
         const float *tp = tpred + K * (nid - 1);
         if (loss == ORC_LOGLOSS) {
             for (int k = 0; k < K; k++) { float v = pi[k] + tp[k]; pi[k] = fminf(fmaxf(v, -15.0f), 15.0f); }
-        } else if (loss == ORC_GAUSSIAN_MLE) {
+        } else if (orc_is_mle(loss)) {
             for (int t = 0; t < K / 2; t++) {
                 pi[2 * t] += tp[2 * t];
                 pi[2 * t + 1] = fmaxf(-15.0f, pi[2 * t + 1] + tp[2 * t + 1]);
@@ -442,7 +467,8 @@ void orc_link(int32_t loss, int32_t K, int64_t nobs, float *pred) {
     for (int64_t i = 0; i < nobs; i++) {
         float *pi = pred + K * i;
         if (loss == ORC_LOGLOSS) { for (int k = 0; k < K; k++) pi[k] = orc_sigmoidf(pi[k]); }
-        else if (loss == ORC_GAUSSIAN_MLE) { for (int k = 1; k < K; k += 2) pi[k] = orc_softplusf(pi[k]); }
+        else if (orc_is_mle(loss)) { for (int k = 1; k < K; k += 2) pi[k] = orc_softplusf(pi[k]); }
+        else if (loss == ORC_POISSON || loss == ORC_GAMMA || loss == ORC_TWEEDIE) { for (int k = 0; k < K; k++) pi[k] = expf(pi[k]); }
         else if (loss == ORC_MLOGLOSS) {
             float s = 0.0f;
             for (int k = 0; k < K; k++) { pi[k] = expf(pi[k]); s += pi[k]; }
@@ -456,7 +482,8 @@ void orc_link(int32_t loss, int32_t K, int64_t nobs, float *pred) {
  * sum(Float64, eval) / sum(Float64, w); out[0] and out[1] are the two sums (the caller divides; rmse takes the
  * square root of the mse ratio, :53-54).  Unpinned, like the rest of this file: the reference's own tests compare
  * the logged metric with a metric recomputed from `predict` (test/metrics.jl:71-123), which tests/ repeats. */
-enum { ORC_METRIC_MSE = 0, ORC_METRIC_MAE = 1, ORC_METRIC_LOGLOSS = 2, ORC_METRIC_MLOGLOSS = 3, ORC_METRIC_GAUSSIAN_MLE = 4 };
+enum { ORC_METRIC_MSE = 0, ORC_METRIC_MAE = 1, ORC_METRIC_LOGLOSS = 2, ORC_METRIC_MLOGLOSS = 3, ORC_METRIC_GAUSSIAN_MLE = 4,
+       ORC_METRIC_POISSON = 5, ORC_METRIC_GAMMA = 6, ORC_METRIC_TWEEDIE = 7, ORC_METRIC_LOGISTIC_MLE = 8 };
 void orc_eval_metric(int32_t metric, int32_t K, int64_t nobs, const float *pred, const void *yv, int32_t ycols,
                      const float *w, float *eval, double out[2]) {
 #pragma omp parallel for schedule(static)
@@ -468,14 +495,15 @@ void orc_eval_metric(int32_t metric, int32_t K, int64_t nobs, const float *pred,
             float isum = 0.0f;
             for (int k = 0; k < K; k++) isum += expf(p[k]);
             eval[i] = wi * (logf(isum) - p[yi - 1]);
-        } else if (metric == ORC_METRIC_GAUSSIAN_MLE) {
+        } else if (metric == ORC_METRIC_GAUSSIAN_MLE || metric == ORC_METRIC_LOGISTIC_MLE) {
             const float *y = (const float *)yv + (size_t)ycols * i;
             const int Y = K / 2;
             float acc = 0.0f;
             for (int t = 0; t < Y; t++) {
                 const float scale = orc_softplusf(p[2 * t + 1]);
                 const float d = y[t] - p[2 * t];
-                acc += -(logf(scale) + d * d / (2.0f * scale * scale));
+                if (metric == ORC_METRIC_GAUSSIAN_MLE) acc += -(logf(scale) + d * d / (2.0f * scale * scale));
+                else { const float az = fabsf(d / scale); acc += -logf(scale) - az - 2.0f * log1pf(expf(-az)); } /* metrics.jl:84-89 */
             }
             eval[i] = wi * acc / (float)Y;
         } else {
@@ -485,7 +513,15 @@ void orc_eval_metric(int32_t metric, int32_t K, int64_t nobs, const float *pred,
                 const float pk = p[k], yk = ycols == 1 ? y[0] : y[k]; /* _target(y, k, i), src/loss.jl:49-50 */
                 if (metric == ORC_METRIC_MSE) acc += (pk - yk) * (pk - yk);
                 else if (metric == ORC_METRIC_MAE) acc += fabsf(pk - yk);
-                else { const float s = orc_sigmoidf(pk); acc += -yk * logf(s) + (yk - 1.0f) * logf(1.0f - s); }
+                else if (metric == ORC_METRIC_LOGLOSS) { const float s = orc_sigmoidf(pk); acc += -yk * logf(s) + (yk - 1.0f) * logf(1.0f - s); }
+                else if (metric == ORC_METRIC_POISSON) { /* metrics.jl:13-17, eps(1f-7) = 2^-47 */
+                    const float pr = expf(pk);
+                    acc += 2.0f * (yk * logf(yk / pr + 7.1054274e-15f) + pr - yk);
+                } else if (metric == ORC_METRIC_GAMMA) { const float pr = expf(pk); acc += 2.0f * (logf(pr / yk) + yk / pr - 1.0f); }
+                else { /* tweedie, rho = 1.5: metrics.jl:24-28 */
+                    const float rho = 1.5f, pr = expf(pk);
+                    acc += 2.0f * (powf(yk, 2.0f - rho) / (1.0f - rho) / (2.0f - rho) - yk * powf(pr, 1.0f - rho) / (1.0f - rho) + powf(pr, 2.0f - rho) / (2.0f - rho));
+                }
             }
             eval[i] = wi * acc / (float)K;
         }

@@ -22,7 +22,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_ref", "libevo_oracle.so")
 
-LOSSES = {"mse": 0, "logloss": 1, "mlogloss": 2, "gaussian_mle": 3}
+LOSSES = {"mse": 0, "logloss": 1, "mlogloss": 2, "gaussian_mle": 3, "poisson": 4, "gamma": 5, "tweedie": 6, "logistic_mle": 7}
 
 
 class OrcParams(C.Structure):
@@ -208,15 +208,21 @@ def init_pred(p: Params, y: np.ndarray) -> np.ndarray:
         cnt = np.bincount(y.astype(np.int64) - 1, minlength=p.K).astype(np.float64)
         mu = np.log(cnt / cnt.sum()).astype(np.float32)
         return (mu - mu.max()).astype(np.float32)
-    if p.loss == "gaussian_mle":
+    if p.loss in ("poisson", "gamma", "tweedie"):
+        return np.array([np.log(np.mean(y.astype(np.float32), dtype=np.float32))], np.float32)
+    if p.loss in ("gaussian_mle", "logistic_mle"):
         y32 = y.astype(np.float32)
         sd = np.float32(np.std(y32.astype(np.float64), ddof=1))
+        if p.loss == "logistic_mle":
+            sd = np.float32(sd * np.sqrt(3.0) / np.pi)   # src/init.jl:86
         return np.array([np.mean(y32, dtype=np.float32), lib().orc_invsoftplus64(float(sd))], np.float32)
     raise ValueError(p.loss)
 
 
-METRICS = {"mse": 0, "rmse": 0, "mae": 1, "logloss": 2, "mlogloss": 3, "gaussian_mle": 4}
-IS_MAXIMISE = {"mse": False, "rmse": False, "mae": False, "logloss": False, "mlogloss": False, "gaussian_mle": True}
+METRICS = {"mse": 0, "rmse": 0, "mae": 1, "logloss": 2, "mlogloss": 3, "gaussian_mle": 4, "poisson": 5, "gamma": 6, "tweedie": 7,
+           "logistic_mle": 8}
+IS_MAXIMISE = {"mse": False, "rmse": False, "mae": False, "logloss": False, "mlogloss": False, "gaussian_mle": True,
+               "poisson": False, "gamma": False, "tweedie": False, "logistic_mle": True}
 
 
 def eval_metric(metric: str, pred: np.ndarray, y: np.ndarray, w: np.ndarray | None = None) -> float:

@@ -30,12 +30,16 @@ def _data(loss, n, seed):
         y = (y > np.median(y)).astype(np.float32)
     if loss == "mlogloss":
         y = np.digitize(y, np.quantile(y, [0.3, 0.6])).astype(np.int64)
+    if loss in ("poisson", "gamma", "tweedie"):
+        y = np.exp(0.5 * (y - y.mean()) / y.std()).astype(np.float32)      # positive target for the log link
     return x, y
 
 
 CASES = [("mse", "mse", "EvoTreeRegressor"), ("mse", "rmse", "EvoTreeRegressor"), ("mse", "mae", "EvoTreeRegressor"),
          ("logloss", "logloss", "EvoTreeRegressor"), ("mlogloss", "mlogloss", "EvoTreeClassifier"),
-         ("gaussian_mle", "gaussian_mle", "EvoTreeMLE")]
+         ("gaussian_mle", "gaussian_mle", "EvoTreeMLE"), ("poisson", "poisson", "EvoTreeRegressor"),
+         ("gamma", "gamma", "EvoTreeRegressor"), ("tweedie", "tweedie", "EvoTreeRegressor"),
+         ("logistic_mle", "logistic_mle", "EvoTreeMLE"), ("gaussian_mle", "logistic_mle", "EvoTreeMLE")]
 
 
 @pytest.mark.parametrize("loss,metric,learner", CASES)
@@ -53,7 +57,7 @@ def test_logged_metric_matches_oracle(pkg, orc, loss, metric, learner):
     np.testing.assert_allclose(np.array(lg["metrics"]), ref, rtol=RTOL)
     # the metric moves in the right direction on data drawn from the training distribution
     better = lg["metrics"][-1] > lg["metrics"][0] if lg["maximise"] else lg["metrics"][-1] < lg["metrics"][0]
-    assert better and lg["maximise"] == (metric == "gaussian_mle")
+    assert better and lg["maximise"] == (metric in ("gaussian_mle", "logistic_mle"))
 
 
 def test_eval_predictions_and_offset(pkg, orc):

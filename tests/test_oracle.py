@@ -291,3 +291,68 @@ def test_eval_metrics_against_float64_formulas(orc):
     p2 = rng.normal(0, 1, (n, 3)).astype(np.float32)
     y2 = rng.normal(0, 1, (n, 3)).astype(np.float32)
     assert np.isclose(orc.eval_metric("mse", p2, y2), np.mean((p2.astype(np.float64) - y2) ** 2), rtol=1e-6)
+
+
+def test_log_link_and_logistic_gradients_against_finite_differences(orc):
+    """poisson / gamma / tweedie / logistic_mle gradients of the oracle (src/loss.jl:59-76, 207-217) against central
+    differences of the losses they derive from, as the reference's test/metrics.jl does for the MLE losses; the
+    hessians of the log-link losses against the derivative of the gradient."""
+    rng = np.random.default_rng(3)
+    n = 400
+    p64 = rng.normal(0.2, 0.7, n)
+    y = np.exp(rng.normal(0.0, 0.6, n)).astype(np.float32)
+
+    def grads(loss, pred, yy, K=1):
+        par = orc.Params(loss=loss, K=K)
+        g = np.zeros((pred.shape[0], 2 * K + 1), np.float32)
+        g[:, -1] = 1.0
+        orc.update_grads(par, np.ascontiguousarray(pred, np.float32), yy, g)
+        return g.astype(np.float64)
+
+    losses = {
+        "poisson": lambda p, yy: np.exp(p) - yy * p,
+        "gamma": lambda p, yy: 2 * (p + yy / np.exp(p)),
+        "tweedie": lambda p, yy: 2 * (np.exp(p) ** 0.5 / 0.5 - yy * np.exp(p) ** -0.5 / -0.5),
+    }
+    h = 1e-4
+    for name, f in losses.items():
+        g = grads(name, p64.reshape(-1, 1), y)
+        fd = (f(p64 + h, y.astype(np.float64)) - f(p64 - h, y.astype(np.float64))) / (2 * h)
+        assert np.allclose(g[:, 0], fd, rtol=2e-4, atol=2e-4), name
+        fd2 = (f(p64 + h, y) - 2 * f(p64, y) + f(p64 - h, y)) / h ** 2
+        assert np.allclose(g[:, 1], fd2, rtol=5e-3, atol=5e-3), name + " hessian"
+
+    # logistic: nll = log(s) + z + 2 log(1 + exp(-z)), z = (y - loc) / s, s = softplus(raw)
+    loc, raw = rng.normal(0, 1, n), rng.normal(0.3, 0.6, n)
+    yl = rng.normal(0, 1.5, n).astype(np.float32)
+
+    def nll(lc, rw):
+        s = np.log1p(np.exp(rw))
+        z = (yl - lc) / s
+        return np.log(s) + z + 2 * np.log1p(np.exp(-z))
+
+    g = grads("logistic_mle", np.stack([loc, raw], axis=1), yl, K=2)
+    assert np.allclose(g[:, 0], (nll(loc + h, raw) - nll(loc - h, raw)) / (2 * h), rtol=2e-3, atol=2e-4)
+    assert np.allclose(g[:, 1], (nll(loc, raw + h) - nll(loc, raw - h)) / (2 * h), rtol=2e-3, atol=2e-4)
+    # Fisher information of Logistic(loc, s): 1 / (3 s^2) and (pi^2 + 3) / (9 s^2) (chain rule with dscale)
+    s = np.log1p(np.exp(raw))
+    ds = 1 / (1 + np.exp(-raw))
+    assert np.allclose(g[:, 2], 1 / (3 * s ** 2), rtol=1e-5)
+    assert np.allclose(g[:, 3], (np.pi ** 2 + 3) / 9 * (ds / s) ** 2, rtol=1e-5)
+
+
+def test_deviance_metrics_against_float64_formulas(orc):
+    rng = np.random.default_rng(8)
+    n = 3000
+    p = rng.normal(0.1, 0.5, (n, 1)).astype(np.float32)
+    y = np.exp(rng.normal(0, 0.5, n)).astype(np.float32)
+    w = rng.uniform(0.5, 2.0, n).astype(np.float32)
+    pr, y64, w64 = np.exp(p[:, 0].astype(np.float64)), y.astype(np.float64), w.astype(np.float64)
+    ref = {"poisson": 2 * (y64 * np.log(y64 / pr) + pr - y64), "gamma": 2 * (np.log(pr / y64) + y64 / pr - 1),
+           "tweedie": 2 * (y64 ** 0.5 / -0.5 / 0.5 - y64 * pr ** -0.5 / -0.5 + pr ** 0.5 / 0.5)}
+    for name, v in ref.items():
+        assert np.isclose(orc.eval_metric(name, p, y, w), np.sum(w64 * v) / w64.sum(), rtol=2e-4, atol=1e-6), name
+    pg = np.stack([rng.normal(0, 1, n), rng.normal(0, 1, n)], axis=1).astype(np.float32)
+    s = np.log1p(np.exp(pg[:, 1].astype(np.float64)))
+    az = np.abs((y64 - pg[:, 0]) / s)
+    assert np.isclose(orc.eval_metric("logistic_mle", pg, y, w), np.sum(w64 * (-np.log(s) - az - 2 * np.log1p(np.exp(-az)))) / w64.sum(), rtol=1e-5)

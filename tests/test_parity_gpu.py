@@ -65,6 +65,49 @@ def test_gaussian_mle(pkg, orc):
     assert s["splits"] > 50, s
 
 
+def _positive_target(n, f, seed, kind):
+    """Count / positive targets with a log-linear mean, the shapes the log-link losses are meant for."""
+    rng = np.random.default_rng(seed)
+    x = rng.random((n, f)).astype(np.float32)
+    mu = np.exp(0.3 + x[:, :4] @ np.array([0.8, -0.6, 0.4, 0.3]))
+    if kind == "poisson":
+        y = rng.poisson(mu)
+    elif kind == "gamma":
+        y = rng.gamma(2.0, mu / 2.0) + 1e-3
+    else:  # tweedie: compound poisson-gamma with exact zeros
+        cnt = rng.poisson(mu)
+        y = np.array([rng.gamma(2.0, 0.5, c).sum() if c > 0 else 0.0 for c in cnt])
+    return x, y.astype(np.float32)
+
+
+@pytest.mark.parametrize("loss", ["poisson", "gamma", "tweedie"])
+def test_log_link_losses(pkg, orc, loss):
+    """poisson / gamma / tweedie (src/loss.jl:59-76): gradients, log-mean bias, trees and predictions in lock-step."""
+    x, y = _positive_target(40_000, 12, seed=31, kind=loss)
+    p = pkg.EvoTreeRegressor(loss=loss, nrounds=3, max_depth=5, nbins=32, eta=0.3)
+    s = lockstep_check(pkg, orc, p, x, y, rounds=3)
+    assert s["splits"] > 20, s
+
+
+def test_evotreecount_is_poisson(pkg, orc):
+    x, y = _positive_target(20_000, 8, seed=4, kind="poisson")
+    p = pkg.EvoTreeCount(nrounds=2, max_depth=4, nbins=16, eta=0.3)
+    assert p.loss == "poisson" and p.metric == "poisson"
+    lockstep_check(pkg, orc, p, x, y, rounds=2)
+
+
+def test_logistic_mle(pkg, orc):
+    """Two-parameter logistic likelihood (src/loss.jl:207-217): same shape as the gaussian case."""
+    rng = np.random.default_rng(23)
+    n, f = 60_000, 20
+    x = rng.random((n, f)).astype(np.float32)
+    y = (x @ rng.normal(size=f) + np.exp(0.5 * x[:, 0]) * rng.logistic(size=n)).astype(np.float32)
+    p = pkg.EvoTreeMLE(loss="logistic_mle", nrounds=3, max_depth=6, nbins=32, eta=0.2)
+    assert p.metric == "logistic_mle" and pkg.EvoTreeMLE(loss="logistic").loss == "logistic_mle"
+    s = lockstep_check(pkg, orc, p, x, y, rounds=3)
+    assert s["splits"] > 30, s
+
+
 @pytest.mark.parametrize("depth", [1, 2, 3])
 def test_shallow_depths(pkg, orc, depth):
     x, y = make_regression(5_000, 7, seed=depth)

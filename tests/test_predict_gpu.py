@@ -25,7 +25,9 @@ def _oracle_predict(orc, m, op, x, ntree_limit=None, link=True):
 
 
 CASES = [("mse", "EvoTreeRegressor", dict(max_depth=5, nbins=32)), ("logloss", "EvoTreeRegressor", dict(max_depth=4, nbins=16)),
-         ("mlogloss", "EvoTreeClassifier", dict(max_depth=4, nbins=16)), ("gaussian_mle", "EvoTreeMLE", dict(max_depth=4, nbins=32))]
+         ("mlogloss", "EvoTreeClassifier", dict(max_depth=4, nbins=16)), ("gaussian_mle", "EvoTreeMLE", dict(max_depth=4, nbins=32)),
+         ("poisson", "EvoTreeRegressor", dict(max_depth=4, nbins=16)), ("gamma", "EvoTreeRegressor", dict(max_depth=4, nbins=16)),
+         ("tweedie", "EvoTreeRegressor", dict(max_depth=4, nbins=16)), ("logistic_mle", "EvoTreeMLE", dict(max_depth=4, nbins=32))]
 
 
 @pytest.mark.parametrize("loss,learner,kw", CASES)
@@ -35,6 +37,8 @@ def test_predict_matches_oracle(pkg, orc, loss, learner, kw):
         y = (y > np.median(y)).astype(np.float32)
     if loss == "mlogloss":
         y = np.digitize(y, np.quantile(y, [0.3, 0.6])).astype(np.int64)
+    if loss in ("poisson", "gamma", "tweedie"):
+        y = np.exp(0.5 * (y - y.mean()) / y.std()).astype(np.float32)      # positive target for the log link
     params = getattr(pkg, learner)(loss=loss, nrounds=6, eta=0.3, **kw)
     m = pkg.fit(params, x_train=x, y_train=y)
     assert len(m.trees) == 7 and m.info["nrounds"] == 6
