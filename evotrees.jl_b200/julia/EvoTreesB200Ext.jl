@@ -174,8 +174,8 @@ function EvoTrees.CallBack(params::EvoTypes, m::EvoTree{L,K}, x_eval::AbstractMa
     if !isnothing(offset_eval)                     # same link transforms as src/callback.jl:110-118
         off = Float32.(offset_eval)
         L == EvoTrees.LogLoss && (off .= EvoTrees.logit.(off))
-        L == EvoTrees.MLogLoss && (off .= log.(off))
-        L == EvoTrees.GaussianMLE && EvoTrees.unconstrain_mle_scale!(off)
+        L in (EvoTrees.MLogLoss, EvoTrees.Poisson, EvoTrees.Gamma, EvoTrees.Tweedie) && (off .= log.(off))
+        L in (EvoTrees.GaussianMLE, EvoTrees.LogisticMLE) && EvoTrees.unconstrain_mle_scale!(off)
         p0 = Matrix{Float32}(reshape(off, size(x_eval, 1), :)')   # K x nobs
     end
     bias = Float32.(m.trees[end].pred[:, 1])
