@@ -216,7 +216,7 @@ def main():
             torch.cuda.synchronize()
 
     # ---- device-resident loop: `value` --------------------------------------------------------------------
-    def run_rounds(cache, k):
+    def run_rounds(cache, k, keep=None):
         """k boosting rounds, the host one tree ahead of the GPU (how `fit` drives the library)."""
         in_flight = 0
         for _ in range(k):
@@ -224,11 +224,15 @@ def main():
             pkg.grow_tree_begin(cache, params, mask, js, True)
             in_flight += 1
             if in_flight == 2:
-                pkg.grow_tree_end(cache, params)
+                t = pkg.grow_tree_end(cache, params)
                 in_flight -= 1
+                if keep is not None:
+                    keep.append(t)
         while in_flight:
-            pkg.grow_tree_end(cache, params)
+            t = pkg.grow_tree_end(cache, params)
             in_flight -= 1
+            if keep is not None:
+                keep.append(t)
 
     cache = create()
     ext = torch.cuda.ExternalStream(cache.stream(), device=torch.device("cuda", local))
@@ -262,6 +266,7 @@ def main():
 
     # ---- end to end through the public C-ABI path from host buffers: `e2e` --------------------------------
     e2e = None
+    inference = None
     if not args.no_e2e:
         sync_all()
         t0 = time.perf_counter()
@@ -276,10 +281,24 @@ def main():
         torch.cuda.synchronize()
         t_first = time.perf_counter() - t0
         t0 = time.perf_counter()
-        run_rounds(cache2, args.steps)                      # every round returns its tree arrays to the host (D2H)
+        grown = []
+        run_rounds(cache2, args.steps, grown)               # every round returns its tree arrays to the host (D2H)
         torch.cuda.synchronize()
         t_loop = time.perf_counter() - t0
         cache2.close()
+        if world == 1 and grown:
+            # inference (`m(x)` on binned input): a model of ROUNDS_PER_JOB trees + the bias tree, made by repeating the
+            # trees just grown (the cost of a tree does not depend on which boosting round it comes from), applied to
+            # all rows from the host matrix: H2D of x_bin, traversal of every tree, D2H of the predictions
+            from evotrees_b200.model import EvoTree, Tree
+            trees = [Tree.bias(mu)] + [grown[i % len(grown)] for i in range(ROUNDS_PER_JOB)]
+            model = EvoTree("mse", K, trees, {"feattypes": np.ones(feats, bool) if feattypes is None else feattypes})
+            pkg.predict_binned(model, xb_host[:1000], device=local)          # warm-up
+            t0 = time.perf_counter()
+            pkg.predict_binned(model, xb_host, device=local)
+            t_pred = time.perf_counter() - t0
+            inference = {"rows_per_s": nloc / t_pred, "seconds": t_pred, "rows": nloc, "trees": len(trees),
+                         "input": "host x_bin (uint8): H2D, traversal of all trees, D2H of the predictions inside the timed region"}
         e2e_s = t_create + t_first + t_loop / args.steps * (ROUNDS_PER_JOB - 1)
         if world > 1:
             t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
@@ -330,6 +349,7 @@ def main():
             "gpu_launches": int(launches),
             "clocks": clocks,
             "e2e": e2e,
+            "inference": inference,
         }
         if not args.no_cpu_baseline and world == 1:
             try:
