@@ -14,7 +14,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libevotrees_b200.so")
 
 EVB_F32, EVB_U32, EVB_F64 = 0, 1, 2
-LOSS_CODES = {"mse": 0, "logloss": 1, "mlogloss": 2, "gaussian_mle": 3, "poisson": 4, "gamma": 5, "tweedie": 6, "logistic_mle": 7}
+LOSS_CODES = {"mse": 0, "logloss": 1, "mlogloss": 2, "gaussian_mle": 3, "poisson": 4, "gamma": 5, "tweedie": 6, "logistic_mle": 7,
+              "mae": 8, "cred_var": 9, "cred_std": 10}
 METRIC_CODES = {"mse": 0, "rmse": 0, "mae": 1, "logloss": 2, "mlogloss": 3, "gaussian_mle": 4, "poisson": 5, "gamma": 6, "tweedie": 7,
                 "logistic_mle": 8}  # rmse = sqrt of the mse sums
 FLAG_TIMING, FLAG_FULL_PARTITION, FLAG_KEEP_ALL_HIST = 1, 2, 4

@@ -271,7 +271,7 @@ extern "C" int32_t evb_create(evb_handle **out, const evb_params *p, int64_t nob
     *out = nullptr;
     if (!p || !x_bin || !y || (!pred0 && !mu)) { evb_set_error("evb_create: null argument"); return EVB_ERR_ARG; }
     if (nobs < 1 || nobs > 2000000000ll || nfeats < 1 || nfeats > 65535) { evb_set_error("evb_create: nobs/nfeats out of range"); return EVB_ERR_ARG; }
-    if (p->loss < 0 || p->loss > EVB_LOGISTIC_MLE) { evb_set_error("evb_create: unknown loss %d", p->loss); return EVB_ERR_ARG; }
+    if (p->loss < 0 || p->loss > EVB_LOSS_LAST) { evb_set_error("evb_create: unknown loss %d", p->loss); return EVB_ERR_ARG; }
     if (p->K < 1 || p->K > 32) { evb_set_error("evb_create: K=%d outside 1..32", p->K); return EVB_ERR_ARG; }
     const bool mle = p->loss == EVB_GAUSSIAN_MLE || p->loss == EVB_LOGISTIC_MLE;
     if ((mle && (p->K % 2 != 0 || ycols != p->K / 2)) || (!mle && p->loss != EVB_MLOGLOSS && ycols != p->K) ||

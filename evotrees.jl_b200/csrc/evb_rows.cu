@@ -43,6 +43,13 @@ __device__ __forceinline__ void grad_row(int loss, int K, int NCH, bool elided, 
             REC(k) = (((uint32_t)(k + 1) == yi) ? prob - 1.0f : prob) * w;
             REC(K + k) = prob * (1.0f - prob) * w;
         }
+    } else if (loss == EVB_MAE || loss == EVB_CRED_VAR || loss == EVB_CRED_STD) { // src/loss.jl:86-91
+        const float *yf = (const float *)y + (size_t)i * ycols;
+        for (int k = 0; k < K; ++k) {
+            const float d = yf[k] - p[k];
+            REC(k) = d * w;
+            REC(K + k) = (loss == EVB_MAE ? 0.0f : d * d) * w;
+        }
     } else if (loss == EVB_POISSON || loss == EVB_GAMMA || loss == EVB_TWEEDIE) { // src/loss.jl:65-84
         const float *yf = (const float *)y + (size_t)i * ycols;
         for (int k = 0; k < K; ++k) {
@@ -684,7 +691,7 @@ static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntr
                             int32_t x_dtype, int32_t x_row_major, const void *edges, int32_t nedges, int64_t nobs, int32_t nfeats,
                             const uint8_t *feattypes, int32_t apply_link, float *out, uint32_t *leaf_idx, double *ms_out) {
     if (!feat || !cond_bin || !split || !leaf_pred || (!x_bin && !x) || !out || nobs < 0 || nfeats < 1 || nfeats > 65535 ||
-        ntrees < 0 || nn < 1 || K < 1 || K > 64 || loss < 0 || loss > EVB_LOGISTIC_MLE) {
+        ntrees < 0 || nn < 1 || K < 1 || K > 64 || loss < 0 || loss > EVB_LOSS_LAST) {
         evb_set_error("evb_predict: invalid argument");
         return EVB_ERR_ARG;
     }

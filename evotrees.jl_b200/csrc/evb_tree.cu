@@ -124,9 +124,35 @@ struct ScanArgs {
 __device__ __forceinline__ double term_gh(double g, double h, double w, double lambda, double L2) {
     return g * g / fmax(DBL_EPSILON, h + lambda * w + L2) / 2.0; // src/split.jl:1
 }
-// pred_leaf_cpu! for output row k (src/predict.jl:198-204, 224-234, 241-247)
+// mae: |mean of the side - mean of the parent| * weight / (1 + lambda + L2 / w)   (src/split.jl:2, 119-130)
+__device__ __forceinline__ double term_shift(double g, double w, double mu_p, double d) { return fabs(g / w - mu_p) * w / d; }
+// credibility losses: Z * |m1| / (1 + L2 / w), Z from the ratio of variances or of standard deviations
+// (src/split.jl:3-4, src/loss.jl:275-289)
+__device__ __forceinline__ double term_cred(int loss, double m1, double m2, double w, double L2) {
+    const double vhm = (m1 / w) * (m1 / w);
+    const double evpv = fmax(DBL_EPSILON, m2 / w - vhm);
+    const double z = loss == EVB_CRED_VAR ? vhm / (vhm + evpv) : sqrt(vhm) / (sqrt(vhm) + sqrt(evpv));
+    return z * fabs(m1) / (1.0 + L2 / w);
+}
+__device__ __forceinline__ bool own_gain(int loss) { return loss >= EVB_MAE; }
+// gain of one output row of a candidate split: left sums (gl, hl, w_l), parent sums (sg, sh, w_p)
+__device__ __forceinline__ double side_gain(const ScanArgs &a, double gl, double hl, double w_l, double sg, double sh, double w_p) {
+    const double w_r = w_p - w_l;
+    if (a.loss == EVB_MAE) {
+        const double d_l = fmax(DBL_EPSILON, 1.0 + a.lambda + a.L2 / w_l), d_r = fmax(DBL_EPSILON, 1.0 + a.lambda + a.L2 / w_r);
+        const double mu_p = sg / w_p;
+        return term_shift(gl, w_l, mu_p, d_l) + term_shift(sg - gl, w_r, mu_p, d_r);
+    }
+    return term_cred(a.loss, gl, hl, w_l, a.L2) + term_cred(a.loss, sg - gl, sh - hl, w_r, a.L2);
+}
+// pred_scalar of the three losses (src/predict.jl:219-222, 257-261): the sign is the gradient's, not minus it
+__device__ __forceinline__ double own_scalar(const ScanArgs &a, double g, double w) {
+    return -a.neb * g / (a.loss == EVB_MAE ? fmax(DBL_EPSILON, w + a.lambda * w + a.L2) : (w + a.L2));
+}
+// pred_leaf_cpu! for output row k (src/predict.jl:198-204, 224-234, 241-247; mae :250-257, cred :211-218)
 __device__ __forceinline__ float leaf_value(const ScanArgs &a, const double *s, int k) {
     const int K = a.K, C = a.C;
+    if (own_gain(a.loss)) return (float)own_scalar(a, s[k], s[C - 1]);
     double g, h;
     if (a.loss == EVB_GAUSSIAN_MLE || a.loss == EVB_LOGISTIC_MLE) {
         const int Y = K / 2, t = k >> 1, j = k & 1;
@@ -174,7 +200,7 @@ __global__ void __launch_bounds__(256) k_peer_reduce(PeerReduceArgs a) {
 // Scan of one (node, feature): applies the sibling subtraction (`subtract_hist!`, fit-utils.jl:321-332) to the
 // staged histogram `sm` of the build node, stores the node's histogram if its children will need it, scans the
 // bins (`_scan_node!`, fit-utils.jl:403-436) and records the best split of this feature.
-template <int MAXCHK>
+template <int MAXCHK, bool OWN>
 __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int f, const double *sm, double *s_sum, int lane, bool first_owned) {
     const int C = a.C, K = a.K, B = a.B, F = a.F;
     const int m = 1 << (a.level - 1);
@@ -197,7 +223,11 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
     __syncwarp();
     double gain_p = 0.0;
     const double w_p = s_sum[C - 1];
-    for (int k = 0; k < K; ++k) gain_p += term_gh(s_sum[k], s_sum[K + k], w_p, a.lambda, a.L2); // node_gain, split.jl:58-66
+    if (!OWN) {
+        for (int k = 0; k < K; ++k) gain_p += term_gh(s_sum[k], s_sum[K + k], w_p, a.lambda, a.L2); // node_gain, split.jl:58-66
+    } else if (a.loss != EVB_MAE) {
+        for (int k = 0; k < K; ++k) gain_p += term_cred(a.loss, s_sum[k], s_sum[K + k], w_p, a.L2);   // split.jl:70-78; mae: 0
+    }
 
     const int nchk = (B + 31) >> 5;
     const uint32_t feat = a.js0[f];
@@ -245,11 +275,13 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
                         hl = warp_incl_scan(hl, lane) + chh; chh = __shfl_sync(FULL, hl, 31);
                     }
                     const double w_l = wl[ch], w_r = w_p - w_l;
-                    gacc[ch] += term_gh(gl, hl, w_l, a.lambda, a.L2) + term_gh(sg - gl, sh - hl, w_r, a.lambda, a.L2);
+                    if (!OWN) gacc[ch] += term_gh(gl, hl, w_l, a.lambda, a.L2) + term_gh(sg - gl, sh - hl, w_r, a.lambda, a.L2);
+                    else gacc[ch] += side_gain(a, gl, hl, w_l, sg, sh, w_p);
                     if (k == 0 && constraint != 0) {
                         // pred_scalar on left / right sums (src/predict.jl:205-208, 235-238)
-                        const double pl = a.neb * gl / fmax(DBL_EPSILON, hl + a.lambda * w_l + a.L2);
-                        const double pr = a.neb * (sg - gl) / fmax(DBL_EPSILON, (sh - hl) + a.lambda * w_r + a.L2);
+                        const double pl = OWN ? own_scalar(a, gl, w_l) : a.neb * gl / fmax(DBL_EPSILON, hl + a.lambda * w_l + a.L2);
+                        const double pr = OWN ? own_scalar(a, sg - gl, w_r)
+                                                           : a.neb * (sg - gl) / fmax(DBL_EPSILON, (sh - hl) + a.lambda * w_r + a.L2);
                         const bool ok = (constraint == -1 && pl > pr) || (constraint == 1 && pl < pr);
                         if (!ok) okmask &= ~(1u << ch);
                     }
@@ -285,7 +317,8 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
 // Stage 1: one warp per (node, owned feature slot), lanes over bins.  The nodes of a level come in pairs sharing a
 // build slot: the build node reads the slot's histogram, its sibling subtracts it from the parent's.  Warps are
 // independent, so even the root level (one node) spreads over many SMs.
-template <int MAXCHK>
+// OWN: the loss brings its own split gain (mae, credibility); the default instance does not carry that code
+template <int MAXCHK, bool OWN>
 __global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
     __shared__ double s_sum_all[8][72];
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
@@ -300,7 +333,7 @@ __global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
     const int f = fi * a.world + a.rank;
     const int nb = a.slot_node[s];
     const double *src = a.hcomp + ((size_t)s * F + f) * C * B;
-    scan_one<MAXCHK>(a, which ? nb ^ 1 : nb, which != 0, f, src, s_sum_all[wid], lane, fi == 0);
+    scan_one<MAXCHK, OWN>(a, which ? nb ^ 1 : nb, which != 0, f, src, s_sum_all[wid], lane, fi == 0);
 }
 
 // Writes everything that follows from the split decision of node n: child sums, tree arrays, leaf values
@@ -773,8 +806,10 @@ int32_t evb_launch_scan(evb_handle *h, int level) {
     const long long warps = (long long)slots * Fown * (level > 1 ? 2 : 1);
     evb_tic(h, EVB_T_SCAN);
     if (warps > 0) {
-        if (h->B <= 64) k_scan_feat<2><<<(unsigned)((warps + 7) / 8), 256, 0, h->st>>>(a);
-        else k_scan_feat<8><<<(unsigned)((warps + 7) / 8), 256, 0, h->st>>>(a);
+        const unsigned grid = (unsigned)((warps + 7) / 8);
+        const bool own = h->p.loss >= EVB_MAE;
+        if (h->B <= 64) { if (own) k_scan_feat<2, true><<<grid, 256, 0, h->st>>>(a); else k_scan_feat<2, false><<<grid, 256, 0, h->st>>>(a); }
+        else { if (own) k_scan_feat<8, true><<<grid, 256, 0, h->st>>>(a); else k_scan_feat<8, false><<<grid, 256, 0, h->st>>>(a); }
     }
     evb_toc(h, EVB_T_SCAN);
     evb_tic(h, EVB_T_SCAN);

@@ -58,11 +58,11 @@ class Comm:
         """Initial bias of the whole data set from per-shard sufficient statistics
         (same formulas as `_init_target`, src/init.jl:19-145)."""
         from .fit import _invsoftplus, _logit
-        if loss in ("mse", "logloss", "poisson", "gamma", "tweedie"):
+        if loss in ("mse", "logloss", "poisson", "gamma", "tweedie", "mae", "cred_var", "cred_std"):
             y2 = y.reshape(y.shape[0], -1).astype(np.float64)
             s = self.allreduce_sum(np.concatenate([y2.sum(axis=0), [y2.shape[0]]]))
             m = s[:-1] / s[-1]
-            return (m if loss == "mse" else _logit(m) if loss == "logloss" else np.log(m)).astype(np.float32)
+            return (_logit(m) if loss == "logloss" else np.log(m) if loss in ("poisson", "gamma", "tweedie") else m).astype(np.float32)
         if loss == "mlogloss":
             cnt = self.allreduce_sum(np.bincount(y.astype(np.int64) - 1, minlength=K))
             mu = np.log(cnt / cnt.sum()).astype(np.float32)

@@ -29,7 +29,7 @@ def init_target(loss: str, y_train: np.ndarray, offset):
     """`_init_target` (src/init.jl:10-146) for the four losses of this path.
     Returns K, y (device dtype), ycols, mu float32 [K], target_levels, offset (link space)."""
     levels = None
-    if loss in ("mse", "logloss", "poisson", "gamma", "tweedie"):
+    if loss in ("mse", "logloss", "poisson", "gamma", "tweedie", "mae", "cred_var", "cred_std"):
         y = np.ascontiguousarray(y_train, np.float32)
         ycols = 1 if y.ndim == 1 else y.shape[1]
         K = ycols
@@ -40,7 +40,7 @@ def init_target(loss: str, y_train: np.ndarray, offset):
             mu = _logit(m).astype(np.float32)
             if offset is not None:
                 offset = _logit(offset)
-        elif loss != "mse":                                   # log link (src/init.jl:31-42)
+        elif loss in ("poisson", "gamma", "tweedie"):          # log link (src/init.jl:31-42)
             mu = np.log(m).astype(np.float32)
             if offset is not None:
                 offset = np.log(offset)

@@ -23,7 +23,8 @@ struct EvbParams
     device::Int32; flags::UInt32
 end
 
-const LOSS_CODE = Dict(:mse => 0, :logloss => 1, :mlogloss => 2, :gaussian_mle => 3, :poisson => 4, :gamma => 5, :tweedie => 6, :logistic_mle => 7)
+const LOSS_CODE = Dict(:mse => 0, :logloss => 1, :mlogloss => 2, :gaussian_mle => 3, :poisson => 4, :gamma => 5, :tweedie => 6, :logistic_mle => 7,
+    :mae => 8, :cred_var => 9, :cred_std => 10)
 
 function check(rc::Int32)
     rc == 0 && return nothing

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-_REG_LOSSES = ("mse", "logloss", "poisson", "gamma", "tweedie")
+_REG_LOSSES = ("mse", "logloss", "poisson", "gamma", "tweedie", "mae", "cred_var", "cred_std")
 _MLE_LOSSES = ("gaussian_mle", "logistic_mle")
 
 
@@ -53,7 +53,8 @@ class EvoTypes:
         if self.loss not in self._losses:
             raise ValueError(f"Invalid loss. Must be one of: {list(self._losses)}")
         # metric defaults to the loss (src/learners.jl:75-87, 260, 352-365)
-        self.metric = self.loss if self.metric is None else str(self.metric)
+        default_metric = "mae" if self.loss in ("cred_var", "cred_std") else self.loss   # src/learners.jl:76-80
+        self.metric = default_metric if self.metric is None else str(self.metric)
         if self.metric == "gaussian":
             self.metric = "gaussian_mle"
         if self.metric == "logistic":

@@ -45,9 +45,13 @@ enum evb_status {
 };
 
 /* 0..3: the losses of the reference's GPU benchmark configurations; 4..7: the other gradient-regression and two-parameter
- * likelihood losses of src/loss.jl:65-84, 207-217 (poisson, gamma, tweedie with rho = 1.5: log link; logistic_mle) */
+ * likelihood losses of src/loss.jl:65-84, 207-217 (poisson, gamma, tweedie with rho = 1.5: log link; logistic_mle);
+ * 8..10: mae and the two credibility losses, whose split gain and leaf value are their own (src/split.jl:2-4, 119-145,
+ * src/predict.jl:211-223, 250-262) */
 enum evb_loss { EVB_MSE = 0, EVB_LOGLOSS = 1, EVB_MLOGLOSS = 2, EVB_GAUSSIAN_MLE = 3,
-                EVB_POISSON = 4, EVB_GAMMA = 5, EVB_TWEEDIE = 6, EVB_LOGISTIC_MLE = 7 };
+                EVB_POISSON = 4, EVB_GAMMA = 5, EVB_TWEEDIE = 6, EVB_LOGISTIC_MLE = 7,
+                EVB_MAE = 8, EVB_CRED_VAR = 9, EVB_CRED_STD = 10 };
+#define EVB_LOSS_LAST EVB_CRED_STD
 enum evb_dtype { EVB_F32 = 0, EVB_U32 = 1, EVB_F64 = 2 };
 
 /* flags of evb_params.flags */

@@ -34,7 +34,8 @@
 #include <omp.h>
 #endif
 
-enum { ORC_MSE = 0, ORC_LOGLOSS = 1, ORC_MLOGLOSS = 2, ORC_GAUSSIAN_MLE = 3, ORC_POISSON = 4, ORC_GAMMA = 5, ORC_TWEEDIE = 6, ORC_LOGISTIC_MLE = 7 };
+enum { ORC_MSE = 0, ORC_LOGLOSS = 1, ORC_MLOGLOSS = 2, ORC_GAUSSIAN_MLE = 3, ORC_POISSON = 4, ORC_GAMMA = 5, ORC_TWEEDIE = 6, ORC_LOGISTIC_MLE = 7,
+       ORC_MAE = 8, ORC_CRED_VAR = 9, ORC_CRED_STD = 10 };
 static inline int orc_is_mle(int loss) { return loss == ORC_GAUSSIAN_MLE || loss == ORC_LOGISTIC_MLE; }
 
 typedef struct {
@@ -94,6 +95,17 @@ void orc_update_grads(const orc_params *p, int64_t nobs, const float *pred, cons
                 }
                 grad[k + C * i] = g * w;
                 grad[K + k + C * i] = h * w;
+            }
+        }
+    } else if (p->loss == ORC_MAE || p->loss == ORC_CRED_VAR || p->loss == ORC_CRED_STD) {
+        const float *y = (const float *)yv; /* mae_grad_hess / cred_grad_hess: src/loss.jl:78-84 */
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < nobs; i++) {
+            float w = grad[(C - 1) + C * i];
+            for (int k = 0; k < K; k++) {
+                float d = y[k + K * i] - pred[k + K * i];
+                grad[k + C * i] = d * w;
+                grad[K + k + C * i] = (p->loss == ORC_MAE ? 0.0f : d * d) * w;
             }
         }
     } else if (p->loss == ORC_MLOGLOSS) {
@@ -157,16 +169,43 @@ void orc_update_grads(const orc_params *p, int64_t nobs, const float *pred, cons
 static inline double term_gh(double g, double h, double w, double lambda, double L2, double eps) {
     return g * g / fmax(eps, h + lambda * w + L2) / 2.0;
 }
-static double node_gain(const double *s, int C, double lambda, double L2, double eps) {
+/* _term_shift / _term_cred / _cred_Z: src/split.jl:2-4, src/loss.jl:275-289 */
+static inline double term_shift(double g, double w, double mu_p, double d) { return fabs(g / w - mu_p) * w / d; }
+static inline double term_cred(int loss, double m1, double m2, double w, double L2, double eps) {
+    double vhm = (m1 / w) * (m1 / w);
+    double evpv = fmax(eps, m2 / w - vhm);
+    double z = loss == ORC_CRED_VAR ? vhm / (vhm + evpv) : sqrt(vhm) / (sqrt(vhm) + sqrt(evpv));
+    return z * fabs(m1) / (1.0 + L2 / w);
+}
+static double node_gain(int loss, const double *s, int C, double lambda, double L2, double eps) {
     int K = (C - 1) / 2;
     double w = s[2 * K], gain = 0.0;
+    if (loss == ORC_MAE) return 0.0;                                                    /* split.jl:68 */
+    if (loss == ORC_CRED_VAR || loss == ORC_CRED_STD) {                                 /* split.jl:70-78 */
+        for (int k = 0; k < K; k++) gain += term_cred(loss, s[k], s[K + k], w, L2, eps);
+        return gain;
+    }
     for (int k = 0; k < K; k++) gain += term_gh(s[k], s[K + k], w, lambda, L2, eps);
     return gain;
 }
-static double split_gain(const double *s, const double *sl, int C, double w_l, double w_r, double lambda,
+static double split_gain(int loss, const double *s, const double *sl, int C, double w_l, double w_r, double lambda,
                          double L2, double eps) {
     int K = (C - 1) / 2;
     double gain = 0.0;
+    if (loss == ORC_MAE) {                                                              /* split.jl:119-130 */
+        double w_p = s[2 * K];
+        double d_l = fmax(eps, 1.0 + lambda + L2 / w_l), d_r = fmax(eps, 1.0 + lambda + L2 / w_r);
+        for (int k = 0; k < K; k++) {
+            double mu_p = s[k] / w_p;
+            gain += term_shift(sl[k], w_l, mu_p, d_l) + term_shift(s[k] - sl[k], w_r, mu_p, d_r);
+        }
+        return gain;
+    }
+    if (loss == ORC_CRED_VAR || loss == ORC_CRED_STD) {                                 /* split.jl:132-141 */
+        for (int k = 0; k < K; k++)
+            gain += term_cred(loss, sl[k], sl[K + k], w_l, L2, eps) + term_cred(loss, s[k] - sl[k], s[K + k] - sl[K + k], w_r, L2, eps);
+        return gain;
+    }
     for (int k = 0; k < K; k++) {
         double g_l = sl[k], h_l = sl[K + k];
         gain += term_gh(g_l, h_l, w_l, lambda, L2, eps) + term_gh(s[k] - g_l, s[K + k] - h_l, w_r, lambda, L2, eps);
@@ -176,6 +215,10 @@ static double split_gain(const double *s, const double *sl, int C, double w_l, d
 /* pred_scalar: src/predict.jl:205-208 (gradient regression), :235-238 (MLE2P) */
 static double pred_scalar(const double *s, const orc_params *p) {
     const double eps = DBL_EPSILON;
+    if (p->loss == ORC_MAE)          /* src/predict.jl:259-262 */
+        return p->eta / p->bagging_size * s[0] / fmax(eps, s[2] + p->lambda * s[2] + p->L2);
+    if (p->loss == ORC_CRED_VAR || p->loss == ORC_CRED_STD)   /* src/predict.jl:220-222 */
+        return p->eta / p->bagging_size * s[0] / (s[2] + p->L2);
     if (orc_is_mle(p->loss))
         return -p->eta / p->bagging_size * s[0] / fmax(eps, s[2] + p->lambda * s[4] + p->L2);
     return -p->eta / p->bagging_size * s[0] / fmax(eps, s[1] + p->lambda * s[2] + p->L2);
@@ -184,7 +227,12 @@ static double pred_scalar(const double *s, const orc_params *p) {
 static void pred_leaf(float *tpred, int n0, const double *s, const orc_params *p) {
     const double eps = DBL_EPSILON;
     const int K = p->K, C = 2 * K + 1;
-    if (orc_is_mle(p->loss)) {
+    if (p->loss == ORC_MAE) {          /* src/predict.jl:250-257 */
+        double wv = s[C - 1], denom = fmax(eps, wv + p->lambda * wv + p->L2);
+        for (int k = 0; k < K; k++) tpred[k + K * n0] = (float)(p->eta / p->bagging_size * s[k] / denom);
+    } else if (p->loss == ORC_CRED_VAR || p->loss == ORC_CRED_STD) {   /* src/predict.jl:211-218 */
+        for (int k = 0; k < K; k++) tpred[k + K * n0] = (float)(p->eta / p->bagging_size * s[k] / (s[C - 1] + p->L2));
+    } else if (orc_is_mle(p->loss)) {
         int Y = K / 2;
         double wsum = s[C - 1];
         for (int t = 0; t < Y; t++) {
@@ -328,7 +376,7 @@ int orc_grow_tree(const orc_params *p, int64_t nobs, int32_t nfeats, const uint8
                 w[n - 1] = (float)s[C - 1];
                 double best_gain = p->gamma; int best_feat = 0, best_bin = 0;
                 double sl[32], sr[32];
-                double gain_p = node_gain(s, C, p->lambda, p->L2, eps);
+                double gain_p = node_gain(p->loss, s, C, p->lambda, p->L2, eps);
                 double w_p = s[C - 1];
                 for (int jj = 0; jj < njs; jj++) {
                     int j = (int)js[jj] - 1;
@@ -350,7 +398,7 @@ int orc_grow_tree(const orc_params *p, int64_t nobs, int32_t nfeats, const uint8
                                 ok = (constraint == -1 && pl > pr) || (constraint == 1 && pl < pr);
                             }
                             if (ok) {
-                                double g = split_gain(s, sl, C, w_l, w_r, p->lambda, p->L2, eps) - gain_p;
+                                double g = split_gain(p->loss, s, sl, C, w_l, w_r, p->lambda, p->L2, eps) - gain_p;
                                 if (g > best_gain) { best_gain = g; best_feat = j + 1; best_bin = bin; }
                             }
                         }

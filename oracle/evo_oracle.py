@@ -22,7 +22,8 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_ref", "libevo_oracle.so")
 
-LOSSES = {"mse": 0, "logloss": 1, "mlogloss": 2, "gaussian_mle": 3, "poisson": 4, "gamma": 5, "tweedie": 6, "logistic_mle": 7}
+LOSSES = {"mse": 0, "logloss": 1, "mlogloss": 2, "gaussian_mle": 3, "poisson": 4, "gamma": 5, "tweedie": 6, "logistic_mle": 7,
+          "mae": 8, "cred_var": 9, "cred_std": 10}
 
 
 class OrcParams(C.Structure):
@@ -199,7 +200,7 @@ def link(p: Params, pred: np.ndarray) -> None:
 
 def init_pred(p: Params, y: np.ndarray) -> np.ndarray:
     """Initial bias mu per loss, `_init_target` (src/init.jl:19-145), returned as float32 [K]."""
-    if p.loss == "mse":
+    if p.loss in ("mse", "mae", "cred_var", "cred_std"):
         return np.array([np.mean(y.astype(np.float32), dtype=np.float32)], np.float32)
     if p.loss == "logloss":
         m = np.float32(np.mean(y.astype(np.float32), dtype=np.float32))

@@ -35,6 +35,19 @@ def _gain_of(op, hist_node, nsum_node, feat0, bin1, numeric=True):
         return g * g / max(eps, hh + op.lambda_ * w + op.L2) / 2.0
 
     wl, wr = sl[C - 1], nsum_node[C - 1] - sl[C - 1]
+    if op.loss == "mae":                         # src/split.jl:2, 119-130
+        wp = nsum_node[C - 1]
+        dl, dr = max(eps, 1 + op.lambda_ + op.L2 / wl), max(eps, 1 + op.lambda_ + op.L2 / wr)
+        return sum(abs(sl[k] / wl - nsum_node[k] / wp) * wl / dl + abs((nsum_node[k] - sl[k]) / wr - nsum_node[k] / wp) * wr / dr
+                   for k in range(K))
+    if op.loss in ("cred_var", "cred_std"):      # src/split.jl:3-4, 70-78, 132-141
+        def cred(m1, m2, w):
+            vhm = (m1 / w) ** 2
+            evpv = max(eps, m2 / w - vhm)
+            z = vhm / (vhm + evpv) if op.loss == "cred_var" else np.sqrt(vhm) / (np.sqrt(vhm) + np.sqrt(evpv))
+            return z * abs(m1) / (1 + op.L2 / w)
+        gp = sum(cred(nsum_node[k], nsum_node[K + k], nsum_node[C - 1]) for k in range(K))
+        return sum(cred(sl[k], sl[K + k], wl) + cred(nsum_node[k] - sl[k], nsum_node[K + k] - sl[K + k], wr) for k in range(K)) - gp
     gp = sum(term(nsum_node[k], nsum_node[K + k], nsum_node[C - 1]) for k in range(K))
     g = sum(term(sl[k], sl[K + k], wl) + term(nsum_node[k] - sl[k], nsum_node[K + k] - sl[K + k], wr) for k in range(K))
     return g - gp

@@ -356,3 +356,35 @@ def test_deviance_metrics_against_float64_formulas(orc):
     s = np.log1p(np.exp(pg[:, 1].astype(np.float64)))
     az = np.abs((y64 - pg[:, 0]) / s)
     assert np.isclose(orc.eval_metric("logistic_mle", pg, y, w), np.sum(w64 * (-np.log(s) - az - 2 * np.log1p(np.exp(-az)))) / w64.sum(), rtol=1e-5)
+
+
+def test_mae_and_credibility_trees_by_hand(orc):
+    """A two-bin, one-feature problem small enough to evaluate by hand: the oracle must split where the formulas of
+    src/split.jl:2-4, 119-141 say and give the leaves of src/predict.jl:211-218, 250-257."""
+    x_bin = np.asfortranarray(np.array([[1], [1], [1], [2], [2], [2], [2], [2]], np.uint8))
+    y = np.array([1.0, 2.0, 3.0, 7.0, 8.0, 9.0, 10.0, 11.0], np.float32)
+    n = y.size
+    for loss in ("mae", "cred_var", "cred_std"):
+        p = orc.Params(loss=loss, K=1, nbins=2, max_depth=2, eta=1.0, lambda_=0.0, L2=0.0, min_weight=0.5)
+        # categorical feature: both bins are candidates (a numeric one only scans bins 1..nbins-1, which is the same here)
+        grad = np.zeros((n, 3), np.float32)
+        grad[:, 2] = 1.0
+        pred = np.full((n, 1), y.mean(), np.float32)
+        orc.update_grads(p, pred, y, grad)
+        t, nidx, _, _ = orc.grow_tree(p, x_bin, grad, np.arange(1, n + 1, dtype=np.uint32), np.array([1], np.uint32))
+        assert t.split[0] and t.feat[0] == 1 and t.cond_bin[0] == 1
+        d = y - y.mean()
+        left, right = d[:3], d[3:]
+        # eta = 1, lambda = L2 = 0: both leaf formulas reduce to the mean residual of the leaf
+        assert np.allclose(t.pred[1, 0], left.mean(), rtol=1e-6) and np.allclose(t.pred[2, 0], right.mean(), rtol=1e-6)
+        if loss == "mae":
+            gain = abs(left.mean()) * 3 + abs(right.mean()) * 5          # parent mean residual is 0, node gain is 0
+        else:
+            def cred(v):
+                m1, m2, w = v.sum(), (v ** 2).sum(), v.size
+                vhm = (m1 / w) ** 2
+                evpv = max(np.finfo(np.float64).eps, m2 / w - vhm)
+                z = vhm / (vhm + evpv) if loss == "cred_var" else np.sqrt(vhm) / (np.sqrt(vhm) + np.sqrt(evpv))
+                return z * abs(m1)
+            gain = cred(left.astype(np.float64)) + cred(right.astype(np.float64)) - cred(d.astype(np.float64))
+        assert np.isclose(t.gain[0], gain, rtol=1e-4), (loss, t.gain[0], gain)

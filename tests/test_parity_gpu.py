@@ -108,6 +108,19 @@ def test_logistic_mle(pkg, orc):
     assert s["splits"] > 30, s
 
 
+@pytest.mark.parametrize("loss", ["mae", "cred_var", "cred_std"])
+def test_losses_with_their_own_gain_and_leaf(pkg, orc, loss):
+    """mae and the credibility losses: split gain and leaf value of their own (src/split.jl:2-4, 119-141,
+    src/predict.jl:211-222, 250-262), with a monotone constraint so that their pred_scalar is exercised too."""
+    x, y = make_regression(40_000, 10, seed=41)
+    y = y + 2.0                                         # a non-zero mean: the credibility terms depend on it
+    p = pkg.EvoTreeRegressor(loss=loss, nrounds=3, max_depth=5, nbins=32, eta=0.3, L2=1.0, lambda_=0.1,
+                             monotone_constraints={1: 1, 2: -1})
+    assert p.metric == ("mae" if loss != "mae" else "mae")
+    s = lockstep_check(pkg, orc, p, x, y, rounds=3)
+    assert s["splits"] > 10, s
+
+
 @pytest.mark.parametrize("depth", [1, 2, 3])
 def test_shallow_depths(pkg, orc, depth):
     x, y = make_regression(5_000, 7, seed=depth)
