@@ -109,7 +109,7 @@ static void free_handle(evb_handle *h) {
     if (h->peer_flags[h->rank]) cudaFree(h->peer_flags[h->rank]);
     if (h->hsum) cudaFree(h->hsum);
     free_eval(h);
-    void *ptrs[] = {h->gradq, h->d_gmax, h->d_qinv, h->xT, h->xC, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
+    void *ptrs[] = {h->qs_cnt, h->qs_prefix, h->qs_rank, h->qs_gamma, h->gradq, h->d_gmax, h->d_qinv, h->xT, h->xC, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
                     h->js_d, h->seg_start, h->seg_cnt, h->gcnt, h->nleft, (h->gnleft != h->nleft) ? h->gnleft : nullptr, h->kind,
                     h->bslot, h->nsum, h->plan /* base of the tree block */, h->cum, h->slot_node, h->item_node, h->item_left,
                     h->item_lprefix, h->item_bits, h->scan_tmp, h->hist, h->hcomp, h->scratch, h->fbest_gain, h->fbest_bin};
@@ -167,6 +167,12 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
 
     EVB_CUDA(dalloc(&h->xT, (size_t)n * h->RS));
     EVB_CUDA(dalloc(&h->grad, (size_t)n * h->GS));
+    if (p->loss == EVB_QUANTILE) {
+        const size_t e = (size_t)2 * (h->nn + 1);
+        EVB_CUDA(dalloc(&h->qs_cnt, e * 256)); EVB_CUDA(dalloc(&h->qs_prefix, e)); EVB_CUDA(dalloc(&h->qs_rank, e));
+        EVB_CUDA(dalloc(&h->qs_gamma, (size_t)h->nn + 1));
+        EVB_CUDA(cudaMemset(h->qs_cnt, 0, e * 256 * sizeof(uint32_t)));
+    }
     if (h->use_q) {
         EVB_CUDA(dalloc(&h->gradq, (size_t)n * (h->unit_w ? 1 : 2)));
         EVB_CUDA(dalloc(&h->d_gmax, (size_t)1));
@@ -285,6 +291,10 @@ extern "C" int32_t evb_create(evb_handle **out, const evb_params *p, int64_t nob
     }
     if (p->nbins < 2 || p->nbins > 255) { evb_set_error("evb_create: nbins=%d outside 2..255", p->nbins); return EVB_ERR_ARG; }
     if (p->max_depth < 1 || p->max_depth > EVB_MAX_DEPTH) { evb_set_error("evb_create: max_depth=%d outside 1..%d", p->max_depth, EVB_MAX_DEPTH); return EVB_ERR_LIMIT; }
+    if (p->loss == EVB_QUANTILE && (p->K != 1 || !(p->alpha > 0.0 && p->alpha < 1.0))) {
+        evb_set_error("evb_create: the quantile loss needs K = 1 and 0 < alpha < 1 (alpha = %g)", p->alpha);
+        return EVB_ERR_ARG;
+    }
     if (p->bagging_size < 1 || p->tree_type != 0) { evb_set_error("evb_create: bagging_size must be >= 1 and tree_type binary"); return EVB_ERR_ARG; }
     int ndev = 0;
     cudaError_t e = cudaGetDeviceCount(&ndev);
@@ -341,7 +351,14 @@ static int32_t enqueue_tree(evb_handle *h, bool use_mask, uint8_t mask_cond, boo
         EVB_CHECK(evb_launch_scan(h, level));
         if (level < D - 1 || (full_part && level == D - 1)) EVB_CHECK(evb_launch_partition(h, level));
     }
-    EVB_CHECK(evb_launch_finalize(h, fuse));
+    if (h->p.loss == EVB_QUANTILE) {
+        // the leaf values need the leaf of every row first: leaf ids, per-leaf quantiles, then the usual update
+        EVB_CHECK(evb_launch_finalize(h, false, 1));
+        EVB_CHECK(evb_launch_quantile_leaves(h, use_mask, mask_cond));
+        EVB_CHECK(evb_launch_finalize(h, fuse, 2));
+    } else {
+        EVB_CHECK(evb_launch_finalize(h, fuse, 0));
+    }
     if (h->ev_n > 0) EVB_CHECK(evb_launch_eval(h, nullptr));
     EVB_CUDA(cudaMemcpyAsync(h->h_tree[slot], h->plan, h->h_tree_bytes, cudaMemcpyDeviceToHost, h->st));
     return EVB_OK;
@@ -555,7 +572,8 @@ extern "C" int32_t evb_eval_attach(evb_handle *h, int64_t nobs, const uint8_t *x
     const bool ok = (loss == EVB_MLOGLOSS) ? metric == EVB_METRIC_MLOGLOSS
                     : (loss == EVB_GAUSSIAN_MLE || loss == EVB_LOGISTIC_MLE) ? (metric == EVB_METRIC_GAUSSIAN_MLE || metric == EVB_METRIC_LOGISTIC_MLE)
                     : (metric == EVB_METRIC_MSE || metric == EVB_METRIC_MAE || metric == EVB_METRIC_LOGLOSS ||
-                       metric == EVB_METRIC_POISSON || metric == EVB_METRIC_GAMMA || metric == EVB_METRIC_TWEEDIE);
+                       metric == EVB_METRIC_POISSON || metric == EVB_METRIC_GAMMA || metric == EVB_METRIC_TWEEDIE ||
+                       metric == EVB_METRIC_QUANTILE);
     if (!ok) { evb_set_error("evb_eval_attach: metric %d is not defined for loss %d", metric, loss); return EVB_ERR_ARG; }
     drop_graphs(h); // the launch sequence of a tree changes
     int32_t rc = eval_attach_impl(h, nobs, x_bin, y, w, pred0, bias, metric, sums);

@@ -133,6 +133,9 @@ struct evb_handle {
     double *d_qinv;       // [2] 2^-s of the g words / of the w words
     float wscale; double winv;
 
+    // quantile loss: work memory of the per-leaf order-statistic selection
+    uint32_t *qs_cnt, *qs_prefix, *qs_rank; float *qs_gamma;
+
     // histograms
     HistGeom hg;
     int hist_mode;    // EVB_HIST_MODE environment override (kernel variants / diagnostics)
@@ -178,7 +181,8 @@ int32_t evb_launch_transpose(evb_handle *h, const uint8_t *xcol_dev, int64_t ld,
 int32_t evb_launch_grads(evb_handle *h);
 int32_t evb_launch_quantize(evb_handle *h);
 int32_t evb_launch_rows_init(evb_handle *h, bool use_mask, uint8_t mask_cond);
-int32_t evb_launch_finalize(evb_handle *h, bool compute_grads);
+int32_t evb_launch_finalize(evb_handle *h, bool compute_grads, int mode); // mode: see FinArgs in evb_rows.cu
+int32_t evb_launch_quantile_leaves(evb_handle *h, bool use_mask, uint8_t mask_cond);
 int32_t evb_launch_nidx_from_partition(evb_handle *h, uint32_t *out_dev);
 int32_t evb_launch_eval(evb_handle *h, const float *fixed_leaf_dev);
 // evb_hist.cu

@@ -4,6 +4,7 @@
 // the gradients of the next round, inference over all trees (`_predict`, src/predict.jl:118-136) and
 // `binarize` (src/fit-utils.jl:66-72).
 #include "evb_internal.cuh"
+#include <float.h>
 
 namespace {
 
@@ -19,7 +20,8 @@ __device__ __forceinline__ int gpos(int c, int NCH) { return (c / NCH) * 4 + (c 
 #define REC(c) rec[gpos((c), NCH)]
 // For mse the hessian channels are not stored (h = 2w is rebuilt when the histogram is reduced): the record is
 // g_1..g_K, w, i.e. `elided` shifts w from channel 2K to channel K.
-__device__ __forceinline__ void grad_row(int loss, int K, int NCH, bool elided, const float *p, const void *y, int ycols, long long i, float *rec) {
+__device__ __forceinline__ void grad_row(int loss, int K, int NCH, bool elided, const float *p, const void *y, int ycols, long long i, float *rec,
+                                         float alpha = 0.5f) {
     const float w = REC(elided ? K : 2 * K);
     if (loss == EVB_MSE) {
         const float *yf = (const float *)y + (size_t)i * ycols;
@@ -42,6 +44,13 @@ __device__ __forceinline__ void grad_row(int loss, int K, int NCH, bool elided, 
             const float prob = expf(p[k]) / isum;
             REC(k) = (((uint32_t)(k + 1) == yi) ? prob - 1.0f : prob) * w;
             REC(K + k) = prob * (1.0f - prob) * w;
+        }
+    } else if (loss == EVB_QUANTILE) { // quantile_grad_diff, src/loss.jl:93-98: the second slot keeps the raw residual
+        const float *yf = (const float *)y + (size_t)i * ycols;
+        for (int k = 0; k < K; ++k) {
+            const float d = yf[k] - p[k];
+            REC(k) = (d > 0.0f ? alpha : alpha - 1.0f) * w;
+            REC(K + k) = d;
         }
     } else if (loss == EVB_MAE || loss == EVB_CRED_VAR || loss == EVB_CRED_STD) { // src/loss.jl:86-91
         const float *yf = (const float *)y + (size_t)i * ycols;
@@ -176,11 +185,12 @@ __device__ __forceinline__ void block_absmax(float v, unsigned *gmax) {
         if (m > *(volatile unsigned *)gmax) atomicMax(gmax, m);
     }
 }
-__global__ void __launch_bounds__(256) k_grads(int loss, int K, int GS, int NCH, int elided, int ycols, long long n, const float *pred, const void *y, float *grad, unsigned *gmax) {
+__global__ void __launch_bounds__(256) k_grads(int loss, int K, int GS, int NCH, int elided, int ycols, long long n, const float *pred, const void *y, float *grad, unsigned *gmax,
+                                               float alpha) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     float g0 = 0.0f;
     if (i < n) {
-        grad_row(loss, K, NCH, elided != 0, pred + (size_t)i * K, y, ycols, i, grad + (size_t)i * GS);
+        grad_row(loss, K, NCH, elided != 0, pred + (size_t)i * K, y, ycols, i, grad + (size_t)i * GS, alpha);
         g0 = grad[(size_t)i * GS];
     }
     if (gmax) block_absmax(g0, gmax);
@@ -299,6 +309,8 @@ struct FinArgs {
     unsigned *gmax; // non-null: track max |g| of the gradients computed here (fixed-point histogram variant)
     long long n;
     int RS, K, GS, NCH, elided, loss, nn, ycols, compute_grads, packed_in_smem;
+    float alpha;
+    int mode; // 0: traverse, add the leaf, next gradients; 1: traverse only (leaf ids); 2: leaf ids are in nidx, add + gradients
 };
 __global__ void __launch_bounds__(256) k_finalize(FinArgs a) {
     extern __shared__ uint32_t s_packed[];
@@ -311,12 +323,12 @@ __global__ void __launch_bounds__(256) k_finalize(FinArgs a) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     float g0 = 0.0f;
     if (i < a.n) {
-        const int nid = traverse(packed, a.xT + (size_t)i * a.RS);
+        const int nid = a.mode == 2 ? (int)a.nidx[i] : traverse(packed, a.xT + (size_t)i * a.RS);
         a.nidx[i] = (uint32_t)nid;
         float *p = a.pred + (size_t)i * a.K;
-        pred_add(a.loss, a.K, p, a.t_pred + (size_t)(nid - 1) * a.K);
-        if (a.compute_grads) {
-            grad_row(a.loss, a.K, a.NCH, a.elided != 0, p, a.y, a.ycols, i, a.grad + (size_t)i * a.GS);
+        if (a.mode != 1) pred_add(a.loss, a.K, p, a.t_pred + (size_t)(nid - 1) * a.K);
+        if (a.compute_grads && a.mode != 1) {
+            grad_row(a.loss, a.K, a.NCH, a.elided != 0, p, a.y, a.ycols, i, a.grad + (size_t)i * a.GS, a.alpha);
             g0 = a.grad[(size_t)i * a.GS];
         }
     }
@@ -352,11 +364,112 @@ __global__ void __launch_bounds__(256) k_finalize_staged(FinArgs a) {
         float *p = a.pred + (size_t)i * a.K;
         pred_add(a.loss, a.K, p, a.t_pred + (size_t)(nid - 1) * a.K);
         if (a.compute_grads) {
-            grad_row(a.loss, a.K, a.NCH, a.elided != 0, p, a.y, a.ycols, i, a.grad + (size_t)i * a.GS);
+            grad_row(a.loss, a.K, a.NCH, a.elided != 0, p, a.y, a.ycols, i, a.grad + (size_t)i * a.GS, a.alpha);
             g0 = a.grad[(size_t)i * a.GS];
         }
     }
     if (a.gmax && a.compute_grads) block_absmax(g0, a.gmax);
+}
+
+// ---------------------------------------------------------------------------------- quantile leaves
+// Leaf values of the quantile loss: the alpha-quantile (linear interpolation between the two neighbouring order
+// statistics, `Statistics.quantile`) of the residuals of the sampled rows of every leaf (src/predict.jl:264-272).
+// The order statistics of all leaves are found together by a radix selection on the order-preserving bit pattern of
+// the residual: four passes of 8 bits, each a counting kernel over the rows (one shared-memory-free atomic per row
+// and wanted rank into the leaf's 256 counters) and a pick kernel (one warp per leaf walks its counters).
+struct QselArgs {
+    const uint32_t *nidx;
+    const float *grad;        // residual of row i: grad[i * GS + roff]
+    const uint8_t *mask;      // rows with mask <= cond are sampled; null: all
+    uint32_t *cnt;            // [2][nn + 1][256]
+    uint32_t *prefix;         // [2][nn + 1] bits decided so far
+    uint32_t *rank;           // [2][nn + 1] rank still to find inside the current prefix
+    float *gamma;             // [nn + 1] interpolation weight
+    const uint8_t *t_split;
+    const double *nsum;
+    float *t_pred;
+    long long n;
+    int GS, roff, nn, C, pass;
+    uint8_t cond;
+    double alpha, eb, lambda, L2; // eb = eta / bagging_size
+};
+__device__ __forceinline__ uint32_t float_key(float v) { const uint32_t b = __float_as_uint(v); return (b & 0x80000000u) ? ~b : b | 0x80000000u; }
+__device__ __forceinline__ float key_float(uint32_t k) { return __uint_as_float((k & 0x80000000u) ? k & 0x7fffffffu : ~k); }
+__global__ void __launch_bounds__(256) k_qsel_count(QselArgs a) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.n || (a.mask && a.mask[i] > a.cond)) return;
+    const uint32_t leaf = a.nidx[i];
+    const uint32_t key = float_key(a.grad[(size_t)i * a.GS + a.roff]);
+    const int shift = 24 - 8 * a.pass;
+    const uint32_t digit = (key >> shift) & 0xffu;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const size_t e = (size_t)r * (a.nn + 1) + leaf;
+        // pass 0 counts every row; later passes only the rows that share the bits decided so far
+        if (a.pass == 0 || (key >> (shift + 8)) == (a.prefix[e] >> (shift + 8))) atomicAdd(&a.cnt[e * 256 + digit], 1u);
+        if (a.pass == 0) break; // the first pass is the same for both ranks: counted once, in the counters of rank 0
+    }
+}
+__global__ void __launch_bounds__(256) k_qsel_pick(QselArgs a) {
+    const int leaf = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (leaf < 1 || leaf > a.nn) return;
+    const int shift = 24 - 8 * a.pass;
+    for (int r = 0; r < 2; ++r) {
+        const size_t e = (size_t)r * (a.nn + 1) + leaf;
+        uint32_t *cnt = a.cnt + (a.pass == 0 ? (size_t)leaf : e) * 256;
+        uint32_t c[8], tot = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { c[q] = cnt[lane * 8 + q]; tot += c[q]; }
+        uint32_t incl = tot;
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t v = __shfl_up_sync(FULL, incl, o); if (lane >= o) incl += v; }
+        const uint32_t total = __shfl_sync(FULL, incl, 31);
+        uint32_t want;
+        if (a.pass == 0) {
+            // ranks of the two order statistics: h = (n - 1) alpha, lo = floor(h), hi = lo + 1 (clamped)
+            const double hpos = total > 0 ? (double)(total - 1) * a.alpha : 0.0;
+            const uint32_t lo = (uint32_t)floor(hpos), hi = lo + 1 < total ? lo + 1 : lo;
+            if (r == 0 && lane == 0) a.gamma[leaf] = total > 0 ? (float)(hpos - floor(hpos)) : -1.0f; // -1: no sampled row
+            want = r == 0 ? lo : hi;
+        } else {
+            want = a.rank[e];
+        }
+        // the digit whose cumulative count first exceeds `want`
+        const uint32_t excl = incl - tot;
+        int found = -1;
+        uint32_t before = 0;
+        if (total > 0 && want >= excl && want < incl) {
+            uint32_t run = excl;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) { if (found < 0 && want < run + c[q]) { found = lane * 8 + q; before = run; } run += c[q]; }
+        }
+        const unsigned who = __ballot_sync(FULL, found >= 0);
+        if (who) {
+            const int src = __ffs(who) - 1;
+            found = __shfl_sync(FULL, found, src);
+            before = __shfl_sync(FULL, before, src);
+            if (lane == 0) {
+                a.prefix[e] = (a.pass == 0 ? 0u : a.prefix[e]) | ((uint32_t)found << shift);
+                a.rank[e] = want - before;
+            }
+        } else if (lane == 0) { a.prefix[e] = 0u; a.rank[e] = 0u; }
+        __syncwarp();
+    }
+    // the counters are used again by the next pass
+    for (int r = 0; r < 2; ++r) {
+        uint32_t *cnt = a.cnt + ((size_t)r * (a.nn + 1) + leaf) * 256;
+        for (int q = lane; q < 256; q += 32) cnt[q] = 0u;
+    }
+}
+// leaf value from the two order statistics (their full keys are in `prefix` after the last pass)
+__global__ void k_qsel_leaf(QselArgs a) {
+    const int leaf = blockIdx.x * blockDim.x + threadIdx.x;
+    if (leaf < 1 || leaf > a.nn || a.t_split[leaf - 1]) return;
+    const float g = a.gamma[leaf];
+    if (g < 0.0f) return; // not a leaf of this tree (or no sampled row reached it): keeps its zero
+    const float lo = key_float(a.prefix[leaf]), hi = key_float(a.prefix[(size_t)(a.nn + 1) + leaf]);
+    const double q = (double)lo + (double)g * ((double)hi - (double)lo);
+    const double w = a.nsum[(size_t)leaf * a.C + a.C - 1];
+    a.t_pred[leaf - 1] = (float)(a.eb * q / fmax(DBL_EPSILON, 1.0 + a.lambda + a.L2 / w));
 }
 
 // node of every sampled row from the row lists left by the partition kernels; one CTA per node
@@ -468,7 +581,7 @@ __global__ void __launch_bounds__(256) k_binarize_rows(const T *x, long long ld,
 // ---------------------------------------------------------------------------------- evaluation data
 // Per-row metric value in float, as `_metric_value` / `_mle2p_metric_value` / `mlogloss` compute it
 // (src/metrics.jl:1-110): the caller multiplies by w and accumulates in double.
-__device__ __forceinline__ float metric_row(int metric, int K, const float *p, const void *y, int ycols, long long i, float w) {
+__device__ __forceinline__ float metric_row(int metric, int K, const float *p, const void *y, int ycols, long long i, float w, float alpha) {
     if (metric == EVB_METRIC_MLOGLOSS) {
         const uint32_t yi = ((const uint32_t *)y)[i];
         float isum = 0.0f;
@@ -491,6 +604,7 @@ __device__ __forceinline__ float metric_row(int metric, int K, const float *p, c
         const float pk = p[k], yk = yf[k];
         if (metric == EVB_METRIC_MSE) acc += (pk - yk) * (pk - yk);
         else if (metric == EVB_METRIC_MAE) acc += fabsf(pk - yk);
+        else if (metric == EVB_METRIC_QUANTILE) acc += alpha * fmaxf(yk - pk, 0.0f) + (1.0f - alpha) * fmaxf(pk - yk, 0.0f); // src/metrics.jl:4-6
         else if (metric == EVB_METRIC_LOGLOSS) { const float s = sigmoidf_(pk); acc += -yk * logf(s) + (yk - 1.0f) * logf(1.0f - s); }
         else if (metric == EVB_METRIC_POISSON) { // src/metrics.jl:13-17; eps(1f-7)
             const float pr = expf(pk);
@@ -515,6 +629,7 @@ struct EvalArgs {
     double *part; // [gridDim.x][2]
     long long n;
     int RS, K, loss, metric, nn, ycols, packed_in_smem;
+    float alpha;
 };
 // `predict!(cb.p, tree, cb.x_bin, cb.feattypes)` followed by the per-row metric (src/callback.jl:123-128).  Every
 // block owns a fixed set of rows and sums them in a fixed order, so the result does not depend on scheduling.
@@ -533,7 +648,7 @@ __global__ void __launch_bounds__(256) k_eval_tree(EvalArgs a) {
         const float *leaf = a.fixed_leaf ? a.fixed_leaf : a.t_pred + (size_t)(traverse(packed, a.xT + (size_t)i * a.RS) - 1) * a.K;
         pred_add(a.loss, a.K, p, leaf);
         const float w = a.w ? a.w[i] : 1.0f;
-        sv += (double)metric_row(a.metric, a.K, p, a.y, a.ycols, i, w);
+        sv += (double)metric_row(a.metric, a.K, p, a.y, a.ycols, i, w, a.alpha);
         sw += (double)w;
     }
     for (int o = 16; o > 0; o >>= 1) { sv += __shfl_down_sync(FULL, sv, o); sw += __shfl_down_sync(FULL, sw, o); }
@@ -586,7 +701,7 @@ int32_t evb_launch_grads(evb_handle *h) {
     if (h->use_q) EVB_CUDA(cudaMemsetAsync(h->d_gmax, 0, sizeof(unsigned), h->st));
     evb_tic(h, EVB_T_GRADS);
     k_grads<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->p.loss, h->K, h->GS, h->rec_nch, h->Ce != h->C, h->ycols, h->n, h->pred, h->y, h->grad,
-                                                                h->use_q ? h->d_gmax : nullptr);
+                                                                h->use_q ? h->d_gmax : nullptr, (float)h->p.alpha);
     evb_toc(h, EVB_T_GRADS);
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
@@ -615,20 +730,20 @@ int32_t evb_launch_rows_init(evb_handle *h, bool use_mask, uint8_t mask_cond) {
     return EVB_OK;
 }
 
-int32_t evb_launch_finalize(evb_handle *h, bool compute_grads) {
+int32_t evb_launch_finalize(evb_handle *h, bool compute_grads, int mode) {
     FinArgs a;
     a.xT = h->xT; a.t_packed = h->t_packed; a.t_pred = h->t_pred; a.pred = h->pred; a.grad = h->grad; a.y = h->y;
     a.nidx = h->nidx; a.n = h->n; a.RS = h->RS; a.K = h->K; a.GS = h->GS; a.NCH = h->rec_nch; a.elided = h->Ce != h->C; a.loss = h->p.loss; a.nn = h->nn;
     a.gmax = h->use_q ? h->d_gmax : nullptr;
     if (h->use_q && compute_grads) EVB_CUDA(cudaMemsetAsync(h->d_gmax, 0, sizeof(unsigned), h->st));
-    a.ycols = h->ycols; a.compute_grads = compute_grads ? 1 : 0;
+    a.ycols = h->ycols; a.compute_grads = compute_grads ? 1 : 0; a.alpha = (float)h->p.alpha; a.mode = mode;
     const size_t smem = (size_t)h->nn * 4;
     a.packed_in_smem = smem <= 40 * 1024 ? 1 : 0;
     const size_t staged = smem + (size_t)256 * (h->RS + 4);
     static bool attr_set[64] = {};
     static const bool direct = getenv("EVB_FINALIZE_DIRECT") != nullptr;
     evb_tic(h, EVB_T_FINALIZE);
-    if (h->RS <= 256 && staged <= 100 * 1024 && !direct && h->dev < 64) {
+    if (mode == 0 && h->RS <= 256 && staged <= 100 * 1024 && !direct && h->dev < 64) {
         if (!attr_set[h->dev]) { cudaFuncSetAttribute(k_finalize_staged, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); attr_set[h->dev] = true; }
         k_finalize_staged<<<(unsigned)((h->n + 255) / 256), 256, staged, h->st>>>(a);
     } else {
@@ -645,7 +760,7 @@ int32_t evb_launch_eval(evb_handle *h, const float *fixed_leaf_dev) {
     EvalArgs a;
     a.xT = h->ev_xT; a.t_packed = h->t_packed; a.t_pred = h->t_pred; a.fixed_leaf = fixed_leaf_dev; a.pred = h->ev_pred;
     a.y = h->ev_y; a.w = h->ev_w; a.part = h->ev_part; a.n = h->ev_n; a.RS = h->RS; a.K = h->K; a.loss = h->p.loss;
-    a.metric = h->ev_metric; a.nn = h->nn; a.ycols = h->ycols;
+    a.metric = h->ev_metric; a.nn = h->nn; a.ycols = h->ycols; a.alpha = (float)h->p.alpha;
     const size_t smem = (size_t)h->nn * 4;
     a.packed_in_smem = smem <= 40 * 1024 ? 1 : 0;
     evb_tic(h, EVB_T_FINALIZE);
@@ -653,6 +768,27 @@ int32_t evb_launch_eval(evb_handle *h, const float *fixed_leaf_dev) {
     k_eval_sum<<<1, 256, 0, h->st>>>(h->ev_part, h->ev_blocks, h->d_evsum);
     evb_toc(h, EVB_T_FINALIZE);
     h->tm.launches[EVB_T_FINALIZE] += 1; // two kernels inside one timed bracket
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+// quantile loss, K = 1: leaf ids are in h->nidx (finalize mode 1); fills the leaf values of the tree
+int32_t evb_launch_quantile_leaves(evb_handle *h, bool use_mask, uint8_t mask_cond) {
+    QselArgs a;
+    a.nidx = h->nidx; a.grad = h->grad; a.mask = use_mask ? h->mask_d : nullptr; a.cnt = h->qs_cnt; a.prefix = h->qs_prefix;
+    a.rank = h->qs_rank; a.gamma = h->qs_gamma; a.t_split = h->t_split; a.nsum = h->nsum; a.t_pred = h->t_pred; a.n = h->n;
+    a.GS = h->GS; a.nn = h->nn; a.C = h->C; a.cond = mask_cond;
+    a.roff = (h->K / h->rec_nch) * 4 + (h->K % h->rec_nch); // gpos(K): the slot of h_1, where the residual is kept
+    a.alpha = h->p.alpha; a.eb = h->p.eta / (double)h->p.bagging_size; a.lambda = h->p.lambda; a.L2 = h->p.L2;
+    evb_tic(h, EVB_T_FINALIZE);
+    for (int pass = 0; pass < 4; ++pass) {
+        a.pass = pass;
+        k_qsel_count<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(a);
+        k_qsel_pick<<<(h->nn + 8) / 8, 256, 0, h->st>>>(a);
+    }
+    k_qsel_leaf<<<(h->nn + 256) / 256, 256, 0, h->st>>>(a);
+    evb_toc(h, EVB_T_FINALIZE);
+    h->tm.launches[EVB_T_FINALIZE] += 8;
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
 }

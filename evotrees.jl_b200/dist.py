@@ -58,7 +58,7 @@ class Comm:
         """Initial bias of the whole data set from per-shard sufficient statistics
         (same formulas as `_init_target`, src/init.jl:19-145)."""
         from .fit import _invsoftplus, _logit
-        if loss in ("mse", "logloss", "poisson", "gamma", "tweedie", "mae", "cred_var", "cred_std"):
+        if loss in ("mse", "logloss", "poisson", "gamma", "tweedie", "mae", "cred_var", "cred_std", "quantile"):
             y2 = y.reshape(y.shape[0], -1).astype(np.float64)
             s = self.allreduce_sum(np.concatenate([y2.sum(axis=0), [y2.shape[0]]]))
             m = s[:-1] / s[-1]

@@ -29,7 +29,7 @@ def init_target(loss: str, y_train: np.ndarray, offset):
     """`_init_target` (src/init.jl:10-146) for the four losses of this path.
     Returns K, y (device dtype), ycols, mu float32 [K], target_levels, offset (link space)."""
     levels = None
-    if loss in ("mse", "logloss", "poisson", "gamma", "tweedie", "mae", "cred_var", "cred_std"):
+    if loss in ("mse", "logloss", "poisson", "gamma", "tweedie", "mae", "cred_var", "cred_std", "quantile"):
         y = np.ascontiguousarray(y_train, np.float32)
         ycols = 1 if y.ndim == 1 else y.shape[1]
         K = ycols
@@ -154,7 +154,7 @@ class Cache:
 
 def make_params(params: EvoTypes, K: int, device: int, flags: int = 0) -> _lib.EvbParams:
     return _lib.EvbParams(_lib.LOSS_CODES[params.loss], K, params.nbins, params.max_depth, params.bagging_size, 0,
-                          params.eta, params.lambda_, params.L2, params.gamma, params.min_weight, device, flags)
+                          params.eta, params.lambda_, params.L2, params.gamma, params.min_weight, device, flags, params.alpha)
 
 
 def init_core_binned(params: EvoTypes, x_bin: np.ndarray, y, ycols: int, K: int, mu: np.ndarray, w=None, pred0=None,
@@ -293,7 +293,7 @@ def grow_evotree(m: EvoTree, cache: Cache, params: EvoTypes) -> None:
 
 
 IS_MAXIMISE = {"mse": False, "rmse": False, "mae": False, "logloss": False, "mlogloss": False, "poisson": False,
-               "gamma": False, "tweedie": False, "gaussian_mle": True, "logistic_mle": True}   # src/metrics.jl:194-205
+               "gamma": False, "tweedie": False, "quantile": False, "gaussian_mle": True, "logistic_mle": True}   # src/metrics.jl:194-205
 
 
 def init_logger(metric: str, maximise: bool, early_stopping_rounds: int, early_stopping_tolerance: float = 0.0) -> dict:

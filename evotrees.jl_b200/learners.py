@@ -8,7 +8,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-_REG_LOSSES = ("mse", "logloss", "poisson", "gamma", "tweedie", "mae", "cred_var", "cred_std")
+_REG_LOSSES = ("mse", "logloss", "poisson", "gamma", "tweedie", "mae", "cred_var", "cred_std", "quantile")
 _MLE_LOSSES = ("gaussian_mle", "logistic_mle")
 
 
@@ -37,6 +37,7 @@ class EvoTypes:
     device: str = "gpu"
     early_stopping_rounds: int = 2 ** 62
     early_stopping_tolerance: float = 0.0
+    alpha: float = 0.5          # quantile loss / metric
     metric: str | None = None
 
     _losses = ()
@@ -75,6 +76,7 @@ class EvoTypes:
         _check("eta", self.eta, 0.0, float("inf"))
         _check("bagging_size", self.bagging_size, 1, 2 ** 31)
         _check("early_stopping_tolerance", self.early_stopping_tolerance, 0.0, float("inf"))
+        _check("alpha", self.alpha, 0.0, 1.0)
         if self.tree_type != "binary":
             raise ValueError("Invalid input for `tree_type` parameter: only `binary` trees are built by this device path")
         if self.device not in ("gpu", "cuda"):
@@ -84,7 +86,7 @@ class EvoTypes:
 @dataclass
 class EvoTreeRegressor(EvoTypes):
     _losses = _REG_LOSSES
-    _metrics = ("mse", "rmse", "mae", "logloss", "poisson", "gamma", "tweedie")
+    _metrics = ("mse", "rmse", "mae", "logloss", "poisson", "gamma", "tweedie", "quantile")
 
 
 @dataclass

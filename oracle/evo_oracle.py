@@ -23,7 +23,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_ref", "libevo_oracle.so")
 
 LOSSES = {"mse": 0, "logloss": 1, "mlogloss": 2, "gaussian_mle": 3, "poisson": 4, "gamma": 5, "tweedie": 6, "logistic_mle": 7,
-          "mae": 8, "cred_var": 9, "cred_std": 10}
+          "mae": 8, "cred_var": 9, "cred_std": 10, "quantile": 11}
 
 
 class OrcParams(C.Structure):
@@ -31,7 +31,7 @@ class OrcParams(C.Structure):
         ("loss", C.c_int32), ("K", C.c_int32), ("nbins", C.c_int32), ("max_depth", C.c_int32),
         ("bagging_size", C.c_int32), ("tree_type", C.c_int32),
         ("eta", C.c_double), ("lambda_", C.c_double), ("L2", C.c_double), ("gamma", C.c_double),
-        ("min_weight", C.c_double),
+        ("min_weight", C.c_double), ("alpha", C.c_double),
     ]
 
 
@@ -82,10 +82,11 @@ class Params:
     L2: float = 1.0
     gamma: float = 0.0
     min_weight: float = 1.0
+    alpha: float = 0.5
 
     def c(self) -> OrcParams:
         return OrcParams(LOSSES[self.loss], self.K, self.nbins, self.max_depth, self.bagging_size, 0,
-                         self.eta, self.lambda_, self.L2, self.gamma, self.min_weight)
+                         self.eta, self.lambda_, self.L2, self.gamma, self.min_weight, self.alpha)
 
 
 @dataclass
@@ -200,7 +201,7 @@ def link(p: Params, pred: np.ndarray) -> None:
 
 def init_pred(p: Params, y: np.ndarray) -> np.ndarray:
     """Initial bias mu per loss, `_init_target` (src/init.jl:19-145), returned as float32 [K]."""
-    if p.loss in ("mse", "mae", "cred_var", "cred_std"):
+    if p.loss in ("mse", "mae", "cred_var", "cred_std", "quantile"):
         return np.array([np.mean(y.astype(np.float32), dtype=np.float32)], np.float32)
     if p.loss == "logloss":
         m = np.float32(np.mean(y.astype(np.float32), dtype=np.float32))
@@ -221,12 +222,12 @@ def init_pred(p: Params, y: np.ndarray) -> np.ndarray:
 
 
 METRICS = {"mse": 0, "rmse": 0, "mae": 1, "logloss": 2, "mlogloss": 3, "gaussian_mle": 4, "poisson": 5, "gamma": 6, "tweedie": 7,
-           "logistic_mle": 8}
+           "logistic_mle": 8, "quantile": 9}
 IS_MAXIMISE = {"mse": False, "rmse": False, "mae": False, "logloss": False, "mlogloss": False, "gaussian_mle": True,
-               "poisson": False, "gamma": False, "tweedie": False, "logistic_mle": True}
+               "poisson": False, "gamma": False, "tweedie": False, "logistic_mle": True, "quantile": False}
 
 
-def eval_metric(metric: str, pred: np.ndarray, y: np.ndarray, w: np.ndarray | None = None) -> float:
+def eval_metric(metric: str, pred: np.ndarray, y: np.ndarray, w: np.ndarray | None = None, alpha: float = 0.5) -> float:
     """Metric functions of src/metrics.jl:31-116 on link-space predictions `pred` [nobs, K] (float32)."""
     pred = np.ascontiguousarray(pred, np.float32)
     nobs, K = pred.shape
@@ -236,7 +237,7 @@ def eval_metric(metric: str, pred: np.ndarray, y: np.ndarray, w: np.ndarray | No
     ev = np.empty(nobs, np.float32)
     out = (C.c_double * 2)()
     lib().orc_eval_metric(C.c_int32(METRICS[metric]), C.c_int32(K), C.c_int64(nobs), _p(pred), _p(y), C.c_int32(ycols),
-                          _p(w32), _p(ev), out)
+                          _p(w32), _p(ev), out, C.c_double(alpha))
     v = out[0] / out[1]
     return float(np.sqrt(v)) if metric == "rmse" else float(v)
 

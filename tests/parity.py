@@ -20,7 +20,7 @@ RTOL = 1e-5
 def oracle_params(orc, params, K):
     return orc.Params(loss=params.loss, K=K, nbins=params.nbins, max_depth=params.max_depth,
                       bagging_size=params.bagging_size, eta=params.eta, lambda_=params.lambda_, L2=params.L2,
-                      gamma=params.gamma, min_weight=params.min_weight)
+                      gamma=params.gamma, min_weight=params.min_weight, alpha=params.alpha)
 
 
 def _gain_of(op, hist_node, nsum_node, feat0, bin1, numeric=True):
@@ -35,7 +35,7 @@ def _gain_of(op, hist_node, nsum_node, feat0, bin1, numeric=True):
         return g * g / max(eps, hh + op.lambda_ * w + op.L2) / 2.0
 
     wl, wr = sl[C - 1], nsum_node[C - 1] - sl[C - 1]
-    if op.loss == "mae":                         # src/split.jl:2, 119-130
+    if op.loss in ("mae", "quantile"):           # src/split.jl:2, 119-130
         wp = nsum_node[C - 1]
         dl, dr = max(eps, 1 + op.lambda_ + op.L2 / wl), max(eps, 1 + op.lambda_ + op.L2 / wr)
         return sum(abs(sl[k] / wl - nsum_node[k] / wp) * wl / dl + abs((nsum_node[k] - sl[k]) / wr - nsum_node[k] / wp) * wr / dr

@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 RTOL = 1e-5  # float32 per-row values (expf / logf of two math libraries), float64 sums
 
 
-def _oracle_log(orc, m, op, metric, x_eval, y_eval, w_eval=None, pred0=None):
+def _oracle_log(orc, m, op, metric, x_eval, y_eval, w_eval=None, pred0=None, alpha=0.5):
     """Metric after the bias tree and after every further tree, from the oracle's traversal and metric."""
     xb = orc.binarize(x_eval, m.info["edges"])
     ft = m.info["feattypes"].astype(np.uint8)
@@ -20,7 +20,7 @@ def _oracle_log(orc, m, op, metric, x_eval, y_eval, w_eval=None, pred0=None):
     for t in m.trees:
         ot = orc.Tree(t.feat, t.cond_bin, t.w, t.gain, t.pred, t.split.astype(np.uint8))
         orc.predict_tree(op, xb, ot, pred, ft)
-        out.append(orc.eval_metric(metric, pred, y_eval, w_eval))
+        out.append(orc.eval_metric(metric, pred, y_eval, w_eval, alpha))
     return np.array(out), pred
 
 
@@ -39,7 +39,8 @@ CASES = [("mse", "mse", "EvoTreeRegressor"), ("mse", "rmse", "EvoTreeRegressor")
          ("logloss", "logloss", "EvoTreeRegressor"), ("mlogloss", "mlogloss", "EvoTreeClassifier"),
          ("gaussian_mle", "gaussian_mle", "EvoTreeMLE"), ("poisson", "poisson", "EvoTreeRegressor"),
          ("gamma", "gamma", "EvoTreeRegressor"), ("tweedie", "tweedie", "EvoTreeRegressor"),
-         ("logistic_mle", "logistic_mle", "EvoTreeMLE"), ("gaussian_mle", "logistic_mle", "EvoTreeMLE")]
+         ("logistic_mle", "logistic_mle", "EvoTreeMLE"), ("gaussian_mle", "logistic_mle", "EvoTreeMLE"),
+         ("quantile", "quantile", "EvoTreeRegressor")]
 
 
 @pytest.mark.parametrize("loss,metric,learner", CASES)
@@ -47,13 +48,13 @@ def test_logged_metric_matches_oracle(pkg, orc, loss, metric, learner):
     x, y = _data(loss, 30_000, 3)
     tr, ev = slice(0, 22_000), slice(22_000, None)
     w_eval = np.random.default_rng(1).uniform(0.5, 2.0, 8_000).astype(np.float32)
-    params = getattr(pkg, learner)(loss=loss, metric=metric, nrounds=8, eta=0.3, max_depth=5, nbins=32)
+    params = getattr(pkg, learner)(loss=loss, metric=metric, nrounds=8, eta=0.3, max_depth=5, nbins=32, alpha=0.3)
     m = pkg.fit(params, x_train=x[tr], y_train=y[tr], x_eval=x[ev], y_eval=y[ev], w_eval=w_eval)
     lg = m.info["logger"]
     assert lg["iter"] == list(range(9)) and lg["nrounds"] == 8 and lg["name"] == metric
     op = oracle_params(orc, params, m.K)
     y_or = y[ev] if loss != "mlogloss" else (np.searchsorted(m.info["target_levels"], y[ev]) + 1).astype(np.uint32)
-    ref, _ = _oracle_log(orc, m, op, metric, x[ev], y_or, w_eval)
+    ref, _ = _oracle_log(orc, m, op, metric, x[ev], y_or, w_eval, alpha=0.3)
     np.testing.assert_allclose(np.array(lg["metrics"]), ref, rtol=RTOL)
     # the metric moves in the right direction on data drawn from the training distribution
     better = lg["metrics"][-1] > lg["metrics"][0] if lg["maximise"] else lg["metrics"][-1] < lg["metrics"][0]

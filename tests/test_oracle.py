@@ -388,3 +388,22 @@ def test_mae_and_credibility_trees_by_hand(orc):
                 return z * abs(m1)
             gain = cred(left.astype(np.float64)) + cred(right.astype(np.float64)) - cred(d.astype(np.float64))
         assert np.isclose(t.gain[0], gain, rtol=1e-4), (loss, t.gain[0], gain)
+
+
+def test_quantile_leaves_by_hand(orc):
+    """One split, two leaves: the leaf values must be numpy's (type-7) quantile of the residuals of each side."""
+    x_bin = np.asfortranarray(np.array([[1]] * 5 + [[2]] * 6, np.uint8))
+    y = np.array([1.0, 2.0, 4.0, 8.0, 3.0, 20.0, 30.0, 25.0, 21.0, 40.0, 22.0], np.float32)
+    n = y.size
+    for alpha in (0.25, 0.5, 0.9):
+        p = orc.Params(loss="quantile", K=1, nbins=2, max_depth=2, eta=1.0, lambda_=0.0, L2=0.0, min_weight=0.5, alpha=alpha)
+        grad = np.zeros((n, 3), np.float32)
+        grad[:, 2] = 1.0
+        pred = np.full((n, 1), y.mean(), np.float32)
+        orc.update_grads(p, pred, y, grad)
+        d = y - np.float32(y.mean())
+        assert np.array_equal(grad[:, 1], d) and np.allclose(grad[:, 0], np.where(d > 0, alpha, alpha - 1))
+        t, _, _, _ = orc.grow_tree(p, x_bin, grad, np.arange(1, n + 1, dtype=np.uint32), np.array([1], np.uint32))
+        assert t.split[0] and t.cond_bin[0] == 1
+        assert np.isclose(t.pred[1, 0], np.quantile(d[:5].astype(np.float64), alpha), rtol=1e-6)
+        assert np.isclose(t.pred[2, 0], np.quantile(d[5:].astype(np.float64), alpha), rtol=1e-6)

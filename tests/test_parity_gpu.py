@@ -121,6 +121,26 @@ def test_losses_with_their_own_gain_and_leaf(pkg, orc, loss):
     assert s["splits"] > 10, s
 
 
+@pytest.mark.parametrize("alpha,rowsample", [(0.5, 1.0), (0.1, 1.0), (0.9, 0.6)])
+def test_quantile_loss(pkg, orc, alpha, rowsample):
+    """Quantile loss (src/loss.jl:93-98, src/predict.jl:264-272): the gain of mae, leaf values = alpha-quantile of the
+    residuals of the leaf's sampled rows, found on the device by a radix selection and by a sort in the oracle."""
+    x, y = make_regression(30_000, 8, seed=int(alpha * 100))
+    p = pkg.EvoTreeRegressor(loss="quantile", alpha=alpha, nrounds=3, max_depth=5, nbins=32, eta=0.5, rowsample=rowsample, L2=0.5)
+    assert p.metric == "quantile"
+    s = lockstep_check(pkg, orc, p, x, y, rounds=3)
+    assert s["splits"] > 10, s
+
+
+def test_quantile_model_covers_its_quantile(pkg):
+    rng = np.random.default_rng(6)
+    x = rng.random((40_000, 5)).astype(np.float32)
+    y = (2 * x[:, 0] + (0.2 + x[:, 1]) * rng.normal(size=40_000)).astype(np.float32)
+    for alpha in (0.2, 0.8):
+        m = pkg.fit(pkg.EvoTreeRegressor(loss="quantile", alpha=alpha, nrounds=40, max_depth=5, nbins=32, eta=0.2), x_train=x, y_train=y)
+        assert abs(float(np.mean(y <= m(x))) - alpha) < 0.03
+
+
 @pytest.mark.parametrize("depth", [1, 2, 3])
 def test_shallow_depths(pkg, orc, depth):
     x, y = make_regression(5_000, 7, seed=depth)
