@@ -107,6 +107,7 @@ static void free_handle(evb_handle *h) {
     for (int i = 0; i < h->n_ipc_opened; ++i) cudaIpcCloseMemHandle(h->ipc_opened[i]);
     if (h->peer_cand[h->rank]) cudaFree(h->peer_cand[h->rank]);
     if (h->peer_flags[h->rank]) cudaFree(h->peer_flags[h->rank]);
+    if (h->d_barrier_seq) cudaFree(h->d_barrier_seq);
     if (h->hsum) cudaFree(h->hsum);
     free_eval(h);
     void *ptrs[] = {h->qs_cnt, h->qs_prefix, h->qs_rank, h->qs_gamma, h->gradq, h->d_gmax, h->d_qinv, h->xT, h->xC, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
@@ -424,9 +425,10 @@ extern "C" int32_t evb_grow_tree_begin(evb_handle *h, const uint8_t *row_mask, u
     const int key = (use_mask ? 1 : 0) | (run_grads ? 2 : 0) | (fuse ? 4 : 0) | (slot ? 8 : 0) | (quantize ? 16 : 0);
     if (h->graph_mask_cond != (int)mask_cond) { drop_graphs(h); h->graph_mask_cond = mask_cond; }
     bool launched = false;
-    // Sharded runs stay on direct launches: a run that captured the NCCL collectives into the graph did not
-    // complete on 2 GPUs, so collectives are never captured.
-    if (h->use_graphs && !h->timing && h->world == 1) {
+    // Sharded runs over NCCL stay on direct launches: a run that captured the NCCL collectives into the graph did not
+    // complete on 2 GPUs, so collectives are never captured.  With peer access the exchange is made of this
+    // library's own kernels (the barrier counts on the device), which replay like any other.
+    if (h->use_graphs && !h->timing && (h->world == 1 || h->p2p)) {
         if (!h->graph[key] && h->tree_seq >= 1) { // the very first tree of a handle always runs directly
             int64_t before[EVB_NTIMERS];
             memcpy(before, h->tm.launches, sizeof(before));
@@ -634,6 +636,8 @@ extern "C" int32_t evb_comm_ipc_export(evb_handle *h, uint8_t blob[256]) {
     EVB_CUDA(dalloc(&flags, (size_t)8));
     EVB_CUDA(cudaMemset(flags, 0, 8 * sizeof(int)));
     h->peer_hcomp[h->rank] = h->hcomp; h->peer_cand[h->rank] = cand; h->peer_flags[h->rank] = flags;
+    EVB_CUDA(dalloc(&h->d_barrier_seq, (size_t)1));
+    EVB_CUDA(cudaMemset(h->d_barrier_seq, 0, sizeof(int)));
     IpcBlob b;
     memset(&b, 0, sizeof(b));
     EVB_CUDA(cudaIpcGetMemHandle(&b.hcomp, h->hcomp));

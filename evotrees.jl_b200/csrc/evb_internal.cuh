@@ -164,7 +164,7 @@ struct evb_handle {
     double *peer_hcomp[8]; double *peer_cand[8]; int *peer_flags[8];
     double *hsum; // sums over the ranks of the owned feature slots of hcomp
     void *ipc_opened[24]; int n_ipc_opened;
-    int barrier_seq;
+    int *d_barrier_seq; // device counter of the peer barriers passed
 
     // timing
     bool timing;

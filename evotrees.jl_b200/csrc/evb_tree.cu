@@ -482,17 +482,21 @@ struct BarrierArgs {
     int *peer_flags[EVB_MAX_PEERS];
     int *flags_local;
     int *err;
-    int world, rank, seq;
+    int world, rank;
+    int *seq_dev; // barriers passed so far: kept on the device so that a replayed CUDA graph keeps counting
 };
 __global__ void k_peer_barrier(BarrierArgs a) {
     const int t = threadIdx.x;
+    int seq = 0;
+    if (t == 0) { seq = *a.seq_dev + 1; *a.seq_dev = seq; } // one warp, launched alone on the stream: no race
+    seq = __shfl_sync(FULL, seq, 0);
     if (t >= a.world) return;
     __threadfence_system();
-    *(volatile int *)(a.peer_flags[t] + a.rank) = a.seq;
+    *(volatile int *)(a.peer_flags[t] + a.rank) = seq;
     __threadfence_system();
     volatile int *mine = a.flags_local + t;
     for (unsigned it = 0; it < 20000000u; ++it) {
-        if (*mine - a.seq >= 0) { __threadfence_system(); return; }
+        if (*mine - seq >= 0) { __threadfence_system(); return; }
         if ((it & 1023u) == 1023u && *(volatile int *)a.err != 0) return;
         __nanosleep(100);
     }
@@ -767,7 +771,7 @@ int32_t evb_launch_root_plan(evb_handle *h) {
 static int32_t launch_peer_barrier(evb_handle *h) {
     BarrierArgs b;
     for (int q = 0; q < EVB_MAX_PEERS; ++q) b.peer_flags[q] = q < h->world ? h->peer_flags[q] : nullptr;
-    b.flags_local = h->peer_flags[h->rank]; b.err = h->d_err; b.world = h->world; b.rank = h->rank; b.seq = ++h->barrier_seq;
+    b.flags_local = h->peer_flags[h->rank]; b.err = h->d_err; b.world = h->world; b.rank = h->rank; b.seq_dev = h->d_barrier_seq;
     k_peer_barrier<<<1, 32, 0, h->st>>>(b);
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
