@@ -334,6 +334,20 @@ def eval_levelcode(y_eval, target_levels) -> np.ndarray:
     return (pos + 1).astype(np.uint32)
 
 
+# losses whose bias the sharded path derives from per-shard sums (`Comm.allreduce_bias`) besides the four original ones
+allreduce_bias_losses = ("poisson", "gamma", "tweedie", "logistic_mle", "mae", "cred_var", "cred_std", "quantile")
+
+
+def metric_from_sums(metric: str, sums, comm=None) -> float:
+    """Metric from the two sums that `evb_eval_attach` / `evb_eval_sums` return for this rank's evaluation shard
+    (sum of w * value, sum of w): the sums are added over the ranks first, then divided (`sqrt` for rmse)."""
+    s = np.array([sums[0], sums[1]], np.float64)
+    if comm is not None:
+        s = comm.allreduce_sum(s)
+    v = float(s[0] / s[1])
+    return math.sqrt(v) if metric == "rmse" else v
+
+
 class CallBack:
     """`CallBack(params, m, x_eval, y_eval, device; w_eval, offset_eval)` (src/callback.jl:82-121): the evaluation
     data is binarized with the model's edges and handed to the training handle (`evb_eval_attach`), which from then
@@ -381,11 +395,7 @@ class CallBack:
         self.initial = self._metric(sums)
 
     def _metric(self, sums) -> float:
-        s = np.array([sums[0], sums[1]], np.float64)
-        if self.comm is not None:
-            s = self.comm.allreduce_sum(s)
-        v = float(s[0] / s[1])
-        return math.sqrt(v) if self.metric == "rmse" else v
+        return metric_from_sums(self.metric, sums, self.comm)
 
     def last(self) -> float:
         """Metric after the tree collected last by `grow_tree` / `grow_tree_end`."""

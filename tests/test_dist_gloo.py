@@ -43,6 +43,16 @@ def _worker(rank, world, port, tmp):
     h = np.stack([np.bincount(xb[:, j].astype(np.int64) - 1, weights=g, minlength=nbins) for j in range(f)])
     out["hist"] = comm.allreduce_sum(h)
     out["nleft"] = comm.allreduce_sum(np.array([(xb[:, 0] <= 7).sum()]))
+    # evaluation shards: every rank holds the metric sums of its rows, the logged metric is the ratio of the added sums
+    from evotrees_b200.fit import metric_from_sums, allreduce_bias_losses
+    w = rng.uniform(0.5, 2.0, n).astype(np.float32)[lo:hi]
+    p = (ys + 0.3).astype(np.float32)
+    sums = (float(np.sum(w.astype(np.float64) * (p.astype(np.float64) - ys) ** 2)), float(w.astype(np.float64).sum()))
+    out["eval_mse"] = np.array([metric_from_sums("mse", sums, comm), metric_from_sums("rmse", sums, comm)])
+    for loss in allreduce_bias_losses:
+        yy = np.abs(ys) + 0.1
+        K, yd, _, mu_local, _, _ = init_target(loss, yy, None)
+        out["mu_" + loss] = comm.allreduce_bias(loss, yd, mu_local, K)
     np.savez(os.path.join(tmp, f"r{rank}.npz"), **out)
     dist.barrier()
     dist.destroy_process_group()
@@ -74,3 +84,10 @@ def test_two_rank_host_plumbing(tmp_path, orc, pkg):
     hfull = np.stack([np.bincount(xb[:, j].astype(np.int64) - 1, weights=gfull, minlength=nbins) for j in range(f)])
     np.testing.assert_allclose(r0["hist"], hfull, rtol=1e-12, atol=1e-9)
     assert int(r0["nleft"][0]) == int((xb[:, 0] <= 7).sum())
+    w = rng.uniform(0.5, 2.0, n).astype(np.float32).astype(np.float64)
+    mse = np.sum(w * 0.09) / w.sum()
+    np.testing.assert_allclose(r0["eval_mse"], [mse, np.sqrt(mse)], rtol=1e-5)
+    from evotrees_b200.fit import allreduce_bias_losses
+    for loss in allreduce_bias_losses:   # the bias of the added losses from per-shard statistics == the bias of the whole
+        K, yd, _, mu, _, _ = init_target(loss, np.abs(y) + 0.1, None)
+        np.testing.assert_allclose(r0["mu_" + loss], mu, rtol=1e-5, atol=1e-6)
