@@ -15,9 +15,9 @@ LIB_PATH = os.path.join(HERE, "libevotrees_b200.so")
 
 EVB_F32, EVB_U32, EVB_F64 = 0, 1, 2
 LOSS_CODES = {"mse": 0, "logloss": 1, "mlogloss": 2, "gaussian_mle": 3, "poisson": 4, "gamma": 5, "tweedie": 6, "logistic_mle": 7,
-              "mae": 8, "cred_var": 9, "cred_std": 10, "quantile": 11}
+              "mae": 8, "cred_var": 9, "cred_std": 10, "quantile": 11, "multiquantile": 12}
 METRIC_CODES = {"mse": 0, "rmse": 0, "mae": 1, "logloss": 2, "mlogloss": 3, "gaussian_mle": 4, "poisson": 5, "gamma": 6, "tweedie": 7,
-                "logistic_mle": 8, "quantile": 9}  # rmse = sqrt of the mse sums
+                "logistic_mle": 8, "quantile": 9, "multiquantile": 10}  # rmse = sqrt of the mse sums
 FLAG_TIMING, FLAG_FULL_PARTITION, FLAG_KEEP_ALL_HIST = 1, 2, 4
 NTIMERS = 12
 TIMER_NAMES = ["grads", "rows_init", "hist", "hist_reduce", "allreduce", "scan", "partition", "plan", "finalize",
@@ -38,7 +38,7 @@ class EvbParams(C.Structure):
     _fields_ = [("loss", C.c_int32), ("K", C.c_int32), ("nbins", C.c_int32), ("max_depth", C.c_int32),
                 ("bagging_size", C.c_int32), ("tree_type", C.c_int32),
                 ("eta", C.c_double), ("lambda_", C.c_double), ("L2", C.c_double), ("gamma", C.c_double),
-                ("min_weight", C.c_double), ("device", C.c_int32), ("flags", C.c_uint32), ("alpha", C.c_double)]
+                ("min_weight", C.c_double), ("device", C.c_int32), ("flags", C.c_uint32), ("alpha", C.c_double), ("alphas", C.c_double * 8)]
 
 
 class EvbTimings(C.Structure):

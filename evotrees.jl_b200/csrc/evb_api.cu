@@ -168,7 +168,7 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
 
     EVB_CUDA(dalloc(&h->xT, (size_t)n * h->RS));
     EVB_CUDA(dalloc(&h->grad, (size_t)n * h->GS));
-    if (p->loss == EVB_QUANTILE) {
+    if (p->loss == EVB_QUANTILE || p->loss == EVB_MULTIQUANTILE) {
         const size_t e = (size_t)2 * (h->nn + 1);
         EVB_CUDA(dalloc(&h->qs_cnt, e * 256)); EVB_CUDA(dalloc(&h->qs_prefix, e)); EVB_CUDA(dalloc(&h->qs_rank, e));
         EVB_CUDA(dalloc(&h->qs_gamma, (size_t)h->nn + 1));
@@ -281,7 +281,8 @@ extern "C" int32_t evb_create(evb_handle **out, const evb_params *p, int64_t nob
     if (p->loss < 0 || p->loss > EVB_LOSS_LAST) { evb_set_error("evb_create: unknown loss %d", p->loss); return EVB_ERR_ARG; }
     if (p->K < 1 || p->K > 32) { evb_set_error("evb_create: K=%d outside 1..32", p->K); return EVB_ERR_ARG; }
     const bool mle = p->loss == EVB_GAUSSIAN_MLE || p->loss == EVB_LOGISTIC_MLE;
-    if ((mle && (p->K % 2 != 0 || ycols != p->K / 2)) || (!mle && p->loss != EVB_MLOGLOSS && ycols != p->K) ||
+    if ((mle && (p->K % 2 != 0 || ycols != p->K / 2)) || (!mle && p->loss != EVB_MLOGLOSS && p->loss != EVB_MULTIQUANTILE && ycols != p->K) ||
+        (p->loss == EVB_MULTIQUANTILE && (ycols != 1 || p->K > 8)) ||
         (p->loss == EVB_MLOGLOSS && p->K < 2)) {
         evb_set_error("evb_create: K=%d / ycols=%d inconsistent with the loss", p->K, ycols);
         return EVB_ERR_ARG;
@@ -295,6 +296,10 @@ extern "C" int32_t evb_create(evb_handle **out, const evb_params *p, int64_t nob
     if (p->loss == EVB_QUANTILE && (p->K != 1 || !(p->alpha > 0.0 && p->alpha < 1.0))) {
         evb_set_error("evb_create: the quantile loss needs K = 1 and 0 < alpha < 1 (alpha = %g)", p->alpha);
         return EVB_ERR_ARG;
+    }
+    if (p->loss == EVB_MULTIQUANTILE) {
+        for (int k = 0; k < p->K; ++k)
+            if (!(p->alphas[k] > 0.0 && p->alphas[k] < 1.0)) { evb_set_error("evb_create: alphas[%d] = %g outside (0, 1)", k, p->alphas[k]); return EVB_ERR_ARG; }
     }
     if (p->bagging_size < 1 || p->tree_type != 0) { evb_set_error("evb_create: bagging_size must be >= 1 and tree_type binary"); return EVB_ERR_ARG; }
     int ndev = 0;
@@ -352,7 +357,7 @@ static int32_t enqueue_tree(evb_handle *h, bool use_mask, uint8_t mask_cond, boo
         EVB_CHECK(evb_launch_scan(h, level));
         if (level < D - 1 || (full_part && level == D - 1)) EVB_CHECK(evb_launch_partition(h, level));
     }
-    if (h->p.loss == EVB_QUANTILE) {
+    if (h->p.loss == EVB_QUANTILE || h->p.loss == EVB_MULTIQUANTILE) {
         // the leaf values need the leaf of every row first: leaf ids, per-leaf quantiles, then the usual update
         EVB_CHECK(evb_launch_finalize(h, false, 1));
         EVB_CHECK(evb_launch_quantile_leaves(h, use_mask, mask_cond));
@@ -575,7 +580,7 @@ extern "C" int32_t evb_eval_attach(evb_handle *h, int64_t nobs, const uint8_t *x
                     : (loss == EVB_GAUSSIAN_MLE || loss == EVB_LOGISTIC_MLE) ? (metric == EVB_METRIC_GAUSSIAN_MLE || metric == EVB_METRIC_LOGISTIC_MLE)
                     : (metric == EVB_METRIC_MSE || metric == EVB_METRIC_MAE || metric == EVB_METRIC_LOGLOSS ||
                        metric == EVB_METRIC_POISSON || metric == EVB_METRIC_GAMMA || metric == EVB_METRIC_TWEEDIE ||
-                       metric == EVB_METRIC_QUANTILE);
+                       metric == EVB_METRIC_QUANTILE || (metric == EVB_METRIC_MULTIQUANTILE && loss == EVB_MULTIQUANTILE));
     if (!ok) { evb_set_error("evb_eval_attach: metric %d is not defined for loss %d", metric, loss); return EVB_ERR_ARG; }
     drop_graphs(h); // the launch sequence of a tree changes
     int32_t rc = eval_attach_impl(h, nobs, x_bin, y, w, pred0, bias, metric, sums);

@@ -20,8 +20,10 @@ __device__ __forceinline__ int gpos(int c, int NCH) { return (c / NCH) * 4 + (c 
 #define REC(c) rec[gpos((c), NCH)]
 // For mse the hessian channels are not stored (h = 2w is rebuilt when the histogram is reduced): the record is
 // g_1..g_K, w, i.e. `elided` shifts w from channel 2K to channel K.
+struct AlphaSet { float a[8]; }; // a[0]: alpha of the quantile loss; a[0..K-1]: alphas of the multiquantile loss
 __device__ __forceinline__ void grad_row(int loss, int K, int NCH, bool elided, const float *p, const void *y, int ycols, long long i, float *rec,
-                                         float alpha = 0.5f) {
+                                         const AlphaSet &al) {
+    const float alpha = al.a[0];
     const float w = REC(elided ? K : 2 * K);
     if (loss == EVB_MSE) {
         const float *yf = (const float *)y + (size_t)i * ycols;
@@ -44,6 +46,13 @@ __device__ __forceinline__ void grad_row(int loss, int K, int NCH, bool elided, 
             const float prob = expf(p[k]) / isum;
             REC(k) = (((uint32_t)(k + 1) == yi) ? prob - 1.0f : prob) * w;
             REC(K + k) = prob * (1.0f - prob) * w;
+        }
+    } else if (loss == EVB_MULTIQUANTILE) { // one target, one quantile per output row (src/loss.jl:160-172)
+        const float yi = ((const float *)y)[i];
+        for (int k = 0; k < K; ++k) {
+            const float d = yi - p[k];
+            REC(k) = (d > 0.0f ? al.a[k] : al.a[k] - 1.0f) * w;
+            REC(K + k) = d;
         }
     } else if (loss == EVB_QUANTILE) { // quantile_grad_diff, src/loss.jl:93-98: the second slot keeps the raw residual
         const float *yf = (const float *)y + (size_t)i * ycols;
@@ -186,7 +195,7 @@ __device__ __forceinline__ void block_absmax(float v, unsigned *gmax) {
     }
 }
 __global__ void __launch_bounds__(256) k_grads(int loss, int K, int GS, int NCH, int elided, int ycols, long long n, const float *pred, const void *y, float *grad, unsigned *gmax,
-                                               float alpha) {
+                                               AlphaSet alpha) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     float g0 = 0.0f;
     if (i < n) {
@@ -309,7 +318,7 @@ struct FinArgs {
     unsigned *gmax; // non-null: track max |g| of the gradients computed here (fixed-point histogram variant)
     long long n;
     int RS, K, GS, NCH, elided, loss, nn, ycols, compute_grads, packed_in_smem;
-    float alpha;
+    AlphaSet alpha;
     int mode; // 0: traverse, add the leaf, next gradients; 1: traverse only (leaf ids); 2: leaf ids are in nidx, add + gradients
 };
 __global__ void __launch_bounds__(256) k_finalize(FinArgs a) {
@@ -389,7 +398,7 @@ struct QselArgs {
     const double *nsum;
     float *t_pred;
     long long n;
-    int GS, roff, nn, C, pass;
+    int GS, roff, nn, C, pass, K, k, clamp; // k: output row being filled; clamp: max(eps, .) on the denominator (quantile)
     uint8_t cond;
     double alpha, eb, lambda, L2; // eb = eta / bagging_size
 };
@@ -469,7 +478,8 @@ __global__ void k_qsel_leaf(QselArgs a) {
     const float lo = key_float(a.prefix[leaf]), hi = key_float(a.prefix[(size_t)(a.nn + 1) + leaf]);
     const double q = (double)lo + (double)g * ((double)hi - (double)lo);
     const double w = a.nsum[(size_t)leaf * a.C + a.C - 1];
-    a.t_pred[leaf - 1] = (float)(a.eb * q / fmax(DBL_EPSILON, 1.0 + a.lambda + a.L2 / w));
+    const double denom = 1.0 + a.lambda + a.L2 / w;
+    a.t_pred[(size_t)(leaf - 1) * a.K + a.k] = (float)(a.eb * q / (a.clamp ? fmax(DBL_EPSILON, denom) : denom));
 }
 
 // node of every sampled row from the row lists left by the partition kernels; one CTA per node
@@ -581,7 +591,8 @@ __global__ void __launch_bounds__(256) k_binarize_rows(const T *x, long long ld,
 // ---------------------------------------------------------------------------------- evaluation data
 // Per-row metric value in float, as `_metric_value` / `_mle2p_metric_value` / `mlogloss` compute it
 // (src/metrics.jl:1-110): the caller multiplies by w and accumulates in double.
-__device__ __forceinline__ float metric_row(int metric, int K, const float *p, const void *y, int ycols, long long i, float w, float alpha) {
+__device__ __forceinline__ float metric_row(int metric, int K, const float *p, const void *y, int ycols, long long i, float w, const AlphaSet &al) {
+    const float alpha = al.a[0];
     if (metric == EVB_METRIC_MLOGLOSS) {
         const uint32_t yi = ((const uint32_t *)y)[i];
         float isum = 0.0f;
@@ -589,6 +600,11 @@ __device__ __forceinline__ float metric_row(int metric, int K, const float *p, c
         return w * (logf(isum) - p[yi - 1]);
     }
     const float *yf = (const float *)y + (size_t)i * ycols;
+    if (metric == EVB_METRIC_MULTIQUANTILE) { // src/metrics.jl:120-141
+        float acc = 0.0f;
+        for (int k = 0; k < K; ++k) acc += al.a[k] * fmaxf(yf[0] - p[k], 0.0f) + (1.0f - al.a[k]) * fmaxf(p[k] - yf[0], 0.0f);
+        return w * acc / (float)K;
+    }
     if (metric == EVB_METRIC_GAUSSIAN_MLE || metric == EVB_METRIC_LOGISTIC_MLE) {
         const int Y = K / 2;
         float acc = 0.0f;
@@ -629,7 +645,7 @@ struct EvalArgs {
     double *part; // [gridDim.x][2]
     long long n;
     int RS, K, loss, metric, nn, ycols, packed_in_smem;
-    float alpha;
+    AlphaSet alpha;
 };
 // `predict!(cb.p, tree, cb.x_bin, cb.feattypes)` followed by the per-row metric (src/callback.jl:123-128).  Every
 // block owns a fixed set of rows and sums them in a fixed order, so the result does not depend on scheduling.
@@ -677,6 +693,13 @@ __global__ void __launch_bounds__(256) k_eval_sum(const double *part, int nblock
 } // namespace
 
 // =====================================================================================================
+static AlphaSet evb_alpha_set(const evb_handle *h) {
+    AlphaSet s;
+    for (int k = 0; k < 8; ++k) s.a[k] = (float)h->p.alphas[k];
+    if (h->p.loss != EVB_MULTIQUANTILE) s.a[0] = (float)h->p.alpha;
+    return s;
+}
+
 int32_t evb_launch_transpose(evb_handle *, const uint8_t *xcol_dev, int64_t ld, int64_t nrows, int j0, int nj, uint8_t *xT,
                              int RS, cudaStream_t st) {
     dim3 grid((unsigned)((nrows + 255) / 256), (unsigned)((nj + 3) / 4));
@@ -701,7 +724,7 @@ int32_t evb_launch_grads(evb_handle *h) {
     if (h->use_q) EVB_CUDA(cudaMemsetAsync(h->d_gmax, 0, sizeof(unsigned), h->st));
     evb_tic(h, EVB_T_GRADS);
     k_grads<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->p.loss, h->K, h->GS, h->rec_nch, h->Ce != h->C, h->ycols, h->n, h->pred, h->y, h->grad,
-                                                                h->use_q ? h->d_gmax : nullptr, (float)h->p.alpha);
+                                                                h->use_q ? h->d_gmax : nullptr, evb_alpha_set(h));
     evb_toc(h, EVB_T_GRADS);
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
@@ -736,7 +759,7 @@ int32_t evb_launch_finalize(evb_handle *h, bool compute_grads, int mode) {
     a.nidx = h->nidx; a.n = h->n; a.RS = h->RS; a.K = h->K; a.GS = h->GS; a.NCH = h->rec_nch; a.elided = h->Ce != h->C; a.loss = h->p.loss; a.nn = h->nn;
     a.gmax = h->use_q ? h->d_gmax : nullptr;
     if (h->use_q && compute_grads) EVB_CUDA(cudaMemsetAsync(h->d_gmax, 0, sizeof(unsigned), h->st));
-    a.ycols = h->ycols; a.compute_grads = compute_grads ? 1 : 0; a.alpha = (float)h->p.alpha; a.mode = mode;
+    a.ycols = h->ycols; a.compute_grads = compute_grads ? 1 : 0; a.alpha = evb_alpha_set(h); a.mode = mode;
     const size_t smem = (size_t)h->nn * 4;
     a.packed_in_smem = smem <= 40 * 1024 ? 1 : 0;
     const size_t staged = smem + (size_t)256 * (h->RS + 4);
@@ -760,7 +783,7 @@ int32_t evb_launch_eval(evb_handle *h, const float *fixed_leaf_dev) {
     EvalArgs a;
     a.xT = h->ev_xT; a.t_packed = h->t_packed; a.t_pred = h->t_pred; a.fixed_leaf = fixed_leaf_dev; a.pred = h->ev_pred;
     a.y = h->ev_y; a.w = h->ev_w; a.part = h->ev_part; a.n = h->ev_n; a.RS = h->RS; a.K = h->K; a.loss = h->p.loss;
-    a.metric = h->ev_metric; a.nn = h->nn; a.ycols = h->ycols; a.alpha = (float)h->p.alpha;
+    a.metric = h->ev_metric; a.nn = h->nn; a.ycols = h->ycols; a.alpha = evb_alpha_set(h);
     const size_t smem = (size_t)h->nn * 4;
     a.packed_in_smem = smem <= 40 * 1024 ? 1 : 0;
     evb_tic(h, EVB_T_FINALIZE);
@@ -778,17 +801,22 @@ int32_t evb_launch_quantile_leaves(evb_handle *h, bool use_mask, uint8_t mask_co
     a.nidx = h->nidx; a.grad = h->grad; a.mask = use_mask ? h->mask_d : nullptr; a.cnt = h->qs_cnt; a.prefix = h->qs_prefix;
     a.rank = h->qs_rank; a.gamma = h->qs_gamma; a.t_split = h->t_split; a.nsum = h->nsum; a.t_pred = h->t_pred; a.n = h->n;
     a.GS = h->GS; a.nn = h->nn; a.C = h->C; a.cond = mask_cond;
-    a.roff = (h->K / h->rec_nch) * 4 + (h->K % h->rec_nch); // gpos(K): the slot of h_1, where the residual is kept
-    a.alpha = h->p.alpha; a.eb = h->p.eta / (double)h->p.bagging_size; a.lambda = h->p.lambda; a.L2 = h->p.L2;
+    a.eb = h->p.eta / (double)h->p.bagging_size; a.lambda = h->p.lambda; a.L2 = h->p.L2; a.K = h->K;
+    a.clamp = h->p.loss == EVB_QUANTILE ? 1 : 0; // src/predict.jl:270 has the max(eps, .), :279 has not
     evb_tic(h, EVB_T_FINALIZE);
-    for (int pass = 0; pass < 4; ++pass) {
-        a.pass = pass;
-        k_qsel_count<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(a);
-        k_qsel_pick<<<(h->nn + 8) / 8, 256, 0, h->st>>>(a);
+    for (int k = 0; k < h->K; ++k) { // one selection per output row: the residual of row k sits in the slot of h_k
+        const int c = h->K + k;
+        a.k = k; a.roff = (c / h->rec_nch) * 4 + (c % h->rec_nch);
+        a.alpha = h->p.loss == EVB_QUANTILE ? h->p.alpha : h->p.alphas[k];
+        for (int pass = 0; pass < 4; ++pass) {
+            a.pass = pass;
+            k_qsel_count<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(a);
+            k_qsel_pick<<<(h->nn + 8) / 8, 256, 0, h->st>>>(a);
+        }
+        k_qsel_leaf<<<(h->nn + 256) / 256, 256, 0, h->st>>>(a);
     }
-    k_qsel_leaf<<<(h->nn + 256) / 256, 256, 0, h->st>>>(a);
     evb_toc(h, EVB_T_FINALIZE);
-    h->tm.launches[EVB_T_FINALIZE] += 8;
+    h->tm.launches[EVB_T_FINALIZE] += 9 * h->K - 1;
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
 }

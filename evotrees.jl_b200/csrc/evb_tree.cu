@@ -138,7 +138,7 @@ __device__ __forceinline__ bool own_gain(int loss) { return loss >= EVB_MAE; }
 // gain of one output row of a candidate split: left sums (gl, hl, w_l), parent sums (sg, sh, w_p)
 __device__ __forceinline__ double side_gain(const ScanArgs &a, double gl, double hl, double w_l, double sg, double sh, double w_p) {
     const double w_r = w_p - w_l;
-    if (a.loss == EVB_MAE || a.loss == EVB_QUANTILE) {
+    if ((a.loss == EVB_MAE || a.loss == EVB_QUANTILE || a.loss == EVB_MULTIQUANTILE)) {
         const double d_l = fmax(DBL_EPSILON, 1.0 + a.lambda + a.L2 / w_l), d_r = fmax(DBL_EPSILON, 1.0 + a.lambda + a.L2 / w_r);
         const double mu_p = sg / w_p;
         return term_shift(gl, w_l, mu_p, d_l) + term_shift(sg - gl, w_r, mu_p, d_r);
@@ -147,7 +147,7 @@ __device__ __forceinline__ double side_gain(const ScanArgs &a, double gl, double
 }
 // pred_scalar of the three losses (src/predict.jl:219-222, 257-261): the sign is the gradient's, not minus it
 __device__ __forceinline__ double own_scalar(const ScanArgs &a, double g, double w) {
-    return -a.neb * g / (a.loss == EVB_MAE || a.loss == EVB_QUANTILE ? fmax(DBL_EPSILON, w + a.lambda * w + a.L2) : (w + a.L2));
+    return -a.neb * g / ((a.loss == EVB_MAE || a.loss == EVB_QUANTILE || a.loss == EVB_MULTIQUANTILE) ? fmax(DBL_EPSILON, w + a.lambda * w + a.L2) : (w + a.L2));
 }
 // pred_leaf_cpu! for output row k (src/predict.jl:198-204, 224-234, 241-247; mae :250-257, cred :211-218)
 __device__ __forceinline__ float leaf_value(const ScanArgs &a, const double *s, int k) {
@@ -225,7 +225,7 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
     const double w_p = s_sum[C - 1];
     if (!OWN) {
         for (int k = 0; k < K; ++k) gain_p += term_gh(s_sum[k], s_sum[K + k], w_p, a.lambda, a.L2); // node_gain, split.jl:58-66
-    } else if (a.loss != EVB_MAE && a.loss != EVB_QUANTILE) {
+    } else if (a.loss != EVB_MAE && a.loss != EVB_QUANTILE && a.loss != EVB_MULTIQUANTILE) {
         for (int k = 0; k < K; ++k) gain_p += term_cred(a.loss, s_sum[k], s_sum[K + k], w_p, a.L2);   // split.jl:70-78; mae: 0
     }
 

@@ -25,7 +25,7 @@ def _invsoftplus(x):
     return x + math.log(-math.expm1(-x))  # src/loss.jl:266-268
 
 
-def init_target(loss: str, y_train: np.ndarray, offset):
+def init_target(loss: str, y_train: np.ndarray, offset, alphas=(0.1, 0.5, 0.9)):
     """`_init_target` (src/init.jl:10-146) for the four losses of this path.
     Returns K, y (device dtype), ycols, mu float32 [K], target_levels, offset (link space)."""
     levels = None
@@ -46,6 +46,12 @@ def init_target(loss: str, y_train: np.ndarray, offset):
                 offset = np.log(offset)
         else:
             mu = m.astype(np.float32)
+    elif loss == "multiquantile":                             # src/init.jl:99-103: one target, one row per quantile
+        y = np.ascontiguousarray(y_train, np.float32)
+        if y.ndim != 1:
+            raise ValueError("multiquantile takes a vector target")
+        ycols, K = 1, len(alphas)
+        mu = np.quantile(y.astype(np.float64), alphas).astype(np.float32)
     elif loss == "mlogloss":
         yt = np.asarray(y_train)
         if yt.ndim != 1 or not (np.issubdtype(yt.dtype, np.integer) or yt.dtype == bool or yt.dtype.kind in "US"):
@@ -154,7 +160,8 @@ class Cache:
 
 def make_params(params: EvoTypes, K: int, device: int, flags: int = 0) -> _lib.EvbParams:
     return _lib.EvbParams(_lib.LOSS_CODES[params.loss], K, params.nbins, params.max_depth, params.bagging_size, 0,
-                          params.eta, params.lambda_, params.L2, params.gamma, params.min_weight, device, flags, params.alpha)
+                          params.eta, params.lambda_, params.L2, params.gamma, params.min_weight, device, flags, params.alpha,
+                          (C.c_double * 8)(*(list(params.alphas) + [0.0] * 8)[:8]))
 
 
 def init_core_binned(params: EvoTypes, x_bin: np.ndarray, y, ycols: int, K: int, mu: np.ndarray, w=None, pred0=None,
@@ -201,7 +208,7 @@ def init_core(params: EvoTypes, x_train: np.ndarray, y_train, w_train=None, offs
     rng = np.random.default_rng(params.seed)
     edges, featbins, feattypes = get_edges(x_train, params.nbins, rng)
     offset = None if offset_train is None else np.array(offset_train, np.float32, copy=True).reshape(nobs, -1)
-    K, y, ycols, mu, levels, offset = init_target(params.loss, y_train, offset)
+    K, y, ycols, mu, levels, offset = init_target(params.loss, y_train, offset, params.alphas)
     if comm is not None:
         edges, mu = comm.broadcast_host(edges), comm.allreduce_bias(params.loss, y, mu, K)
     x_bin = binarize(x_train, edges, device)
@@ -293,7 +300,8 @@ def grow_evotree(m: EvoTree, cache: Cache, params: EvoTypes) -> None:
 
 
 IS_MAXIMISE = {"mse": False, "rmse": False, "mae": False, "logloss": False, "mlogloss": False, "poisson": False,
-               "gamma": False, "tweedie": False, "quantile": False, "gaussian_mle": True, "logistic_mle": True}   # src/metrics.jl:194-205
+               "gamma": False, "tweedie": False, "quantile": False, "multiquantile": False, "gaussian_mle": True,
+               "logistic_mle": True}   # src/metrics.jl:194-205
 
 
 def init_logger(metric: str, maximise: bool, early_stopping_rounds: int, early_stopping_tolerance: float = 0.0) -> dict:

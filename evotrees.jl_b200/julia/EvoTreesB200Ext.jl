@@ -22,10 +22,11 @@ struct EvbParams
     eta::Float64; lambda::Float64; L2::Float64; gamma::Float64; min_weight::Float64
     device::Int32; flags::UInt32
     alpha::Float64
+    alphas::NTuple{8,Float64}
 end
 
 const LOSS_CODE = Dict(:mse => 0, :logloss => 1, :mlogloss => 2, :gaussian_mle => 3, :poisson => 4, :gamma => 5, :tweedie => 6, :logistic_mle => 7,
-    :mae => 8, :cred_var => 9, :cred_std => 10, :quantile => 11)
+    :mae => 8, :cred_var => 9, :cred_std => 10, :quantile => 11, :multiquantile => 12)
 
 function check(rc::Int32)
     rc == 0 && return nothing
@@ -77,7 +78,8 @@ function EvoTrees.init_core(params::EvoTypes, ::Type{<:GPU}, data, feature_names
     end
     p = Ref(EvbParams(LOSS_CODE[params.loss], K, params.nbins, params.max_depth, params.bagging_size, 0,
         params.eta, params.lambda, params.L2, params.gamma, params.min_weight, 0, 0,
-        hasproperty(params, :alpha) ? Float64(params.alpha) : 0.5))
+        hasproperty(params, :alpha) ? Float64(params.alpha) : 0.5,
+        ntuple(k -> hasproperty(params, :alphas) && k <= length(params.alphas) ? Float64(params.alphas[k]) : 0.0, 8)))
     ydt, ycols = y isa Vector{UInt32} ? (Int32(1), Int32(1)) : (Int32(0), Int32(ndims(y) == 1 ? 1 : size(y, 1)))
     handle = Ref{Ptr{Cvoid}}(C_NULL)
     ft = UInt8.(feattypes)
@@ -156,7 +158,7 @@ end
 # cache it created last (e.g. `LAST_CACHE[] = cache`); the reference's `fit` then works unchanged.
 const LAST_CACHE = Ref{Union{Nothing,B200Cache}}(nothing)
 const METRIC_CODE = Dict(:mse => 0, :rmse => 0, :mae => 1, :logloss => 2, :mlogloss => 3, :gaussian_mle => 4, :gaussian => 4,
-    :poisson => 5, :poisson_deviance => 5, :gamma => 6, :gamma_deviance => 6, :tweedie => 7, :tweedie_deviance => 7, :logistic_mle => 8, :quantile => 9, :wmae => 9)
+    :poisson => 5, :poisson_deviance => 5, :gamma => 6, :gamma_deviance => 6, :tweedie => 7, :tweedie_deviance => 7, :logistic_mle => 8, :quantile => 9, :wmae => 9, :multiquantile => 10)
 
 struct B200CallBack
     feval::Function        # only read by `fit` for is_maximise(cb.feval), src/fit.jl:415

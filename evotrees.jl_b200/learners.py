@@ -8,7 +8,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-_REG_LOSSES = ("mse", "logloss", "poisson", "gamma", "tweedie", "mae", "cred_var", "cred_std", "quantile")
+_REG_LOSSES = ("mse", "logloss", "poisson", "gamma", "tweedie", "mae", "cred_var", "cred_std", "quantile", "multiquantile")
 _MLE_LOSSES = ("gaussian_mle", "logistic_mle")
 
 
@@ -38,6 +38,7 @@ class EvoTypes:
     early_stopping_rounds: int = 2 ** 62
     early_stopping_tolerance: float = 0.0
     alpha: float = 0.5          # quantile loss / metric
+    alphas: tuple = (0.1, 0.5, 0.9)   # multiquantile loss / metric (src/learners.jl:45)
     metric: str | None = None
 
     _losses = ()
@@ -77,6 +78,10 @@ class EvoTypes:
         _check("bagging_size", self.bagging_size, 1, 2 ** 31)
         _check("early_stopping_tolerance", self.early_stopping_tolerance, 0.0, float("inf"))
         _check("alpha", self.alpha, 0.0, 1.0)
+        if self.loss == "multiquantile":       # check_alphas, src/learners.jl:505-520
+            self.alphas = tuple(float(a) for a in self.alphas)
+            if not 1 <= len(self.alphas) <= 8 or any(not 0.0 < a < 1.0 for a in self.alphas):
+                raise ValueError("`alphas` must hold 1 to 8 values strictly between 0 and 1")
         if self.tree_type != "binary":
             raise ValueError("Invalid input for `tree_type` parameter: only `binary` trees are built by this device path")
         if self.device not in ("gpu", "cuda"):
@@ -86,7 +91,7 @@ class EvoTypes:
 @dataclass
 class EvoTreeRegressor(EvoTypes):
     _losses = _REG_LOSSES
-    _metrics = ("mse", "rmse", "mae", "logloss", "poisson", "gamma", "tweedie", "quantile")
+    _metrics = ("mse", "rmse", "mae", "logloss", "poisson", "gamma", "tweedie", "quantile", "multiquantile")
 
 
 @dataclass

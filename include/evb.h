@@ -51,8 +51,9 @@ enum evb_status {
  * alpha-quantile of the residuals of the leaf's sampled rows (src/loss.jl:93-98, src/predict.jl:264-272) */
 enum evb_loss { EVB_MSE = 0, EVB_LOGLOSS = 1, EVB_MLOGLOSS = 2, EVB_GAUSSIAN_MLE = 3,
                 EVB_POISSON = 4, EVB_GAMMA = 5, EVB_TWEEDIE = 6, EVB_LOGISTIC_MLE = 7,
-                EVB_MAE = 8, EVB_CRED_VAR = 9, EVB_CRED_STD = 10, EVB_QUANTILE = 11 };
-#define EVB_LOSS_LAST EVB_QUANTILE
+                EVB_MAE = 8, EVB_CRED_VAR = 9, EVB_CRED_STD = 10, EVB_QUANTILE = 11,
+                EVB_MULTIQUANTILE = 12 /* one target, K = number of quantiles evb_params.alphas[0..K-1], K <= 8 (src/loss.jl:160-172) */ };
+#define EVB_LOSS_LAST EVB_MULTIQUANTILE
 enum evb_dtype { EVB_F32 = 0, EVB_U32 = 1, EVB_F64 = 2 };
 
 /* flags of evb_params.flags */
@@ -74,6 +75,7 @@ typedef struct {
     int32_t device;        /* CUDA device ordinal of this shard */
     uint32_t flags;
     double alpha;          /* quantile loss / metric: the target quantile in (0, 1) (src/learners.jl:44); else unused */
+    double alphas[8];      /* multiquantile loss / metric: the K target quantiles (src/learners.jl:45); else unused */
 } evb_params;
 
 /* Accumulated device time per kernel class since the last evb_reset_timings (EVB_FLAG_TIMING). */
@@ -176,7 +178,8 @@ EVB_API int32_t evb_grow_tree_end(evb_handle *h, int64_t *feat, uint8_t *cond_bi
  */
 enum evb_metric { EVB_METRIC_MSE = 0, EVB_METRIC_MAE = 1, EVB_METRIC_LOGLOSS = 2, EVB_METRIC_MLOGLOSS = 3, EVB_METRIC_GAUSSIAN_MLE = 4,
                   EVB_METRIC_POISSON = 5, EVB_METRIC_GAMMA = 6, EVB_METRIC_TWEEDIE = 7, EVB_METRIC_LOGISTIC_MLE = 8,
-                  EVB_METRIC_QUANTILE = 9 /* pinball loss at evb_params.alpha (`wmae`, src/metrics.jl:4-6) */ };
+                  EVB_METRIC_QUANTILE = 9 /* pinball loss at evb_params.alpha (`wmae`, src/metrics.jl:4-6) */,
+                  EVB_METRIC_MULTIQUANTILE = 10 /* mean pinball loss over evb_params.alphas (src/metrics.jl:120-141) */ };
 EVB_API int32_t evb_eval_attach(evb_handle *h, int64_t nobs, const uint8_t *x_bin, const void *y, const float *w, const float *pred0,
                                 const float *bias, int32_t metric, double sums[2]);
 EVB_API int32_t evb_eval_sums(evb_handle *h, double sums[2]);

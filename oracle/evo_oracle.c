@@ -35,14 +35,16 @@
 #endif
 
 enum { ORC_MSE = 0, ORC_LOGLOSS = 1, ORC_MLOGLOSS = 2, ORC_GAUSSIAN_MLE = 3, ORC_POISSON = 4, ORC_GAMMA = 5, ORC_TWEEDIE = 6, ORC_LOGISTIC_MLE = 7,
-       ORC_MAE = 8, ORC_CRED_VAR = 9, ORC_CRED_STD = 10, ORC_QUANTILE = 11 };
+       ORC_MAE = 8, ORC_CRED_VAR = 9, ORC_CRED_STD = 10, ORC_QUANTILE = 11, ORC_MULTIQUANTILE = 12 };
 static inline int orc_is_mle(int loss) { return loss == ORC_GAUSSIAN_MLE || loss == ORC_LOGISTIC_MLE; }
 
 typedef struct {
     int32_t loss, K, nbins, max_depth, bagging_size, tree_type;
     double eta, lambda, L2, gamma, min_weight;
-    double alpha; /* quantile loss */
+    double alpha;     /* quantile loss */
+    double alphas[8]; /* multiquantile loss: K values */
 } orc_params;
+static inline int orc_is_shift(int loss) { return loss == 8 || loss == 11 || loss == 12; } /* mae-type gain: MAE, Quantile, MultiQuantile (split.jl:68, 119) */
 
 /* ---- scalar math: src/loss.jl:239-268 ------------------------------------------------ */
 static inline float orc_sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }     /* loss.jl:249-251 */
@@ -96,6 +98,17 @@ void orc_update_grads(const orc_params *p, int64_t nobs, const float *pred, cons
                 }
                 grad[k + C * i] = g * w;
                 grad[K + k + C * i] = h * w;
+            }
+        }
+    } else if (p->loss == ORC_MULTIQUANTILE) {
+        const float *y = (const float *)yv; /* one target; update_grads! src/loss.jl:160-172 */
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < nobs; i++) {
+            float w = grad[(C - 1) + C * i];
+            for (int k = 0; k < K; k++) {
+                float a = (float)p->alphas[k], d = y[i] - pred[k + K * i];
+                grad[k + C * i] = (d > 0.0f ? a : a - 1.0f) * w;
+                grad[K + k + C * i] = d;
             }
         }
     } else if (p->loss == ORC_QUANTILE) {
@@ -193,7 +206,7 @@ static inline double term_cred(int loss, double m1, double m2, double w, double 
 static double node_gain(int loss, const double *s, int C, double lambda, double L2, double eps) {
     int K = (C - 1) / 2;
     double w = s[2 * K], gain = 0.0;
-    if (loss == ORC_MAE || loss == ORC_QUANTILE) return 0.0;                            /* split.jl:68 */
+    if (orc_is_shift(loss)) return 0.0;                                                 /* split.jl:68 */
     if (loss == ORC_CRED_VAR || loss == ORC_CRED_STD) {                                 /* split.jl:70-78 */
         for (int k = 0; k < K; k++) gain += term_cred(loss, s[k], s[K + k], w, L2, eps);
         return gain;
@@ -205,7 +218,7 @@ static double split_gain(int loss, const double *s, const double *sl, int C, dou
                          double L2, double eps) {
     int K = (C - 1) / 2;
     double gain = 0.0;
-    if (loss == ORC_MAE || loss == ORC_QUANTILE) {                                      /* split.jl:119-130 */
+    if (orc_is_shift(loss)) {                                                           /* split.jl:119-130 */
         double w_p = s[2 * K];
         double d_l = fmax(eps, 1.0 + lambda + L2 / w_l), d_r = fmax(eps, 1.0 + lambda + L2 / w_r);
         for (int k = 0; k < K; k++) {
@@ -228,7 +241,7 @@ static double split_gain(int loss, const double *s, const double *sl, int C, dou
 /* pred_scalar: src/predict.jl:205-208 (gradient regression), :235-238 (MLE2P) */
 static double pred_scalar(const double *s, const orc_params *p) {
     const double eps = DBL_EPSILON;
-    if (p->loss == ORC_MAE || p->loss == ORC_QUANTILE) /* src/predict.jl:259-262 (the reference defines none for Quantile; used for monotone tests only) */
+    if (orc_is_shift(p->loss)) /* src/predict.jl:259-262 (the reference defines none for Quantile; used for monotone tests only) */
         return p->eta / p->bagging_size * s[0] / fmax(eps, s[2] + p->lambda * s[2] + p->L2);
     if (p->loss == ORC_CRED_VAR || p->loss == ORC_CRED_STD)   /* src/predict.jl:220-222 */
         return p->eta / p->bagging_size * s[0] / (s[2] + p->L2);
@@ -278,11 +291,12 @@ static int cmp_float(const void *a, const void *b) { float x = *(const float *)a
 static void pred_leaf_quantile(float *tpred, int n0, const double *s, const orc_params *p, const float *grad, const uint32_t *rows, int64_t len) {
     const int K = p->K, C = 2 * K + 1;
     float *v = (float *)malloc(sizeof(float) * (len > 0 ? len : 1));
-    double denom = fmax(DBL_EPSILON, 1.0 + p->lambda + p->L2 / s[C - 1]);
+    double denom = 1.0 + p->lambda + p->L2 / s[C - 1];
+    if (p->loss == ORC_QUANTILE) denom = fmax(DBL_EPSILON, denom); /* :270 clamps, the multiquantile method (:279) does not */
     for (int k = 0; k < K; k++) {
         for (int64_t r = 0; r < len; r++) v[r] = grad[K + k + C * ((int64_t)rows[r] - 1)];
         qsort(v, (size_t)len, sizeof(float), cmp_float);
-        double h = (double)(len - 1) * p->alpha;
+        double h = (double)(len - 1) * (p->loss == ORC_QUANTILE ? p->alpha : p->alphas[k]);
         int64_t lo = (int64_t)floor(h), hi = lo + 1 < len ? lo + 1 : lo;
         double q = len > 0 ? (double)v[lo] + (h - (double)lo) * ((double)v[hi] - (double)v[lo]) : 0.0;
         tpred[k + K * n0] = (float)(p->eta / p->bagging_size * q / denom);
@@ -334,7 +348,7 @@ int orc_grow_tree(const orc_params *p, int64_t nobs, int32_t nfeats, const uint8
             for (int a = 0; a < ncur; a++) {
                 int n = cur[a];
                 w[n - 1] = (float)nsum[(C - 1) + C * n];
-                if (p->loss == ORC_QUANTILE) pred_leaf_quantile(tpred, n - 1, &nsum[C * n], p, grad, is + seg[n].start, seg[n].len);
+                if (p->loss == ORC_QUANTILE || p->loss == ORC_MULTIQUANTILE) pred_leaf_quantile(tpred, n - 1, &nsum[C * n], p, grad, is + seg[n].start, seg[n].len);
                 else pred_leaf(tpred, n - 1, &nsum[C * n], p);
             }
         } else {
@@ -472,7 +486,7 @@ int orc_grow_tree(const orc_params *p, int64_t nobs, int32_t nfeats, const uint8
                     if (nr >= nl) { nxt[nnext++] = nL; nxt[nnext++] = nR; }
                     else { nxt[nnext++] = nR; nxt[nnext++] = nL; }
                 } else {
-                    if (p->loss == ORC_QUANTILE) pred_leaf_quantile(tpred, n - 1, &nsum[C * n], p, grad, is + seg[n].start, seg[n].len);
+                    if (p->loss == ORC_QUANTILE || p->loss == ORC_MULTIQUANTILE) pred_leaf_quantile(tpred, n - 1, &nsum[C * n], p, grad, is + seg[n].start, seg[n].len);
                 else pred_leaf(tpred, n - 1, &nsum[C * n], p);
                 }
             }
@@ -564,9 +578,9 @@ void orc_link(int32_t loss, int32_t K, int64_t nobs, float *pred) {
  * square root of the mse ratio, :53-54).  Unpinned, like the rest of this file: the reference's own tests compare
  * the logged metric with a metric recomputed from `predict` (test/metrics.jl:71-123), which tests/ repeats. */
 enum { ORC_METRIC_MSE = 0, ORC_METRIC_MAE = 1, ORC_METRIC_LOGLOSS = 2, ORC_METRIC_MLOGLOSS = 3, ORC_METRIC_GAUSSIAN_MLE = 4,
-       ORC_METRIC_POISSON = 5, ORC_METRIC_GAMMA = 6, ORC_METRIC_TWEEDIE = 7, ORC_METRIC_LOGISTIC_MLE = 8, ORC_METRIC_QUANTILE = 9 };
+       ORC_METRIC_POISSON = 5, ORC_METRIC_GAMMA = 6, ORC_METRIC_TWEEDIE = 7, ORC_METRIC_LOGISTIC_MLE = 8, ORC_METRIC_QUANTILE = 9, ORC_METRIC_MULTIQUANTILE = 10 };
 void orc_eval_metric(int32_t metric, int32_t K, int64_t nobs, const float *pred, const void *yv, int32_t ycols,
-                     const float *w, float *eval, double out[2], double alpha_d) {
+                     const float *w, float *eval, double out[2], double alpha_d, const double *alphas) {
     const float alpha = (float)alpha_d; /* `wmae` with the learner's alpha: src/metrics.jl:4-6, src/callback.jl:62 */
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < nobs; i++) {
@@ -577,6 +591,14 @@ void orc_eval_metric(int32_t metric, int32_t K, int64_t nobs, const float *pred,
             float isum = 0.0f;
             for (int k = 0; k < K; k++) isum += expf(p[k]);
             eval[i] = wi * (logf(isum) - p[yi - 1]);
+        } else if (metric == ORC_METRIC_MULTIQUANTILE) { /* src/metrics.jl:120-141 */
+            const float yi = ((const float *)yv)[i];
+            float acc = 0.0f;
+            for (int k = 0; k < K; k++) {
+                const float a = (float)alphas[k];
+                acc += a * fmaxf(yi - p[k], 0.0f) + (1.0f - a) * fmaxf(p[k] - yi, 0.0f);
+            }
+            eval[i] = wi * acc / (float)K;
         } else if (metric == ORC_METRIC_GAUSSIAN_MLE || metric == ORC_METRIC_LOGISTIC_MLE) {
             const float *y = (const float *)yv + (size_t)ycols * i;
             const int Y = K / 2;

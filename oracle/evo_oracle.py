@@ -23,7 +23,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_ref", "libevo_oracle.so")
 
 LOSSES = {"mse": 0, "logloss": 1, "mlogloss": 2, "gaussian_mle": 3, "poisson": 4, "gamma": 5, "tweedie": 6, "logistic_mle": 7,
-          "mae": 8, "cred_var": 9, "cred_std": 10, "quantile": 11}
+          "mae": 8, "cred_var": 9, "cred_std": 10, "quantile": 11, "multiquantile": 12}
 
 
 class OrcParams(C.Structure):
@@ -31,7 +31,7 @@ class OrcParams(C.Structure):
         ("loss", C.c_int32), ("K", C.c_int32), ("nbins", C.c_int32), ("max_depth", C.c_int32),
         ("bagging_size", C.c_int32), ("tree_type", C.c_int32),
         ("eta", C.c_double), ("lambda_", C.c_double), ("L2", C.c_double), ("gamma", C.c_double),
-        ("min_weight", C.c_double), ("alpha", C.c_double),
+        ("min_weight", C.c_double), ("alpha", C.c_double), ("alphas", C.c_double * 8),
     ]
 
 
@@ -83,10 +83,12 @@ class Params:
     gamma: float = 0.0
     min_weight: float = 1.0
     alpha: float = 0.5
+    alphas: tuple = (0.1, 0.5, 0.9)
 
     def c(self) -> OrcParams:
+        al = (C.c_double * 8)(*(list(self.alphas) + [0.0] * 8)[:8])
         return OrcParams(LOSSES[self.loss], self.K, self.nbins, self.max_depth, self.bagging_size, 0,
-                         self.eta, self.lambda_, self.L2, self.gamma, self.min_weight, self.alpha)
+                         self.eta, self.lambda_, self.L2, self.gamma, self.min_weight, self.alpha, al)
 
 
 @dataclass
@@ -222,12 +224,12 @@ def init_pred(p: Params, y: np.ndarray) -> np.ndarray:
 
 
 METRICS = {"mse": 0, "rmse": 0, "mae": 1, "logloss": 2, "mlogloss": 3, "gaussian_mle": 4, "poisson": 5, "gamma": 6, "tweedie": 7,
-           "logistic_mle": 8, "quantile": 9}
+           "logistic_mle": 8, "quantile": 9, "multiquantile": 10}
 IS_MAXIMISE = {"mse": False, "rmse": False, "mae": False, "logloss": False, "mlogloss": False, "gaussian_mle": True,
-               "poisson": False, "gamma": False, "tweedie": False, "logistic_mle": True, "quantile": False}
+               "poisson": False, "gamma": False, "tweedie": False, "logistic_mle": True, "quantile": False, "multiquantile": False}
 
 
-def eval_metric(metric: str, pred: np.ndarray, y: np.ndarray, w: np.ndarray | None = None, alpha: float = 0.5) -> float:
+def eval_metric(metric: str, pred: np.ndarray, y: np.ndarray, w: np.ndarray | None = None, alpha: float = 0.5, alphas=(0.1, 0.5, 0.9)) -> float:
     """Metric functions of src/metrics.jl:31-116 on link-space predictions `pred` [nobs, K] (float32)."""
     pred = np.ascontiguousarray(pred, np.float32)
     nobs, K = pred.shape
@@ -237,7 +239,7 @@ def eval_metric(metric: str, pred: np.ndarray, y: np.ndarray, w: np.ndarray | No
     ev = np.empty(nobs, np.float32)
     out = (C.c_double * 2)()
     lib().orc_eval_metric(C.c_int32(METRICS[metric]), C.c_int32(K), C.c_int64(nobs), _p(pred), _p(y), C.c_int32(ycols),
-                          _p(w32), _p(ev), out, C.c_double(alpha))
+                          _p(w32), _p(ev), out, C.c_double(alpha), (C.c_double * 8)(*(list(alphas) + [0.0] * 8)[:8]))
     v = out[0] / out[1]
     return float(np.sqrt(v)) if metric == "rmse" else float(v)
 

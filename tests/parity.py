@@ -20,7 +20,7 @@ RTOL = 1e-5
 def oracle_params(orc, params, K):
     return orc.Params(loss=params.loss, K=K, nbins=params.nbins, max_depth=params.max_depth,
                       bagging_size=params.bagging_size, eta=params.eta, lambda_=params.lambda_, L2=params.L2,
-                      gamma=params.gamma, min_weight=params.min_weight, alpha=params.alpha)
+                      gamma=params.gamma, min_weight=params.min_weight, alpha=params.alpha, alphas=tuple(params.alphas))
 
 
 def _gain_of(op, hist_node, nsum_node, feat0, bin1, numeric=True):
@@ -35,7 +35,7 @@ def _gain_of(op, hist_node, nsum_node, feat0, bin1, numeric=True):
         return g * g / max(eps, hh + op.lambda_ * w + op.L2) / 2.0
 
     wl, wr = sl[C - 1], nsum_node[C - 1] - sl[C - 1]
-    if op.loss in ("mae", "quantile"):           # src/split.jl:2, 119-130
+    if op.loss in ("mae", "quantile", "multiquantile"):   # src/split.jl:2, 119-130
         wp = nsum_node[C - 1]
         dl, dr = max(eps, 1 + op.lambda_ + op.L2 / wl), max(eps, 1 + op.lambda_ + op.L2 / wr)
         return sum(abs(sl[k] / wl - nsum_node[k] / wp) * wl / dl + abs((nsum_node[k] - sl[k]) / wr - nsum_node[k] / wp) * wr / dr
@@ -124,7 +124,7 @@ def lockstep_check(pkg, orc, params, x, y, rounds, w=None, feattypes=None, x_bin
         xb_cpu = orc.binarize(x, edges)
         assert np.array_equal(x_bin, xb_cpu), "device binarize differs from the oracle"
     nobs, nfeats = x_bin.shape
-    K, yd, ycols, mu, _, _ = init_target(params.loss, y, None)
+    K, yd, ycols, mu, _, _ = init_target(params.loss, y, None, params.alphas)
     op = oracle_params(orc, params, K)
     flags = _lib.FLAG_FULL_PARTITION | _lib.FLAG_KEEP_ALL_HIST | _lib.FLAG_TIMING
     cache = pkg.init_core_binned(params, x_bin, yd, ycols, K, mu, w, None, feattypes, device, flags)

@@ -132,6 +132,18 @@ def test_quantile_loss(pkg, orc, alpha, rowsample):
     assert s["splits"] > 10, s
 
 
+def test_multiquantile_loss(pkg, orc):
+    """One target, one output row per quantile (src/loss.jl:160-172, src/predict.jl:274-281): three selections per tree."""
+    x, y = make_regression(30_000, 8, seed=77)
+    p = pkg.EvoTreeRegressor(loss="multiquantile", alphas=(0.2, 0.5, 0.85), nrounds=3, max_depth=5, nbins=32, eta=0.5, L2=0.5)
+    assert p.metric == "multiquantile"
+    s = lockstep_check(pkg, orc, p, x, y, rounds=3)
+    assert s["splits"] > 10, s
+    m = pkg.fit(pkg.EvoTreeRegressor(loss="multiquantile", alphas=(0.2, 0.8), nrounds=30, max_depth=4, nbins=32, eta=0.3), x_train=x, y_train=y)
+    q = m(x)
+    assert q.shape == (30_000, 2) and abs(float(np.mean(y <= q[:, 0])) - 0.2) < 0.04 and abs(float(np.mean(y <= q[:, 1])) - 0.8) < 0.04
+
+
 def test_quantile_model_covers_its_quantile(pkg):
     rng = np.random.default_rng(6)
     x = rng.random((40_000, 5)).astype(np.float32)
