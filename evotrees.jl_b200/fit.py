@@ -26,7 +26,7 @@ def _invsoftplus(x):
 
 
 def init_target(loss: str, y_train: np.ndarray, offset, alphas=(0.1, 0.5, 0.9)):
-    """`_init_target` (src/init.jl:10-146) for the four losses of this path.
+    """`_init_target` (src/init.jl:10-146) for the losses of this path.
     Returns K, y (device dtype), ycols, mu float32 [K], target_levels, offset (link space)."""
     levels = None
     if loss in ("mse", "logloss", "poisson", "gamma", "tweedie", "mae", "cred_var", "cred_std", "quantile"):
