@@ -113,7 +113,7 @@ static void free_handle(evb_handle *h) {
     void *ptrs[] = {h->qs_cnt, h->qs_prefix, h->qs_rank, h->qs_gamma, h->gradq, h->d_gmax, h->d_qinv, h->xT, h->xC, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
                     h->js_d, h->seg_start, h->seg_cnt, h->gcnt, h->nleft, (h->gnleft != h->nleft) ? h->gnleft : nullptr, h->kind,
                     h->bslot, h->nsum, h->plan /* base of the tree block */, h->cum, h->slot_node, h->item_node, h->item_left,
-                    h->item_lprefix, h->item_bits, h->scan_tmp, h->hist, h->hcomp, h->scratch, h->fbest_gain, h->fbest_bin};
+                    h->item_lprefix, h->item_bits, h->scan_tmp, h->hist, h->hcomp, h->scratch, h->fbest_gain, h->fbest_bin, h->obl_gain, h->obl_best};
     for (void *p : ptrs) if (p) cudaFree(p);
     drop_graphs(h);
     for (int q = 0; q < 2; ++q) {
@@ -221,6 +221,10 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
     {
         const size_t lv = (size_t)evb_level_nodes(D > 1 ? D - 1 : 1) * nfeats;
         EVB_CUDA(dalloc(&h->fbest_gain, lv)); EVB_CUDA(dalloc(&h->fbest_bin, lv));
+        if (p->tree_type == 1) {
+            EVB_CUDA(dalloc(&h->obl_gain, ((size_t)evb_level_nodes(D > 1 ? D - 1 : 1) + 1) * nfeats * h->B));
+            EVB_CUDA(dalloc(&h->obl_best, (size_t)2));
+        }
     }
 
     const bool keep_all = (p->flags & EVB_FLAG_KEEP_ALL_HIST) != 0;
@@ -301,7 +305,8 @@ extern "C" int32_t evb_create(evb_handle **out, const evb_params *p, int64_t nob
         for (int k = 0; k < p->K; ++k)
             if (!(p->alphas[k] > 0.0 && p->alphas[k] < 1.0)) { evb_set_error("evb_create: alphas[%d] = %g outside (0, 1)", k, p->alphas[k]); return EVB_ERR_ARG; }
     }
-    if (p->bagging_size < 1 || p->tree_type != 0) { evb_set_error("evb_create: bagging_size must be >= 1 and tree_type binary"); return EVB_ERR_ARG; }
+    if (p->bagging_size < 1 || p->tree_type < 0 || p->tree_type > 1) { evb_set_error("evb_create: bagging_size must be >= 1 and tree_type 0 (binary) or 1 (oblivious)"); return EVB_ERR_ARG; }
+    if (p->tree_type == 1 && !(p->gamma >= 0.0)) { evb_set_error("evb_create: oblivious trees need gamma >= 0"); return EVB_ERR_ARG; }
     int ndev = 0;
     cudaError_t e = cudaGetDeviceCount(&ndev);
     if (e != cudaSuccess || ndev == 0) {
@@ -622,6 +627,7 @@ extern "C" int32_t evb_comm_ipc_export(evb_handle *h, uint8_t blob[256]) {
     if (!blob) { evb_set_error("null blob"); return EVB_ERR_ARG; }
     if (h->world < 2 || h->world > 8) { evb_set_error("evb_comm_ipc_export: needs evb_comm_init with 2..8 ranks first"); return EVB_ERR_ARG; }
     if (h->p2p || h->peer_cand[h->rank]) { evb_set_error("evb_comm_ipc_export: already exported"); return EVB_ERR_ARG; }
+    if (h->p.tree_type == 1) { evb_set_error("evb_comm_ipc_export: oblivious trees sum their histograms with NCCL (no feature-sharded scan)"); return EVB_ERR_ARG; }
     EVB_CUDA(cudaStreamSynchronize(h->st));
     const int D = h->D;
     // every scanned node keeps the summed histogram of the features this rank owns (children subtract from it)

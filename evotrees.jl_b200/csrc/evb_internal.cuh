@@ -112,6 +112,8 @@ struct evb_handle {
     int32_t *scan_tmp;     // block counts for the mask compaction
     double *fbest_gain;    // [nodes of a level][nfeats] per-feature best split of the scan
     int32_t *fbest_bin;
+    double *obl_gain;      // oblivious trees: [nodes of a level + 1][nfeats * B] gain of every candidate, last row = level totals
+    double *obl_best;      // [2] gain and candidate index (-1: none) of the level's shared split
     int *d_err;            // device error word
     int *h_err;            // pinned mirror
 

@@ -109,6 +109,9 @@ struct ScanArgs {
     uint32_t *t_packed;
     double *fbest_gain; // [nodes of the level][F] best gain of each feature
     int32_t *fbest_bin; // [nodes of the level][F] its bin (0-based) or -1
+    // oblivious trees (null otherwise): [nodes of the level + 1][F * B] gain of every candidate (0: not eligible),
+    // the last row receives the level totals; obl_best = {gain, candidate index or -1} of the shared split
+    double *obl_gain, *obl_best;
     const LevelPlan *plan;
     const int32_t *slot_node;
     // Row-sharded runs with peer access: every rank scans the feature slots f with f % world == rank (`hcomp` then
@@ -294,10 +297,13 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
             if (ch < nchk) {
                 const int b = ch * 32 + lane;
                 const double w_l = wl[ch], w_r = w_p - w_l;
-                if (b < b_max && w_l > a.min_weight && w_r > a.min_weight && ((okmask >> ch) & 1u)) {
-                    const double g = gacc[ch] - gain_p;
+                double g = 0.0;
+                const bool elig = b < b_max && w_l > a.min_weight && w_r > a.min_weight && ((okmask >> ch) & 1u);
+                if (elig) {
+                    g = gacc[ch] - gain_p;
                     if (g > lg) { lg = g; lb = b; }
                 }
+                if (a.obl_gain && b < B) a.obl_gain[((size_t)(n - m) * F + f) * B + b] = g; // update_gains!, fit-utils.jl:457-463
             }
         }
 #pragma unroll
@@ -334,6 +340,57 @@ __global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
     const int nb = a.slot_node[s];
     const double *src = a.hcomp + ((size_t)s * F + f) * C * B;
     scan_one<MAXCHK, OWN>(a, which ? nb ^ 1 : nb, which != 0, f, src, s_sum_all[wid], lane, fi == 0);
+}
+
+// Oblivious trees, stage 1b: one thread per candidate (feature slot, bin) adds the gains of the level's nodes in
+// ascending node order and drops the candidate if any node holds no positive gain for it (src/fit.jl:196-211; at
+// the root level the reference applies no mask, which changes nothing for gamma >= 0).
+__global__ void __launch_bounds__(128) k_obl_sum(ScanArgs a) {
+    const int m = 1 << (a.level - 1);
+    const size_t FB = (size_t)a.F * a.B;
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= FB) return;
+    double tot = 0.0;
+    bool ok = true;
+    for (int i = 0; i < m; ++i) {
+        const double g = a.obl_gain[(size_t)i * FB + e];
+        tot += g;
+        ok = ok && g > 0.0;
+    }
+    a.obl_gain[(size_t)m * FB + e] = ok ? tot : 0.0;
+}
+
+// Oblivious trees, stage 1c: first maximum of the level totals in (feature slot, bin) order (`findmax`,
+// src/fit.jl:213-217); it is the level's split if it exceeds gamma.  One CTA.
+__global__ void __launch_bounds__(1024) k_obl_pick(ScanArgs a) {
+    __shared__ double s_g[32];
+    __shared__ int s_e[32];
+    const int m = 1 << (a.level - 1);
+    const int FB = a.F * a.B;
+    const double *tot = a.obl_gain + (size_t)m * FB;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    double bg = a.gamma;
+    int be = 0x7fffffff;
+    for (int e = threadIdx.x; e < FB; e += blockDim.x) {
+        const double g = tot[e];
+        if (g > bg) { bg = g; be = e; }
+    }
+    auto red = [&]() {
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) {
+            const double og = __shfl_xor_sync(FULL, bg, d);
+            const int oe = __shfl_xor_sync(FULL, be, d);
+            if (oe != 0x7fffffff && (og > bg || (og == bg && oe < be))) { bg = og; be = oe; }
+        }
+    };
+    red();
+    if (lane == 0) { s_g[wid] = bg; s_e[wid] = be; }
+    __syncthreads();
+    if (wid == 0) {
+        bg = s_g[lane]; be = s_e[lane];
+        red();
+        if (lane == 0) { a.obl_best[0] = bg; a.obl_best[1] = be == 0x7fffffff ? -1.0 : (double)be; }
+    }
 }
 
 // Writes everything that follows from the split decision of node n: child sums, tree arrays, leaf values
@@ -398,6 +455,10 @@ __global__ void __launch_bounds__(256) k_scan_node(ScanArgs a) {
     double bg = a.gamma;
     int bs = 0x7fffffff, bb = -1;
     const int Fown = (F - a.rank + a.world - 1) / a.world;
+    if (a.obl_gain) { // oblivious: every node of the level takes the split k_obl_pick chose (src/fit.jl:213-225)
+        const double e = a.obl_best[1];
+        if (e >= 0.0) { bg = a.obl_best[0]; bs = (int)e / B; bb = (int)e % B; }
+    } else {
     for (int fi = lane; fi < Fown; fi += 32) {
         const int f = fi * a.world + a.rank;
         const double g = a.fbest_gain[(size_t)i * F + f];
@@ -409,6 +470,7 @@ __global__ void __launch_bounds__(256) k_scan_node(ScanArgs a) {
         const double og = __shfl_xor_sync(FULL, bg, d);
         const int os = __shfl_xor_sync(FULL, bs, d), ob = __shfl_xor_sync(FULL, bb, d);
         if (os != 0x7fffffff && (og > bg || (og == bg && os < bs))) { bg = og; bs = os; bb = ob; }
+    }
     }
     const bool has = bs != 0x7fffffff;
     if (has) {
@@ -786,6 +848,7 @@ int32_t evb_launch_scan(evb_handle *h, int level) {
     a.loss = h->p.loss; a.neb = -h->p.eta / (double)h->p.bagging_size;
     a.lambda = h->p.lambda; a.L2 = h->p.L2; a.gamma = h->p.gamma; a.min_weight = h->p.min_weight;
     a.fbest_gain = h->fbest_gain; a.fbest_bin = h->fbest_bin;
+    a.obl_gain = h->obl_gain; a.obl_best = h->obl_best;
     a.plan = h->plan + level; a.slot_node = h->slot_node;
     const bool p2p = h->p2p && h->world > 1;
     a.world = p2p ? h->world : 1; a.rank = p2p ? h->rank : 0;
@@ -816,6 +879,12 @@ int32_t evb_launch_scan(evb_handle *h, int level) {
         else { if (own) k_scan_feat<8, true><<<grid, 256, 0, h->st>>>(a); else k_scan_feat<8, false><<<grid, 256, 0, h->st>>>(a); }
     }
     evb_toc(h, EVB_T_SCAN);
+    if (h->obl_gain && level < h->D) {
+        evb_tic(h, EVB_T_SCAN);
+        k_obl_sum<<<(h->F * h->B + 127) / 128, 128, 0, h->st>>>(a);
+        k_obl_pick<<<1, 1024, 0, h->st>>>(a);
+        evb_toc(h, EVB_T_SCAN);
+    }
     evb_tic(h, EVB_T_SCAN);
     k_scan_node<<<(m + 7) / 8, 256, 0, h->st>>>(a);
     evb_toc(h, EVB_T_SCAN);

@@ -159,8 +159,8 @@ class Cache:
 
 
 def make_params(params: EvoTypes, K: int, device: int, flags: int = 0) -> _lib.EvbParams:
-    return _lib.EvbParams(_lib.LOSS_CODES[params.loss], K, params.nbins, params.max_depth, params.bagging_size, 0,
-                          params.eta, params.lambda_, params.L2, params.gamma, params.min_weight, device, flags, params.alpha,
+    return _lib.EvbParams(_lib.LOSS_CODES[params.loss], K, params.nbins, params.max_depth, params.bagging_size,
+                          1 if params.tree_type == "oblivious" else 0, params.eta, params.lambda_, params.L2, params.gamma, params.min_weight, device, flags, params.alpha,
                           (C.c_double * 8)(*(list(params.alphas) + [0.0] * 8)[:8]))
 
 

@@ -59,7 +59,7 @@ EvoTrees.post_fit_gc(::Type{<:GPU}) = nothing              # the handle outlives
 
 # replaces ext/EvoTreesKernelAbstractionsExt/init.jl:1-151
 function EvoTrees.init_core(params::EvoTypes, ::Type{<:GPU}, data, feature_names, y_train, w, offset)
-    params.tree_type == :binary || error("EvoTreesB200Ext builds binary trees only")
+    params.tree_type in (:binary, :oblivious) || error("EvoTreesB200Ext: tree_type must be :binary or :oblivious")
     haskey(LOSS_CODE, params.loss) || error("EvoTreesB200Ext supports losses $(collect(keys(LOSS_CODE)))")
     rng = Xoshiro(params.seed)
     edges, featbins, feattypes = get_edges(data; feature_names, nbins=params.nbins, rng)   # same RNG stream as the CPU path
@@ -76,7 +76,7 @@ function EvoTrees.init_core(params::EvoTypes, ::Type{<:GPU}, data, feature_names
     hasproperty(params, :monotone_constraints) && for (k, v) in params.monotone_constraints
         monotone[k] = v
     end
-    p = Ref(EvbParams(LOSS_CODE[params.loss], K, params.nbins, params.max_depth, params.bagging_size, 0,
+    p = Ref(EvbParams(LOSS_CODE[params.loss], K, params.nbins, params.max_depth, params.bagging_size, params.tree_type == :oblivious ? 1 : 0,
         params.eta, params.lambda, params.L2, params.gamma, params.min_weight, 0, 0,
         hasproperty(params, :alpha) ? Float64(params.alpha) : 0.5,
         ntuple(k -> hasproperty(params, :alphas) && k <= length(params.alphas) ? Float64(params.alphas[k]) : 0.0, 8)))

@@ -82,8 +82,9 @@ class EvoTypes:
             self.alphas = tuple(float(a) for a in self.alphas)
             if not 1 <= len(self.alphas) <= 8 or any(not 0.0 < a < 1.0 for a in self.alphas):
                 raise ValueError("`alphas` must hold 1 to 8 values strictly between 0 and 1")
-        if self.tree_type != "binary":
-            raise ValueError("Invalid input for `tree_type` parameter: only `binary` trees are built by this device path")
+        self.tree_type = str(self.tree_type).lstrip(":")
+        if self.tree_type not in ("binary", "oblivious"):   # src/learners.jl: tree_type ∈ (:binary, :oblivious)
+            raise ValueError("Invalid input for `tree_type` parameter: must be `binary` or `oblivious`")
         if self.device not in ("gpu", "cuda"):
             raise ValueError("device must be :gpu / :cuda: this package has no CPU path")
 

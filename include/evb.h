@@ -70,7 +70,7 @@ typedef struct {
     int32_t nbins;         /* 2..255 */
     int32_t max_depth;     /* 1..15 */
     int32_t bagging_size;  /* >= 1 */
-    int32_t tree_type;     /* 0 = binary (the only one built) */
+    int32_t tree_type;     /* 0 = binary, 1 = oblivious (one split per depth, src/fit.jl:147-263) */
     double eta, lambda, L2, gamma, min_weight;
     int32_t device;        /* CUDA device ordinal of this shard */
     uint32_t flags;

@@ -332,7 +332,8 @@ int orc_grow_tree(const orc_params *p, int64_t nobs, int32_t nfeats, const uint8
     int *nxt = (int *)malloc(sizeof(int) * (nn + 1));
     memcpy(is, is_in, sizeof(uint32_t) * nis);
     const double eps = DBL_EPSILON;
-
+    /* tree_type 1 = oblivious: gains of every node of the widest split level + the table they are added into */
+    double *obl_gains = p->tree_type == 1 ? (double *)malloc(sizeof(double) * ((size_t)(nn + 1) / 2 + 1) * njs * B) : NULL;
 
     /* root sums: Float64 sequential sum of grad over `is`  (src/fit.jl:66) */
     seg[1].start = 0; seg[1].len = nis;
@@ -424,6 +425,9 @@ int orc_grow_tree(const orc_params *p, int64_t nobs, int32_t nfeats, const uint8
                 double sl[32], sr[32];
                 double gain_p = node_gain(p->loss, s, C, p->lambda, p->L2, eps);
                 double w_p = s[C - 1];
+                /* oblivious: update_gains! keeps every eligible gain, 0 elsewhere (fit-utils.jl:457-463) */
+                double *gn = obl_gains ? obl_gains + (size_t)a * njs * B : NULL;
+                if (gn) memset(gn, 0, sizeof(double) * njs * B);
                 for (int jj = 0; jj < njs; jj++) {
                     int j = (int)js[jj] - 1;
                     int constraint = monotone ? monotone[j] : 0;
@@ -445,7 +449,8 @@ int orc_grow_tree(const orc_params *p, int64_t nobs, int32_t nfeats, const uint8
                             }
                             if (ok) {
                                 double g = split_gain(p->loss, s, sl, C, w_l, w_r, p->lambda, p->L2, eps) - gain_p;
-                                if (g > best_gain) { best_gain = g; best_feat = j + 1; best_bin = bin; }
+                                if (gn) gn[(size_t)jj * B + (bin - 1)] = g;
+                                else if (g > best_gain) { best_gain = g; best_feat = j + 1; best_bin = bin; }
                             }
                         }
                     }
@@ -457,7 +462,31 @@ int orc_grow_tree(const orc_params *p, int64_t nobs, int32_t nfeats, const uint8
                     split[n - 1] = 1;
                 }
             }
-            /* split_set! / _child_sums! / next level (src/fit.jl:100-137) */
+            if (obl_gains) {
+                /* one split for the whole depth (grow_otree!, src/fit.jl:196-225): the nodes' gains are added in
+                   ascending node order into a zeroed table, a candidate that is not eligible (gain <= 0) in any
+                   node is dropped, the first maximum in (feature, bin) order wins if it exceeds gamma */
+                const size_t NG = (size_t)njs * B;
+                double *tot = obl_gains + (size_t)ncur * NG;
+                if (depth == 1) memcpy(tot, obl_gains, sizeof(double) * NG);
+                else {
+                    for (size_t e = 0; e < NG; e++) tot[e] = 0.0;
+                    for (int a = 0; a < ncur; a++) for (size_t e = 0; e < NG; e++) tot[e] += obl_gains[(size_t)a * NG + e];
+                    for (int a = 0; a < ncur; a++) for (size_t e = 0; e < NG; e++) tot[e] *= obl_gains[(size_t)a * NG + e] > 0.0 ? 1.0 : 0.0;
+                }
+                size_t be = 0;
+                for (size_t e = 1; e < NG; e++) if (tot[e] > tot[be]) be = e;
+                if (tot[be] > p->gamma) {
+                    for (int a = 0; a < ncur; a++) {
+                        int n = cur[a];
+                        gain[n - 1] = (float)tot[be];
+                        cond_bin[n - 1] = (uint8_t)(be % B + 1);
+                        feat[n - 1] = (int64_t)js[be / B];
+                        split[n - 1] = 1;
+                    }
+                }
+            }
+            /* split_set! / _child_sums! / next level (src/fit.jl:100-137, 226-253) */
             for (int a = 0; a < ncur; a++) {
                 int n = cur[a];
                 if (split[n - 1]) {
@@ -506,7 +535,7 @@ int orc_grow_tree(const orc_params *p, int64_t nobs, int32_t nfeats, const uint8
     }
     if (nsum_out) memcpy(nsum_out, nsum + C, sizeof(double) * C * nn);
     if (!hist_out) free(hist);
-    free(nsum); free(seg); free(is); free(tmp); free(cur); free(nxt);
+    free(nsum); free(seg); free(is); free(tmp); free(cur); free(nxt); free(obl_gains);
     return 0;
 }
 

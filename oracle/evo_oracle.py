@@ -84,10 +84,11 @@ class Params:
     min_weight: float = 1.0
     alpha: float = 0.5
     alphas: tuple = (0.1, 0.5, 0.9)
+    tree_type: int = 0   # 0 binary, 1 oblivious (grow_otree!, src/fit.jl:147-263)
 
     def c(self) -> OrcParams:
         al = (C.c_double * 8)(*(list(self.alphas) + [0.0] * 8)[:8])
-        return OrcParams(LOSSES[self.loss], self.K, self.nbins, self.max_depth, self.bagging_size, 0,
+        return OrcParams(LOSSES[self.loss], self.K, self.nbins, self.max_depth, self.bagging_size, self.tree_type,
                          self.eta, self.lambda_, self.L2, self.gamma, self.min_weight, self.alpha, al)
 
 

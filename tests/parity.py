@@ -20,7 +20,8 @@ RTOL = 1e-5
 def oracle_params(orc, params, K):
     return orc.Params(loss=params.loss, K=K, nbins=params.nbins, max_depth=params.max_depth,
                       bagging_size=params.bagging_size, eta=params.eta, lambda_=params.lambda_, L2=params.L2,
-                      gamma=params.gamma, min_weight=params.min_weight, alpha=params.alpha, alphas=tuple(params.alphas))
+                      gamma=params.gamma, min_weight=params.min_weight, alpha=params.alpha, alphas=tuple(params.alphas),
+                      tree_type=1 if getattr(params, "tree_type", "binary") == "oblivious" else 0)
 
 
 def _gain_of(op, hist_node, nsum_node, feat0, bin1, numeric=True):
@@ -79,6 +80,7 @@ def compare_tree(op, tg, to, ohist, onsum, feattypes=None):
                 np.testing.assert_allclose(tg.pred[n - 1], to.pred[n - 1], rtol=RTOL, atol=1e-6, err_msg=f"leaf {n}")
             continue
         # structural difference: only acceptable as a near tie by the oracle's own numbers
+        assert op.tree_type == 0, f"oblivious tree differs at node {n} (the level's split is a sum over nodes: no per-node tie rule)"
         assert ohist is not None, f"tree differs at node {n} and no oracle histogram to arbitrate"
         best = float(to.gain[n - 1]) if so else op.gamma
         if sg:

@@ -47,7 +47,7 @@ def test_learner_defaults_and_validation(pkg):
     assert pkg.EvoTreeClassifier().loss == "mlogloss"
     assert pkg.EvoTreeRegressor(loss="linear").loss == "mse"
     for bad in (dict(nbins=1), dict(nbins=256), dict(max_depth=0), dict(rowsample=0.0), dict(colsample=1.5), dict(eta=-1),
-                dict(loss="nope"), dict(tree_type="oblivious"), dict(device="cpu"), dict(gamma=-1.0)):
+                dict(loss="nope"), dict(tree_type="ternary"), dict(device="cpu"), dict(gamma=-1.0)):
         with pytest.raises(ValueError):
             pkg.EvoTreeRegressor(**bad)
 

@@ -407,3 +407,43 @@ def test_quantile_leaves_by_hand(orc):
         assert t.split[0] and t.cond_bin[0] == 1
         assert np.isclose(t.pred[1, 0], np.quantile(d[:5].astype(np.float64), alpha), rtol=1e-6)
         assert np.isclose(t.pred[2, 0], np.quantile(d[5:].astype(np.float64), alpha), rtol=1e-6)
+
+
+def test_oblivious_tree_levels_by_hand(orc):
+    """grow_otree! (src/fit.jl:147-263): one (feature, bin) per depth = first maximum of the gains summed over the
+    depth's nodes, candidates that are not eligible or not positive in any node dropped; checked against a numpy
+    restatement on the oracle's own histograms.  test/oblivious.jl:28-146 pins the same learner by loss thresholds."""
+    from tests.parity import _gain_of
+    b, xb, y, (t, nidx, hist, nsum) = _fit_oracle(orc, depth=4, rounds=3, tree_type=1, min_weight=20.0)
+    p = b.p
+    B, F = p.nbins, xb.shape[1]
+    assert np.array_equal(orc.leaf_idx(xb, t), nidx)
+    for d in range(1, p.max_depth):
+        nodes = list(range(2 ** (d - 1), 2 ** d))
+        if not t.split[nodes[0] - 1]:
+            assert not any(t.split[n - 1] for n in range(nodes[0], t.split.size + 1))
+            break
+        assert all(t.split[n - 1] for n in nodes)
+        assert len({(int(t.feat[n - 1]), int(t.cond_bin[n - 1])) for n in nodes}) == 1
+        tot = np.zeros((F, B))
+        ok = np.ones((F, B), bool)
+        for n in nodes:
+            for j in range(F):
+                wl = np.cumsum(hist[n - 1, j, :, 2])
+                for bin1 in range(1, B):
+                    g = 0.0
+                    if wl[bin1 - 1] > p.min_weight and nsum[n - 1, 2] - wl[bin1 - 1] > p.min_weight:
+                        g = _gain_of(p, hist[n - 1], nsum[n - 1], j, bin1)
+                    tot[j, bin1 - 1] += g
+                    ok[j, bin1 - 1] &= g > 0
+        tot = np.where(ok, tot, 0.0)
+        j, bi = np.unravel_index(np.argmax(tot), tot.shape)       # row-major over (feature, bin) = the reference's order
+        assert (int(t.feat[nodes[0] - 1]), int(t.cond_bin[nodes[0] - 1])) == (j + 1, bi + 1)
+        np.testing.assert_allclose(t.gain[nodes[0] - 1], tot[j, bi], rtol=1e-6)
+    assert t.split[0] and t.split[1] and t.split[2]               # the data supports at least two shared levels
+
+
+def test_oblivious_training_beats_the_bias_model(orc):
+    b, xb, y, _ = _fit_oracle(orc, depth=5, rounds=40, nbins=32, tree_type=1)   # test/oblivious.jl: eval loss thresholds
+    pred = b.pred[:, 0]
+    assert np.mean((pred - y) ** 2) < 0.25 * np.mean((y.mean() - y) ** 2)

@@ -248,3 +248,68 @@ def test_softmax_many_classes(pkg, orc):
     p = pkg.EvoTreeClassifier(nrounds=2, max_depth=5, nbins=32, eta=0.3)
     s = lockstep_check(pkg, orc, p, x, y, rounds=2)
     assert s["splits"] > 20, s
+
+
+# ---- oblivious trees (tree_type = :oblivious, grow_otree!, src/fit.jl:147-263; test/oblivious.jl) -----------------
+def test_oblivious_mse_lockstep(pkg, orc):
+    """One (feature, bin) per depth: the same trees as the oracle, node for node (fixed-point histogram kernel)."""
+    x, y = make_regression(60_000, 12, seed=21, dtype=np.float64)
+    p = pkg.EvoTreeRegressor(loss="mse", nrounds=4, max_depth=6, nbins=32, eta=0.2, tree_type="oblivious")
+    s = lockstep_check(pkg, orc, p, x, y, rounds=4)
+    assert s["splits"] >= 4 * 31 and s["diverged"] == 0, s
+
+
+def test_oblivious_sampling_and_weights(pkg, orc):
+    x, y = make_regression(50_000, 40, seed=22)
+    w = np.random.default_rng(3).uniform(0.5, 2.0, size=x.shape[0]).astype(np.float32)
+    p = pkg.EvoTreeRegressor(loss="mse", nrounds=3, max_depth=5, nbins=64, eta=0.1, rowsample=0.6, colsample=0.5,
+                             tree_type="oblivious", min_weight=10.0)
+    s = lockstep_check(pkg, orc, p, x, y, rounds=3, w=w)
+    assert s["splits"] >= 3 * 7 and s["diverged"] == 0, s
+
+
+def test_oblivious_logloss_monotone(pkg, orc):
+    x, y = make_regression(40_000, 10, seed=23)
+    yb = (y > np.median(y)).astype(np.float32)
+    p = pkg.EvoTreeRegressor(loss="logloss", nrounds=3, max_depth=5, nbins=32, eta=0.3, tree_type="oblivious",
+                             monotone_constraints={1: 1, 2: -1})
+    s = lockstep_check(pkg, orc, p, x, yb, rounds=3)
+    assert s["diverged"] == 0, s
+
+
+def test_oblivious_softmax_and_mae(pkg, orc):
+    x, yc = _softmax_data(40_000, 12, 3)
+    s = lockstep_check(pkg, orc, pkg.EvoTreeClassifier(nrounds=2, max_depth=5, nbins=32, eta=0.2, tree_type="oblivious"), x, yc, rounds=2)
+    assert s["splits"] >= 2 * 7 and s["diverged"] == 0, s
+    x, y = make_regression(30_000, 8, seed=24)
+    s = lockstep_check(pkg, orc, pkg.EvoTreeRegressor(loss="mae", nrounds=2, max_depth=4, nbins=32, tree_type="oblivious"), x, y, rounds=2)
+    assert s["diverged"] == 0, s
+
+
+def test_oblivious_fit_through_the_graph_path(pkg, orc):
+    """`fit` (CUDA-graph replay, pipelined trees): every depth of every tree shares one split; same trees as the
+    oracle's booster on the same bins; the model beats the bias model (test/oblivious.jl thresholds)."""
+    x, y = make_regression(50_000, 10, seed=25)
+    p = pkg.EvoTreeRegressor(loss="mse", nrounds=30, max_depth=5, nbins=32, eta=0.2, tree_type="oblivious")
+    m = pkg.fit(p, x_train=x, y_train=y)
+    assert len(m.trees) == 31
+    for t in m.trees[1:]:
+        for d in range(1, 5):
+            nodes = range(2 ** (d - 1), 2 ** d)
+            if t.split[2 ** (d - 1) - 1]:
+                assert len({(int(t.feat[n - 1]), int(t.cond_bin[n - 1])) for n in nodes}) == 1
+            else:
+                assert not any(t.split[n - 1] for n in nodes)
+    pred = np.asarray(m(x)).reshape(x.shape[0], -1)[:, 0]
+    assert np.mean((pred - y) ** 2) < 0.25 * np.var(y)
+    rng = np.random.default_rng(p.seed)
+    edges, _, _ = pkg.get_edges(x, p.nbins, rng)
+    xb = orc.binarize(x, edges)
+    b = orc.Booster(orc.Params(loss="mse", nbins=32, max_depth=5, eta=0.2, tree_type=1), xb, y.astype(np.float32))
+    js = np.arange(1, 11, dtype=np.uint32)
+    same = 0
+    for r in range(5):
+        to = b.round(None, 255, js)[0]
+        tg = m.trees[r + 1]
+        same += int(np.array_equal(to.feat, tg.feat) and np.array_equal(to.cond_bin, tg.cond_bin))
+    assert same == 5
