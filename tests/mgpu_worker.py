@@ -26,14 +26,17 @@ def main(out_path):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     comm = Comm(dist, torch.device("cuda", local))
     results = {}
-    for case, (loss, n, f, depth, nbins, rowsample) in enumerate([("mse", 60_001, 20, 7, 32, 1.0), ("mse", 40_000, 9, 5, 16, 0.6),
-                                                                   ("gaussian_mle", 30_000, 12, 5, 32, 1.0), ("mlogloss", 30_000, 8, 5, 16, 1.0)]):
+    # the last case grows oblivious trees: the peer-access export declines and all ranks stay on the NCCL sums
+    for case, (loss, n, f, depth, nbins, rowsample, tree_type) in enumerate([
+            ("mse", 60_001, 20, 7, 32, 1.0, "binary"), ("mse", 40_000, 9, 5, 16, 0.6, "binary"),
+            ("gaussian_mle", 30_000, 12, 5, 32, 1.0, "binary"), ("mlogloss", 30_000, 8, 5, 16, 1.0, "binary"),
+            ("mse", 50_000, 10, 5, 32, 1.0, "oblivious")]):
         rng = np.random.default_rng(100 + case)
         x = rng.random((n, f)).astype(np.float32)
         raw = x @ rng.normal(size=f) + 0.2 * rng.normal(size=n)
         y = raw.astype(np.float32) if loss != "mlogloss" else np.digitize(raw, np.quantile(raw, [0.3, 0.7])).astype(np.int64)
         learner = {"mlogloss": pkg.EvoTreeClassifier, "gaussian_mle": pkg.EvoTreeMLE}.get(loss, pkg.EvoTreeRegressor)
-        params = learner(loss=loss, nrounds=3, max_depth=depth, nbins=nbins, eta=0.3, rowsample=rowsample)
+        params = learner(loss=loss, nrounds=3, max_depth=depth, nbins=nbins, eta=0.3, rowsample=rowsample, tree_type=tree_type)
         edges = orc.get_edges(x, nbins, np.random.default_rng(1))
         x_bin = orc.binarize(x, edges)
         K, yd, ycols, mu, _, _ = init_target(loss, y, None)
