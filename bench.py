@@ -43,6 +43,7 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="headline_10Mx100_d11", choices=list(WORKLOADS))
     ap.add_argument("--rows", type=int, default=0, help="override the number of rows (for quick checks)")
+    ap.add_argument("--tree-type", default="binary", choices=["binary", "oblivious"], help="not the headline: side measurements")
     ap.add_argument("--cpu-rounds", type=int, default=2, help="rounds of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -107,10 +108,10 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_baseline(x_bin, y, depth, nbins, eta, rounds):
+def cpu_baseline(x_bin, y, depth, nbins, eta, rounds, tree_type=0):
     """Times the oracle (C + OpenMP restatement of the reference's CPU path) on the full matrix for a few rounds."""
     from oracle import evo_oracle as orc
-    p = orc.Params(loss="mse", K=1, nbins=nbins, max_depth=depth, eta=eta)
+    p = orc.Params(loss="mse", K=1, nbins=nbins, max_depth=depth, eta=eta, tree_type=tree_type)
     b = orc.Booster(p, x_bin, y, use_x_bin_T=True)
     js = np.arange(1, x_bin.shape[1] + 1, dtype=np.uint32)
     b.round(None, 255, js)  # warm-up round (page faults, thread pool)
@@ -135,7 +136,7 @@ def run_reference(args):
     edges = orc.get_edges(x[: min(rows, 1000 * nbins)], nbins, rng)
     x_bin = orc.binarize(x, edges)
     del x
-    p = orc.Params(loss="mse", K=1, nbins=nbins, max_depth=depth, eta=eta)
+    p = orc.Params(loss="mse", K=1, nbins=nbins, max_depth=depth, eta=eta, tree_type=int(args.tree_type == "oblivious"))
     b = orc.Booster(p, x_bin, y, use_x_bin_T=True)
     js = np.arange(1, feats + 1, dtype=np.uint32)
     steps = max(1, min(args.steps, 8))      # bounded sample: every step is one full boosting round on all rows
@@ -184,7 +185,7 @@ def main():
     rows, feats, depth, nbins, eta, rowsample, colsample = WORKLOADS[args.workload]
     rows = args.rows or rows
     params = pkg.EvoTreeRegressor(loss="mse", nrounds=ROUNDS_PER_JOB, max_depth=depth, nbins=nbins, eta=eta,
-                                  rowsample=rowsample, colsample=colsample)
+                                  rowsample=rowsample, colsample=colsample, tree_type=args.tree_type)
     x, y = make_shard(rows, feats, rank, world)
     nloc = x.shape[0]
 
@@ -331,7 +332,7 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32 gradients, exact 32-bit fixed-point partial sums in shared memory, f64 histograms and split scan", "data": "synthetic",
-            "config": {"workload": args.workload, "rows": rows, "feats": feats, "max_depth": depth, "nbins": nbins, "loss": "mse",
+            "config": {"workload": args.workload, "rows": rows, "feats": feats, "max_depth": depth, "nbins": nbins, "loss": "mse", "tree_type": args.tree_type,
                        "eta": eta, "rowsample": rowsample, "colsample": colsample, "rows_per_gpu": nloc,
                        "l2_policy": "inputs larger than L2 (x_bin shard %.0f MB)" % (nloc * 128 / 1e6)},
             "roofline": {"bound": "hbm", "kernel": "k_histq", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -353,7 +354,7 @@ def main():
         }
         if not args.no_cpu_baseline and world == 1:
             try:
-                dt, cores = cpu_baseline(np.asfortranarray(xb_host), y, depth, nbins, eta, args.cpu_rounds)
+                dt, cores = cpu_baseline(np.asfortranarray(xb_host), y, depth, nbins, eta, args.cpu_rounds, int(args.tree_type == "oblivious"))
                 out["cpu_baseline"] = {"value": dt * ROUNDS_PER_JOB, "unit": "s", "cores": cores, "kind": "port",
                                        "sample": f"{args.cpu_rounds} full boosting rounds on all {rows} rows (of {ROUNDS_PER_JOB}), scaled linearly"}
             except Exception as e:  # the baseline is reported, never required
