@@ -438,7 +438,9 @@ extern "C" int32_t evb_grow_tree_begin(evb_handle *h, const uint8_t *row_mask, u
     // Sharded runs over NCCL stay on direct launches: a run that captured the NCCL collectives into the graph did not
     // complete on 2 GPUs, so collectives are never captured.  With peer access the exchange is made of this
     // library's own kernels (the barrier counts on the device), which replay like any other.
-    if (h->use_graphs && !h->timing && (h->world == 1 || h->p2p)) {
+    // (The quantile losses add their leaves' digit counts with NCCL on every sharded path.)
+    const bool quantile_leaves = h->p.loss == EVB_QUANTILE || h->p.loss == EVB_MULTIQUANTILE;
+    if (h->use_graphs && !h->timing && (h->world == 1 || (h->p2p && !quantile_leaves))) {
         if (!h->graph[key] && h->tree_seq >= 1) { // the very first tree of a handle always runs directly
             int64_t before[EVB_NTIMERS];
             memcpy(before, h->tm.launches, sizeof(before));

@@ -811,6 +811,12 @@ int32_t evb_launch_quantile_leaves(evb_handle *h, bool use_mask, uint8_t mask_co
         for (int pass = 0; pass < 4; ++pass) {
             a.pass = pass;
             k_qsel_count<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(a);
+            if (h->world > 1) {
+                // row-sharded: the digit counts of all ranks are added, so every rank walks to the same order
+                // statistics of the leaf's rows on all ranks (integer sums: the same leaves as on one GPU)
+                int32_t *c32 = reinterpret_cast<int32_t *>(h->qs_cnt);
+                EVB_CHECK(evb_nccl_allreduce_i32(h, c32, c32, (size_t)2 * (h->nn + 1) * 256));
+            }
             k_qsel_pick<<<(h->nn + 8) / 8, 256, 0, h->st>>>(a);
         }
         k_qsel_leaf<<<(h->nn + 256) / 256, 256, 0, h->st>>>(a);

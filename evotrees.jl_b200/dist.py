@@ -54,7 +54,7 @@ class Comm:
         self.dist.all_reduce(t)
         return t.cpu().numpy()
 
-    def allreduce_bias(self, loss: str, y: np.ndarray, mu_local: np.ndarray, K: int) -> np.ndarray:
+    def allreduce_bias(self, loss: str, y: np.ndarray, mu_local: np.ndarray, K: int, alphas=None) -> np.ndarray:
         """Initial bias of the whole data set from per-shard sufficient statistics
         (same formulas as `_init_target`, src/init.jl:19-145)."""
         from .fit import _invsoftplus, _logit
@@ -78,6 +78,15 @@ class Comm:
             f = np.sqrt(3.0) / np.pi if loss == "logistic_mle" else 1.0
             mu[1::2] = [_invsoftplus(float(np.sqrt(v)) * f) for v in var]
             return mu
+        if loss == "multiquantile":
+            # quantiles of the whole target (src/init.jl:99-103): the shards' targets are gathered on every rank
+            # (4 bytes per row, once per fit), padded to the longest shard
+            sizes = self.allgather_host(np.array([y.shape[0]], np.int64))[:, 0]
+            pad = np.full(int(sizes.max()), np.nan, np.float32)
+            pad[: y.shape[0]] = np.asarray(y, np.float32).reshape(-1)
+            allv = self.allgather_host(pad)
+            yy = np.concatenate([allv[q, : int(sizes[q])] for q in range(self.world)]).astype(np.float64)
+            return np.quantile(yy, list(alphas)).astype(np.float32)
         raise ValueError(loss)
 
     def attach(self, cache) -> None:

@@ -210,7 +210,7 @@ def init_core(params: EvoTypes, x_train: np.ndarray, y_train, w_train=None, offs
     offset = None if offset_train is None else np.array(offset_train, np.float32, copy=True).reshape(nobs, -1)
     K, y, ycols, mu, levels, offset = init_target(params.loss, y_train, offset, params.alphas)
     if comm is not None:
-        edges, mu = comm.broadcast_host(edges), comm.allreduce_bias(params.loss, y, mu, K)
+        edges, mu = comm.broadcast_host(edges), comm.allreduce_bias(params.loss, y, mu, K, params.alphas)
     x_bin = binarize(x_train, edges, device)
     pred0 = None
     if offset is not None:
@@ -343,7 +343,7 @@ def eval_levelcode(y_eval, target_levels) -> np.ndarray:
 
 
 # losses whose bias the sharded path derives from per-shard sums (`Comm.allreduce_bias`) besides the four original ones
-allreduce_bias_losses = ("poisson", "gamma", "tweedie", "logistic_mle", "mae", "cred_var", "cred_std", "quantile")
+allreduce_bias_losses = ("poisson", "gamma", "tweedie", "logistic_mle", "mae", "cred_var", "cred_std", "quantile", "multiquantile")
 
 
 def metric_from_sums(metric: str, sums, comm=None) -> float:

@@ -26,11 +26,13 @@ def main(out_path):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     comm = Comm(dist, torch.device("cuda", local))
     results = {}
-    # the last case grows oblivious trees: the peer-access export declines and all ranks stay on the NCCL sums
+    # case 4 grows oblivious trees: the peer-access export declines and all ranks stay on the NCCL sums
     for case, (loss, n, f, depth, nbins, rowsample, tree_type) in enumerate([
             ("mse", 60_001, 20, 7, 32, 1.0, "binary"), ("mse", 40_000, 9, 5, 16, 0.6, "binary"),
             ("gaussian_mle", 30_000, 12, 5, 32, 1.0, "binary"), ("mlogloss", 30_000, 8, 5, 16, 1.0, "binary"),
-            ("mse", 50_000, 10, 5, 32, 1.0, "oblivious")]):
+            ("mse", 50_000, 10, 5, 32, 1.0, "oblivious"),
+            # quantile leaves: the ranks add the digit counts of the selection, so the leaves are those of one GPU
+            ("quantile", 40_001, 8, 4, 32, 0.7, "binary")]):
         rng = np.random.default_rng(100 + case)
         x = rng.random((n, f)).astype(np.float32)
         raw = x @ rng.normal(size=f) + 0.2 * rng.normal(size=n)

@@ -51,8 +51,8 @@ def _worker(rank, world, port, tmp):
     out["eval_mse"] = np.array([metric_from_sums("mse", sums, comm), metric_from_sums("rmse", sums, comm)])
     for loss in allreduce_bias_losses:
         yy = np.abs(ys) + 0.1
-        K, yd, _, mu_local, _, _ = init_target(loss, yy, None)
-        out["mu_" + loss] = comm.allreduce_bias(loss, yd, mu_local, K)
+        K, yd, _, mu_local, _, _ = init_target(loss, yy, None, (0.1, 0.5, 0.9))
+        out["mu_" + loss] = comm.allreduce_bias(loss, yd, mu_local, K, (0.1, 0.5, 0.9))
     np.savez(os.path.join(tmp, f"r{rank}.npz"), **out)
     dist.barrier()
     dist.destroy_process_group()
@@ -89,5 +89,5 @@ def test_two_rank_host_plumbing(tmp_path, orc, pkg):
     np.testing.assert_allclose(r0["eval_mse"], [mse, np.sqrt(mse)], rtol=1e-5)
     from evotrees_b200.fit import allreduce_bias_losses
     for loss in allreduce_bias_losses:   # the bias of the added losses from per-shard statistics == the bias of the whole
-        K, yd, _, mu, _, _ = init_target(loss, np.abs(y) + 0.1, None)
+        K, yd, _, mu, _, _ = init_target(loss, np.abs(y) + 0.1, None, (0.1, 0.5, 0.9))
         np.testing.assert_allclose(r0["mu_" + loss], mu, rtol=1e-5, atol=1e-6)
