@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(256) k_peer_reduce(PeerReduceArgs a) {
 // Scan of one (node, feature): applies the sibling subtraction (`subtract_hist!`, fit-utils.jl:321-332) to the
 // staged histogram `sm` of the build node, stores the node's histogram if its children will need it, scans the
 // bins (`_scan_node!`, fit-utils.jl:403-436) and records the best split of this feature.
-template <int MAXCHK, bool OWN>
+template <int MAXCHK, bool OWN, bool OBL>
 __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int f, const double *sm, double *s_sum, int lane, bool first_owned) {
     const int C = a.C, K = a.K, B = a.B, F = a.F;
     const int m = 1 << (a.level - 1);
@@ -303,7 +303,7 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
                     g = gacc[ch] - gain_p;
                     if (g > lg) { lg = g; lb = b; }
                 }
-                if (a.obl_gain && b < B) a.obl_gain[((size_t)(n - m) * F + f) * B + b] = g; // update_gains!, fit-utils.jl:457-463
+                if (OBL && b < B) a.obl_gain[((size_t)(n - m) * F + f) * B + b] = g; // update_gains!, fit-utils.jl:457-463
             }
         }
 #pragma unroll
@@ -323,8 +323,9 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
 // Stage 1: one warp per (node, owned feature slot), lanes over bins.  The nodes of a level come in pairs sharing a
 // build slot: the build node reads the slot's histogram, its sibling subtracts it from the parent's.  Warps are
 // independent, so even the root level (one node) spreads over many SMs.
-// OWN: the loss brings its own split gain (mae, credibility); the default instance does not carry that code
-template <int MAXCHK, bool OWN>
+// OWN: the loss brings its own split gain (mae, credibility); OBL: oblivious trees, the gain of every candidate is
+// stored as well.  The default instance carries neither code.
+template <int MAXCHK, bool OWN, bool OBL>
 __global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
     __shared__ double s_sum_all[8][72];
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
@@ -339,7 +340,7 @@ __global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
     const int f = fi * a.world + a.rank;
     const int nb = a.slot_node[s];
     const double *src = a.hcomp + ((size_t)s * F + f) * C * B;
-    scan_one<MAXCHK, OWN>(a, which ? nb ^ 1 : nb, which != 0, f, src, s_sum_all[wid], lane, fi == 0);
+    scan_one<MAXCHK, OWN, OBL>(a, which ? nb ^ 1 : nb, which != 0, f, src, s_sum_all[wid], lane, fi == 0);
 }
 
 // Oblivious trees, stage 1b: one thread per candidate (feature slot, bin) adds the gains of the level's nodes in
@@ -875,8 +876,14 @@ int32_t evb_launch_scan(evb_handle *h, int level) {
     if (warps > 0) {
         const unsigned grid = (unsigned)((warps + 7) / 8);
         const bool own = h->p.loss >= EVB_MAE;
-        if (h->B <= 64) { if (own) k_scan_feat<2, true><<<grid, 256, 0, h->st>>>(a); else k_scan_feat<2, false><<<grid, 256, 0, h->st>>>(a); }
-        else { if (own) k_scan_feat<8, true><<<grid, 256, 0, h->st>>>(a); else k_scan_feat<8, false><<<grid, 256, 0, h->st>>>(a); }
+        const bool obl = h->obl_gain != nullptr;
+#define EVB_SCAN(M) do { \
+            if (own && obl) k_scan_feat<M, true, true><<<grid, 256, 0, h->st>>>(a); \
+            else if (own) k_scan_feat<M, true, false><<<grid, 256, 0, h->st>>>(a); \
+            else if (obl) k_scan_feat<M, false, true><<<grid, 256, 0, h->st>>>(a); \
+            else k_scan_feat<M, false, false><<<grid, 256, 0, h->st>>>(a); } while (0)
+        if (h->B <= 64) EVB_SCAN(2); else EVB_SCAN(8);
+#undef EVB_SCAN
     }
     evb_toc(h, EVB_T_SCAN);
     if (h->obl_gain && level < h->D) {
