@@ -629,7 +629,6 @@ extern "C" int32_t evb_comm_ipc_export(evb_handle *h, uint8_t blob[256]) {
     if (!blob) { evb_set_error("null blob"); return EVB_ERR_ARG; }
     if (h->world < 2 || h->world > 8) { evb_set_error("evb_comm_ipc_export: needs evb_comm_init with 2..8 ranks first"); return EVB_ERR_ARG; }
     if (h->p2p || h->peer_cand[h->rank]) { evb_set_error("evb_comm_ipc_export: already exported"); return EVB_ERR_ARG; }
-    if (h->p.tree_type == 1) { evb_set_error("evb_comm_ipc_export: oblivious trees sum their histograms with NCCL (no feature-sharded scan)"); return EVB_ERR_ARG; }
     EVB_CUDA(cudaStreamSynchronize(h->st));
     const int D = h->D;
     // every scanned node keeps the summed histogram of the features this rank owns (children subtract from it)

@@ -345,15 +345,18 @@ __global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
 
 // Oblivious trees, stage 1b: one thread per candidate (feature slot, bin) adds the gains of the level's nodes in
 // ascending node order and drops the candidate if any node holds no positive gain for it (src/fit.jl:196-211; at
-// the root level the reference applies no mask, which changes nothing for gamma >= 0).
+// the root level the reference applies no mask, which changes nothing for gamma >= 0).  Sharded with peer access,
+// every rank does this for its own feature slots; k_scan_node then publishes the rank's best split with each
+// node's left sums and k_scan_final takes the best of the ranks (the same for every node: the gains are level totals).
 __global__ void __launch_bounds__(128) k_obl_sum(ScanArgs a) {
     const int m = 1 << (a.level - 1);
     const size_t FB = (size_t)a.F * a.B;
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= FB) return;
     double tot = 0.0;
-    bool ok = true;
-    for (int i = 0; i < m; ++i) {
+    // sharded with peer access: only the feature slots this rank scans hold gains; the others never win here
+    bool ok = (int)(e / a.B) % a.world == a.rank;
+    for (int i = 0; ok && i < m; ++i) {
         const double g = a.obl_gain[(size_t)i * FB + e];
         tot += g;
         ok = ok && g > 0.0;

@@ -26,13 +26,16 @@ def main(out_path):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     comm = Comm(dist, torch.device("cuda", local))
     results = {}
-    # case 4 grows oblivious trees: the peer-access export declines and all ranks stay on the NCCL sums
+    # cases 4 and 6 grow oblivious trees, over peer access and over the NCCL sums
     for case, (loss, n, f, depth, nbins, rowsample, tree_type) in enumerate([
             ("mse", 60_001, 20, 7, 32, 1.0, "binary"), ("mse", 40_000, 9, 5, 16, 0.6, "binary"),
             ("gaussian_mle", 30_000, 12, 5, 32, 1.0, "binary"), ("mlogloss", 30_000, 8, 5, 16, 1.0, "binary"),
             ("mse", 50_000, 10, 5, 32, 1.0, "oblivious"),
             # quantile leaves: the ranks add the digit counts of the selection, so the leaves are those of one GPU
-            ("quantile", 40_001, 8, 4, 32, 0.7, "binary")]):
+            ("quantile", 40_001, 8, 4, 32, 0.7, "binary"), ("mse", 30_000, 10, 5, 32, 1.0, "oblivious_nccl")]):
+        p2p_default = comm.p2p
+        comm.p2p = p2p_default and not tree_type.endswith("_nccl")
+        tree_type = tree_type.split("_")[0]
         rng = np.random.default_rng(100 + case)
         x = rng.random((n, f)).astype(np.float32)
         raw = x @ rng.normal(size=f) + 0.2 * rng.normal(size=n)
@@ -68,6 +71,7 @@ def main(out_path):
                     results[f"c{case}_1_{name}{r}"] = getattr(trees_1[r], name)
             results[f"c{case}_s_pred"] = np.concatenate(gathered)
             results[f"c{case}_1_pred"] = pred_1
+        comm.p2p = p2p_default
         dist.barrier()
     if rank == 0:
         np.savez(out_path, **results)

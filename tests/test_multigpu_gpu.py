@@ -29,7 +29,7 @@ def test_two_gpus_equal_one_gpu(tmp_path):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     z = np.load(out)
-    for case in range(6):
+    for case in range(7):
         for rr in range(3):
             k = f"c{case}_"
             assert np.array_equal(z[k + f"s_feat{rr}"], z[k + f"1_feat{rr}"]), (case, rr)
