@@ -110,7 +110,7 @@ static void free_handle(evb_handle *h) {
     if (h->d_barrier_seq) cudaFree(h->d_barrier_seq);
     if (h->hsum) cudaFree(h->hsum);
     free_eval(h);
-    void *ptrs[] = {h->qs_cnt, h->qs_prefix, h->qs_rank, h->qs_gamma, h->gradq, h->d_gmax, h->d_qinv, h->xT, h->xC, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
+    void *ptrs[] = {h->xH, h->xE, h->hsum_q, h->hcnt_q, h->qs_cnt, h->qs_prefix, h->qs_rank, h->qs_gamma, h->gradq, h->d_gmax, h->d_qinv, h->xT, h->xC, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
                     h->js_d, h->seg_start, h->seg_cnt, h->gcnt, h->nleft, (h->gnleft != h->nleft) ? h->gnleft : nullptr, h->kind,
                     h->bslot, h->nsum, h->plan /* base of the tree block */, h->cum, h->slot_node, h->item_node, h->item_left,
                     h->item_lprefix, h->item_bits, h->scan_tmp, h->hist, h->hcomp, h->scratch, h->fbest_gain, h->fbest_bin, h->obl_gain, h->obl_best};
@@ -174,8 +174,10 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
         EVB_CUDA(dalloc(&h->qs_gamma, (size_t)h->nn + 1));
         EVB_CUDA(cudaMemset(h->qs_cnt, 0, e * 256 * sizeof(uint32_t)));
     }
+    // unit weights: the register-direct kernel (EVB_HIST_Q2=0: the staged fixed-point kernel)
+    { const char *e = getenv("EVB_HIST_Q2"); h->use_q2 = h->use_q && h->unit_w && !(e && atoi(e) == 0) && evb_q2_configure(h) == EVB_OK; }
     if (h->use_q) {
-        EVB_CUDA(dalloc(&h->gradq, (size_t)n * (h->unit_w ? 1 : 2)));
+        if (!h->use_q2) EVB_CUDA(dalloc(&h->gradq, (size_t)n * (h->unit_w ? 1 : 2)));
         EVB_CUDA(dalloc(&h->d_gmax, (size_t)1));
         EVB_CUDA(dalloc(&h->d_qinv, (size_t)2));
         EVB_CUDA(cudaMemset(h->d_gmax, 0, sizeof(unsigned)));
@@ -241,6 +243,16 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
     EVB_CUDA(dalloc(&h->xC, (size_t)n * nfeats));
     EVB_CUDA(cudaMemcpyAsync(h->xC, x_bin, (size_t)n * nfeats, cudaMemcpyHostToDevice, h->st));
     EVB_CHECK(evb_launch_transpose(h, h->xC, n, n, 0, nfeats, h->xT, h->RS, h->st));
+    if (h->use_q2) {
+        const size_t acc = (size_t)h->maxslots * h->B * h->q2.SC;
+        EVB_CUDA(dalloc(&h->xH, (size_t)(n + 1) * h->q2.RSH));
+        EVB_CUDA(dalloc(&h->xE, (size_t)n + 1));
+        EVB_CUDA(dalloc(&h->hsum_q, acc));
+        EVB_CUDA(dalloc(&h->hcnt_q, acc));
+        EVB_CUDA(cudaMemsetAsync(h->hsum_q, 0, acc * sizeof(unsigned long long), h->st));
+        EVB_CUDA(cudaMemsetAsync(h->hcnt_q, 0, acc * sizeof(uint32_t), h->st));
+        EVB_CHECK(evb_q2_build_layout(h));
+    }
     {
         const size_t ybytes = (size_t)n * (y_dtype == EVB_U32 ? 4 : 4 * (size_t)ycols);
         EVB_CUDA(cudaMalloc(&h->y, ybytes ? ybytes : 1));
@@ -344,15 +356,20 @@ static int32_t enqueue_tree(evb_handle *h, bool use_mask, uint8_t mask_cond, boo
     const int D = h->D;
     EVB_CUDA(cudaMemcpyAsync(h->js_d, h->h_js[slot], sizeof(uint32_t) * h->F, cudaMemcpyHostToDevice, h->st));
     if (run_grads) EVB_CHECK(evb_launch_grads(h));
-    if (quantize) EVB_CHECK(evb_launch_quantize(h)); // fixed-point histogram kernel: the gradients changed since the last tree
+    if (quantize) EVB_CHECK(h->use_q2 ? evb_launch_q2_quantize(h) : evb_launch_quantize(h)); // fixed-point histogram kernel: the gradients changed since the last tree
     EVB_CHECK(evb_launch_tree_reset(h));
     EVB_CHECK(evb_launch_rows_init(h, use_mask, mask_cond));
     EVB_CHECK(evb_launch_root_plan(h));
     const int last = D > 1 ? D - 1 : 1;
     const bool full_part = (h->p.flags & EVB_FLAG_FULL_PARTITION) != 0;
     for (int level = 1; level <= last; ++level) {
-        EVB_CHECK(evb_launch_hist(h, level));
-        EVB_CHECK(evb_launch_hist_reduce(h, level));
+        if (h->use_q2) {
+            EVB_CHECK(evb_launch_histq2(h, level));
+            EVB_CHECK(evb_launch_q2_reduce(h, level));
+        } else {
+            EVB_CHECK(evb_launch_hist(h, level));
+            EVB_CHECK(evb_launch_hist_reduce(h, level));
+        }
         if (h->world > 1 && !h->p2p) { // with peer access the ranks' histograms are summed inside the split scan instead
             evb_tic(h, EVB_T_ALLREDUCE);
             int32_t s = evb_nccl_allreduce_f64(h, h->hcomp, (size_t)evb_level_slots(level) * h->F * h->C * h->B);
@@ -397,6 +414,11 @@ extern "C" int32_t evb_grow_tree_begin(evb_handle *h, const uint8_t *row_mask, u
         h->h_js[slot][i] = js[i] - 1;
     }
     if (h->world > 1) EVB_CHECK(evb_nccl_check(h));
+    if (njs != h->F && h->use_q2) { // this kernel always accumulates all features; the scan reads the sampled ones
+        EVB_CUDA(cudaStreamSynchronize(h->st));
+        h->F = njs;
+        drop_graphs(h);
+    }
     if (njs != h->F) {
         HistGeom g;
         EVB_CUDA(cudaStreamSynchronize(h->st));
@@ -430,7 +452,7 @@ extern "C" int32_t evb_grow_tree_begin(evb_handle *h, const uint8_t *row_mask, u
     // One CUDA graph per variant of the launch sequence, captured on the second call of a variant (the first
     // one runs directly: it also sets function attributes).  Per-kernel timing needs the direct path.
     if (update_grads) h->gradq_valid = false;
-    const bool quantize = h->q_active && !h->gradq_valid;
+    const bool quantize = (h->q_active || h->use_q2) && !h->gradq_valid;
     if (quantize) h->gradq_valid = true;
     const int key = (use_mask ? 1 : 0) | (run_grads ? 2 : 0) | (fuse ? 4 : 0) | (slot ? 8 : 0) | (quantize ? 16 : 0);
     if (h->graph_mask_cond != (int)mask_cond) { drop_graphs(h); h->graph_mask_cond = mask_cond; }

@@ -63,6 +63,20 @@ struct HistGeom {
     size_t img_floats;   // floats per unit image in scratch: FPL*NCH*nbins*32
 };
 
+// geometry of the register-direct fixed-point histogram kernel (evb_histq2.cu)
+struct Q2Geom {
+    int NC;        // 16-byte chunks (16 features) per CTA group
+    int ngroups;   // CTA groups (grid.y); xH rows hold ngroups * NC chunks
+    int ntail;     // features kept beside the gradient word in xE (nfeats % 16 when that is 1..4, else 0)
+    int nmain;     // features kept in xH
+    int RSH;       // bytes per row of xH
+    int SC;        // feature columns per bin of the accumulators
+    int G;         // grid.x
+    int TE;        // tiles of 32 rows between two flushes of a CTA's image
+    int min_rows;  // rows per CTA below which fewer CTAs take part
+    size_t smem;
+};
+
 struct evb_handle {
     evb_params p;
     int K, C, B, D, nn;        // nn = 2^D-1
@@ -135,6 +149,14 @@ struct evb_handle {
     double *d_qinv;       // [2] 2^-s of the g words / of the w words
     float wscale; double winv;
 
+    // register-direct variant (unit weights): rows as 16-byte chunks + {q, tail bins} per row, integer accumulators
+    bool use_q2;
+    Q2Geom q2;
+    uint8_t *xH;                  // [n][q2.RSH]
+    uint2 *xE;                    // [n] {fixed-point gradient, bins of the tail features}
+    unsigned long long *hsum_q;   // [maxslots][B][q2.SC] sums of q per build slot
+    uint32_t *hcnt_q;             // [maxslots][B][q2.SC] row counts
+
     // quantile loss: work memory of the per-leaf order-statistic selection
     uint32_t *qs_cnt, *qs_prefix, *qs_rank; float *qs_gamma;
 
@@ -191,6 +213,12 @@ int32_t evb_launch_eval(evb_handle *h, const float *fixed_leaf_dev);
 int32_t evb_hist_configure(evb_handle *h);   // fills h->hg from p / nfeats (uses max F = nfeats)
 int32_t evb_launch_hist(evb_handle *h, int level);
 int32_t evb_launch_hist_reduce(evb_handle *h, int level);
+// evb_histq2.cu
+int32_t evb_q2_configure(evb_handle *h);
+int32_t evb_q2_build_layout(evb_handle *h);
+int32_t evb_launch_q2_quantize(evb_handle *h);
+int32_t evb_launch_histq2(evb_handle *h, int level);
+int32_t evb_launch_q2_reduce(evb_handle *h, int level);
 // evb_tree.cu
 int32_t evb_launch_tree_reset(evb_handle *h);
 int32_t evb_launch_scan(evb_handle *h, int level);

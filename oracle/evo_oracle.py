@@ -20,7 +20,7 @@ from dataclasses import dataclass
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_SO = os.path.join(_HERE, "_ref", "libevo_oracle.so")
+_SO = os.path.join(_HERE, "_build", "libevo_oracle.so")
 
 LOSSES = {"mse": 0, "logloss": 1, "mlogloss": 2, "gaussian_mle": 3, "poisson": 4, "gamma": 5, "tweedie": 6, "logistic_mle": 7,
           "mae": 8, "cred_var": 9, "cred_std": 10, "quantile": 11, "multiquantile": 12}
