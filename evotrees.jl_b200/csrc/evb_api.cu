@@ -129,7 +129,9 @@ static void free_handle(evb_handle *h) {
 
 extern "C" void evb_destroy(evb_handle *h) { free_handle(h); }
 
-static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int32_t nfeats, const uint8_t *x_bin, const void *y,
+// x_bin != NULL: the binned matrix; else the raw matrix x (x_dtype) with its edges, binarized on the device
+static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int32_t nfeats, const uint8_t *x_bin, const void *x,
+                           int32_t x_dtype, const void *edges, int32_t nedges, const void *y,
                            int32_t y_dtype, int32_t ycols, const float *w, const float *pred0, const float *mu,
                            const uint8_t *feattypes, const int32_t *monotone) {
     h->p = *p;
@@ -241,7 +243,8 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
     // observation-major rows for the histogram gathers and the tree traversal
     EVB_CUDA(cudaMemsetAsync(h->xT, 0, (size_t)n * h->RS, h->st));
     EVB_CUDA(dalloc(&h->xC, (size_t)n * nfeats));
-    EVB_CUDA(cudaMemcpyAsync(h->xC, x_bin, (size_t)n * nfeats, cudaMemcpyHostToDevice, h->st));
+    if (x_bin) EVB_CHECK(evb_h2d_staged(h->xC, x_bin, (size_t)n * nfeats, h->st));
+    else EVB_CHECK(evb_upload_binarize(h, x, x_dtype, edges, nedges));
     EVB_CHECK(evb_launch_transpose(h, h->xC, n, n, 0, nfeats, h->xT, h->RS, h->st));
     if (h->use_q2) {
         const size_t acc = (size_t)h->maxslots * h->B * h->q2.SC;
@@ -284,15 +287,23 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
         evb_set_error("x_bin holds values outside 1..nbins (%d)", h->B);
         return EVB_ERR_ARG;
     }
+    if (err == EVB_DERR_NAN) {
+        evb_set_error("the feature matrix holds NaN: missing values are not supported");
+        return EVB_ERR_ARG;
+    }
     return EVB_OK;
 }
 
-extern "C" int32_t evb_create(evb_handle **out, const evb_params *p, int64_t nobs, int32_t nfeats, const uint8_t *x_bin,
-                              const void *y, int32_t y_dtype, int32_t ycols, const float *w, const float *pred0, const float *mu,
-                              const uint8_t *feattypes, const int32_t *monotone) {
+static int32_t create_common(evb_handle **out, const evb_params *p, int64_t nobs, int32_t nfeats, const uint8_t *x_bin, const void *x,
+                             int32_t x_dtype, const void *edges, int32_t nedges, const void *y, int32_t y_dtype, int32_t ycols,
+                             const float *w, const float *pred0, const float *mu, const uint8_t *feattypes, const int32_t *monotone) {
     if (!out) { evb_set_error("evb_create: out is null"); return EVB_ERR_ARG; }
     *out = nullptr;
-    if (!p || !x_bin || !y || (!pred0 && !mu)) { evb_set_error("evb_create: null argument"); return EVB_ERR_ARG; }
+    if (!p || (!x_bin && !x) || !y || (!pred0 && !mu)) { evb_set_error("evb_create: null argument"); return EVB_ERR_ARG; }
+    if (x && (!edges || (x_dtype != EVB_F32 && x_dtype != EVB_F64) || nedges != p->nbins - 1)) {
+        evb_set_error("evb_create_x: x needs EVB_F32 / EVB_F64 and nbins - 1 edges per feature");
+        return EVB_ERR_ARG;
+    }
     if (nobs < 1 || nobs > 2000000000ll || nfeats < 1 || nfeats > 65535) { evb_set_error("evb_create: nobs/nfeats out of range"); return EVB_ERR_ARG; }
     if (p->loss < 0 || p->loss > EVB_LOSS_LAST) { evb_set_error("evb_create: unknown loss %d", p->loss); return EVB_ERR_ARG; }
     if (p->K < 1 || p->K > 32) { evb_set_error("evb_create: K=%d outside 1..32", p->K); return EVB_ERR_ARG; }
@@ -330,10 +341,24 @@ extern "C" int32_t evb_create(evb_handle **out, const evb_params *p, int64_t nob
     evb_handle *h = new (std::nothrow) evb_handle();
     if (!h) { evb_set_error("out of host memory"); return EVB_ERR_ARG; }
     memset(&h->tm, 0, sizeof(h->tm));
-    int32_t rc = create_impl(h, p, nobs, nfeats, x_bin, y, y_dtype, ycols, w, pred0, mu, feattypes, monotone);
+    int32_t rc = create_impl(h, p, nobs, nfeats, x_bin, x, x_dtype, edges, nedges, y, y_dtype, ycols, w, pred0, mu, feattypes, monotone);
     if (rc != EVB_OK) { free_handle(h); return rc; }
     *out = h;
     return EVB_OK;
+}
+
+extern "C" int32_t evb_create(evb_handle **out, const evb_params *p, int64_t nobs, int32_t nfeats, const uint8_t *x_bin,
+                              const void *y, int32_t y_dtype, int32_t ycols, const float *w, const float *pred0, const float *mu,
+                              const uint8_t *feattypes, const int32_t *monotone) {
+    if (!x_bin) { evb_set_error("evb_create: x_bin is null"); return EVB_ERR_ARG; }
+    return create_common(out, p, nobs, nfeats, x_bin, nullptr, 0, nullptr, 0, y, y_dtype, ycols, w, pred0, mu, feattypes, monotone);
+}
+
+extern "C" int32_t evb_create_x(evb_handle **out, const evb_params *p, int64_t nobs, int32_t nfeats, const void *x, int32_t x_dtype,
+                                const void *edges, int32_t nedges, const void *y, int32_t y_dtype, int32_t ycols, const float *w,
+                                const float *pred0, const float *mu, const uint8_t *feattypes, const int32_t *monotone) {
+    if (!x) { evb_set_error("evb_create_x: x is null"); return EVB_ERR_ARG; }
+    return create_common(out, p, nobs, nfeats, nullptr, x, x_dtype, edges, nedges, y, y_dtype, ycols, w, pred0, mu, feattypes, monotone);
 }
 
 extern "C" int32_t evb_comm_unique_id(uint8_t id[128]) {
@@ -344,7 +369,7 @@ extern "C" int32_t evb_comm_unique_id(uint8_t id[128]) {
 extern "C" int32_t evb_comm_init(evb_handle *h, const uint8_t id[128], int32_t rank, int32_t world) {
     EVB_ENTER(h);
     if (!id || world < 1 || rank < 0 || rank >= world) { evb_set_error("evb_comm_init: bad rank/world"); return EVB_ERR_ARG; }
-    if (h->nccl_comm) { evb_set_error("evb_comm_init: communicator already initialised"); return EVB_ERR_ARG; }
+    if (h->nccl_comm || h->nccl_pending) { evb_set_error("evb_comm_init: communicator already initialised"); return EVB_ERR_ARG; }
     if (world == 1) return EVB_OK;
     EVB_CHECK(evb_nccl_init(h, id, rank, world));
     return EVB_OK;

@@ -26,7 +26,7 @@ void evb_set_error(const char *fmt, ...);
     } while (0)
 
 // device-side error codes written to evb_handle::d_err
-enum { EVB_DERR_NONE = 0, EVB_DERR_WAIT_FULL = 1, EVB_DERR_WAIT_EMPTY = 2, EVB_DERR_BIN_RANGE = 3, EVB_DERR_PLAN = 4, EVB_DERR_PEER = 5 };
+enum { EVB_DERR_NONE = 0, EVB_DERR_WAIT_FULL = 1, EVB_DERR_WAIT_EMPTY = 2, EVB_DERR_BIN_RANGE = 3, EVB_DERR_PLAN = 4, EVB_DERR_PEER = 5, EVB_DERR_NAN = 6 };
 
 // ---- geometry constants ---------------------------------------------------------------------------
 constexpr int EVB_TILE_ROWS = 32;    // rows per staged tile (one per producer lane)
@@ -183,6 +183,7 @@ struct evb_handle {
 
     // multi-GPU
     void *nccl_comm; int rank, world;
+    uint8_t nccl_id[128]; bool nccl_pending; // id recorded by evb_comm_init; the communicator is created by the first collective
     // peer access between the ranks' processes (CUDA IPC): histograms are summed by peer loads inside the split scan
     bool p2p;
     double *peer_hcomp[8]; double *peer_cand[8]; int *peer_flags[8];
@@ -209,6 +210,7 @@ int32_t evb_launch_finalize(evb_handle *h, bool compute_grads, int mode); // mod
 int32_t evb_launch_quantile_leaves(evb_handle *h, bool use_mask, uint8_t mask_cond);
 int32_t evb_launch_nidx_from_partition(evb_handle *h, uint32_t *out_dev);
 int32_t evb_launch_eval(evb_handle *h, const float *fixed_leaf_dev);
+int32_t evb_upload_binarize(evb_handle *h, const void *x, int32_t dtype, const void *edges, int32_t nedges); // raw host matrix -> h->xC
 // evb_hist.cu
 int32_t evb_hist_configure(evb_handle *h);   // fills h->hg from p / nfeats (uses max F = nfeats)
 int32_t evb_launch_hist(evb_handle *h, int level);
@@ -229,6 +231,9 @@ int32_t evb_nccl_init(evb_handle *h, const uint8_t id[128], int rank, int world)
 int32_t evb_nccl_allreduce_f64(evb_handle *h, double *buf, size_t count);
 int32_t evb_nccl_allreduce_i32(evb_handle *h, const int32_t *src, int32_t *dst, size_t count);
 void evb_nccl_destroy(evb_handle *h);
+
+// evb_stage.cu: pageable host memory -> device through a ring of pinned buffers filled by several host threads
+int32_t evb_h2d_staged(void *dst_dev, const void *src_host, size_t bytes, cudaStream_t st);
 
 // timing helpers (evb_api.cu)
 void evb_tic(evb_handle *h, int cls);

@@ -5,6 +5,7 @@
 // `binarize` (src/fit-utils.jl:66-72).
 #include "evb_internal.cuh"
 #include <float.h>
+#include <algorithm>
 
 namespace {
 
@@ -547,7 +548,8 @@ __global__ void k_pack_trees(const long long *feat, const uint8_t *bin, const ui
 // ---------------------------------------------------------------------------------- binarize
 // searchsortedfirst(edges[j], x): 1 + number of edges strictly below x
 template <typename T>
-__global__ void __launch_bounds__(256) k_binarize(const T *x, long long ld, long long n, const T *edges, int nedges, uint8_t *out, long long ldo) {
+__global__ void __launch_bounds__(256) k_binarize(const T *x, long long ld, long long n, const T *edges, int nedges, uint8_t *out, long long ldo,
+                                                   int *nan_err = nullptr) {
     extern __shared__ unsigned char s_raw[];
     T *e = reinterpret_cast<T *>(s_raw);
     const int j = blockIdx.y;
@@ -555,6 +557,7 @@ __global__ void __launch_bounds__(256) k_binarize(const T *x, long long ld, long
     __syncthreads();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         const T v = x[(size_t)j * ld + i];
+        if (nan_err && v != v) atomicCAS(nan_err, 0, EVB_DERR_NAN); // missing values are not supported (test/missings.jl)
         int lo = 0, hi = nedges;
         while (lo < hi) { const int mid = (lo + hi) >> 1; if (e[mid] < v) lo = mid + 1; else hi = mid; }
         out[(size_t)j * ldo + i] = (uint8_t)(lo + 1);
@@ -832,6 +835,41 @@ int32_t evb_launch_nidx_from_partition(evb_handle *h, uint32_t *out_dev) {
     int blocks = h->nn < 1024 ? h->nn : 1024;
     k_nidx_from_partition<<<blocks, 256, 0, h->st>>>(h->rows[0], h->rows[1], h->seg_start, h->seg_cnt, h->t_split, h->nn, out_dev);
     EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+// ---- training matrix from raw features -----------------------------------------------------------------
+struct DevBufT {
+    void *p = nullptr;
+    ~DevBufT() { if (p) cudaFree(p); }
+};
+// `binarize(x_train; edges)` of `init_core` (ext/EvoTreesKernelAbstractionsExt/init.jl:3-6, src/fit-utils.jl:66-72) on the
+// device: the raw column-major matrix travels in blocks of whole features (each at most 256 MB) and every block is
+// binarized straight into the feature-major bin matrix h->xC; the bins never visit the host.  NaN sets the error word.
+int32_t evb_upload_binarize(evb_handle *h, const void *x, int32_t dtype, const void *edges, int32_t nedges) {
+    const size_t es = dtype == EVB_F64 ? 8 : 4;
+    const int64_t n = h->n;
+    const int nfeats = h->nfeats;
+    int cf = (int)std::max<int64_t>(1, std::min<int64_t>(nfeats, ((int64_t)256 << 20) / (int64_t)(n * es)));
+    DevBufT d_x, d_e;
+    EVB_CUDA(cudaMalloc(&d_x.p, (size_t)cf * n * es));
+    EVB_CUDA(cudaMalloc(&d_e.p, (size_t)nedges * nfeats * es));
+    EVB_CUDA(cudaMemcpyAsync(d_e.p, edges, (size_t)nedges * nfeats * es, cudaMemcpyHostToDevice, h->st));
+    unsigned bx = (unsigned)((n + 255) / 256);
+    if (bx > 4096) bx = 4096;
+    for (int j0 = 0; j0 < nfeats; j0 += cf) {
+        const int nj = std::min(cf, nfeats - j0);
+        EVB_CHECK(evb_h2d_staged(d_x.p, (const char *)x + (size_t)j0 * n * es, (size_t)nj * n * es, h->st));
+        dim3 grid(bx, (unsigned)nj);
+        if (dtype == EVB_F32)
+            k_binarize<float><<<grid, 256, (size_t)nedges * 4, h->st>>>((const float *)d_x.p, n, n, (const float *)d_e.p + (size_t)j0 * nedges, nedges,
+                                                                           h->xC + (size_t)j0 * n, n, h->d_err);
+        else
+            k_binarize<double><<<grid, 256, (size_t)nedges * 8, h->st>>>((const double *)d_x.p, n, n, (const double *)d_e.p + (size_t)j0 * nedges, nedges,
+                                                                            h->xC + (size_t)j0 * n, n, h->d_err);
+        EVB_CUDA(cudaGetLastError());
+    }
+    EVB_CUDA(cudaStreamSynchronize(h->st)); // the staging buffers are freed on return
     return EVB_OK;
 }
 

@@ -1,0 +1,91 @@
+// Host-to-device copies of ordinary (pageable) host memory at pinned-memory speed: the data goes through a small ring
+// of pinned buffers that several host threads fill while the copy engine drains the previous one.  A plain
+// cudaMemcpy from pageable memory does the same staging inside the driver with one thread, which caps a 4 GB feature
+// matrix at a fraction of the PCIe rate.  The ring is allocated on first use and kept for the life of the process.
+#include "evb_internal.cuh"
+#include <mutex>
+#include <stdlib.h>
+#include <string.h>
+#include <thread>
+
+namespace {
+
+constexpr int STAGE_NB = 3;
+constexpr size_t STAGE_BYTES = (size_t)32 << 20;
+
+struct StageRing {
+    void *buf[STAGE_NB] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev[STAGE_NB] = {nullptr, nullptr, nullptr};
+    bool used[STAGE_NB] = {false, false, false};
+    bool ready = false;
+    std::mutex mu;
+};
+StageRing g_rings[64]; // one ring per device (events belong to a device)
+
+int stage_threads() {
+    static const int n = [] {
+        if (const char *e = getenv("EVB_STAGE_THREADS")) { const int v = atoi(e); if (v >= 1 && v <= 64) return v; }
+        const unsigned hc = std::thread::hardware_concurrency();
+        int v = hc ? (int)hc / 2 : 4;
+        return v < 1 ? 1 : v > 8 ? 8 : v;
+    }();
+    return n;
+}
+
+void parallel_memcpy(char *dst, const char *src, size_t bytes) {
+    const int nt = bytes < ((size_t)4 << 20) ? 1 : stage_threads();
+    if (nt == 1) { memcpy(dst, src, bytes); return; }
+    std::thread th[64];
+    const size_t per = (bytes / nt + 4095) & ~(size_t)4095;
+    int started = 0;
+    for (int t = 0; t < nt; ++t) {
+        const size_t o = (size_t)t * per;
+        if (o >= bytes) break;
+        const size_t len = bytes - o < per ? bytes - o : per;
+        th[started++] = std::thread([=] { memcpy(dst + o, src + o, len); });
+    }
+    for (int t = 0; t < started; ++t) th[t].join();
+}
+
+} // namespace
+
+// Copies `bytes` of pageable host memory to the device on stream `st`.  Returns when the host memory has been read
+// (the caller may reuse or free it); the last device copies may still be in flight on `st`.  One copy at a time per
+// process (the ring is shared); concurrent callers wait for each other.
+int32_t evb_h2d_staged(void *dst_dev, const void *src_host, size_t bytes, cudaStream_t st) {
+    if (bytes == 0) return EVB_OK;
+    if (bytes < ((size_t)1 << 20) || getenv("EVB_STAGE_OFF")) { // small: the driver's own staging is as good
+        EVB_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, st));
+        return EVB_OK;
+    }
+    int dev = 0;
+    EVB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        EVB_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, st));
+        return EVB_OK;
+    }
+    StageRing &g_ring = g_rings[dev];
+    std::lock_guard<std::mutex> lock(g_ring.mu);
+    if (!g_ring.ready) {
+        for (int b = 0; b < STAGE_NB; ++b) {
+            EVB_CUDA(cudaHostAlloc(&g_ring.buf[b], STAGE_BYTES, cudaHostAllocDefault));
+            EVB_CUDA(cudaEventCreateWithFlags(&g_ring.ev[b], cudaEventDisableTiming));
+        }
+        g_ring.ready = true;
+    }
+    const char *src = static_cast<const char *>(src_host);
+    char *dst = static_cast<char *>(dst_dev);
+    int b = 0;
+    for (size_t off = 0; off < bytes; off += STAGE_BYTES, b = (b + 1) % STAGE_NB) {
+        const size_t len = bytes - off < STAGE_BYTES ? bytes - off : STAGE_BYTES;
+        if (g_ring.used[b]) EVB_CUDA(cudaEventSynchronize(g_ring.ev[b])); // the copy that last used this buffer has left it
+        parallel_memcpy(static_cast<char *>(g_ring.buf[b]), src + off, len);
+        EVB_CUDA(cudaMemcpyAsync(dst + off, g_ring.buf[b], len, cudaMemcpyHostToDevice, st));
+        EVB_CUDA(cudaEventRecord(g_ring.ev[b], st));
+        g_ring.used[b] = true;
+    }
+    // the ring may be reused by the next call (possibly on another stream or device) right away: drain it
+    for (int q = 0; q < STAGE_NB; ++q)
+        if (g_ring.used[q]) { EVB_CUDA(cudaEventSynchronize(g_ring.ev[q])); g_ring.used[q] = false; }
+    return EVB_OK;
+}

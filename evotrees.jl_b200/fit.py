@@ -158,6 +158,13 @@ class Cache:
         _lib.check(_lib.lib().evb_reset_timings(self.handle))
 
 
+def make_rngs(seed: int, rank: int = 0):
+    """Generators of one rank: row masks come from a per-rank stream; the column sample from a stream of its own that
+    depends on the seed only, so that every rank of a sharded fit draws the same `js` whatever its shard size is
+    (the library sums the ranks' histograms slot by slot)."""
+    return np.random.default_rng([seed, rank]), np.random.default_rng([seed, 0x6A73])
+
+
 def make_params(params: EvoTypes, K: int, device: int, flags: int = 0) -> _lib.EvbParams:
     return _lib.EvbParams(_lib.LOSS_CODES[params.loss], K, params.nbins, params.max_depth, params.bagging_size,
                           1 if params.tree_type == "oblivious" else 0, params.eta, params.lambda_, params.L2, params.gamma, params.min_weight, device, flags, params.alpha,
@@ -165,16 +172,22 @@ def make_params(params: EvoTypes, K: int, device: int, flags: int = 0) -> _lib.E
 
 
 def init_core_binned(params: EvoTypes, x_bin: np.ndarray, y, ycols: int, K: int, mu: np.ndarray, w=None, pred0=None,
-                     feattypes=None, device: int = 0, flags: int = 0, comm=None) -> Cache:
-    """Creates the device handle from an already binned matrix (uint8, Fortran order, values 1..nbins)."""
-    assert x_bin.dtype == np.uint8 and x_bin.flags.f_contiguous
-    nobs, nfeats = x_bin.shape
+                     feattypes=None, device: int = 0, flags: int = 0, comm=None, x_raw=None, edges=None) -> Cache:
+    """Creates the device handle from an already binned matrix (uint8, Fortran order, values 1..nbins), or -- with
+    `x_raw` (float32 / float64, Fortran order) and `edges` [nfeats, nbins - 1] -- from the raw features, which are then
+    binarized on the device (`evb_create_x`)."""
+    if x_raw is None:
+        assert x_bin.dtype == np.uint8 and x_bin.flags.f_contiguous
+        nobs, nfeats = x_bin.shape
+    else:
+        assert x_raw.dtype in (np.float32, np.float64) and x_raw.flags.f_contiguous
+        nobs, nfeats = x_raw.shape
     cache = Cache()
     cache.nobs, cache.nfeats, cache.K, cache.nn = nobs, nfeats, K, 2 ** params.max_depth - 1
     cache.njs = math.ceil(params.colsample * nfeats)            # src/init.jl:181
     cache.mask_cond = int(np.uint8(round(255 * params.rowsample)))  # src/subsample.jl:9
     cache.use_mask = params.rowsample < 1.0
-    cache.rng = np.random.default_rng(params.seed)
+    cache.rng, cache.rng_js = make_rngs(params.seed, 0 if comm is None else comm.rank)
     mono = np.zeros(nfeats, np.int32)
     for k, v in params.monotone_constraints.items():
         mono[int(k) - 1] = int(v)
@@ -186,9 +199,21 @@ def init_core_binned(params: EvoTypes, x_bin: np.ndarray, y, ycols: int, K: int,
     cp = make_params(params, K, device, flags)
     ydt = _lib.EVB_U32 if params.loss == "mlogloss" else _lib.EVB_F32
     mu32 = np.ascontiguousarray(mu, np.float32)
-    _lib.check(_lib.lib().evb_create(C.byref(cache.handle), C.byref(cp), C.c_int64(nobs), C.c_int32(nfeats), _lib.ptr(x_bin),
-                                     _lib.ptr(y), C.c_int32(ydt), C.c_int32(ycols), _lib.ptr(w32), _lib.ptr(p0), _lib.ptr(mu32),
-                                     _lib.ptr(ft), _lib.ptr(mono)))
+    if x_raw is None:
+        _lib.check(_lib.lib().evb_create(C.byref(cache.handle), C.byref(cp), C.c_int64(nobs), C.c_int32(nfeats), _lib.ptr(x_bin),
+                                         _lib.ptr(y), C.c_int32(ydt), C.c_int32(ycols), _lib.ptr(w32), _lib.ptr(p0), _lib.ptr(mu32),
+                                         _lib.ptr(ft), _lib.ptr(mono)))
+    else:
+        e = np.ascontiguousarray(edges, dtype=x_raw.dtype)  # [nfeats, nedges] C order == [nedges x nfeats] column-major
+        xdt = _lib.EVB_F32 if x_raw.dtype == np.float32 else _lib.EVB_F64
+        try:
+            _lib.check(_lib.lib().evb_create_x(C.byref(cache.handle), C.byref(cp), C.c_int64(nobs), C.c_int32(nfeats), _lib.ptr(x_raw),
+                                               C.c_int32(xdt), _lib.ptr(e), C.c_int32(e.shape[1]), _lib.ptr(y), C.c_int32(ydt),
+                                               C.c_int32(ycols), _lib.ptr(w32), _lib.ptr(p0), _lib.ptr(mu32), _lib.ptr(ft), _lib.ptr(mono)))
+        except _lib.EvbError as err:
+            if "NaN" in str(err):
+                raise ValueError("missing / NaN feature values are not supported") from err   # test/missings.jl
+            raise
     if comm is not None:
         comm.attach(cache)
     return cache
@@ -202,22 +227,22 @@ def init_core(params: EvoTypes, x_train: np.ndarray, y_train, w_train=None, offs
     x_train = np.asarray(x_train)
     if x_train.dtype not in (np.float32, np.float64):
         x_train = x_train.astype(np.float64)
-    if np.isnan(x_train).any():
-        raise ValueError("missing / NaN feature values are not supported")   # test/missings.jl
+    x_train = np.asfortranarray(x_train)      # a Julia Matrix is column-major; no copy when it already is
     nobs, nfeats = x_train.shape
     rng = np.random.default_rng(params.seed)
     edges, featbins, feattypes = get_edges(x_train, params.nbins, rng)
+    if np.isnan(edges).any():                 # the device check below covers the rows the sample did not see
+        raise ValueError("missing / NaN feature values are not supported")   # test/missings.jl
     offset = None if offset_train is None else np.array(offset_train, np.float32, copy=True).reshape(nobs, -1)
     K, y, ycols, mu, levels, offset = init_target(params.loss, y_train, offset, params.alphas)
     if comm is not None:
         edges, mu = comm.broadcast_host(edges), comm.allreduce_bias(params.loss, y, mu, K, params.alphas)
-    x_bin = binarize(x_train, edges, device)
     pred0 = None
     if offset is not None:
         mu = np.zeros_like(mu)                                               # src/init.jl:164
         pred0 = np.ascontiguousarray(np.broadcast_to(mu, (nobs, K)) + offset, np.float32)
-    cache = init_core_binned(params, x_bin, y, ycols, K, mu, w_train, pred0, feattypes, device, flags, comm)
-    cache.rng = rng
+    # `binarize(x_train; edges)` runs on the device inside evb_create_x: raw features up, bins never down
+    cache = init_core_binned(params, None, y, ycols, K, mu, w_train, pred0, feattypes, device, flags, comm, x_raw=x_train, edges=edges)
     names = [f"feat_{i + 1}" for i in range(nfeats)] if feature_names is None else [str(s) for s in feature_names]
     if len(names) != nfeats:
         raise ValueError("feature_names must have one entry per column of x_train")
@@ -235,7 +260,7 @@ def sample_round(cache: Cache, params: EvoTypes):
     if cache.njs >= cache.nfeats:
         js = np.arange(1, cache.nfeats + 1, dtype=np.uint32)
     else:
-        js = (np.sort(cache.rng.choice(cache.nfeats, size=cache.njs, replace=False)) + 1).astype(np.uint32)
+        js = (np.sort(cache.rng_js.choice(cache.nfeats, size=cache.njs, replace=False)) + 1).astype(np.uint32)
     return mask, js
 
 

@@ -111,6 +111,19 @@ EVB_API int32_t evb_version(void);
 EVB_API int32_t evb_create(evb_handle **out, const evb_params *p, int64_t nobs, int32_t nfeats, const uint8_t *x_bin,
                    const void *y, int32_t y_dtype, int32_t ycols, const float *w, const float *pred0, const float *mu,
                    const uint8_t *feattypes, const int32_t *monotone);
+/*
+ * evb_create_x -- the same with `binarize` included, as `init_core` does it (ext/EvoTreesKernelAbstractionsExt/init.jl:3-12:
+ * `get_edges` on the host, then `binarize(x_train; edges)`): the raw feature matrix is streamed to the device in blocks of
+ * whole features and binarized there (`searchsortedfirst`, src/fit-utils.jl:66-72) straight into the training layouts; the
+ * bins never visit the host.  A NaN in x fails the call (missing values are rejected, test/missings.jl).
+ *   x       host, EVB_F32 / EVB_F64, column-major [nobs x nfeats]; ordinary (pageable) memory is fine: it is staged
+ *           through pinned buffers by several host threads
+ *   edges   host [nedges x nfeats] column-major, same dtype as x, ascending per feature; nedges = nbins - 1
+ * All other arguments as evb_create.
+ */
+EVB_API int32_t evb_create_x(evb_handle **out, const evb_params *p, int64_t nobs, int32_t nfeats, const void *x, int32_t x_dtype,
+                             const void *edges, int32_t nedges, const void *y, int32_t y_dtype, int32_t ycols, const float *w,
+                             const float *pred0, const float *mu, const uint8_t *feattypes, const int32_t *monotone);
 EVB_API void evb_destroy(evb_handle *h);
 
 /*

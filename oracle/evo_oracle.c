@@ -701,3 +701,14 @@ int orc_num_threads(void) {
     return 1;
 #endif
 }
+
+/* Thread count of the parallel loops, set explicitly: a launcher may export OMP_NUM_THREADS=1 to every rank
+ * (torch.distributed.run does), which must not shrink the CPU baseline (the reference runs with
+ * Threads.nthreads() = all host cores). */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

@@ -274,6 +274,16 @@ def num_threads() -> int:
     return lib().orc_num_threads()
 
 
+def use_all_cores() -> int:
+    """Sets the OpenMP thread count to the cores this process may run on, whatever OMP_NUM_THREADS says."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().orc_set_num_threads(C.c_int(n))
+    return num_threads()
+
+
 class Booster:
     """Boosting loop of `grow_evotree!` (src/fit.jl:6-42) on top of the C pieces.  The caller supplies
     the per-tree row mask / column sample so that both sides of a parity test consume the same draws."""

@@ -53,6 +53,17 @@ def _worker(rank, world, port, tmp):
         yy = np.abs(ys) + 0.1
         K, yd, _, mu_local, _, _ = init_target(loss, yy, None, (0.1, 0.5, 0.9))
         out["mu_" + loss] = comm.allreduce_bias(loss, yd, mu_local, K, (0.1, 0.5, 0.9))
+    # uneven shards (5001 rows over 2 ranks), row and column sampling: every rank must draw the same `js` in every round,
+    # because the ranks' histograms are added slot by slot; the row masks are per rank
+    from evotrees_b200.fit import Cache, make_rngs, sample_round
+    import evotrees_b200 as pkg
+    params = pkg.EvoTreeRegressor(loss="mse", rowsample=0.5, colsample=0.5, seed=77)
+    c = Cache()
+    c.nobs, c.nfeats, c.njs, c.use_mask = hi - lo, 40, 20, True
+    c.rng, c.rng_js = make_rngs(params.seed, rank)
+    draws = [sample_round(c, params) for _ in range(6)]
+    assert all(m.size == hi - lo for m, _ in draws)
+    out["js_rounds"] = np.stack([js for _, js in draws])
     np.savez(os.path.join(tmp, f"r{rank}.npz"), **out)
     dist.barrier()
     dist.destroy_process_group()
@@ -71,6 +82,7 @@ def test_two_rank_host_plumbing(tmp_path, orc, pkg):
     x = rng.random((n, f))
     y = (x @ np.array([1.0, -2.0, 0.5, 0.0]) + 0.1 * rng.normal(size=n)).astype(np.float32)
     K, yd, _, mu, _, _ = init_target("mse", y, None)
+    assert r0["js_rounds"].shape == (6, 20) and len({tuple(r) for r in r0["js_rounds"]}) > 1   # equal on both ranks (above), not constant
     np.testing.assert_allclose(r0["mu_mse"], mu, rtol=1e-6)
     K, yd, _, mu, _, _ = init_target("gaussian_mle", y, None)
     np.testing.assert_allclose(r0["mu_gaussian_mle"], mu, rtol=1e-5)
