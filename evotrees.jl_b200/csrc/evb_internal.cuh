@@ -234,6 +234,7 @@ void evb_nccl_destroy(evb_handle *h);
 
 // evb_stage.cu: pageable host memory -> device through a ring of pinned buffers filled by several host threads
 int32_t evb_h2d_staged(void *dst_dev, const void *src_host, size_t bytes, cudaStream_t st);
+int32_t evb_h2d_staged_strided(void *dst_dev, const void *src_host, size_t seg_bytes, size_t nseg, size_t stride, cudaStream_t st);
 
 // timing helpers (evb_api.cu)
 void evb_tic(evb_handle *h, int cls);

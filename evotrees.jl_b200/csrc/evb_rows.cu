@@ -533,6 +533,92 @@ __global__ void __launch_bounds__(256) k_predict(PredArgs a) {
     for (int k = 0; k < K; ++k) a.out[(size_t)k * a.nobs_total + a.row0 + i] = p[k];
 }
 
+
+// The same with everything a thread touches in shared memory: the CTA's rows of bins are staged once (coalesced
+// 16-byte loads, rows padded by one word so that equal byte offsets of different rows fall into different banks) and
+// the packed trees + their leaf tables stream through two shared-memory buffers of TB trees each: while the threads
+// walk the trees of one buffer, `cp.async` fills the other, so a traversal step costs two shared-memory loads and the
+// trip to L2 is off the critical path.  One thread = one row; trees are applied in order (the clamps of `predict!` do
+// not commute).  `tw` = words per tree in `trees` ([nnp] packed nodes, then [nnp * K] leaf values; nnp = nn rounded up
+// to a multiple of four so that every tree starts on a 16-byte boundary).  Used when 2 * TB trees fit beside the rows.
+template <int KMAX>
+__global__ void __launch_bounds__(1024) k_predict_staged(PredArgs a, const uint32_t *trees, int nnp, int rows_per_cta, int TB) {
+    extern __shared__ __align__(16) uint32_t s_pr[]; // [rows_per_cta][RS / 4 + 1] bins, then 2 x TB x tw tree words
+    const int rw = a.RS >> 2, rwp = rw + 1;
+    uint32_t *s_rows = s_pr;
+    const int K = a.K, tw = nnp * (1 + K);
+    uint32_t *s_trees = s_pr + (((size_t)rows_per_cta * rwp + 3) & ~(size_t)3);
+    const long long row0 = (long long)blockIdx.x * rows_per_cta;
+    const int nr = (int)min((long long)rows_per_cta, a.n - row0);
+    auto load_block = [&](int t0, int buf) { // trees t0 .. t0 + TB - 1 -> buffer `buf`, 16 bytes per copy
+        const int nt = min(TB, a.ntrees - t0);
+        const uint4 *src = reinterpret_cast<const uint4 *>(trees + (size_t)t0 * tw);
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(s_trees + (size_t)buf * TB * tw);
+        for (int c = threadIdx.x; c < nt * (tw >> 2); c += blockDim.x)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)c * 16u), "l"(src + c) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_block(0, 0);
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.xT + (size_t)row0 * a.RS);
+        const int cpr = a.RS >> 4, nchunk = nr * cpr;
+        for (int c = threadIdx.x; c < nchunk; c += blockDim.x) {
+            const uint4 v = src[c];
+            const int r = c / cpr, part = c - r * cpr;
+            uint32_t *d = s_rows + r * rwp + part * 4;
+            d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+        }
+    }
+    const bool act = (int)threadIdx.x < nr;
+    const long long i = row0 + threadIdx.x;
+    const uint8_t *xrow = reinterpret_cast<const uint8_t *>(s_rows + threadIdx.x * rwp);
+    float p[KMAX];
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k) p[k] = 0.0f;
+    int buf = 0;
+    for (int t0 = 0; t0 < a.ntrees; t0 += TB, buf ^= 1) {
+        const int nt = min(TB, a.ntrees - t0);
+        if (t0 + TB < a.ntrees) load_block(t0 + TB, buf ^ 1); // the other buffer was consumed before the last barrier
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads(); // this block's trees (and, the first time, the rows) are in place for everybody
+        if (act) {
+            for (int t = 0; t < nt; ++t) {
+                const uint32_t *pk = s_trees + ((size_t)buf * TB + t) * tw;
+                const int nid = traverse(pk, xrow);
+                if (a.leaf_idx) a.leaf_idx[(size_t)(t0 + t) * a.nobs_total + a.row0 + i] = (uint32_t)nid;
+                pred_add(a.loss, K, p, reinterpret_cast<const float *>(pk + nnp) + (size_t)(nid - 1) * K);
+            }
+        }
+        __syncthreads(); // everybody is done with this buffer: the next iteration refills it
+    }
+    if (!act) return;
+    if (a.apply_link) { // apply_prediction_link! (src/predict.jl:105-116)
+        if (a.loss == EVB_LOGLOSS) { for (int k = 0; k < K; ++k) p[k] = sigmoidf_(p[k]); }
+        else if (a.loss == EVB_GAUSSIAN_MLE || a.loss == EVB_LOGISTIC_MLE) { for (int k = 1; k < K; k += 2) p[k] = softplusf_(p[k]); }
+        else if (a.loss == EVB_POISSON || a.loss == EVB_GAMMA || a.loss == EVB_TWEEDIE) { for (int k = 0; k < K; ++k) p[k] = expf(p[k]); }
+        else if (a.loss == EVB_MLOGLOSS) {
+            float sm = 0.0f;
+            for (int k = 0; k < K; ++k) { p[k] = expf(p[k]); sm += p[k]; }
+            for (int k = 0; k < K; ++k) p[k] /= sm;
+        }
+    }
+    for (int k = 0; k < K; ++k) a.out[(size_t)k * a.nobs_total + a.row0 + i] = p[k];
+}
+
+// trees in the layout k_predict_staged streams: tree t = [nnp] packed nodes, then [nnp][K] leaf values (zero padded)
+__global__ void k_pack_staged(const uint32_t *packed, const float *leaf, int ntrees, int nn, int nnp, int K, uint32_t *out) {
+    const int tw = nnp * (1 + K);
+    const long long total = (long long)ntrees * tw;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(e / tw), o = (int)(e - (long long)t * tw);
+        uint32_t v = 0u;
+        if (o < nnp) { if (o < nn) v = packed[(size_t)t * nn + o]; }
+        else { const int q = o - nnp; if (q < nn * K) v = __float_as_uint(leaf[(size_t)t * nn * K + q]); }
+        out[e] = v;
+    }
+}
+
 __global__ void k_pack_trees(const long long *feat, const uint8_t *bin, const uint8_t *split, const uint8_t *feattypes,
                              long long total, uint32_t *packed) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -914,15 +1000,34 @@ static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntr
     const int RS = (nfeats + 31) / 32 * 32;
     const size_t es = x_dtype == EVB_F64 ? 8 : 4;
     const long long total = (long long)ntrees * nn;
-    const int64_t chunk = nobs < (int64_t)2 << 20 ? nobs : (int64_t)2 << 20;
-    DevBuf d_feat, d_bin, d_split, d_ft, d_packed, d_leaf, d_in, d_xT, d_out, d_lidx, d_edges;
-    cudaEvent_t ev[2] = {nullptr, nullptr};
+    const int64_t chunk = nobs < (int64_t)1 << 20 ? nobs : (int64_t)1 << 20;
+    // Blocks of `chunk` rows, two of everything: while the kernels of block k run, the host stages block k + 1 through
+    // the pinned ring (several threads) and the copy engine brings it over.
+    DevBuf d_feat, d_bin, d_split, d_ft, d_packed, d_leaf, d_in[2], d_xT[2], d_out, d_lidx, d_edges;
+    cudaEvent_t ev_free[2] = {nullptr, nullptr}, ev_k0[2] = {nullptr, nullptr}, ev_k1[2] = {nullptr, nullptr};
+    cudaStream_t cs = nullptr;
     float kernel_ms = 0.f;
+    // traversal out of shared memory when a tree (packed nodes + leaf table) fits a block of it
+    const int nnp = (nn + 3) & ~3;
+    const size_t treebytes = (size_t)nnp * (1 + K) * 4;
+    int rows_cta = 1024;
+    while (rows_cta > 128 && (size_t)rows_cta * (RS + 4) > (size_t)120 * 1024) rows_cta >>= 1;
+    const size_t rows_smem = ((size_t)rows_cta * (RS + 4) + 15) & ~(size_t)15;
+    int TB = rows_smem < (size_t)200 * 1024 ? (int)(((size_t)200 * 1024 - rows_smem) / (2 * treebytes)) : 0;
+    if (TB > 8) TB = 8;
+    const bool staged = TB >= 1 && RS % 16 == 0 && !getenv("EVB_PREDICT_DIRECT");
+    const size_t pred_smem = rows_smem + (size_t)2 * TB * treebytes;
+    DevBuf d_staged;
     auto body = [&]() -> int32_t {
-        EVB_CUDA(cudaEventCreate(&ev[0])); EVB_CUDA(cudaEventCreate(&ev[1]));
+        EVB_CUDA(cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking));
+        for (int q = 0; q < 2; ++q) {
+            EVB_CUDA(cudaEventCreateWithFlags(&ev_free[q], cudaEventDisableTiming));
+            EVB_CUDA(cudaEventCreate(&ev_k0[q])); EVB_CUDA(cudaEventCreate(&ev_k1[q]));
+            EVB_CUDA(d_in[q].alloc((size_t)chunk * nfeats * (x ? es : 1))); EVB_CUDA(d_xT[q].alloc((size_t)chunk * RS));
+            EVB_CUDA(cudaMemsetAsync(d_xT[q].p, 0, (size_t)chunk * RS, st));
+        }
         EVB_CUDA(d_feat.alloc(total * 8)); EVB_CUDA(d_bin.alloc(total)); EVB_CUDA(d_split.alloc(total));
         EVB_CUDA(d_packed.alloc(total * 4)); EVB_CUDA(d_leaf.alloc((size_t)total * K * 4));
-        EVB_CUDA(d_in.alloc((size_t)chunk * nfeats * (x ? es : 1))); EVB_CUDA(d_xT.alloc((size_t)chunk * RS));
         EVB_CUDA(d_out.alloc((size_t)nobs * K * 4));
         if (leaf_idx) EVB_CUDA(d_lidx.alloc((size_t)nobs * ntrees * 4));
         if (feattypes) { EVB_CUDA(d_ft.alloc(nfeats)); EVB_CUDA(cudaMemcpyAsync(d_ft.p, feattypes, nfeats, cudaMemcpyHostToDevice, st)); }
@@ -936,56 +1041,81 @@ static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntr
                                                                            feattypes ? d_ft.as<uint8_t>() : nullptr, total, d_packed.as<uint32_t>());
             EVB_CUDA(cudaGetLastError());
         }
-        EVB_CUDA(cudaMemsetAsync(d_xT.p, 0, (size_t)chunk * RS, st));
-        for (int64_t r0 = 0; r0 < nobs; r0 += chunk) {
+        if (staged && total > 0) {
+            EVB_CUDA(d_staged.alloc((size_t)ntrees * treebytes));
+            k_pack_staged<<<512, 256, 0, st>>>(d_packed.as<uint32_t>(), d_leaf.as<float>(), ntrees, nn, nnp, K, d_staged.as<uint32_t>());
+            EVB_CUDA(cudaGetLastError());
+        }
+        EVB_CUDA(cudaStreamSynchronize(st)); // trees, edges and the cleared row buffers are in place before the copy stream starts
+        int k = 0;
+        for (int64_t r0 = 0; r0 < nobs; r0 += chunk, ++k) {
+            const int q = k & 1;
             const int64_t nr = nobs - r0 < chunk ? nobs - r0 : chunk;
-            if (x) {
-                if (x_row_major) {
-                    EVB_CUDA(cudaMemcpyAsync(d_in.p, (const char *)x + (size_t)r0 * nfeats * es, (size_t)nr * nfeats * es, cudaMemcpyHostToDevice, st));
-                } else {
-                    EVB_CUDA(cudaMemcpy2DAsync(d_in.p, (size_t)chunk * es, (const char *)x + (size_t)r0 * es, (size_t)nobs * es, (size_t)nr * es,
-                                               (size_t)nfeats, cudaMemcpyHostToDevice, st));
-                }
-            } else {
-                EVB_CUDA(cudaMemcpy2DAsync(d_in.p, (size_t)chunk, x_bin + r0, (size_t)nobs, (size_t)nr, (size_t)nfeats, cudaMemcpyHostToDevice, st));
+            if (k >= 2) { // the kernels of block k - 2 are done with these buffers
+                EVB_CUDA(cudaEventSynchronize(ev_free[q]));
+                float ms = 0.f;
+                if (cudaEventElapsedTime(&ms, ev_k0[q], ev_k1[q]) == cudaSuccess) kernel_ms += ms;
             }
-            EVB_CUDA(cudaEventRecord(ev[0], st));
+            // rows r0 .. r0 + nr of every column (column-major input: one segment per feature), packed as [nfeats][nr]
+            if (x && x_row_major) EVB_CHECK(evb_h2d_staged(d_in[q].p, (const char *)x + (size_t)r0 * nfeats * es, (size_t)nr * nfeats * es, cs));
+            else if (x) EVB_CHECK(evb_h2d_staged_strided(d_in[q].p, (const char *)x + (size_t)r0 * es, (size_t)nr * es, (size_t)nfeats, (size_t)nobs * es, cs));
+            else EVB_CHECK(evb_h2d_staged_strided(d_in[q].p, x_bin + r0, (size_t)nr, (size_t)nfeats, (size_t)nobs, cs));
+            EVB_CUDA(cudaStreamSynchronize(cs));
+            EVB_CUDA(cudaEventRecord(ev_k0[q], st));
             if (x) {
                 const unsigned blocks = (unsigned)((nr + 255) / 256);
-                const long long ld = x_row_major ? nfeats : chunk;
+                const long long ld = x_row_major ? nfeats : nr;
                 if (x_dtype == EVB_F32)
-                    k_binarize_rows<float><<<blocks, 256, 256 * RS, st>>>(d_in.as<float>(), ld, x_row_major, nr, nfeats, d_edges.as<float>(), nedges, d_xT.as<uint8_t>(), RS);
+                    k_binarize_rows<float><<<blocks, 256, 256 * RS, st>>>(d_in[q].as<float>(), ld, x_row_major, nr, nfeats, d_edges.as<float>(), nedges, d_xT[q].as<uint8_t>(), RS);
                 else
-                    k_binarize_rows<double><<<blocks, 256, 256 * RS, st>>>(d_in.as<double>(), ld, x_row_major, nr, nfeats, d_edges.as<double>(), nedges, d_xT.as<uint8_t>(), RS);
+                    k_binarize_rows<double><<<blocks, 256, 256 * RS, st>>>(d_in[q].as<double>(), ld, x_row_major, nr, nfeats, d_edges.as<double>(), nedges, d_xT[q].as<uint8_t>(), RS);
                 EVB_CUDA(cudaGetLastError());
             } else {
-                EVB_CHECK(evb_launch_transpose(nullptr, d_in.as<uint8_t>(), chunk, nr, 0, nfeats, d_xT.as<uint8_t>(), RS, st));
+                EVB_CHECK(evb_launch_transpose(nullptr, d_in[q].as<uint8_t>(), nr, nr, 0, nfeats, d_xT[q].as<uint8_t>(), RS, st));
             }
             PredArgs a;
-            a.xT = d_xT.as<uint8_t>(); a.packed = d_packed.as<uint32_t>(); a.leaf = d_leaf.as<float>(); a.out = d_out.as<float>();
+            a.xT = d_xT[q].as<uint8_t>(); a.packed = d_packed.as<uint32_t>(); a.leaf = d_leaf.as<float>(); a.out = d_out.as<float>();
             a.leaf_idx = leaf_idx ? d_lidx.as<uint32_t>() : nullptr; a.n = nr; a.row0 = r0; a.nobs_total = nobs; a.RS = RS; a.K = K;
             a.loss = loss; a.ntrees = ntrees; a.nn = nn; a.apply_link = apply_link;
-            const unsigned blocks = (unsigned)((nr + 255) / 256);
-            if (K <= 1) k_predict<1><<<blocks, 256, 0, st>>>(a);
-            else if (K <= 2) k_predict<2><<<blocks, 256, 0, st>>>(a);
-            else if (K <= 8) k_predict<8><<<blocks, 256, 0, st>>>(a);
-            else k_predict<64><<<blocks, 256, 0, st>>>(a);
+            if (staged) {
+                const unsigned blocks = (unsigned)((nr + rows_cta - 1) / rows_cta);
+#define EVB_PRED_STAGED(KM) do { \
+                    EVB_CUDA(cudaFuncSetAttribute(k_predict_staged<KM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pred_smem)); \
+                    k_predict_staged<KM><<<blocks, rows_cta, pred_smem, st>>>(a, d_staged.as<uint32_t>(), nnp, rows_cta, TB); } while (0)
+                if (K <= 1) EVB_PRED_STAGED(1);
+                else if (K <= 2) EVB_PRED_STAGED(2);
+                else if (K <= 8) EVB_PRED_STAGED(8);
+                else EVB_PRED_STAGED(64);
+#undef EVB_PRED_STAGED
+            } else {
+                const unsigned blocks = (unsigned)((nr + 255) / 256);
+                if (K <= 1) k_predict<1><<<blocks, 256, 0, st>>>(a);
+                else if (K <= 2) k_predict<2><<<blocks, 256, 0, st>>>(a);
+                else if (K <= 8) k_predict<8><<<blocks, 256, 0, st>>>(a);
+                else k_predict<64><<<blocks, 256, 0, st>>>(a);
+            }
             EVB_CUDA(cudaGetLastError());
-            EVB_CUDA(cudaEventRecord(ev[1], st));
-            EVB_CUDA(cudaEventSynchronize(ev[1]));
-            float ms = 0.f;
-            cudaEventElapsedTime(&ms, ev[0], ev[1]);
-            kernel_ms += ms;
+            EVB_CUDA(cudaEventRecord(ev_k1[q], st));
+            EVB_CUDA(cudaEventRecord(ev_free[q], st));
         }
         EVB_CUDA(cudaMemcpyAsync(out, d_out.p, (size_t)nobs * K * 4, cudaMemcpyDeviceToHost, st));
         if (leaf_idx) EVB_CUDA(cudaMemcpyAsync(leaf_idx, d_lidx.p, (size_t)nobs * ntrees * 4, cudaMemcpyDeviceToHost, st));
         EVB_CUDA(cudaStreamSynchronize(st));
+        for (int q = 0; q < 2 && q < k; ++q) { // the last (up to) two blocks have not been read yet
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, ev_k0[q], ev_k1[q]) == cudaSuccess) kernel_ms += ms;
+        }
         return EVB_OK;
     };
     int32_t rc = body();
     cudaStreamSynchronize(st);
+    if (cs) { cudaStreamSynchronize(cs); cudaStreamDestroy(cs); }
     if (ms_out) *ms_out = kernel_ms;
-    for (cudaEvent_t e : ev) if (e) cudaEventDestroy(e);
+    for (int q = 0; q < 2; ++q) {
+        if (ev_free[q]) cudaEventDestroy(ev_free[q]);
+        if (ev_k0[q]) cudaEventDestroy(ev_k0[q]);
+        if (ev_k1[q]) cudaEventDestroy(ev_k1[q]);
+    }
     cudaStreamDestroy(st);
     return rc;
 }

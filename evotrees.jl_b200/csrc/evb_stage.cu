@@ -32,9 +32,20 @@ int stage_threads() {
     return n;
 }
 
-void parallel_memcpy(char *dst, const char *src, size_t bytes) {
+// copies bytes [off, off + len) of the packed sequence (nseg segments of seg_bytes, segment k starting at src + k * stride)
+void gather_copy(char *dst, const char *src, size_t seg_bytes, size_t stride, size_t off, size_t len) {
+    size_t p = off;
+    const size_t end = off + len;
+    while (p < end) {
+        const size_t seg = p / seg_bytes, within = p - seg * seg_bytes;
+        const size_t n = seg_bytes - within < end - p ? seg_bytes - within : end - p;
+        memcpy(dst + (p - off), src + seg * stride + within, n);
+        p += n;
+    }
+}
+void parallel_gather(char *dst, const char *src, size_t seg_bytes, size_t stride, size_t off, size_t bytes) {
     const int nt = bytes < ((size_t)4 << 20) ? 1 : stage_threads();
-    if (nt == 1) { memcpy(dst, src, bytes); return; }
+    if (nt == 1) { gather_copy(dst, src, seg_bytes, stride, off, bytes); return; }
     std::thread th[64];
     const size_t per = (bytes / nt + 4095) & ~(size_t)4095;
     int started = 0;
@@ -42,26 +53,25 @@ void parallel_memcpy(char *dst, const char *src, size_t bytes) {
         const size_t o = (size_t)t * per;
         if (o >= bytes) break;
         const size_t len = bytes - o < per ? bytes - o : per;
-        th[started++] = std::thread([=] { memcpy(dst + o, src + o, len); });
+        th[started++] = std::thread([=] { gather_copy(dst + o, src, seg_bytes, stride, off + o, len); });
     }
     for (int t = 0; t < started; ++t) th[t].join();
 }
 
 } // namespace
 
-// Copies `bytes` of pageable host memory to the device on stream `st`.  Returns when the host memory has been read
-// (the caller may reuse or free it); the last device copies may still be in flight on `st`.  One copy at a time per
-// process (the ring is shared); concurrent callers wait for each other.
-int32_t evb_h2d_staged(void *dst_dev, const void *src_host, size_t bytes, cudaStream_t st) {
+// Copies nseg segments of seg_bytes (segment k at src_host + k * stride) of pageable host memory to the device, packed
+// back to back at dst_dev, on stream `st`: a block of rows of a column-major matrix, or (nseg = 1) a plain range.
+// Returns when the host memory has been read (the caller may reuse or free it) and the ring has drained.  One copy at
+// a time per device (the ring is shared); concurrent callers wait for each other.
+int32_t evb_h2d_staged_strided(void *dst_dev, const void *src_host, size_t seg_bytes, size_t nseg, size_t stride, cudaStream_t st) {
+    const size_t bytes = seg_bytes * nseg;
     if (bytes == 0) return EVB_OK;
-    if (bytes < ((size_t)1 << 20) || getenv("EVB_STAGE_OFF")) { // small: the driver's own staging is as good
-        EVB_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, st));
-        return EVB_OK;
-    }
     int dev = 0;
     EVB_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) {
-        EVB_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, st));
+    if (bytes < ((size_t)1 << 20) || getenv("EVB_STAGE_OFF") || dev < 0 || dev >= 64) { // small: the driver's own staging is as good
+        if (nseg == 1) EVB_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, st));
+        else EVB_CUDA(cudaMemcpy2DAsync(dst_dev, seg_bytes, src_host, stride, seg_bytes, nseg, cudaMemcpyHostToDevice, st));
         return EVB_OK;
     }
     StageRing &g_ring = g_rings[dev];
@@ -79,13 +89,17 @@ int32_t evb_h2d_staged(void *dst_dev, const void *src_host, size_t bytes, cudaSt
     for (size_t off = 0; off < bytes; off += STAGE_BYTES, b = (b + 1) % STAGE_NB) {
         const size_t len = bytes - off < STAGE_BYTES ? bytes - off : STAGE_BYTES;
         if (g_ring.used[b]) EVB_CUDA(cudaEventSynchronize(g_ring.ev[b])); // the copy that last used this buffer has left it
-        parallel_memcpy(static_cast<char *>(g_ring.buf[b]), src + off, len);
+        parallel_gather(static_cast<char *>(g_ring.buf[b]), src, seg_bytes, stride, off, len);
         EVB_CUDA(cudaMemcpyAsync(dst + off, g_ring.buf[b], len, cudaMemcpyHostToDevice, st));
         EVB_CUDA(cudaEventRecord(g_ring.ev[b], st));
         g_ring.used[b] = true;
     }
-    // the ring may be reused by the next call (possibly on another stream or device) right away: drain it
+    // the ring may be reused by the next call (possibly on another stream) right away: drain it
     for (int q = 0; q < STAGE_NB; ++q)
         if (g_ring.used[q]) { EVB_CUDA(cudaEventSynchronize(g_ring.ev[q])); g_ring.used[q] = false; }
     return EVB_OK;
+}
+
+int32_t evb_h2d_staged(void *dst_dev, const void *src_host, size_t bytes, cudaStream_t st) {
+    return evb_h2d_staged_strided(dst_dev, src_host, bytes, 1, bytes, st);
 }

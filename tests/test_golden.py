@@ -50,7 +50,7 @@ def test_library_matches_golden(pkg, loss):
             assert np.array_equal(t.split.astype(np.uint8), g[f"split{r}"])
             assert np.array_equal(cache.nidx(from_partition=True), g[f"nidx{r}"])
             # 1e-5 relative: gains, node weights, leaf values, predictions
-            np.testing.assert_allclose(t.gain, g[f"gain{r}"], rtol=1e-4, atol=1e-6)
+            np.testing.assert_allclose(t.gain, g[f"gain{r}"], rtol=1e-5, atol=1e-6)
             np.testing.assert_allclose(t.w, g[f"w{r}"], rtol=1e-5, atol=1e-6)
             np.testing.assert_allclose(t.pred, g[f"leaf{r}"], rtol=1e-5, atol=1e-6)
             np.testing.assert_allclose(cache.pred(), g[f"pred{r}"], rtol=1e-5, atol=1e-5)
