@@ -5,6 +5,10 @@
 #include <stdlib.h>
 #include <new>
 #include <algorithm>
+#include <nvtx3/nvToolsExt.h>
+
+static const char *const g_timer_names[EVB_NTIMERS] = {"evb:grads", "evb:rows_init", "evb:hist", "evb:hist_reduce", "evb:allreduce", "evb:scan",
+                                                        "evb:partition", "evb:plan", "evb:finalize", "evb:d2h", "evb:h2d", "evb:tree"};
 
 int32_t evb_launch_check_bins(evb_handle *h);
 int32_t evb_launch_init_state(evb_handle *h, const float *w_dev, const float *pred0_dev, const float *mu_dev);
@@ -20,14 +24,22 @@ void evb_set_error(const char *fmt, ...) {
     va_end(ap);
 }
 extern "C" const char *evb_last_error(void) { return g_err; }
+int evb_hist_mode_env() {
+    const char *e = getenv("EVB_HIST_MODE");
+#ifdef EVB_DIAG
+    return e ? atoi(e) : 1;
+#else
+    return e ? (atoi(e) & 1) : 1;
+#endif
+}
 extern "C" int32_t evb_version(void) { return EVB_VERSION; }
 
 // ---- timing -----------------------------------------------------------------------------------------
 // tic/toc bracket one kernel class (brackets do not nest); the events are read after the stream is
 // synchronised at the end of evb_grow_tree.
 void evb_tic(evb_handle *h, int cls) {
-    (void)cls;
     if (!h->timing) return;
+    nvtxRangePushA(g_timer_names[cls]); // with EVB_FLAG_TIMING every kernel class is also an NVTX range on the host timeline
     while (h->ev_used + 2 > h->ev.size()) {
         cudaEvent_t e;
         if (cudaEventCreate(&e) != cudaSuccess) { h->timing = false; return; }
@@ -38,6 +50,7 @@ void evb_tic(evb_handle *h, int cls) {
 void evb_toc(evb_handle *h, int cls) {
     h->tm.launches[cls] += 1;
     if (!h->timing) return;
+    nvtxRangePop();
     cudaEventRecord(h->ev[h->ev_used + 1], h->st);
     h->ev_class.push_back(cls);
     h->ev_used += 2;
@@ -66,8 +79,14 @@ struct BusyGuard {
     if (!_guard.ok) { evb_set_error("handle is in use by another thread"); return EVB_ERR_BUSY; } \
     EVB_CUDA(cudaSetDevice((h)->dev))
 
+// Failure injection for the tests of the error paths: EVB_TEST_FAIL_ALLOC=k makes the k-th device allocation of the
+// next evb_create* of this thread fail as if the device were out of memory (nothing is allocated, nothing faults).
+static thread_local int g_alloc_countdown = 0;
 template <typename T>
-static cudaError_t dalloc(T **p, size_t count) { return cudaMalloc((void **)p, (count ? count : 1) * sizeof(T)); }
+static cudaError_t dalloc(T **p, size_t count) {
+    if (g_alloc_countdown > 0 && --g_alloc_countdown == 0) { *p = nullptr; return cudaErrorMemoryAllocation; }
+    return cudaMalloc((void **)p, (count ? count : 1) * sizeof(T));
+}
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -156,7 +175,7 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
     h->dev = p->device; h->y_dtype = y_dtype; h->ycols = ycols;
     h->timing = (p->flags & EVB_FLAG_TIMING) != 0;
     h->world = 1; h->rank = 0; h->F = nfeats;
-    { const char *e = getenv("EVB_HIST_MODE"); h->hist_mode = e ? atoi(e) : 1; }
+    h->hist_mode = evb_hist_mode_env();
     cudaDeviceProp prop;
     EVB_CUDA(cudaGetDeviceProperties(&prop, h->dev));
     if (prop.major < 10) {
@@ -341,7 +360,9 @@ static int32_t create_common(evb_handle **out, const evb_params *p, int64_t nobs
     evb_handle *h = new (std::nothrow) evb_handle();
     if (!h) { evb_set_error("out of host memory"); return EVB_ERR_ARG; }
     memset(&h->tm, 0, sizeof(h->tm));
+    { const char *e = getenv("EVB_TEST_FAIL_ALLOC"); g_alloc_countdown = e ? atoi(e) : 0; }
     int32_t rc = create_impl(h, p, nobs, nfeats, x_bin, x, x_dtype, edges, nedges, y, y_dtype, ycols, w, pred0, mu, feattypes, monotone);
+    g_alloc_countdown = 0;
     if (rc != EVB_OK) { free_handle(h); return rc; }
     *out = h;
     return EVB_OK;
@@ -729,6 +750,26 @@ extern "C" int32_t evb_comm_ipc_import(evb_handle *h, const uint8_t *blobs) {
     }
     h->p2p = true;
     return EVB_OK;
+}
+
+extern "C" int32_t evb_test_peer_timeout(evb_handle *h, int32_t max_polls) {
+    EVB_ENTER(h);
+    if (max_polls < 1 || max_polls > 20000000) { evb_set_error("evb_test_peer_timeout: max_polls outside 1..20000000"); return EVB_ERR_ARG; }
+    if (h->pending > 0) { evb_set_error("evb_test_peer_timeout: a tree is in flight"); return EVB_ERR_BUSY; }
+    int *flags = nullptr;
+    EVB_CUDA(cudaMalloc((void **)&flags, 16 * sizeof(int)));
+    int derr = 0;
+    cudaError_t e = cudaMemsetAsync(flags, 0, 16 * sizeof(int), h->st);
+    int32_t rc = e == cudaSuccess ? evb_launch_lonely_barrier(h, flags, flags + 8, (unsigned)max_polls) : EVB_ERR_CUDA;
+    if (rc == EVB_OK) e = cudaMemcpyAsync(&derr, h->d_err, sizeof(int), cudaMemcpyDeviceToHost, h->st);
+    if (rc == EVB_OK && e == cudaSuccess) e = cudaStreamSynchronize(h->st);
+    cudaMemsetAsync(h->d_err, 0, sizeof(int), h->st); // the handle stays usable
+    cudaStreamSynchronize(h->st);
+    cudaFree(flags);
+    if (rc != EVB_OK || e != cudaSuccess) { evb_set_error("evb_test_peer_timeout: CUDA error %s", cudaGetErrorString(e)); return EVB_ERR_CUDA; }
+    if (derr == EVB_DERR_PEER) { evb_set_error("device self-check failed (code %d: bounded wait for the other ranks expired)", derr); return EVB_ERR_DEVICE; }
+    evb_set_error("evb_test_peer_timeout: the wait did not run out (error word %d)", derr);
+    return EVB_ERR_ARG;
 }
 
 extern "C" int32_t evb_set_timing(evb_handle *h, int32_t on) {

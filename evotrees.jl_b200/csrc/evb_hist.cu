@@ -5,10 +5,10 @@
 //   * The rows of every build node are a contiguous segment of a row-index list.  The concatenation of
 //     all build segments of a level is cut into gridDim.x equal row ranges, one per CTA, so every CTA
 //     streams the same number of rows whatever the node sizes are.  A (CTA, node) intersection is a "piece".
-//   * One producer warp stages tiles of 32 rows: each lane issues two TMA bulk copies
-//     (cp.async.bulk global->shared, completion on an mbarrier): the row of the observation-major bin
-//     matrix (RS bytes) and the row's gradient record (GS floats).  Consumers never touch global memory
-//     in the inner loop.
+//   * One producer warp stages tiles of 32 rows: the row of the observation-major bin matrix (RS bytes) and the
+//     row's gradient record (GS floats), with 16-byte `cp.async` copies that arrive on an mbarrier (the default:
+//     measured 7.95 ms per tree at 10M x 100 against 12.16 ms for the other staging path, one TMA bulk copy
+//     per row, which EVB_HIST_MODE=0 still selects).  Consumers never touch global memory in the inner loop.
 //   * Each consumer warp owns one "unit": 32 feature slots (lane = feature) x up to 4 gradient channels,
 //     with a private image img[channel][bin][lane] in shared memory.  Lane l only ever touches bank l, so
 //     the accumulation is a plain load/add/store: no atomics, no bank conflicts, and a fixed summation
@@ -18,6 +18,7 @@
 //     bit-reproducible from run to run, and transposes them to hcomp[slot][feature][channel][bin].
 //   Every wait on an mbarrier is bounded; on expiry the kernel records an error code and returns.
 #include "evb_internal.cuh"
+#include <mutex>
 #include <stdlib.h>
 
 namespace {
@@ -73,7 +74,7 @@ struct HistArgs {
     int *err;
     int RS, GS, F, nbins, C, NFG, U, UB, stages, PG;
     uint32_t img_floats;
-    int mode;   // bit 0: stage rows with cp.async (LDGSTS) instead of TMA bulk copies; bit 4: diagnostic, skip the accumulation
+    int mode;   // bit 0: stage rows with cp.async (LDGSTS) instead of TMA bulk copies (builds with -DEVB_DIAG: bit 4 skips the accumulation)
     int contig; // 1 when feature slot s is feature s (no column sample): a lane's FPL bins are adjacent bytes of the row
 };
 
@@ -379,7 +380,11 @@ __global__ void __launch_bounds__((EVB_MAX_UNITS_PER_BLOCK + 1) * 32) k_hist(His
                 if (!mbar_wait(&full[st], (it / S) & 1u, a.err, EVB_DERR_WAIT_FULL)) return;
                 const uint32_t xs = stage0_s + (uint32_t)st * stage_bytes;
                 const uint32_t gs = xs + xbytes + ct * 16;
-                if (act && !(a.mode & 16)) {
+#ifdef EVB_DIAG
+                if (act && !(a.mode & 16)) { // profiling builds only: mode bit 4 stages the rows and skips the accumulation
+#else
+                if (act) {
+#endif
                     // the common strides are passed as literals so that the row offsets fold into the instructions
                     if (a.contig && RS == 128 && GS == 4) accumulate_tile<BP, NCH, FPL, true>(xs, gs, nrows, 128, 16, foff, u0, u1);
                     else if (a.contig && RS == 64 && GS == 8) accumulate_tile<BP, NCH, FPL, true>(xs, gs, nrows, 64, 32, foff, u0, u1);
@@ -464,9 +469,6 @@ __device__ __forceinline__ void red_row(uint32_t addr, const uint32_t (&w)[4]) {
     red_off<0>(addr, w[0]);
     red_off<WSZ>(addr, w[1]);
     if constexpr (NW == 4) { red_off<2 * WSZ>(addr, w[2]); red_off<3 * WSZ>(addr, w[3]); }
-}
-__device__ __forceinline__ void lds_v4(uint32_t addr, uint32_t (&w)[4]) {
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
 }
 // All rows of one staged tile.  4 * REP rows at a time.  With REP = 1 lane (k = lane & 7, rr = lane >> 3) loads the
 // 32-bit word with the bins of features 4k .. 4k+3 of row r + rr -- one conflict-free load brings the 128 bins of
@@ -582,7 +584,11 @@ __global__ void __launch_bounds__(EVB_MAX_UNITS_PER_BLOCK * QT * 32) k_histq(His
     const int32_t *gq = reinterpret_cast<const int32_t *>(a.grad);
     const size_t RS = a.RS;
     const uint32_t team_bar = 1 + team, unit_bar = 1 + QT + uw;
-    const bool skip_acc = (a.mode & 16) != 0; // diagnostic: stage only
+#ifdef EVB_DIAG
+    const bool skip_acc = (a.mode & 16) != 0; // profiling builds only: stage the rows, skip the accumulation
+#else
+    constexpr bool skip_acc = false;
+#endif
     const int team_threads = nact * 32;
 
     long long pos = lo;
@@ -1232,6 +1238,7 @@ struct NoAllocDev {
     bool ready = false;
 };
 NoAllocDev g_noalloc_dev[64];
+std::mutex g_noalloc_mu;
 
 int32_t rows_hist_check_args(int32_t device, const void *x_rows, int64_t nobs, int32_t nfeats, int32_t row_stride, int32_t nbins,
                              const void *grad, int32_t nch, const void *rows, int64_t nrows, const void *out) {
@@ -1314,8 +1321,7 @@ extern "C" int32_t evb_hist_rows(int32_t device, void *stream, const uint8_t *x_
         evb_set_error("evb_hist_rows: out of device memory");
         rc = EVB_ERR_CUDA;
     } else {
-        const char *e = getenv("EVB_HIST_MODE");
-        rc = rows_hist_run(device, st, x_rows, nfeats, row_stride, nbins, grad, nch, rows, nrows, out, scratch, floats, plan, js, e ? atoi(e) : 1);
+        rc = rows_hist_run(device, st, x_rows, nfeats, row_stride, nbins, grad, nch, rows, nrows, out, scratch, floats, plan, js, evb_hist_mode_env());
     }
     cudaStreamSynchronize(st);
     if (scratch) cudaFree(scratch);
@@ -1334,15 +1340,17 @@ extern "C" int32_t evb_hist_rows_noalloc(int32_t device, void *stream, const uin
     }
     EVB_CUDA(cudaSetDevice(device));
     NoAllocDev &d = g_noalloc_dev[device];
-    if (!d.ready) {
+    {
         // once per device, with that device current: the symbols' names are host-side stand-ins, the kernels need
-        // the device addresses
-        EVB_CUDA(cudaGetSymbolAddress((void **)&d.scratch, g_noalloc_scratch));
-        EVB_CUDA(cudaGetSymbolAddress((void **)&d.plan, g_noalloc_plan));
-        EVB_CUDA(cudaGetSymbolAddress((void **)&d.js, g_noalloc_js));
-        d.ready = true;
+        // the device addresses.  The lock makes two host threads that call for the first time at once safe.
+        std::lock_guard<std::mutex> lock(g_noalloc_mu);
+        if (!d.ready) {
+            EVB_CUDA(cudaGetSymbolAddress((void **)&d.scratch, g_noalloc_scratch));
+            EVB_CUDA(cudaGetSymbolAddress((void **)&d.plan, g_noalloc_plan));
+            EVB_CUDA(cudaGetSymbolAddress((void **)&d.js, g_noalloc_js));
+            d.ready = true;
+        }
     }
-    const char *e = getenv("EVB_HIST_MODE");
     return rows_hist_run(device, (cudaStream_t)stream, x_rows, nfeats, row_stride, nbins, grad, nch, rows, nrows, out, d.scratch,
-                         NOALLOC_SCRATCH_FLOATS, d.plan, d.js, e ? atoi(e) : 1);
+                         NOALLOC_SCRATCH_FLOATS, d.plan, d.js, evb_hist_mode_env());
 }

@@ -225,6 +225,7 @@ int32_t evb_launch_q2_reduce(evb_handle *h, int level);
 int32_t evb_launch_tree_reset(evb_handle *h);
 int32_t evb_launch_scan(evb_handle *h, int level);
 int32_t evb_launch_partition(evb_handle *h, int level); // plan + flags + prefix (+allreduce) + level plan + scatter
+int32_t evb_launch_lonely_barrier(evb_handle *h, int *flags, int *seq, unsigned max_polls);
 // evb_nccl.cpp
 int32_t evb_nccl_unique_id(uint8_t id[128]);
 int32_t evb_nccl_init(evb_handle *h, const uint8_t id[128], int rank, int world);
@@ -236,6 +237,8 @@ void evb_nccl_destroy(evb_handle *h);
 int32_t evb_h2d_staged(void *dst_dev, const void *src_host, size_t bytes, cudaStream_t st);
 int32_t evb_h2d_staged_strided(void *dst_dev, const void *src_host, size_t seg_bytes, size_t nseg, size_t stride, cudaStream_t st);
 
+// EVB_HIST_MODE of the environment, reduced to the documented values (0: TMA bulk staging, 1: cp.async staging)
+int evb_hist_mode_env();
 // timing helpers (evb_api.cu)
 void evb_tic(evb_handle *h, int cls);
 void evb_toc(evb_handle *h, int cls);

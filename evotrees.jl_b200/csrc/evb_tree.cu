@@ -550,6 +550,7 @@ struct BarrierArgs {
     int *err;
     int world, rank;
     int *seq_dev; // barriers passed so far: kept on the device so that a replayed CUDA graph keeps counting
+    unsigned max_polls; // polls of ~100 ns before the wait gives up with EVB_DERR_PEER (20 M: about two seconds)
 };
 __global__ void k_peer_barrier(BarrierArgs a) {
     const int t = threadIdx.x;
@@ -561,7 +562,7 @@ __global__ void k_peer_barrier(BarrierArgs a) {
     *(volatile int *)(a.peer_flags[t] + a.rank) = seq;
     __threadfence_system();
     volatile int *mine = a.flags_local + t;
-    for (unsigned it = 0; it < 20000000u; ++it) {
+    for (unsigned it = 0; it < a.max_polls; ++it) {
         if (*mine - seq >= 0) { __threadfence_system(); return; }
         if ((it & 1023u) == 1023u && *(volatile int *)a.err != 0) return;
         __nanosleep(100);
@@ -838,6 +839,19 @@ static int32_t launch_peer_barrier(evb_handle *h) {
     BarrierArgs b;
     for (int q = 0; q < EVB_MAX_PEERS; ++q) b.peer_flags[q] = q < h->world ? h->peer_flags[q] : nullptr;
     b.flags_local = h->peer_flags[h->rank]; b.err = h->d_err; b.world = h->world; b.rank = h->rank; b.seq_dev = h->d_barrier_seq;
+    b.max_polls = 20000000u;
+    k_peer_barrier<<<1, 32, 0, h->st>>>(b);
+    EVB_CUDA(cudaGetLastError());
+    return EVB_OK;
+}
+
+// Diagnostic: one flag barrier of a two-rank world whose second rank does not exist, on the handle's own GPU: rank 1's
+// flag is never written, so the wait runs out after `max_polls` polls and the kernel leaves EVB_DERR_PEER in the
+// error word -- the path a sharded run takes when a peer stops answering, without a second GPU and without a hang.
+int32_t evb_launch_lonely_barrier(evb_handle *h, int *flags, int *seq, unsigned max_polls) {
+    BarrierArgs b;
+    for (int q = 0; q < EVB_MAX_PEERS; ++q) b.peer_flags[q] = q < 2 ? flags : nullptr;
+    b.flags_local = flags; b.err = h->d_err; b.world = 2; b.rank = 0; b.seq_dev = seq; b.max_polls = max_polls;
     k_peer_barrier<<<1, 32, 0, h->st>>>(b);
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;

@@ -57,7 +57,7 @@ enum evb_loss { EVB_MSE = 0, EVB_LOGLOSS = 1, EVB_MLOGLOSS = 2, EVB_GAUSSIAN_MLE
 enum evb_dtype { EVB_F32 = 0, EVB_U32 = 1, EVB_F64 = 2 };
 
 /* flags of evb_params.flags */
-#define EVB_FLAG_TIMING 1u         /* record a CUDA-event pair around every kernel class (see evb_get_timings) */
+#define EVB_FLAG_TIMING 1u         /* record a CUDA-event pair (and an NVTX range) around every kernel class (see evb_get_timings) */
 #define EVB_FLAG_FULL_PARTITION 2u /* also partition the rows of the last split level (only evb_get_nidx(.., 1) reads that) */
 #define EVB_FLAG_KEEP_ALL_HIST 4u  /* retain the histograms of the last split level too (for evb_get_hist)               */
 
@@ -199,7 +199,16 @@ EVB_API int32_t evb_eval_sums(evb_handle *h, double sums[2]);
 EVB_API int32_t evb_eval_get_pred(evb_handle *h, float *pred /* [K x nobs_eval] */);
 EVB_API int32_t evb_eval_detach(evb_handle *h);
 
-/* Switches the per-kernel CUDA-event timing of EVB_FLAG_TIMING on or off (timed trees run without graphs). */
+/*
+ * Diagnostic of the failure path of sharded runs (no counterpart in the reference, which is single-GPU): runs one flag
+ * barrier of a two-rank world whose second rank does not exist, on the handle's own GPU.  The wait gives up after
+ * max_polls polls of about 100 ns each and the call returns EVB_ERR_DEVICE with the message of the expired wait; the
+ * handle stays usable.  Nothing hangs or faults: it exercises what a sharded run does when a peer stops answering.
+ */
+EVB_API int32_t evb_test_peer_timeout(evb_handle *h, int32_t max_polls);
+
+/* Switches the per-kernel CUDA-event timing of EVB_FLAG_TIMING on or off (timed trees run without graphs); with it
+ * on, every kernel class is also an NVTX range ("evb:hist", "evb:scan", ...). */
 EVB_API int32_t evb_set_timing(evb_handle *h, int32_t on);
 
 /* State read-back for parity checks (each synchronises the handle's stream). */
@@ -279,8 +288,11 @@ EVB_API int32_t evb_hist_rows(int32_t device, void *stream, const uint8_t *x_row
  * every GPU that loads the library (held until the process exits), so:
  *   - limits: nfeats <= 1024, nbins <= 255, nch <= 4, and two partial images (one per feature group of 32 features:
  *     32 x nbins x nch floats, per group) must fit in the 8 MiB; larger problems are rejected with EVB_ERR_LIMIT;
- *   - the first call on a device looks up the device addresses of that block (cudaGetSymbolAddress); make that first
- *     call outside any stream capture;
+ *   - the first call on a device looks up the device addresses of that block (cudaGetSymbolAddress), under a lock, so
+ *     two host threads may make it at once;
+ *   - like evb_hist_rows the call waits for its work (it synchronises the stream to read the kernels' error word back),
+ *     so it must never be made while the stream is being captured into a CUDA graph -- neither the first call nor a
+ *     later one;
  *   - all calls on one GPU share the block and it keeps the previous call's contents: every value that is read is
  *     rewritten by the same call first, but two calls that overlap in time on the same GPU race with each other.
  *     Serialise them (one stream, or events).

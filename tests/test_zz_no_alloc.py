@@ -40,6 +40,33 @@ def test_noalloc_matches_allocating_entry_point_twice_in_a_row(pkg):
     assert_hist_close(again, reference_hist(x, g, rows, nfeats, nbins, nch), g)
 
 
+def test_noalloc_leaves_the_free_device_memory_untouched(pkg):
+    """The promise itself: with the inputs and the output already on the device, a call changes nothing about the free
+    device memory -- neither while it runs (nothing it could have allocated is left behind) nor afterwards."""
+    import ctypes as C
+    import torch
+    from evotrees_b200 import _lib
+    lib = _lib.lib()
+    n, nfeats, nbins, nch, nrows, seed = PROBLEMS[1]
+    x, g, rows = make_inputs(n, nfeats, nbins, nch, nrows, seed)
+    dev = torch.device("cuda", 0)
+    xd, gd = torch.from_numpy(x).to(dev), torch.from_numpy(g).to(dev)
+    rd = torch.from_numpy(rows.view(np.int32)).to(dev)
+    out = torch.zeros((nfeats, nch, nbins), dtype=torch.float64, device=dev)
+
+    def run():
+        return lib.evb_hist_rows_noalloc(C.c_int32(0), C.c_void_p(0), C.c_void_p(xd.data_ptr()), C.c_int64(n), C.c_int32(nfeats),
+                                         C.c_int32(x.shape[1]), C.c_int32(nbins), C.c_void_p(gd.data_ptr()), C.c_int32(nch),
+                                         C.c_void_p(rd.data_ptr()), C.c_int64(rows.size), C.c_void_p(out.data_ptr()))
+
+    _lib.check(run())                       # first call on the device (address look-up, kernel attributes)
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(0)[0]
+    _lib.check(run())
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(0)[0] == free_before
+
+
 def test_noalloc_rejects_sizes_beyond_its_block(pkg):
     import torch
     from evotrees_b200 import _lib
