@@ -534,20 +534,33 @@ __global__ void __launch_bounds__(256) k_predict(PredArgs a) {
 }
 
 
-// The same with everything a thread touches in shared memory: the CTA's rows of bins are staged once (coalesced
-// 16-byte loads, rows padded by one word so that equal byte offsets of different rows fall into different banks) and
-// the packed trees + their leaf tables stream through two shared-memory buffers of TB trees each: while the threads
-// walk the trees of one buffer, `cp.async` fills the other, so a traversal step costs two shared-memory loads and the
-// trip to L2 is off the critical path.  One thread = one row; trees are applied in order (the clamps of `predict!` do
-// not commute).  `tw` = words per tree in `trees` ([nnp] packed nodes, then [nnp * K] leaf values; nnp = nn rounded up
-// to a multiple of four so that every tree starts on a 16-byte boundary).  Used when 2 * TB trees fit beside the rows.
+// The same with everything a thread touches in shared memory: the CTA's rows of bins are staged once, word-major
+// ([word of the row][row]: thread t only ever reads column t, so its loads never conflict with its neighbours'
+// whatever features the trees test), and the packed trees + their leaf tables stream through two shared-memory buffers
+// of TB trees each: while the threads walk the trees of one buffer, `cp.async` fills the other, so a traversal step
+// costs two shared-memory loads and the trip to L2 is off the critical path.  One thread = one row; trees are applied
+// in order (the clamps of `predict!` do not commute).  `tw` = words per tree in `trees` ([nnp] packed nodes, then
+// [nnp * K] leaf values; nnp = nn rounded up to a multiple of four so that every tree starts on a 16-byte boundary).
+// Used when 2 * TB trees fit beside the rows.
+__device__ __forceinline__ int traverse_wm(const uint32_t *packed, const uint32_t *xcol, int rows) {
+    int nid = 1;
+    uint32_t pk = packed[0];
+    while ((pk >> 24) & 1u) {
+        const uint32_t f = pk & 0xffffu, bin = (pk >> 16) & 0xffu;
+        const uint32_t x = (xcol[(f >> 2) * rows] >> (8u * (f & 3u))) & 0xffu;
+        const bool cond = ((pk >> 25) & 1u) ? (x <= bin) : (x == bin);
+        nid = (nid << 1) + (cond ? 0 : 1);
+        pk = packed[nid - 1];
+    }
+    return nid;
+}
 template <int KMAX>
 __global__ void __launch_bounds__(1024) k_predict_staged(PredArgs a, const uint32_t *trees, int nnp, int rows_per_cta, int TB) {
-    extern __shared__ __align__(16) uint32_t s_pr[]; // [rows_per_cta][RS / 4 + 1] bins, then 2 x TB x tw tree words
-    const int rw = a.RS >> 2, rwp = rw + 1;
+    extern __shared__ __align__(16) uint32_t s_pr[]; // [RS / 4][rows_per_cta] bins, then 2 x TB x tw tree words
+    const int rw = a.RS >> 2;
     uint32_t *s_rows = s_pr;
     const int K = a.K, tw = nnp * (1 + K);
-    uint32_t *s_trees = s_pr + (((size_t)rows_per_cta * rwp + 3) & ~(size_t)3);
+    uint32_t *s_trees = s_pr + (size_t)rows_per_cta * rw;
     const long long row0 = (long long)blockIdx.x * rows_per_cta;
     const int nr = (int)min((long long)rows_per_cta, a.n - row0);
     auto load_block = [&](int t0, int buf) { // trees t0 .. t0 + TB - 1 -> buffer `buf`, 16 bytes per copy
@@ -565,13 +578,13 @@ __global__ void __launch_bounds__(1024) k_predict_staged(PredArgs a, const uint3
         for (int c = threadIdx.x; c < nchunk; c += blockDim.x) {
             const uint4 v = src[c];
             const int r = c / cpr, part = c - r * cpr;
-            uint32_t *d = s_rows + r * rwp + part * 4;
-            d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+            uint32_t *d = s_rows + (size_t)(part * 4) * rows_per_cta + r;
+            d[0] = v.x; d[rows_per_cta] = v.y; d[2 * rows_per_cta] = v.z; d[3 * rows_per_cta] = v.w;
         }
     }
     const bool act = (int)threadIdx.x < nr;
     const long long i = row0 + threadIdx.x;
-    const uint8_t *xrow = reinterpret_cast<const uint8_t *>(s_rows + threadIdx.x * rwp);
+    const uint32_t *xcol = s_rows + threadIdx.x;
     float p[KMAX];
 #pragma unroll
     for (int k = 0; k < KMAX; ++k) p[k] = 0.0f;
@@ -585,7 +598,7 @@ __global__ void __launch_bounds__(1024) k_predict_staged(PredArgs a, const uint3
         if (act) {
             for (int t = 0; t < nt; ++t) {
                 const uint32_t *pk = s_trees + ((size_t)buf * TB + t) * tw;
-                const int nid = traverse(pk, xrow);
+                const int nid = traverse_wm(pk, xcol, rows_per_cta);
                 if (a.leaf_idx) a.leaf_idx[(size_t)(t0 + t) * a.nobs_total + a.row0 + i] = (uint32_t)nid;
                 pred_add(a.loss, K, p, reinterpret_cast<const float *>(pk + nnp) + (size_t)(nid - 1) * K);
             }
@@ -655,10 +668,11 @@ __global__ void __launch_bounds__(256) k_binarize(const T *x, long long ld, long
 template <typename T>
 __global__ void __launch_bounds__(256) k_binarize_rows(const T *x, long long ld, int row_major, long long n, int nfeats, const T *edges,
                                                        int nedges, uint8_t *xT, int RS) {
-    extern __shared__ unsigned char s_tile[]; // [256][RS]
+    extern __shared__ unsigned char s_tile[]; // [256][RS + 4]: one word of padding, so that the same feature of adjacent rows sits in different banks
+    const int RSP = RS + 4;
     const long long row0 = (long long)blockIdx.x * 256;
     const int nr = (int)min((long long)256, n - row0);
-    for (int e = threadIdx.x; e < 256 * RS; e += 256) s_tile[e] = 0;
+    for (int e = threadIdx.x; e < 64 * RSP; e += 256) reinterpret_cast<uint32_t *>(s_tile)[e] = 0u;
     __syncthreads();
     const int total = nr * nfeats;
     for (int e = threadIdx.x; e < total; e += 256) {
@@ -669,12 +683,16 @@ __global__ void __launch_bounds__(256) k_binarize_rows(const T *x, long long ld,
         const T *ed = edges + (size_t)j * nedges;
         int lo = 0, hi = nedges;
         while (lo < hi) { const int mid = (lo + hi) >> 1; if (__ldg(ed + mid) < v) lo = mid + 1; else hi = mid; }
-        s_tile[r * RS + j] = (uint8_t)(lo + 1);
+        s_tile[r * RSP + j] = (uint8_t)(lo + 1);
     }
     __syncthreads();
-    const uint4 *src = reinterpret_cast<const uint4 *>(s_tile);
     uint4 *dst = reinterpret_cast<uint4 *>(xT + (size_t)row0 * RS);
-    for (int e = threadIdx.x; e < nr * (RS / 16); e += 256) dst[e] = src[e];
+    const int cpr = RS / 16;
+    for (int e = threadIdx.x; e < nr * cpr; e += 256) {
+        const int r = e / cpr, part = e - r * cpr;
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(s_tile + (size_t)r * RSP) + part * 4;
+        dst[e] = make_uint4(src[0], src[1], src[2], src[3]);
+    }
 }
 
 // ---------------------------------------------------------------------------------- evaluation data
@@ -1011,8 +1029,8 @@ static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntr
     const int nnp = (nn + 3) & ~3;
     const size_t treebytes = (size_t)nnp * (1 + K) * 4;
     int rows_cta = 1024;
-    while (rows_cta > 128 && (size_t)rows_cta * (RS + 4) > (size_t)120 * 1024) rows_cta >>= 1;
-    const size_t rows_smem = ((size_t)rows_cta * (RS + 4) + 15) & ~(size_t)15;
+    while (rows_cta > 128 && (size_t)rows_cta * RS > (size_t)132 * 1024) rows_cta >>= 1;
+    const size_t rows_smem = (size_t)rows_cta * RS;
     int TB = rows_smem < (size_t)200 * 1024 ? (int)(((size_t)200 * 1024 - rows_smem) / (2 * treebytes)) : 0;
     if (TB > 8) TB = 8;
     const bool staged = TB >= 1 && RS % 16 == 0 && !getenv("EVB_PREDICT_DIRECT");
@@ -1065,10 +1083,14 @@ static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntr
             if (x) {
                 const unsigned blocks = (unsigned)((nr + 255) / 256);
                 const long long ld = x_row_major ? nfeats : nr;
+                if (256 * (RS + 4) > 48 * 1024) { // rows of more than 188 bins: the tile needs the opt-in shared memory
+                    EVB_CUDA(cudaFuncSetAttribute(k_binarize_rows<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * (RS + 4)));
+                    EVB_CUDA(cudaFuncSetAttribute(k_binarize_rows<double>, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * (RS + 4)));
+                }
                 if (x_dtype == EVB_F32)
-                    k_binarize_rows<float><<<blocks, 256, 256 * RS, st>>>(d_in[q].as<float>(), ld, x_row_major, nr, nfeats, d_edges.as<float>(), nedges, d_xT[q].as<uint8_t>(), RS);
+                    k_binarize_rows<float><<<blocks, 256, 256 * (RS + 4), st>>>(d_in[q].as<float>(), ld, x_row_major, nr, nfeats, d_edges.as<float>(), nedges, d_xT[q].as<uint8_t>(), RS);
                 else
-                    k_binarize_rows<double><<<blocks, 256, 256 * RS, st>>>(d_in[q].as<double>(), ld, x_row_major, nr, nfeats, d_edges.as<double>(), nedges, d_xT[q].as<uint8_t>(), RS);
+                    k_binarize_rows<double><<<blocks, 256, 256 * (RS + 4), st>>>(d_in[q].as<double>(), ld, x_row_major, nr, nfeats, d_edges.as<double>(), nedges, d_xT[q].as<uint8_t>(), RS);
                 EVB_CUDA(cudaGetLastError());
             } else {
                 EVB_CHECK(evb_launch_transpose(nullptr, d_in[q].as<uint8_t>(), nr, nr, 0, nfeats, d_xT[q].as<uint8_t>(), RS, st));
