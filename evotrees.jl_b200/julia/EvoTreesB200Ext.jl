@@ -27,6 +27,8 @@ end
 
 const LOSS_CODE = Dict(:mse => 0, :logloss => 1, :mlogloss => 2, :gaussian_mle => 3, :poisson => 4, :gamma => 5, :tweedie => 6, :logistic_mle => 7,
     :mae => 8, :cred_var => 9, :cred_std => 10, :quantile => 11, :multiquantile => 12)
+# loss type of a fitted model (the `L` of `EvoTree{L,K}`) -> code: the inverse of the reference's own table (src/loss.jl:20-34)
+const LOSS_TYPE_CODE = Dict(T => LOSS_CODE[s] for (s, T) in _loss2type_dict)
 
 function check(rc::Int32)
     rc == 0 && return nothing
@@ -63,8 +65,11 @@ function EvoTrees.init_core(params::EvoTypes, ::Type{<:GPU}, data, feature_names
     haskey(LOSS_CODE, params.loss) || error("EvoTreesB200Ext supports losses $(collect(keys(LOSS_CODE)))")
     rng = Xoshiro(params.seed)
     edges, featbins, feattypes = get_edges(data; feature_names, nbins=params.nbins, rng)   # same RNG stream as the CPU path
-    x_bin = binarize(data; feature_names, edges)                                           # Matrix{UInt8}, column-major
-    nobs, nfeats = size(x_bin)
+    # A dense Float32 / Float64 matrix is binarized on the device (evb_create_x below); anything else (a table, mixed
+    # column types, categorical columns) goes through the reference's own `binarize` and travels as bins.
+    raw = data isa Matrix{Float32} || data isa Matrix{Float64}
+    x_bin = raw ? nothing : binarize(data; feature_names, edges)                           # Matrix{UInt8}, column-major
+    nobs, nfeats = raw ? size(data) : size(x_bin)
     T = Float32
     L = _loss2type_dict[params.loss]
     K, y, μ, target_levels, target_isordered = _init_target(L, y_train, params, offset, T)
@@ -83,9 +88,17 @@ function EvoTrees.init_core(params::EvoTypes, ::Type{<:GPU}, data, feature_names
     ydt, ycols = y isa Vector{UInt32} ? (Int32(1), Int32(1)) : (Int32(0), Int32(ndims(y) == 1 ? 1 : size(y, 1)))
     handle = Ref{Ptr{Cvoid}}(C_NULL)
     ft = UInt8.(feattypes)
-    GC.@preserve x_bin y w pred0 ft monotone check(ccall((:evb_create, LIB), Int32,
-        (Ref{Ptr{Cvoid}}, Ref{EvbParams}, Int64, Int32, Ptr{UInt8}, Ptr{Cvoid}, Int32, Int32, Ptr{Float32}, Ptr{Float32}, Ptr{Float32}, Ptr{UInt8}, Ptr{Int32}),
-        handle, p, nobs, nfeats, x_bin, y, ydt, ycols, w, pred0, C_NULL, ft, monotone))
+    if raw
+        E = eltype(data)
+        edges_mat = reduce(hcat, [E.(e) for e in edges])                                   # [nbins - 1, nfeats], column-major
+        GC.@preserve data edges_mat y w pred0 ft monotone check(ccall((:evb_create_x, LIB), Int32,
+            (Ref{Ptr{Cvoid}}, Ref{EvbParams}, Int64, Int32, Ptr{Cvoid}, Int32, Ptr{Cvoid}, Int32, Ptr{Cvoid}, Int32, Int32, Ptr{Float32}, Ptr{Float32}, Ptr{Float32}, Ptr{UInt8}, Ptr{Int32}),
+            handle, p, nobs, nfeats, data, E == Float32 ? 0 : 2, edges_mat, size(edges_mat, 1), y, ydt, ycols, w, pred0, C_NULL, ft, monotone))
+    else
+        GC.@preserve x_bin y w pred0 ft monotone check(ccall((:evb_create, LIB), Int32,
+            (Ref{Ptr{Cvoid}}, Ref{EvbParams}, Int64, Int32, Ptr{UInt8}, Ptr{Cvoid}, Int32, Int32, Ptr{Float32}, Ptr{Float32}, Ptr{Float32}, Ptr{UInt8}, Ptr{Int32}),
+            handle, p, nobs, nfeats, x_bin, y, ydt, ycols, w, pred0, C_NULL, ft, monotone))
+    end
     info = Dict(:nrounds => 0, :feature_names => feature_names, :target_levels => target_levels,
         :target_isordered => target_isordered, :edges => edges, :featbins => featbins, :feattypes => feattypes)
     m = EvoTree{L,K}(L, K, [Tree{L,K}(μ)], info)
@@ -133,7 +146,7 @@ function EvoTrees._predict(m::EvoTree{L,K}, data, ::Type{<:GPU}; ntree_limit=len
     nn, feat, cb, sp, lp = pack(m, ntree_limit)
     out = zeros(Float32, nobs, K)
     ft = UInt8.(m.info[:feattypes])
-    code = LOSS_CODE[Symbol(lowercase(replace(string(nameof(L)), "GaussianMLE" => "gaussian_mle")))]
+    code = LOSS_TYPE_CODE[L]
     GC.@preserve x_bin feat cb sp lp ft out check(ccall((:evb_predict, LIB), Int32,
         (Int32, Int32, Int32, Int32, Int32, Ptr{Int64}, Ptr{UInt8}, Ptr{UInt8}, Ptr{Float32}, Ptr{UInt8}, Int64, Int32, Ptr{UInt8}, Int32, Ptr{Float32}, Ptr{UInt32}),
         0, code, K, ntree_limit, nn, feat, cb, sp, lp, x_bin, nobs, nfeats, ft, 1, out, C_NULL))

@@ -160,3 +160,23 @@ def test_no_gpu_fails_loudly(pkg):
         pkg.fit(pkg.EvoTreeRegressor(nrounds=1), x_train=x, y_train=x[:, 0])
     with pytest.raises(pkg.EvbError, match="no CPU fallback"):
         pkg.binarize(x, np.zeros((3, 7), np.float32))
+
+
+def test_julia_glue_loss_codes_match_the_header_and_the_python_binding(pkg):
+    """The Julia glue is not executed here (no Julia runtime), so its loss table is checked as text: every loss symbol it
+    maps must carry the code of include/evb.h's enum and of the ctypes binding, and the model-type lookup must go through
+    the reference's own symbol -> type table instead of a name transformation."""
+    import re
+    from evotrees_b200 import _lib
+    src = open(os.path.join(ROOT, "evotrees.jl_b200", "julia", "EvoTreesB200Ext.jl")).read()
+    table = src[src.index("const LOSS_CODE = Dict("):]
+    table = table[:table.index(")\n") + 1]
+    julia = {m.group(1): int(m.group(2)) for m in re.finditer(r":(\w+)\s*=>\s*(\d+)", table)}
+    assert julia == _lib.LOSS_CODES
+    header = open(os.path.join(ROOT, "include", "evb.h")).read()
+    enum = header[header.index("enum evb_loss {"):]
+    enum = enum[:enum.index("};")]
+    codes = {m.group(1).lower(): int(m.group(2)) for m in re.finditer(r"EVB_(\w+)\s*=\s*(\d+)", enum)}
+    assert codes == julia
+    assert "LOSS_TYPE_CODE = Dict(T => LOSS_CODE[s] for (s, T) in _loss2type_dict)" in src
+    assert "lowercase(" not in src and "LOSS_TYPE_CODE[L]" in src
