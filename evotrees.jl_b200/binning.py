@@ -35,6 +35,8 @@ def get_edges(x: np.ndarray, nbins: int, rng: np.random.Generator):
             a, b = v[j - 1], v[j]
         close = np.isfinite(a) & np.isfinite(b) & (np.abs(a - b) <= rtol * np.maximum(np.abs(a), np.abs(b)))
         edges[f] = np.where(close, a + g * (b - a), (1.0 - g) * a + g * b).astype(x.dtype)
+        if nbins == 2:      # a single edge is replaced by the sample minimum (src/fit-utils.jl:17-19)
+            edges[f, 0] = v[0]
     featbins = np.full(nfeats, nbins, dtype=np.uint8)
     feattypes = np.ones(nfeats, dtype=bool)
     return edges, featbins, feattypes

@@ -133,6 +133,8 @@ def get_edges(x: np.ndarray, nbins: int, rng: np.random.Generator) -> np.ndarray
         v = np.sort(x[idx, j])
         for b in range(1, nbins):
             edges[j, b - 1] = quantile_type7(v, b / nbins)
+        if nbins == 2:      # `length(edges[j]) == 1` -> the sample minimum (src/fit-utils.jl:17-19)
+            edges[j, 0] = v[0]
     return edges
 
 

@@ -61,6 +61,8 @@ def test_get_edges_equals_the_oracle_restatement(pkg, orc):
         assert (fb == 64).all() and ft.all()
         e3, _, _ = pkg.get_edges(x[:100], 8, np.random.default_rng(7))
         assert np.array_equal(e3, orc.get_edges(x[:100], 8, np.random.default_rng(7)))
+        e4, _, _ = pkg.get_edges(x[:100], 2, np.random.default_rng(7))      # one edge -> the sample minimum (src/fit-utils.jl:17-19)
+        assert np.array_equal(e4, orc.get_edges(x[:100], 2, np.random.default_rng(7))) and np.array_equal(e4[:, 0], x[:100].min(axis=0))
 
 
 def test_init_target(pkg, orc):
