@@ -411,7 +411,7 @@ static int32_t enqueue_tree(evb_handle *h, bool use_mask, uint8_t mask_cond, boo
     for (int level = 1; level <= last; ++level) {
         if (h->use_q2) {
             EVB_CHECK(evb_launch_histq2(h, level));
-            EVB_CHECK(evb_launch_q2_reduce(h, level));
+            if (!evb_q2_direct(h)) EVB_CHECK(evb_launch_q2_reduce(h, level));
         } else {
             EVB_CHECK(evb_launch_hist(h, level));
             EVB_CHECK(evb_launch_hist_reduce(h, level));
@@ -423,6 +423,7 @@ static int32_t enqueue_tree(evb_handle *h, bool use_mask, uint8_t mask_cond, boo
             EVB_CHECK(s);
         }
         EVB_CHECK(evb_launch_scan(h, level));
+        if (evb_q2_direct(h)) EVB_CHECK(evb_launch_q2_clear(h, level));
         if (level < D - 1 || (full_part && level == D - 1)) EVB_CHECK(evb_launch_partition(h, level));
     }
     if (h->p.loss == EVB_QUANTILE || h->p.loss == EVB_MULTIQUANTILE) {

@@ -12,12 +12,12 @@
 // registers of a step are refilled for a later step (of this tile or of the warp's next one) as soon as they have
 // been accumulated, so a few loads per lane are always in flight and no shared memory is spent on rows.
 // The CTA (one per SM) keeps one packed image [bin][plane][column] of 32-bit words in shared memory; a row adds two
-// words per feature with `red.shared.add.u32`: q >> 8 into plane 0 and (q & 0xff) | 1 << 20 into plane 1 (the row
-// count rides in the top 12 bits).  Integer sums do not depend on the order, so all warps share the image.  The 32
+// words per feature with `red.shared.add.u32`: q >> 6 into plane 0 and (q & 0x3f) | 1 << 19 into plane 1 (the row
+// count rides in the top 13 bits; |q| < 2^24).  Integer sums do not depend on the order, so all warps share the image.  The 32
 // lanes of a reduction always hit 32 different banks: lanes differ in the chunk's parity, in the word of the chunk
 // they work on (the four registers of a chunk are rotated by (l >> 1) & 3) and in the byte of that word
 // ((l >> 3) & 3).
-// The packed counters hold 4095 rows: after at most 127 tiles the CTA moves the packed image into a wide image in
+// The packed counters hold 8191 rows: after at most 255 tiles the CTA moves the packed image into a wide image in
 // shared memory (64-bit sums, 32-bit counts; measured: emptying it into global memory with atomics instead cost 40 %
 // of the kernel), and at the end of a node's rows packed + wide go to the node's accumulators in global memory
 // (`red.global.add`).  Every histogram entry is therefore the exact integer sum of the quantised gradients,
@@ -29,7 +29,10 @@ namespace {
 
 constexpr unsigned FULL = 0xffffffffu;
 constexpr int Q2_THREADS = 768; // measured on B200 (10M x 100, depth 11): 768 threads 2.22 ms per tree, 1024: 2.29, 512: 2.33
-constexpr int Q2_MAX_EPOCH = 127; // tiles of 32 rows that the packed 12-bit row count can hold
+// Word format.  q has QB bits (|q| < 2^QB); plane 0 takes q >> LB, plane 1 takes (q & (2^LB - 1)) | 1 << CS, and an image
+// cell must hold 2^CB - 1 rows: QB - LB + CB <= 31 (signed plane 0), LB + CB <= CS and CS + CB <= 32 (plane 1).
+// QB = 26: LB 8, CS 20, CB 12 (4095 rows, 127 tiles between flushes); QB = 24: LB 6, CS 19, CB 13 (8191 rows, 255 tiles).
+constexpr int Q2_MAX_EPOCH_26 = 127, Q2_MAX_EPOCH_24 = 255;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -45,6 +48,7 @@ struct Q2Args {
     int nmain;                // features held in xH
     int ntail;                // features held in xE (0..4)
     int TE;                   // tiles between two flushes
+    int LB, CS;               // word format: low bits in plane 1, position of the row count
     int min_rows;             // rows per CTA below which fewer CTAs take part
     uint32_t zrow;            // index of an all-zero row of xH / xE (bins 0, q 0)
 };
@@ -185,70 +189,63 @@ __global__ void __launch_bounds__(NT, 1) k_histq2(Q2Args a) {
     constexpr int WC = 16 * NC + (TAIL ? 4 : 0); // columns of the wide image
     long long *wsum = reinterpret_cast<long long *>(smem + (size_t)(a.B + 1) * 2 * NCOL * 4);
     uint32_t *wcnt = reinterpret_cast<uint32_t *>(wsum + (size_t)a.B * WC);
+    const int LB = a.LB, CS = a.CS;
+    const uint32_t cmask = (1u << CS) - 1u, lmask = (1u << LB) - 1u, one = 1u << CS;
     auto flush = [&](int slot, bool final) {
         __syncthreads();
-        const size_t base = (size_t)slot * a.B;
         constexpr int QPR = 4 * NC; // quads of main columns per bin row
         for (int e = tid; e < a.B * QPR; e += NT) {
             const int bin = e / QPR, col = (e % QPR) * 4;
             uint32_t *p = img_w + (size_t)(bin + 1) * 2 * NCOL + col;
             const uint4 vh = *reinterpret_cast<const uint4 *>(p), vp = *reinterpret_cast<const uint4 *>(p + NCOL);
-            const bool nz = (vh.x | vh.y | vh.z | vh.w | vp.x | vp.y | vp.z | vp.w) != 0u;
-            if (!nz && !final) continue;
-            if (nz) {
-                *reinterpret_cast<uint4 *>(p) = make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4 *>(p + NCOL) = make_uint4(0u, 0u, 0u, 0u);
-            }
+            if ((vh.x | vh.y | vh.z | vh.w | vp.x | vp.y | vp.z | vp.w) == 0u) continue;
+            *reinterpret_cast<uint4 *>(p) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4 *>(p + NCOL) = make_uint4(0u, 0u, 0u, 0u);
             const uint32_t h4[4] = {vh.x, vh.y, vh.z, vh.w}, p4[4] = {vp.x, vp.y, vp.z, vp.w};
             long long sm4[4];
             uint32_t c4[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) { sm4[k] = (long long)(int32_t)h4[k] * 256 + (long long)(p4[k] & 0xfffffu); c4[k] = p4[k] >> 20; }
+            for (int k = 0; k < 4; ++k) { sm4[k] = ((long long)(int32_t)h4[k] << LB) + (long long)(p4[k] & cmask); c4[k] = p4[k] >> CS; }
             longlong2 *ws = reinterpret_cast<longlong2 *>(wsum + (size_t)bin * WC + col);
             uint4 *wc = reinterpret_cast<uint4 *>(wcnt + (size_t)bin * WC + col);
             longlong2 s0 = ws[0], s1 = ws[1];
             uint4 cw = *wc;
             s0.x += sm4[0]; s0.y += sm4[1]; s1.x += sm4[2]; s1.y += sm4[3];
             cw.x += c4[0]; cw.y += c4[1]; cw.z += c4[2]; cw.w += c4[3];
-            if (!final) { ws[0] = s0; ws[1] = s1; *wc = cw; continue; }
-            if ((cw.x | cw.y | cw.z | cw.w) == 0u) continue;
-            ws[0] = make_longlong2(0, 0); ws[1] = make_longlong2(0, 0); *wc = make_uint4(0u, 0u, 0u, 0u);
-            const int f = chunk0 * 16 + col;
-            const size_t o = (base + bin) * a.SC + f;
-            const long long st[4] = {s0.x, s0.y, s1.x, s1.y};
-            const uint32_t ct[4] = {cw.x, cw.y, cw.z, cw.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                if (ct[k] != 0u && f + k < a.nmain) {
-                    asm volatile("red.global.add.u64 [%0], %1;" ::"l"(a.hsum + o + k), "l"(st[k]) : "memory");
-                    asm volatile("red.global.add.u32 [%0], %1;" ::"l"(a.hcnt + o + k), "r"(ct[k]) : "memory");
-                }
-            }
+            ws[0] = s0; ws[1] = s1; *wc = cw;
         }
         if (TAIL) { // 8 replicas of the 4 tail features: one warp per bin row, lane = column of the packed image
             for (int bin = wid; bin < a.B; bin += NW) {
                 uint32_t *p = img_w + (size_t)(bin + 1) * 2 * NCOL + Cf::TAILCOL + l;
                 const uint32_t vh = p[0], vp = p[NCOL];
-                const bool nz = __ballot_sync(FULL, (vh | vp) != 0u) != 0u;
-                if (!nz && !final) continue;
-                if (nz) { p[0] = 0u; p[NCOL] = 0u; }
-                long long sum = (long long)(int32_t)vh * 256 + (long long)(vp & 0xfffffu);
-                uint32_t cnt = vp >> 20;
+                if (__ballot_sync(FULL, (vh | vp) != 0u) == 0u) continue;
+                p[0] = 0u; p[NCOL] = 0u;
+                long long sum = ((long long)(int32_t)vh << LB) + (long long)(vp & cmask);
+                uint32_t cnt = vp >> CS;
 #pragma unroll
                 for (int o = 4; o < 32; o <<= 1) { sum += __shfl_xor_sync(FULL, sum, o); cnt += __shfl_xor_sync(FULL, cnt, o); }
                 if (l < 4) {
-                    long long *ws = wsum + (size_t)bin * WC + 16 * NC + l;
-                    uint32_t *wc = wcnt + (size_t)bin * WC + 16 * NC + l;
-                    sum += *ws; cnt += *wc;
-                    if (!final) { *ws = sum; *wc = cnt; }
-                    else if (cnt != 0u) {
-                        *ws = 0; *wc = 0u;
-                        if (l < a.ntail) {
-                            const size_t o = (base + bin) * a.SC + a.nmain + l;
-                            asm volatile("red.global.add.u64 [%0], %1;" ::"l"(a.hsum + o), "l"(sum) : "memory");
-                            asm volatile("red.global.add.u32 [%0], %1;" ::"l"(a.hcnt + o), "r"(cnt) : "memory");
-                        }
-                    }
+                    wsum[(size_t)bin * WC + 16 * NC + l] += sum;
+                    wcnt[(size_t)bin * WC + 16 * NC + l] += cnt;
+                }
+            }
+        }
+        if (final) {
+            // the wide image goes to the slot's accumulators cell by cell: consecutive lanes, consecutive addresses
+            __syncthreads();
+            const size_t base = (size_t)slot * a.B;
+            for (int c = tid; c < a.B * WC; c += NT) {
+                const uint32_t cnt = wcnt[c];
+                if (cnt == 0u) continue;
+                const long long sum = wsum[c];
+                wsum[c] = 0; wcnt[c] = 0u;
+                const int bin = c / WC, col = c - bin * WC;
+                const bool main_col = col < 16 * NC;
+                const int f = main_col ? chunk0 * 16 + col : a.nmain + col - 16 * NC;
+                if (main_col ? f < a.nmain : col - 16 * NC < a.ntail) {
+                    const size_t o = (base + bin) * a.SC + f;
+                    asm volatile("red.global.add.u64 [%0], %1;" ::"l"(a.hsum + o), "l"(sum) : "memory");
+                    asm volatile("red.global.add.u32 [%0], %1;" ::"l"(a.hcnt + o), "r"(cnt) : "memory");
                 }
             }
         }
@@ -303,7 +300,7 @@ __global__ void __launch_bounds__(NT, 1) k_histq2(Q2Args a) {
         for (int s = 0; s < NC; ++s) {
             const int ch = ch_of(s);
             const uint32_t q = __shfl_sync(FULL, extC.x, row_of(s));
-            const uint32_t w0 = (uint32_t)((int32_t)q >> 8), w1 = (q & 0xffu) | (1u << 20);
+            const uint32_t w0 = (uint32_t)((int32_t)q >> LB), w1 = (q & lmask) | one;
             const uint4 c = v[s % NSET];
             const uint32_t t0 = r1 ? c.y : c.x, t1 = r1 ? c.z : c.y, t2 = r1 ? c.w : c.z, t3 = r1 ? c.x : c.w;
             const uint32_t u0 = r2 ? t2 : t0, u1 = r2 ? t3 : t1, u2 = r2 ? t0 : t2, u3 = r2 ? t1 : t3;
@@ -318,7 +315,7 @@ __global__ void __launch_bounds__(NT, 1) k_histq2(Q2Args a) {
         }
         if (TAIL) { // lane = row of the tile
             const uint32_t q = extC.x;
-            const uint32_t w0 = (uint32_t)((int32_t)q >> 8), w1 = (q & 0xffu) | (1u << 20);
+            const uint32_t w0 = (uint32_t)((int32_t)q >> LB), w1 = (q & lmask) | one;
             q2_word<ROWB, X>(extC.y, At, Cb0, sel, w0, w1);
         }
         extC = extN;
@@ -384,16 +381,16 @@ __global__ void __launch_bounds__(256) k_q2_tail(const uint8_t *xC, long long n,
     xE[i] = make_uint2(0u, t);
 }
 
-// q = rint(g * 2^s), 2^s the largest power of two with max |g| * 2^s < 2^26, into xE[i].x; 2^-s into qinv[0]
-__global__ void __launch_bounds__(256) k_q2_quantize(const float *grad, int GS, uint2 *xE, long long n, const unsigned *gmax, double *qinv) {
+// q = rint(g * 2^s), 2^s the largest power of two with max |g| * 2^s < 2^QB, into xE[i].x; 2^-s into qinv[0]
+__global__ void __launch_bounds__(256) k_q2_quantize(const float *grad, int GS, uint2 *xE, long long n, const unsigned *gmax, double *qinv, int QB) {
     const float m = __uint_as_float(*gmax);
     float sc = 1.0f;
     double inv = 1.0;
     if (m > 0.0f && m < INFINITY) {
         int e;
         frexpf(m, &e);
-        sc = ldexpf(1.0f, 26 - e);
-        inv = ldexp(1.0, e - 26);
+        sc = ldexpf(1.0f, QB - e);
+        inv = ldexp(1.0, e - QB);
     }
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i == 0) { qinv[0] = inv; qinv[1] = 1.0; }
@@ -485,8 +482,11 @@ int32_t evb_q2_configure(evb_handle *h) {
     if (occ < 1) { evb_set_error("fixed-point histogram kernel cannot be resident (smem=%zu)", g.smem); return EVB_ERR_CUDA; }
     g.G = occ * h->num_sms;
     const int NW = g_q2_threads / 32;
-    g.TE = Q2_MAX_EPOCH / NW * NW;
-    if (const char *e = getenv("EVB_Q2_EPOCH")) { const int want = atoi(e); if (want >= 1 && want <= Q2_MAX_EPOCH) g.TE = want; }
+    g.QB = 24;
+    if (const char *e = getenv("EVB_Q2_QBITS")) { const int want = atoi(e); if (want == 24 || want == 26) g.QB = want; }
+    const int max_epoch = g.QB == 26 ? Q2_MAX_EPOCH_26 : Q2_MAX_EPOCH_24;
+    g.TE = max_epoch / NW * NW;
+    if (const char *e = getenv("EVB_Q2_EPOCH")) { const int want = atoi(e); if (want >= 1 && want <= max_epoch) g.TE = want; }
     g.min_rows = 1024;
     if (const char *e = getenv("EVB_Q2_MIN_ROWS")) { const int want = atoi(e); if (want >= 32) g.min_rows = want; }
     return EVB_OK;
@@ -505,7 +505,7 @@ int32_t evb_q2_build_layout(evb_handle *h) {
 
 int32_t evb_launch_q2_quantize(evb_handle *h) {
     evb_tic(h, EVB_T_GRADS);
-    k_q2_quantize<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->grad, h->GS, h->xE, h->n, h->d_gmax, h->d_qinv);
+    k_q2_quantize<<<(unsigned)((h->n + 255) / 256), 256, 0, h->st>>>(h->grad, h->GS, h->xE, h->n, h->d_gmax, h->d_qinv, h->q2.QB);
     evb_toc(h, EVB_T_GRADS);
     EVB_CUDA(cudaGetLastError());
     return EVB_OK;
@@ -518,10 +518,32 @@ int32_t evb_launch_histq2(evb_handle *h, int level) {
     a.plan = h->plan + level; a.cum = h->cum; a.slot_node = h->slot_node; a.seg_start = h->seg_start;
     a.hsum = h->hsum_q; a.hcnt = h->hcnt_q;
     a.RSH = g.RSH; a.B = h->B; a.SC = g.SC; a.nmain = g.nmain; a.ntail = g.ntail; a.TE = g.TE; a.min_rows = g.min_rows; a.zrow = (uint32_t)h->n;
+    a.LB = g.QB == 26 ? 8 : 6; a.CS = g.QB == 26 ? 20 : 19;
     evb_tic(h, EVB_T_HIST);
     const cudaError_t e = (cudaError_t)q2_dispatch(g.NC, g.ntail > 0, true, &a, dim3(g.G, g.ngroups), g.smem, h->st);
     evb_toc(h, EVB_T_HIST);
     EVB_CUDA(e);
+    return EVB_OK;
+}
+
+// The split scan reads the integer accumulators itself when nothing else needs the doubles: one GPU (no exchange of
+// hcomp between ranks).  EVB_Q2_DIRECT=0 keeps the conversion kernel.
+bool evb_q2_direct(const evb_handle *h) {
+    static const bool off = getenv("EVB_Q2_DIRECT") != nullptr && atoi(getenv("EVB_Q2_DIRECT")) == 0;
+    return h->use_q2 && h->world == 1 && !off;
+}
+
+// clears the accumulators of the level's build slots (after the scan has read them)
+int32_t evb_launch_q2_clear(evb_handle *h, int level) {
+    const Q2Geom &g = h->q2;
+    const int slots = evb_level_slots(level);
+    const size_t per_slot = (size_t)h->B * g.SC;
+    size_t blocks = ((size_t)slots * per_slot + 255) / 256;
+    if (blocks > (size_t)h->num_sms * 8) blocks = (size_t)h->num_sms * 8;
+    evb_tic(h, EVB_T_HIST_REDUCE);
+    k_q2_clear<<<(unsigned)blocks, 256, 0, h->st>>>(h->hsum_q, h->hcnt_q, h->plan + level, per_slot);
+    evb_toc(h, EVB_T_HIST_REDUCE);
+    EVB_CUDA(cudaGetLastError());
     return EVB_OK;
 }
 

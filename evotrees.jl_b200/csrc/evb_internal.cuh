@@ -74,6 +74,7 @@ struct Q2Geom {
     int G;         // grid.x
     int TE;        // tiles of 32 rows between two flushes of a CTA's image
     int min_rows;  // rows per CTA below which fewer CTAs take part
+    int QB;        // bits of the fixed-point gradient: |q| < 2^QB (26 or 24)
     size_t smem;
 };
 
@@ -221,6 +222,8 @@ int32_t evb_q2_build_layout(evb_handle *h);
 int32_t evb_launch_q2_quantize(evb_handle *h);
 int32_t evb_launch_histq2(evb_handle *h, int level);
 int32_t evb_launch_q2_reduce(evb_handle *h, int level);
+int32_t evb_launch_q2_clear(evb_handle *h, int level);
+bool evb_q2_direct(const evb_handle *h);
 // evb_tree.cu
 int32_t evb_launch_tree_reset(evb_handle *h);
 int32_t evb_launch_scan(evb_handle *h, int level);

@@ -120,6 +120,13 @@ struct ScanArgs {
     const double *cand_local; // [nodes of the level][world][3 + C]: gain, feature slot, bin, left sums
     int world, rank;          // world == 1: no peers (single GPU, or histograms already summed by NCCL)
     int F, C, K, B, level, D, hist_nodes, loss;
+    int elide_h;        // mse: the h channels equal twice the w channel and are rebuilt instead of read
+    // non-null: the built histograms are read straight from the integer accumulators of the fixed-point kernel
+    // ([slot][bin][SC] sums of q and row counts; g = sum * qinv[0], w = count, h = 2w) instead of from hcomp
+    const unsigned long long *qsum;
+    const uint32_t *qcnt;
+    const double *qinv;
+    int SC;
     double neb; // -eta / bagging_size
     double lambda, L2, gamma, min_weight;
 };
@@ -204,8 +211,21 @@ __global__ void __launch_bounds__(256) k_peer_reduce(PeerReduceArgs a) {
 // staged histogram `sm` of the build node, stores the node's histogram if its children will need it, scans the
 // bins (`_scan_node!`, fit-utils.jl:403-436) and records the best split of this feature.
 template <int MAXCHK, bool OWN, bool OBL>
-__device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int f, const double *sm, double *s_sum, int lane, bool first_owned) {
+__device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int f, int slot, double *s_sum, int lane, bool first_owned) {
     const int C = a.C, K = a.K, B = a.B, F = a.F;
+    const uint32_t feat = a.js0[f];
+    const double *__restrict__ sm = a.hcomp + ((size_t)slot * F + f) * C * B;
+    const double qi = a.qsum ? a.qinv[0] : 0.0;
+    // entry (channel c, bin b) of the histogram built for `slot` and feature slot f
+    auto built = [&](int c, int b) -> double {
+        if (a.qsum) {
+            const size_t o = ((size_t)slot * B + b) * a.SC + feat;
+            if (c < K) return (double)(long long)a.qsum[o] * qi;
+            const double w = (double)a.qcnt[o];
+            return c == C - 1 ? w : 2.0 * w;
+        }
+        return sm[c * B + b];
+    };
     const int m = 1 << (a.level - 1);
     const size_t FCB = (size_t)F * C * B;
     const double *__restrict__ hp = a.hist + (size_t)(n >> 1) * FCB;
@@ -216,7 +236,7 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
         // the reference sums the gradients of the sampled rows directly (src/fit.jl:66)
         for (int c = 0; c < C; ++c) {
             double v = 0.0;
-            for (int b = lane; b < B; b += 32) v += __ldg(a.hcomp + (size_t)c * B + b);
+            for (int b = lane; b < B; b += 32) v += built(c, b);
             v = warp_sum(v);
             if (lane == 0) { s_sum[c] = v; if (first_owned) a.nsum[(size_t)C + c] = v; }
         }
@@ -232,79 +252,85 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
         for (int k = 0; k < K; ++k) gain_p += term_cred(a.loss, s_sum[k], s_sum[K + k], w_p, a.L2);   // split.jl:70-78; mae: 0
     }
 
-    const int nchk = (B + 31) >> 5;
-    const uint32_t feat = a.js0[f];
+    // lane l holds the CH adjacent bins l * CH .. l * CH + CH - 1 (CH * 32 >= B): a running sum over the bins is a
+    // running sum inside the lane plus ONE warp scan of the lanes' totals, whatever CH is
+    constexpr int CH = MAXCHK;
+    const int bin0 = lane * CH;
     const bool numeric = a.feattypes[feat] != 0;
     const int constraint = a.mono[feat];
     const int b_max = numeric ? B - 1 : B;
     const size_t fo = (size_t)f * C * B;
+    const bool elide = a.elide_h != 0; // mse: every h entry is exactly twice the w entry (src/loss.jl:52), it is not read
     auto val = [&](int c, int b) -> double {
         const int o = c * B + b;
-        double v = sm[o];
+        double v = built(c, b);
         if (sub) v = __ldg(hp + fo + o) - v;
         if (keep) hn[fo + o] = v;
         return v;
     };
+    auto running = [&](double (&v)[CH]) { // inclusive running sum over the bins (numeric features only)
+        if (!numeric) return;
+#pragma unroll
+        for (int j = 1; j < CH; ++j) v[j] += v[j - 1];
+        const double incl = warp_incl_scan(v[CH - 1], lane);
+        double before = __shfl_up_sync(FULL, incl, 1);
+        if (lane == 0) before = 0.0;
+#pragma unroll
+        for (int j = 0; j < CH; ++j) v[j] += before;
+    };
     double lg = a.gamma; // get_best_split starts at gamma and takes strict improvements (fit-utils.jl:444-450)
     int lb = 0x7fffffff;
     if (a.level < a.D) {
-        double wl[MAXCHK], gacc[MAXCHK];
+        double wl[CH], gacc[CH];
         unsigned okmask = 0xffu;
-        {
-            double carry = 0.0;
 #pragma unroll
-            for (int ch = 0; ch < MAXCHK; ++ch) {
-                gacc[ch] = 0.0;
-                wl[ch] = 0.0;
-                if (ch < nchk) {
-                    const int b = ch * 32 + lane;
-                    double v = b < B ? val(C - 1, b) : 0.0;
-                    if (numeric) { v = warp_incl_scan(v, lane) + carry; carry = __shfl_sync(FULL, v, 31); }
-                    wl[ch] = v;
-                }
-            }
+        for (int j = 0; j < CH; ++j) {
+            gacc[j] = 0.0;
+            const int b = bin0 + j;
+            wl[j] = b < B ? val(C - 1, b) : 0.0;
+            if (elide && keep && b < B)
+                for (int k = 0; k < K; ++k) hn[fo + (size_t)(K + k) * B + b] = 2.0 * wl[j];
         }
+        running(wl);
         for (int k = 0; k < K; ++k) {
-            double cg = 0.0, chh = 0.0;
             const double sg = s_sum[k], sh = s_sum[K + k];
+            double gl[CH], hl[CH];
 #pragma unroll
-            for (int ch = 0; ch < MAXCHK; ++ch) {
-                if (ch < nchk) {
-                    const int b = ch * 32 + lane;
-                    double gl = b < B ? val(k, b) : 0.0;
-                    double hl = b < B ? val(K + k, b) : 0.0;
-                    if (numeric) {
-                        gl = warp_incl_scan(gl, lane) + cg; cg = __shfl_sync(FULL, gl, 31);
-                        hl = warp_incl_scan(hl, lane) + chh; chh = __shfl_sync(FULL, hl, 31);
-                    }
-                    const double w_l = wl[ch], w_r = w_p - w_l;
-                    if (!OWN) gacc[ch] += term_gh(gl, hl, w_l, a.lambda, a.L2) + term_gh(sg - gl, sh - hl, w_r, a.lambda, a.L2);
-                    else gacc[ch] += side_gain(a, gl, hl, w_l, sg, sh, w_p);
-                    if (k == 0 && constraint != 0) {
-                        // pred_scalar on left / right sums (src/predict.jl:205-208, 235-238)
-                        const double pl = OWN ? own_scalar(a, gl, w_l) : a.neb * gl / fmax(DBL_EPSILON, hl + a.lambda * w_l + a.L2);
-                        const double pr = OWN ? own_scalar(a, sg - gl, w_r)
-                                                           : a.neb * (sg - gl) / fmax(DBL_EPSILON, (sh - hl) + a.lambda * w_r + a.L2);
-                        const bool ok = (constraint == -1 && pl > pr) || (constraint == 1 && pl < pr);
-                        if (!ok) okmask &= ~(1u << ch);
-                    }
+            for (int j = 0; j < CH; ++j) {
+                const int b = bin0 + j;
+                gl[j] = b < B ? val(k, b) : 0.0;
+                if (!elide) hl[j] = b < B ? val(K + k, b) : 0.0;
+            }
+            running(gl);
+            if (!elide) running(hl);
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+                if (elide) hl[j] = 2.0 * wl[j];
+                const double w_l = wl[j], w_r = w_p - w_l;
+                if (!OWN) gacc[j] += term_gh(gl[j], hl[j], w_l, a.lambda, a.L2) + term_gh(sg - gl[j], sh - hl[j], w_r, a.lambda, a.L2);
+                else gacc[j] += side_gain(a, gl[j], hl[j], w_l, sg, sh, w_p);
+                if (k == 0 && constraint != 0) {
+                    // pred_scalar on left / right sums (src/predict.jl:205-208, 235-238)
+                    const double pl = OWN ? own_scalar(a, gl[j], w_l) : a.neb * gl[j] / fmax(DBL_EPSILON, hl[j] + a.lambda * w_l + a.L2);
+                    const double pr = OWN ? own_scalar(a, sg - gl[j], w_r)
+                                          : a.neb * (sg - gl[j]) / fmax(DBL_EPSILON, (sh - hl[j]) + a.lambda * w_r + a.L2);
+                    const bool ok = (constraint == -1 && pl > pr) || (constraint == 1 && pl < pr);
+                    if (!ok) okmask &= ~(1u << j);
                 }
             }
         }
         // candidate of this lane: lowest bin among its strict maxima
 #pragma unroll
-        for (int ch = 0; ch < MAXCHK; ++ch) {
-            if (ch < nchk) {
-                const int b = ch * 32 + lane;
-                const double w_l = wl[ch], w_r = w_p - w_l;
-                double g = 0.0;
-                const bool elig = b < b_max && w_l > a.min_weight && w_r > a.min_weight && ((okmask >> ch) & 1u);
-                if (elig) {
-                    g = gacc[ch] - gain_p;
-                    if (g > lg) { lg = g; lb = b; }
-                }
-                if (OBL && b < B) a.obl_gain[((size_t)(n - m) * F + f) * B + b] = g; // update_gains!, fit-utils.jl:457-463
+        for (int j = 0; j < CH; ++j) {
+            const int b = bin0 + j;
+            const double w_l = wl[j], w_r = w_p - w_l;
+            double g = 0.0;
+            const bool elig = b < b_max && w_l > a.min_weight && w_r > a.min_weight && ((okmask >> j) & 1u);
+            if (elig) {
+                g = gacc[j] - gain_p;
+                if (g > lg) { lg = g; lb = b; }
             }
+            if (OBL && b < B) a.obl_gain[((size_t)(n - m) * F + f) * B + b] = g; // update_gains!, fit-utils.jl:457-463
         }
 #pragma unroll
         for (int d = 16; d >= 1; d >>= 1) {
@@ -326,10 +352,10 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
 // OWN: the loss brings its own split gain (mae, credibility); OBL: oblivious trees, the gain of every candidate is
 // stored as well.  The default instance carries neither code.
 template <int MAXCHK, bool OWN, bool OBL>
-__global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
+__global__ void __launch_bounds__(256, MAXCHK <= 2 ? 3 : 2) k_scan_feat(ScanArgs a) {
     __shared__ double s_sum_all[8][72];
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
-    const int C = a.C, B = a.B, F = a.F;
+    const int F = a.F;
     const int Fown = (F - a.rank + a.world - 1) / a.world;
     if (Fown <= 0) return;
     long long gw = (long long)blockIdx.x * wpb + wid;
@@ -339,8 +365,7 @@ __global__ void __launch_bounds__(256) k_scan_feat(ScanArgs a) {
     if (s >= a.plan->nbuild) return;
     const int f = fi * a.world + a.rank;
     const int nb = a.slot_node[s];
-    const double *src = a.hcomp + ((size_t)s * F + f) * C * B;
-    scan_one<MAXCHK, OWN, OBL>(a, which ? nb ^ 1 : nb, which != 0, f, src, s_sum_all[wid], lane, fi == 0);
+    scan_one<MAXCHK, OWN, OBL>(a, which ? nb ^ 1 : nb, which != 0, f, s, s_sum_all[wid], lane, fi == 0);
 }
 
 // Oblivious trees, stage 1b: one thread per candidate (feature slot, bin) adds the gains of the level's nodes in
@@ -446,24 +471,41 @@ __global__ void __launch_bounds__(256) k_scan_node(ScanArgs a) {
     double *s_sum = s_sum_all[wid], *s_left = s_left_all[wid], *s_right = s_right_all[wid];
     if (i >= m) return;
     const int n = m + i;
+    // this kernel is a chain of dependent loads: everything that does not depend on the winner is requested up front
     const int kd = a.kind[n];
+    const int slot_n = a.bslot[n];
+    const int Fown = (F - a.rank + a.world - 1) / a.world;
+    double fg[4];
+    int fb[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int fi = lane + 32 * u;
+        fb[u] = -1; fg[u] = 0.0;
+        if (fi < Fown && !a.obl_gain) {
+            const int f = fi * a.world + a.rank;
+            fg[u] = a.fbest_gain[(size_t)i * F + f];
+            fb[u] = a.fbest_bin[(size_t)i * F + f];
+        }
+    }
+    for (int c = lane; c < C; c += 32) s_sum[c] = a.nsum[(size_t)n * C + c];
     if (kd == EVB_KIND_NONE) return;
     const size_t FCB = (size_t)F * C * B;
-    const double *hc = a.hcomp + (size_t)a.bslot[n] * FCB;
+    const double *hc = a.hcomp + (size_t)slot_n * FCB;
     const bool sub = kd == EVB_KIND_SUB;
     const double *hp = a.hist + (size_t)(n >> 1) * FCB;
     const double *hn = a.hist + (size_t)n * FCB;
-    for (int c = lane; c < C; c += 32) s_sum[c] = a.nsum[(size_t)n * C + c];
     __syncwarp();
 
     double bg = a.gamma;
     int bs = 0x7fffffff, bb = -1;
-    const int Fown = (F - a.rank + a.world - 1) / a.world;
     if (a.obl_gain) { // oblivious: every node of the level takes the split k_obl_pick chose (src/fit.jl:213-225)
         const double e = a.obl_best[1];
         if (e >= 0.0) { bg = a.obl_best[0]; bs = (int)e / B; bb = (int)e % B; }
     } else {
-    for (int fi = lane; fi < Fown; fi += 32) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+        if (fb[u] >= 0 && fg[u] > bg) { bg = fg[u]; bs = (lane + 32 * u) * a.world + a.rank; bb = fb[u]; }
+    for (int fi = lane + 128; fi < Fown; fi += 32) {
         const int f = fi * a.world + a.rank;
         const double g = a.fbest_gain[(size_t)i * F + f];
         const int b = a.fbest_bin[(size_t)i * F + f];
@@ -480,13 +522,22 @@ __global__ void __launch_bounds__(256) k_scan_node(ScanArgs a) {
     if (has) {
         const bool numeric = a.feattypes[a.js0[bs]] != 0;
         const size_t fo = (size_t)bs * C * B;
+        const size_t qo = a.qsum ? (size_t)slot_n * B * a.SC + a.js0[bs] : 0;
+        const double qi = a.qsum ? a.qinv[0] : 0.0;
         for (int c = 0; c < C; ++c) {
             double v = 0.0;
             const int b0 = numeric ? lane : bb, b1 = bb;
             for (int b = b0; b <= b1; b += 32) {
                 const size_t o = fo + (size_t)c * B + b;
                 // sharded: the summed histogram of every scanned node is retained locally for the owned features
-                v += a.world > 1 ? hn[o] : (sub ? hp[o] - hc[o] : hc[o]);
+                double built;
+                if (a.qsum) {
+                    const size_t q = qo + (size_t)b * a.SC;
+                    built = c < a.K ? (double)(long long)a.qsum[q] * qi : (c == C - 1 ? 1.0 : 2.0) * (double)a.qcnt[q];
+                } else {
+                    built = hc[o];
+                }
+                v += a.world > 1 ? hn[o] : (sub ? hp[o] - built : built);
                 if (!numeric) break;
             }
             if (numeric) v = warp_sum(v);
@@ -583,7 +634,8 @@ struct PartArgs {
     const int32_t *gnleft;
     uint8_t *kind;
     int32_t *ibase;       // [level nodes + 1] exclusive prefix of items per node
-    int32_t *item_left, *item_lprefix;
+    int32_t *item_left, *item_lprefix; // left rows of every item; their running sum over all items of the level
+    int32_t *nbase;       // [level nodes] value of the running sum at the node's first item
     uint32_t *item_bits;
     LevelPlan *plan;
     const double *nsum; // node sums [id][C]; channel C-1 is the sum of weights
@@ -634,15 +686,20 @@ __global__ void __launch_bounds__(EVB_PART_THREADS) k_part_flags(PartArgs a) {
         const uint32_t feat = pk & 0xffffu, bin = (pk >> 16) & 0xffu;
         const bool numeric = (pk >> 25) & 1u;
         int local = 0;
+        constexpr int NI = EVB_PART_CHUNK / EVB_PART_THREADS;
+        // all row ids first, then all gathers: eight independent loads in flight per thread in each phase
+        uint32_t row[NI], x[NI];
 #pragma unroll
-        for (int i8 = 0; i8 < EVB_PART_CHUNK / EVB_PART_THREADS; ++i8) {
+        for (int i8 = 0; i8 < NI; ++i8) {
             const int pos = i8 * EVB_PART_THREADS + threadIdx.x;
-            bool left = false;
-            if (pos < cnt) {
-                const uint32_t row = a.rows_in[start + pos];
-                const uint32_t x = a.xC[(size_t)feat * a.n + row];
-                left = numeric ? (x <= bin) : (x == bin); // split_set! predicate (fit-utils.jl:173, 291)
-            }
+            row[i8] = pos < cnt ? __ldg(a.rows_in + start + pos) : 0xffffffffu;
+        }
+        const uint8_t *xf = a.xC + (size_t)feat * a.n;
+#pragma unroll
+        for (int i8 = 0; i8 < NI; ++i8) x[i8] = row[i8] != 0xffffffffu ? (uint32_t)__ldg(xf + row[i8]) : 0xffffu;
+#pragma unroll
+        for (int i8 = 0; i8 < NI; ++i8) {
+            const bool left = x[i8] != 0xffffu && (numeric ? (x[i8] <= bin) : (x[i8] == bin)); // split_set! predicate (fit-utils.jl:173, 291)
             const unsigned bal = __ballot_sync(FULL, left);
             if (lane == 0) {
                 a.item_bits[(size_t)item * (EVB_PART_CHUNK / 32) + i8 * (EVB_PART_THREADS / 32) + wid] = bal;
@@ -661,44 +718,30 @@ __global__ void __launch_bounds__(EVB_PART_THREADS) k_part_flags(PartArgs a) {
 }
 
 // Exclusive prefix of the left counts of every split node's work items and the node's left total.  Runs inside the
-// single-CTA plan kernel: levels with few nodes (many items per node) scan each node with the whole CTA, deeper
-// levels give every node to one warp.
+// single-CTA plan kernel.
 __device__ void part_prefix(const PartArgs &a, int *sm) {
     const int lo = 1 << (a.level - 1), m = lo;
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    if (m <= 2) {
-        for (int i = 0; i < m; ++i) {
-            const int n = lo + i;
-            int running = 0;
-            if (a.t_split[n - 1]) {
-                const int j0 = a.ibase[i], j1 = a.ibase[i + 1];
-                for (int j = j0; j < j1; j += blockDim.x) {
-                    const int idx = j + threadIdx.x;
-                    const int v = idx < j1 ? a.item_left[idx] : 0;
-                    int total;
-                    const int ex = block_excl_scan(v, sm, &total);
-                    if (idx < j1) a.item_lprefix[idx] = running + ex;
-                    running += total;
-                    __syncthreads();
-                }
-            }
-            if (threadIdx.x == 0) a.nleft[n] = running;
-        }
-    } else {
-        for (int i = wid; i < m; i += nw) {
-            const int n = lo + i;
-            int running = 0;
-            if (a.t_split[n - 1]) {
-                const int j0 = a.ibase[i], j1 = a.ibase[i + 1];
-                for (int j = j0; j < j1; j += 32) {
-                    const int v = (j + lane < j1) ? a.item_left[j + lane] : 0;
-                    const int incl = warp_incl_scan_i(v, lane);
-                    if (j + lane < j1) a.item_lprefix[j + lane] = running + incl - v;
-                    running += __shfl_sync(FULL, incl, 31);
-                }
-            }
-            if (lane == 0) a.nleft[n] = running;
-        }
+    const int nitems = a.ibase[m];
+    // one running sum over the items of all nodes (they are ordered by node) ...
+    int running = 0;
+    for (int base = 0; base < nitems; base += blockDim.x) {
+        const int idx = base + threadIdx.x;
+        const int v = idx < nitems ? a.item_left[idx] : 0;
+        int total;
+        const int ex = block_excl_scan(v, sm, &total);
+        if (idx < nitems) a.item_lprefix[idx] = running + ex;
+        running += total;
+        __syncthreads();
+    }
+    __threadfence_block();
+    __syncthreads();
+    // ... and per node the value it had at the node's first item: k_part_scatter subtracts it
+    for (int i = threadIdx.x; i < m; i += blockDim.x) {
+        const int j0 = a.ibase[i], j1 = a.ibase[i + 1];
+        const int p0 = j0 < nitems ? a.item_lprefix[j0] : running;
+        const int p1 = j1 < nitems ? a.item_lprefix[j1] : running;
+        a.nbase[i] = p0;
+        a.nleft[lo + i] = p1 - p0; // a node that is not split has no items: 0
     }
     __threadfence_block();
     __syncthreads();
@@ -767,7 +810,7 @@ __global__ void __launch_bounds__(EVB_PART_THREADS) k_part_scatter(PartArgs a) {
         item_lookup(a, item, n, chunk);
         const int start = a.seg_start[n] + chunk * EVB_PART_CHUNK;
         const int cnt = min(EVB_PART_CHUNK, a.seg_cnt[n] - chunk * EVB_PART_CHUNK);
-        const int nL = a.nleft[n], lp = a.item_lprefix[item];
+        const int nL = a.nleft[n], lp = a.item_lprefix[item] - a.nbase[n - (1 << (a.level - 1))];
         if (threadIdx.x < NW) s_bits[threadIdx.x] = a.item_bits[(size_t)item * NW + threadIdx.x];
         __syncthreads();
         if (threadIdx.x < 32) { // NW == 64: two words per lane
@@ -779,15 +822,21 @@ __global__ void __launch_bounds__(EVB_PART_THREADS) k_part_scatter(PartArgs a) {
         __syncthreads();
         const int dstL = a.seg_start[n] + lp;
         const int dstR = a.seg_start[n] + nL + (chunk * EVB_PART_CHUNK - lp);
+        constexpr int NI = EVB_PART_CHUNK / EVB_PART_THREADS;
+        uint32_t row[NI];
 #pragma unroll
-        for (int i8 = 0; i8 < EVB_PART_CHUNK / EVB_PART_THREADS; ++i8) {
+        for (int i8 = 0; i8 < NI; ++i8) {
+            const int pos = i8 * EVB_PART_THREADS + threadIdx.x;
+            row[i8] = pos < cnt ? __ldg(a.rows_in + start + pos) : 0u;
+        }
+#pragma unroll
+        for (int i8 = 0; i8 < NI; ++i8) {
             const int pos = i8 * EVB_PART_THREADS + threadIdx.x;
             if (pos < cnt) {
-                const uint32_t row = a.rows_in[start + pos];
                 const uint32_t word = s_bits[pos >> 5];
                 const int before = s_pref[pos >> 5] + __popc(word & ((1u << lane) - 1u));
-                if ((word >> lane) & 1u) a.rows_out[dstL + before] = row;
-                else a.rows_out[dstR + (pos - before)] = row;
+                if ((word >> lane) & 1u) a.rows_out[dstL + before] = row[i8];
+                else a.rows_out[dstR + (pos - before)] = row[i8];
             }
         }
         __syncthreads();
@@ -800,7 +849,7 @@ PartArgs make_part_args(evb_handle *h, int level) {
     a.t_split = h->t_split; a.t_packed = h->t_packed;
     a.seg_start = h->seg_start; a.seg_cnt = h->seg_cnt; a.gcnt = h->gcnt; a.nleft = h->nleft; a.gnleft = h->gnleft;
     a.bslot = h->bslot; a.cum = h->cum; a.slot_node = h->slot_node; a.kind = h->kind;
-    a.ibase = h->item_node; a.item_left = h->item_left; a.item_lprefix = h->item_lprefix; a.item_bits = h->item_bits;
+    a.ibase = h->item_node; a.nbase = h->item_node + (1 << (h->D > 1 ? h->D - 1 : 0)) + 1; a.item_left = h->item_left; a.item_lprefix = h->item_lprefix; a.item_bits = h->item_bits;
     a.plan = h->plan; a.RS = h->RS; a.level = level; a.D = h->D; a.max_items = h->max_items; a.err = h->d_err;
     a.nsum = h->nsum; a.C = h->C; a.by_weight = h->world > 1 ? 1 : 0;
     return a;
@@ -864,6 +913,9 @@ int32_t evb_launch_scan(evb_handle *h, int level) {
     a.t_gain = h->t_gain; a.t_w = h->t_w; a.t_pred = h->t_pred; a.t_packed = h->t_packed;
     a.F = h->F; a.C = h->C; a.K = h->K; a.B = h->B; a.level = level; a.D = h->D; a.hist_nodes = h->hist_nodes;
     a.loss = h->p.loss; a.neb = -h->p.eta / (double)h->p.bagging_size;
+    a.elide_h = h->Ce != h->C ? 1 : 0;
+    const bool direct = evb_q2_direct(h);
+    a.qsum = direct ? h->hsum_q : nullptr; a.qcnt = direct ? h->hcnt_q : nullptr; a.qinv = h->d_qinv; a.SC = h->q2.SC;
     a.lambda = h->p.lambda; a.L2 = h->p.L2; a.gamma = h->p.gamma; a.min_weight = h->p.min_weight;
     a.fbest_gain = h->fbest_gain; a.fbest_bin = h->fbest_bin;
     a.obl_gain = h->obl_gain; a.obl_best = h->obl_best;
@@ -899,7 +951,7 @@ int32_t evb_launch_scan(evb_handle *h, int level) {
             else if (own) k_scan_feat<M, true, false><<<grid, 256, 0, h->st>>>(a); \
             else if (obl) k_scan_feat<M, false, true><<<grid, 256, 0, h->st>>>(a); \
             else k_scan_feat<M, false, false><<<grid, 256, 0, h->st>>>(a); } while (0)
-        if (h->B <= 64) EVB_SCAN(2); else EVB_SCAN(8);
+        if (h->B <= 32) EVB_SCAN(1); else if (h->B <= 64) EVB_SCAN(2); else if (h->B <= 128) EVB_SCAN(4); else EVB_SCAN(8);
 #undef EVB_SCAN
     }
     evb_toc(h, EVB_T_SCAN);
