@@ -8,9 +8,19 @@ from __future__ import annotations
 
 import ctypes as C
 
+import os
+
 import numpy as np
 
 from . import _lib
+
+
+def _edge_threads() -> int:
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(1, min(16, n))
 
 
 def get_edges(x: np.ndarray, nbins: int, rng: np.random.Generator):
@@ -27,7 +37,8 @@ def get_edges(x: np.ndarray, nbins: int, rng: np.random.Generator):
     g = np.clip(aleph - j, 0.0, 1.0)
     rtol = np.sqrt(np.finfo(x.dtype).eps)
     edges = np.empty((nfeats, nbins - 1), dtype=x.dtype)
-    for f in range(nfeats):
+
+    def one(f):
         v = np.sort(x[idx, f]).astype(np.float64)
         if ns == 1:
             a = b = np.full(nbins - 1, v[0])
@@ -37,6 +48,16 @@ def get_edges(x: np.ndarray, nbins: int, rng: np.random.Generator):
         edges[f] = np.where(close, a + g * (b - a), (1.0 - g) * a + g * b).astype(x.dtype)
         if nbins == 2:      # a single edge is replaced by the sample minimum (src/fit-utils.jl:17-19)
             edges[f, 0] = v[0]
+
+    # the reference runs this loop under `@threads` (src/fit-utils.jl:15); the gather and the sort release the GIL
+    nthreads = min(nfeats, _edge_threads()) if ns * nfeats >= 1 << 18 else 1
+    if nthreads > 1:
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(nthreads) as pool:
+            list(pool.map(one, range(nfeats)))
+    else:
+        for f in range(nfeats):
+            one(f)
     featbins = np.full(nfeats, nbins, dtype=np.uint8)
     feattypes = np.ones(nfeats, dtype=bool)
     return edges, featbins, feattypes

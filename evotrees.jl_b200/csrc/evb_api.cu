@@ -1,5 +1,6 @@
 // C ABI of libevotrees_b200.so (declarations and per-function contracts: include/evb.h).
 #include "evb_internal.cuh"
+#include <chrono>
 #include <stdarg.h>
 #include <string.h>
 #include <stdlib.h>
@@ -153,6 +154,16 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
                            int32_t x_dtype, const void *edges, int32_t nedges, const void *y,
                            int32_t y_dtype, int32_t ycols, const float *w, const float *pred0, const float *mu,
                            const uint8_t *feattypes, const int32_t *monotone) {
+    // EVB_INIT_TRACE=1: host-side milliseconds of the phases of evb_create / evb_create_x on stderr
+    static const bool trace = getenv("EVB_INIT_TRACE") != nullptr;
+    auto t_last = std::chrono::steady_clock::now();
+    auto phase = [&](const char *name) {
+        if (!trace) return;
+        cudaStreamSynchronize(h->st);
+        const auto now = std::chrono::steady_clock::now();
+        fprintf(stderr, "[evb init] %-24s %8.2f ms\n", name, std::chrono::duration<double, std::milli>(now - t_last).count());
+        t_last = now;
+    };
     h->p = *p;
     h->K = p->K; h->C = 2 * p->K + 1; h->B = p->nbins; h->D = p->max_depth; h->nn = (1 << p->max_depth) - 1;
     h->Ce = (p->loss == EVB_MSE && !getenv("EVB_NO_ELISION")) ? p->K + 1 : h->C;
@@ -260,11 +271,15 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
 
     // ---- uploads: x_bin is kept feature-major (as given) for the row partition and transposed on the device to
     // observation-major rows for the histogram gathers and the tree traversal
+    phase("allocations");
     EVB_CUDA(cudaMemsetAsync(h->xT, 0, (size_t)n * h->RS, h->st));
     EVB_CUDA(dalloc(&h->xC, (size_t)n * nfeats));
+    phase("xC alloc + xT memset");
     if (x_bin) EVB_CHECK(evb_h2d_staged(h->xC, x_bin, (size_t)n * nfeats, h->st));
     else EVB_CHECK(evb_upload_binarize(h, x, x_dtype, edges, nedges));
+    phase("upload (+ binarize)");
     EVB_CHECK(evb_launch_transpose(h, h->xC, n, n, 0, nfeats, h->xT, h->RS, h->st));
+    phase("transpose to xT");
     if (h->use_q2) {
         const size_t acc = (size_t)h->maxslots * h->B * h->q2.SC;
         EVB_CUDA(dalloc(&h->xH, (size_t)(n + 1) * h->q2.RSH));
@@ -274,6 +289,7 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
         EVB_CUDA(cudaMemsetAsync(h->hsum_q, 0, acc * sizeof(unsigned long long), h->st));
         EVB_CUDA(cudaMemsetAsync(h->hcnt_q, 0, acc * sizeof(uint32_t), h->st));
         EVB_CHECK(evb_q2_build_layout(h));
+        phase("chunk rows (xH, xE)");
     }
     {
         const size_t ybytes = (size_t)n * (y_dtype == EVB_U32 ? 4 : 4 * (size_t)ycols);
@@ -298,7 +314,10 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
         EVB_CUDA(cudaMemcpy(h->feattypes_d, ft.data(), nfeats, cudaMemcpyHostToDevice));
         EVB_CUDA(cudaMemcpy(h->mono_d, mo.data(), sizeof(int32_t) * nfeats, cudaMemcpyHostToDevice));
     }
-    EVB_CHECK(evb_launch_check_bins(h));
+    phase("targets + state");
+    // bins made by the device binarize are 1 + (number of edges below the value): in range by construction
+    if (x_bin) EVB_CHECK(evb_launch_check_bins(h));
+    phase("bin range check");
     int err = 0;
     EVB_CUDA(cudaMemcpyAsync(&err, h->d_err, sizeof(int), cudaMemcpyDeviceToHost, h->st));
     EVB_CUDA(cudaStreamSynchronize(h->st));

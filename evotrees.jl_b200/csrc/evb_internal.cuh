@@ -237,8 +237,8 @@ int32_t evb_nccl_allreduce_i32(evb_handle *h, const int32_t *src, int32_t *dst, 
 void evb_nccl_destroy(evb_handle *h);
 
 // evb_stage.cu: pageable host memory -> device through a ring of pinned buffers filled by several host threads
-int32_t evb_h2d_staged(void *dst_dev, const void *src_host, size_t bytes, cudaStream_t st);
-int32_t evb_h2d_staged_strided(void *dst_dev, const void *src_host, size_t seg_bytes, size_t nseg, size_t stride, cudaStream_t st);
+int32_t evb_h2d_staged(void *dst_dev, const void *src_host, size_t bytes, cudaStream_t st, bool drain = true);
+int32_t evb_h2d_staged_strided(void *dst_dev, const void *src_host, size_t seg_bytes, size_t nseg, size_t stride, cudaStream_t st, bool drain = true);
 
 // EVB_HIST_MODE of the environment, reduced to the documented values (0: TMA bulk staging, 1: cp.async staging)
 int evb_hist_mode_env();

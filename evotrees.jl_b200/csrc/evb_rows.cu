@@ -1073,7 +1073,8 @@ int32_t evb_upload_binarize(evb_handle *h, const void *x, int32_t dtype, const v
     if (bx > 4096) bx = 4096;
     for (int j0 = 0; j0 < nfeats; j0 += cf) {
         const int nj = std::min(cf, nfeats - j0);
-        EVB_CHECK(evb_h2d_staged(d_x.p, (const char *)x + (size_t)j0 * n * es, (size_t)nj * n * es, h->st));
+        // no wait at the end of a block: its last chunks travel while the host gathers the next block's first ones
+        EVB_CHECK(evb_h2d_staged(d_x.p, (const char *)x + (size_t)j0 * n * es, (size_t)nj * n * es, h->st, false));
         dim3 grid(bx, (unsigned)nj);
         if (dtype == EVB_F32)
             k_binarize<float><<<grid, 256, (size_t)nedges * 4, h->st>>>((const float *)d_x.p, n, n, (const float *)d_e.p + (size_t)j0 * nedges, nedges,

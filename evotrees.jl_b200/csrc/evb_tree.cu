@@ -220,8 +220,8 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
     auto built = [&](int c, int b) -> double {
         if (a.qsum) {
             const size_t o = ((size_t)slot * B + b) * a.SC + feat;
-            if (c < K) return (double)(long long)a.qsum[o] * qi;
-            const double w = (double)a.qcnt[o];
+            if (c < K) return (double)(long long)__ldg(a.qsum + o) * qi;
+            const double w = (double)__ldg(a.qcnt + o);
             return c == C - 1 ? w : 2.0 * w;
         }
         return sm[c * B + b];
