@@ -1133,7 +1133,7 @@ static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntr
     // Blocks of `chunk` rows, two of everything: while the kernels of block k run, the host stages block k + 1 through
     // the pinned ring (several threads) and the copy engine brings it over.
     DevBuf d_feat, d_bin, d_split, d_ft, d_packed, d_leaf, d_in[2], d_xT[2], d_out, d_lidx, d_edges;
-    cudaEvent_t ev_free[2] = {nullptr, nullptr}, ev_k0[2] = {nullptr, nullptr}, ev_k1[2] = {nullptr, nullptr};
+    cudaEvent_t ev_free[2] = {nullptr, nullptr}, ev_k0[2] = {nullptr, nullptr}, ev_k1[2] = {nullptr, nullptr}, ev_in[2] = {nullptr, nullptr};
     cudaStream_t cs = nullptr;
     float kernel_ms = 0.f;
     // traversal out of shared memory when a tree (packed nodes + leaf table) fits a block of it
@@ -1151,6 +1151,7 @@ static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntr
         EVB_CUDA(cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking));
         for (int q = 0; q < 2; ++q) {
             EVB_CUDA(cudaEventCreateWithFlags(&ev_free[q], cudaEventDisableTiming));
+            EVB_CUDA(cudaEventCreateWithFlags(&ev_in[q], cudaEventDisableTiming));
             EVB_CUDA(cudaEventCreate(&ev_k0[q])); EVB_CUDA(cudaEventCreate(&ev_k1[q]));
             EVB_CUDA(d_in[q].alloc((size_t)chunk * nfeats * (x ? es : 1))); EVB_CUDA(d_xT[q].alloc((size_t)chunk * RS));
             EVB_CUDA(cudaMemsetAsync(d_xT[q].p, 0, (size_t)chunk * RS, st));
@@ -1186,10 +1187,12 @@ static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntr
                 if (cudaEventElapsedTime(&ms, ev_k0[q], ev_k1[q]) == cudaSuccess) kernel_ms += ms;
             }
             // rows r0 .. r0 + nr of every column (column-major input: one segment per feature), packed as [nfeats][nr]
-            if (x && x_row_major) EVB_CHECK(evb_h2d_staged(d_in[q].p, (const char *)x + (size_t)r0 * nfeats * es, (size_t)nr * nfeats * es, cs));
-            else if (x) EVB_CHECK(evb_h2d_staged_strided(d_in[q].p, (const char *)x + (size_t)r0 * es, (size_t)nr * es, (size_t)nfeats, (size_t)nobs * es, cs));
-            else EVB_CHECK(evb_h2d_staged_strided(d_in[q].p, x_bin + r0, (size_t)nr, (size_t)nfeats, (size_t)nobs, cs));
-            EVB_CUDA(cudaStreamSynchronize(cs));
+            // the host does not wait for the copies: the kernels do (event), and the host goes on gathering the next block
+            if (x && x_row_major) EVB_CHECK(evb_h2d_staged(d_in[q].p, (const char *)x + (size_t)r0 * nfeats * es, (size_t)nr * nfeats * es, cs, false));
+            else if (x) EVB_CHECK(evb_h2d_staged_strided(d_in[q].p, (const char *)x + (size_t)r0 * es, (size_t)nr * es, (size_t)nfeats, (size_t)nobs * es, cs, false));
+            else EVB_CHECK(evb_h2d_staged_strided(d_in[q].p, x_bin + r0, (size_t)nr, (size_t)nfeats, (size_t)nobs, cs, false));
+            EVB_CUDA(cudaEventRecord(ev_in[q], cs));
+            EVB_CUDA(cudaStreamWaitEvent(st, ev_in[q], 0));
             EVB_CUDA(cudaEventRecord(ev_k0[q], st));
             if (x) {
                 const unsigned blocks = (unsigned)((nr + 255) / 256);
@@ -1246,6 +1249,7 @@ static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntr
     if (ms_out) *ms_out = kernel_ms;
     for (int q = 0; q < 2; ++q) {
         if (ev_free[q]) cudaEventDestroy(ev_free[q]);
+        if (ev_in[q]) cudaEventDestroy(ev_in[q]);
         if (ev_k0[q]) cudaEventDestroy(ev_k0[q]);
         if (ev_k1[q]) cudaEventDestroy(ev_k1[q]);
     }
