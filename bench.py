@@ -365,7 +365,7 @@ def main():
             "metric": "train_seconds_per_200_rounds", "value": ms_step * ROUNDS_PER_JOB / 1e3, "unit": "s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-            "dtype": ("f32 gradients, exact 26-bit fixed-point sums (u32 reductions in shared memory, 64-bit accumulators), f64 histograms and split scan"
+            "dtype": ("f32 gradients, exact 24-bit fixed-point sums (u32 reductions in shared memory, 64-bit accumulators), f64 split scan"
                       if w["loss"] == "mse" else "f32 gradients, f32 partial sums in shared memory, f64 histograms and split scan"),
             "data": "synthetic",
             "config": {"workload": args.workload, "rows": rows, "feats": feats, "max_depth": depth, "nbins": nbins, "loss": w["loss"], "tree_type": args.tree_type,
