@@ -25,7 +25,7 @@ TIMER_NAMES = ["grads", "rows_init", "hist", "hist_reduce", "allreduce", "scan",
 
 EXPORTS = ["evb_last_error", "evb_version", "evb_create", "evb_create_x", "evb_destroy", "evb_comm_unique_id", "evb_comm_init", "evb_comm_ipc_export", "evb_comm_ipc_import",
            "evb_grow_tree", "evb_grow_tree_begin", "evb_grow_tree_end", "evb_eval_attach", "evb_eval_sums", "evb_eval_get_pred", "evb_eval_detach", "evb_test_peer_timeout", "evb_set_timing", "evb_get_pred", "evb_get_grads", "evb_get_nidx", "evb_get_hist", "evb_get_node_sums",
-           "evb_get_stream", "evb_get_timings", "evb_reset_timings", "evb_predict", "evb_predict_x", "evb_binarize", "evb_hist_rows", "evb_hist_rows_noalloc"]
+           "evb_get_stream", "evb_get_timings", "evb_reset_timings", "evb_predict", "evb_predict_x", "evb_binarize", "evb_hist_rows", "evb_hist_rows_noalloc", "evb_trim_cache"]
 
 
 class EvbError(RuntimeError):

@@ -9,7 +9,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libevotrees_b200.so")
-SOURCES = ["evb_api.cu", "evb_hist.cu", "evb_histq2.cu", "evb_tree.cu", "evb_rows.cu", "evb_nccl.cu", "evb_stage.cu"]
+SOURCES = ["evb_api.cu", "evb_hist.cu", "evb_histq2.cu", "evb_tree.cu", "evb_rows.cu", "evb_nccl.cu", "evb_stage.cu", "evb_alloc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 

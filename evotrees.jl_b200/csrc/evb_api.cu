@@ -68,6 +68,9 @@ static void resolve_timing(evb_handle *h) {
     h->ev_class.clear();
 }
 
+// stream on which dalloc() clears the blocks it hands out: the stream of the handle the calling thread works on
+static thread_local cudaStream_t g_alloc_stream = nullptr;
+
 struct BusyGuard {
     evb_handle *h;
     bool ok;
@@ -78,15 +81,21 @@ struct BusyGuard {
     if (!(h)) { evb_set_error("null handle"); return EVB_ERR_ARG; }                    \
     BusyGuard _guard(h);                                                               \
     if (!_guard.ok) { evb_set_error("handle is in use by another thread"); return EVB_ERR_BUSY; } \
-    EVB_CUDA(cudaSetDevice((h)->dev))
+    EVB_CUDA(cudaSetDevice((h)->dev));                                                 \
+    g_alloc_stream = (h)->st
 
 // Failure injection for the tests of the error paths: EVB_TEST_FAIL_ALLOC=k makes the k-th device allocation of the
 // next evb_create* of this thread fail as if the device were out of memory (nothing is allocated, nothing faults).
 static thread_local int g_alloc_countdown = 0;
+// Blocks may come from the library's cache with the previous owner's contents.  Everything below 256 MB is cleared on
+// the creating handle's stream (the large buffers -- bins, gradients, row lists -- are written in full before use).
 template <typename T>
 static cudaError_t dalloc(T **p, size_t count) {
     if (g_alloc_countdown > 0 && --g_alloc_countdown == 0) { *p = nullptr; return cudaErrorMemoryAllocation; }
-    return cudaMalloc((void **)p, (count ? count : 1) * sizeof(T));
+    const size_t bytes = (count ? count : 1) * sizeof(T);
+    cudaError_t e = evb_dev_alloc((void **)p, bytes);
+    if (e == cudaSuccess && bytes < ((size_t)256 << 20)) e = cudaMemsetAsync(*p, 0, bytes, g_alloc_stream);
+    return e;
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -115,7 +124,7 @@ static TreeBlockLayout tree_block_layout(int D, int nn, int K) {
 static void drop_graphs(evb_handle *h);
 static void free_eval(evb_handle *h) {
     void *ptrs[] = {h->ev_xT, h->ev_y, h->ev_w, h->ev_pred, h->ev_part};
-    for (void *p : ptrs) if (p) cudaFree(p);
+    for (void *p : ptrs) evb_dev_free(p);
     h->ev_xT = nullptr; h->ev_y = nullptr; h->ev_w = nullptr; h->ev_pred = nullptr; h->ev_part = nullptr;
     h->ev_n = 0;
 }
@@ -123,19 +132,33 @@ static void free_handle(evb_handle *h) {
     if (!h) return;
     cudaSetDevice(h->dev);
     if (h->st) cudaStreamSynchronize(h->st);
+    static const bool trace = getenv("EVB_INIT_TRACE") != nullptr;
+    auto t_last = std::chrono::steady_clock::now();
+    auto phase = [&](const char *name) {
+        if (!trace) return;
+        const auto now = std::chrono::steady_clock::now();
+        fprintf(stderr, "[evb destroy] %-21s %8.2f ms\n", name, std::chrono::duration<double, std::milli>(now - t_last).count());
+        t_last = now;
+    };
     evb_nccl_destroy(h);
     for (int i = 0; i < h->n_ipc_opened; ++i) cudaIpcCloseMemHandle(h->ipc_opened[i]);
-    if (h->peer_cand[h->rank]) cudaFree(h->peer_cand[h->rank]);
-    if (h->peer_flags[h->rank]) cudaFree(h->peer_flags[h->rank]);
-    if (h->d_barrier_seq) cudaFree(h->d_barrier_seq);
-    if (h->hsum) cudaFree(h->hsum);
+    // blocks that the other ranks mapped through CUDA IPC go back to the driver, not into the cache
+    const bool exported = h->peer_cand[h->rank] != nullptr;
+    evb_dev_free(h->peer_cand[h->rank], true);
+    evb_dev_free(h->peer_flags[h->rank], true);
+    evb_dev_free(h->d_barrier_seq);
+    evb_dev_free(h->hsum);
+    if (exported) { evb_dev_free(h->hcomp, true); h->hcomp = nullptr; }
     free_eval(h);
     void *ptrs[] = {h->xH, h->xE, h->hsum_q, h->hcnt_q, h->qs_cnt, h->qs_prefix, h->qs_rank, h->qs_gamma, h->gradq, h->d_gmax, h->d_qinv, h->xT, h->xC, h->grad, h->pred, h->y, h->nidx, h->rows[0], h->rows[1], h->mask_d, h->feattypes_d, h->mono_d,
                     h->js_d, h->seg_start, h->seg_cnt, h->gcnt, h->nleft, (h->gnleft != h->nleft) ? h->gnleft : nullptr, h->kind,
                     h->bslot, h->nsum, h->plan /* base of the tree block */, h->cum, h->slot_node, h->item_node, h->item_left,
                     h->item_lprefix, h->item_bits, h->scan_tmp, h->hist, h->hcomp, h->scratch, h->fbest_gain, h->fbest_bin, h->obl_gain, h->obl_best};
-    for (void *p : ptrs) if (p) cudaFree(p);
+    phase("exchange buffers");
+    for (void *p : ptrs) evb_dev_free(p);
+    phase("device buffers");
     drop_graphs(h);
+    phase("graphs");
     for (int q = 0; q < 2; ++q) {
         if (h->h_tree[q]) cudaFreeHost(h->h_tree[q]);
         if (h->h_js[q]) cudaFreeHost(h->h_js[q]);
@@ -144,6 +167,7 @@ static void free_handle(evb_handle *h) {
     for (cudaEvent_t e : h->ev) cudaEventDestroy(e);
     for (cudaEvent_t e : h->ev_tot) if (e) cudaEventDestroy(e);
     if (h->st) cudaStreamDestroy(h->st);
+    phase("pinned, events, stream");
     delete h;
 }
 
@@ -187,14 +211,16 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
     h->timing = (p->flags & EVB_FLAG_TIMING) != 0;
     h->world = 1; h->rank = 0; h->F = nfeats;
     h->hist_mode = evb_hist_mode_env();
-    cudaDeviceProp prop;
-    EVB_CUDA(cudaGetDeviceProperties(&prop, h->dev));
-    if (prop.major < 10) {
-        evb_set_error("device %d is sm_%d%d; this library is built for sm_100a only", h->dev, prop.major, prop.minor);
+    int cc_major = 0, cc_minor = 0; // single attributes: cudaGetDeviceProperties queries everything and takes milliseconds
+    EVB_CUDA(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, h->dev));
+    EVB_CUDA(cudaDeviceGetAttribute(&cc_minor, cudaDevAttrComputeCapabilityMinor, h->dev));
+    if (cc_major < 10) {
+        evb_set_error("device %d is sm_%d%d; this library is built for sm_100a only", h->dev, cc_major, cc_minor);
         return EVB_ERR_CUDA;
     }
-    h->num_sms = prop.multiProcessorCount;
+    EVB_CUDA(cudaDeviceGetAttribute(&h->num_sms, cudaDevAttrMultiProcessorCount, h->dev));
     EVB_CUDA(cudaStreamCreateWithFlags(&h->st, cudaStreamNonBlocking));
+    g_alloc_stream = h->st;
     const int64_t n = nobs;
     const int nids = h->nn + 2, C = h->C, K = h->K, D = h->D;
 
@@ -293,7 +319,7 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
     }
     {
         const size_t ybytes = (size_t)n * (y_dtype == EVB_U32 ? 4 : 4 * (size_t)ycols);
-        EVB_CUDA(cudaMalloc(&h->y, ybytes ? ybytes : 1));
+        EVB_CUDA(evb_dev_alloc(&h->y, ybytes ? ybytes : 1));
         EVB_CUDA(cudaMemcpyAsync(h->y, y, ybytes, cudaMemcpyHostToDevice, h->st));
         float *w_d = nullptr, *p0_d = nullptr, *mu_d = nullptr;
         if (w) { EVB_CUDA(dalloc(&w_d, (size_t)n)); EVB_CUDA(cudaMemcpyAsync(w_d, w, sizeof(float) * n, cudaMemcpyHostToDevice, h->st)); }
@@ -301,9 +327,9 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
         else { EVB_CUDA(dalloc(&mu_d, (size_t)K)); EVB_CUDA(cudaMemcpyAsync(mu_d, mu, sizeof(float) * K, cudaMemcpyHostToDevice, h->st)); }
         int32_t rc = evb_launch_init_state(h, w_d, p0_d, mu_d);
         cudaStreamSynchronize(h->st);
-        if (w_d) cudaFree(w_d);
-        if (p0_d) cudaFree(p0_d);
-        if (mu_d) cudaFree(mu_d);
+        evb_dev_free(w_d);
+        evb_dev_free(p0_d);
+        evb_dev_free(mu_d);
         EVB_CHECK(rc);
     }
     {
@@ -492,7 +518,7 @@ extern "C" int32_t evb_grow_tree_begin(evb_handle *h, const uint8_t *row_mask, u
         EVB_CHECK(evb_hist_geometry(h, njs, &g));
         const size_t need = (size_t)g.NUG * g.PG * g.UB * g.img_floats;
         if (need > h->scratch_floats) {
-            EVB_CUDA(cudaFree(h->scratch));
+            evb_dev_free(h->scratch);
             h->scratch = nullptr;
             EVB_CUDA(dalloc(&h->scratch, need));
             h->scratch_floats = need;
@@ -623,7 +649,7 @@ static int32_t eval_attach_impl(evb_handle *h, int64_t nobs, const uint8_t *x_bi
     EVB_CUDA(dalloc(&h->ev_pred, (size_t)nobs * K));
     EVB_CUDA(dalloc(&h->ev_part, (size_t)h->ev_blocks * 2));
     const size_t ybytes = (size_t)nobs * (h->y_dtype == EVB_U32 ? 4 : 4 * (size_t)h->ycols);
-    EVB_CUDA(cudaMalloc(&h->ev_y, ybytes));
+    EVB_CUDA(evb_dev_alloc(&h->ev_y, ybytes));
     EVB_CUDA(cudaMemcpyAsync(h->ev_y, y, ybytes, cudaMemcpyHostToDevice, h->st));
     if (w) {
         EVB_CUDA(dalloc(&h->ev_w, (size_t)nobs));
@@ -653,8 +679,8 @@ static int32_t eval_attach_impl(evb_handle *h, int64_t nobs, const uint8_t *x_bi
         if (rc == EVB_OK && cudaMemcpyAsync(h->last_eval, h->d_evsum, sizeof(h->last_eval), cudaMemcpyDeviceToHost, h->st) != cudaSuccess) rc = EVB_ERR_CUDA;
     }
     cudaError_t e = cudaStreamSynchronize(h->st);
-    if (stage) cudaFree(stage);
-    if (leaf_d) cudaFree(leaf_d);
+    evb_dev_free(stage);
+    evb_dev_free(leaf_d);
     if (rc == EVB_ERR_CUDA || e != cudaSuccess) {
         evb_set_error("evb_eval_attach: CUDA error %s", cudaGetErrorString(e != cudaSuccess ? e : cudaGetLastError()));
         return EVB_ERR_CUDA;
@@ -722,7 +748,7 @@ extern "C" int32_t evb_comm_ipc_export(evb_handle *h, uint8_t blob[256]) {
     // every scanned node keeps the summed histogram of the features this rank owns (children subtract from it)
     const int keep_nodes = 1 << (D > 1 ? D - 1 : 0);
     if (keep_nodes > h->hist_nodes) {
-        EVB_CUDA(cudaFree(h->hist));
+        evb_dev_free(h->hist);
         h->hist = nullptr;
         EVB_CUDA(dalloc(&h->hist, (size_t)keep_nodes * h->nfeats * h->C * h->B));
         h->hist_nodes = keep_nodes;
@@ -846,7 +872,7 @@ extern "C" int32_t evb_get_nidx(evb_handle *h, uint32_t *nidx, int32_t from_part
             if (e == cudaSuccess) e = cudaStreamSynchronize(h->st);
             if (e != cudaSuccess) { evb_set_error("CUDA error %s", cudaGetErrorString(e)); rc = EVB_ERR_CUDA; }
         }
-        cudaFree(tmp);
+        evb_dev_free(tmp);
         return rc;
     }
     EVB_CUDA(cudaMemcpyAsync(nidx, h->nidx, sizeof(uint32_t) * h->n, cudaMemcpyDeviceToHost, h->st));

@@ -237,6 +237,11 @@ int32_t evb_nccl_allreduce_i32(evb_handle *h, const int32_t *src, int32_t *dst, 
 void evb_nccl_destroy(evb_handle *h);
 
 // evb_stage.cu: pageable host memory -> device through a ring of pinned buffers filled by several host threads
+// device memory through the library's block cache (evb_alloc.cu)
+cudaError_t evb_dev_alloc(void **p, size_t bytes);
+void evb_dev_free(void *p, bool really = false);
+template <typename T> inline cudaError_t evb_dev_alloc(T **p, size_t bytes) { return evb_dev_alloc(reinterpret_cast<void **>(p), bytes); }
+
 int32_t evb_h2d_staged(void *dst_dev, const void *src_host, size_t bytes, cudaStream_t st, bool drain = true);
 int32_t evb_h2d_staged_strided(void *dst_dev, const void *src_host, size_t seg_bytes, size_t nseg, size_t stride, cudaStream_t st, bool drain = true);
 

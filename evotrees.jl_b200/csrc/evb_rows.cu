@@ -1055,7 +1055,7 @@ int32_t evb_launch_nidx_from_partition(evb_handle *h, uint32_t *out_dev) {
 // ---- training matrix from raw features -----------------------------------------------------------------
 struct DevBufT {
     void *p = nullptr;
-    ~DevBufT() { if (p) cudaFree(p); }
+    ~DevBufT() { evb_dev_free(p); }
 };
 // `binarize(x_train; edges)` of `init_core` (ext/EvoTreesKernelAbstractionsExt/init.jl:3-6, src/fit-utils.jl:66-72) on the
 // device: the raw column-major matrix travels in blocks of whole features (each at most 256 MB) and every block is
@@ -1066,8 +1066,8 @@ int32_t evb_upload_binarize(evb_handle *h, const void *x, int32_t dtype, const v
     const int nfeats = h->nfeats;
     int cf = (int)std::max<int64_t>(1, std::min<int64_t>(nfeats, ((int64_t)256 << 20) / (int64_t)(n * es)));
     DevBufT d_x, d_e;
-    EVB_CUDA(cudaMalloc(&d_x.p, (size_t)cf * n * es));
-    EVB_CUDA(cudaMalloc(&d_e.p, (size_t)nedges * nfeats * es));
+    EVB_CUDA(evb_dev_alloc(&d_x.p, (size_t)cf * n * es));
+    EVB_CUDA(evb_dev_alloc(&d_e.p, (size_t)nedges * nfeats * es));
     EVB_CUDA(cudaMemcpyAsync(d_e.p, edges, (size_t)nedges * nfeats * es, cudaMemcpyHostToDevice, h->st));
     unsigned bx = (unsigned)((n + 255) / 256);
     if (bx > 4096) bx = 4096;
@@ -1103,8 +1103,8 @@ static int32_t check_device(int device) {
 
 struct DevBuf {
     void *p = nullptr;
-    ~DevBuf() { if (p) cudaFree(p); }
-    cudaError_t alloc(size_t bytes) { return cudaMalloc(&p, bytes ? bytes : 1); }
+    ~DevBuf() { evb_dev_free(p); }
+    cudaError_t alloc(size_t bytes) { return evb_dev_alloc(&p, bytes ? bytes : 1); }
     template <typename T> T *as() { return reinterpret_cast<T *>(p); }
 };
 

@@ -125,6 +125,14 @@ EVB_API int32_t evb_create_x(evb_handle **out, const evb_params *p, int64_t nobs
                              const void *edges, int32_t nedges, const void *y, int32_t y_dtype, int32_t ycols, const float *w,
                              const float *pred0, const float *mu, const uint8_t *feattypes, const int32_t *monotone);
 EVB_API void evb_destroy(evb_handle *h);
+/*
+ * Device memory released by evb_destroy and by the inference calls is kept by the library and reused by the next
+ * evb_create* / evb_predict* of about the same size (cudaMalloc and cudaFree take driver-wide locks: a second `fit` of
+ * the same shape then makes no allocator call).  The reference leaves this to CUDA.jl's memory pool and to
+ * `post_fit_gc` (ext/EvoTreesCUDAExt.jl:7-12).  evb_trim_cache gives the kept blocks of one GPU back to the driver; the
+ * library does so by itself when an allocation fails.  EVB_CACHE=0 in the environment turns the cache off.
+ */
+EVB_API int32_t evb_trim_cache(int32_t device);
 
 /*
  * Row sharding over several GPUs (one handle per GPU, normally one process per GPU).  Rank 0 obtains an

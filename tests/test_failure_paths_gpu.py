@@ -82,6 +82,7 @@ def test_failed_allocation_inside_create_frees_everything(pkg, kth):
     from evotrees_b200 import _lib
     cache, _ = _cache(pkg, n=50_000)        # warm-up: context, pinned staging ring, kernel attributes
     cache.close()
+    assert _lib.lib().evb_trim_cache(C.c_int32(0)) == 0     # released blocks are kept for reuse: hand them back first
     torch.cuda.synchronize()
     free_before = torch.cuda.mem_get_info(0)[0]
     os.environ["EVB_TEST_FAIL_ALLOC"] = str(kth)
@@ -91,9 +92,43 @@ def test_failed_allocation_inside_create_frees_everything(pkg, kth):
         assert ei.value.code == -2 and "out of memory" in str(ei.value).lower()
     finally:
         del os.environ["EVB_TEST_FAIL_ALLOC"]
+    assert _lib.lib().evb_trim_cache(C.c_int32(0)) == 0
     torch.cuda.synchronize()
     assert torch.cuda.mem_get_info(0)[0] == free_before, "a failed evb_create left device memory behind"
     cache, params = _cache(pkg, n=50_000)   # and the next create works
     js = np.arange(1, cache.nfeats + 1, dtype=np.uint32)
     assert pkg.grow_tree(cache, params, None, js, True).split[0]
     cache.close()
+
+
+def test_released_blocks_are_reused_and_trimmed(pkg):
+    """evb_destroy keeps the device blocks; an equal evb_create takes them back (no growth), evb_trim_cache returns them."""
+    import torch
+    from evotrees_b200 import _lib
+    lib = _lib.lib()
+    cache, _ = _cache(pkg, n=200_000)
+    cache.close()
+    assert lib.evb_trim_cache(C.c_int32(0)) == 0
+    torch.cuda.synchronize()
+    free_empty = torch.cuda.mem_get_info(0)[0]
+    cache, params = _cache(pkg, n=200_000)
+    torch.cuda.synchronize()
+    free_live = torch.cuda.mem_get_info(0)[0]
+    assert free_live < free_empty
+    cache.close()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(0)[0] == free_live          # nothing went back to the driver
+    cache, params = _cache(pkg, n=200_000)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(0)[0] == free_live          # and nothing new was taken
+    js = np.arange(1, cache.nfeats + 1, dtype=np.uint32)
+    t1 = pkg.grow_tree(cache, params, None, js, True)
+    cache.close()
+    cache, params = _cache(pkg, n=200_000)                     # reused blocks hold the old handle's data: same tree all the same
+    t2 = pkg.grow_tree(cache, params, None, js, True)
+    assert np.array_equal(t1.feat, t2.feat) and np.array_equal(t1.cond_bin, t2.cond_bin) and np.array_equal(t1.pred, t2.pred)
+    cache.close()
+    assert lib.evb_trim_cache(C.c_int32(0)) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(0)[0] == free_empty
+    assert lib.evb_trim_cache(C.c_int32(99)) == -1
