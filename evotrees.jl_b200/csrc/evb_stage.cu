@@ -10,6 +10,10 @@
 #include <stdlib.h>
 #include <string.h>
 #include <thread>
+#if defined(__x86_64__)
+#include <emmintrin.h>
+#endif
+#include <stdint.h>
 
 namespace {
 
@@ -36,6 +40,29 @@ int stage_threads() {
     return n;
 }
 
+// Copy into the pinned ring with streaming stores: the destination is read next by the copy engine, not by this core,
+// so it should not be pulled into the cache first (a plain memcpy reads every destination line before writing it,
+// and the host's memory bandwidth is what limits the whole upload).
+#if defined(__x86_64__)
+void stream_copy(char *dst, const char *src, size_t n) {
+    size_t head = (16 - ((uintptr_t)dst & 15)) & 15;
+    if (head > n) head = n;
+    if (head) { memcpy(dst, src, head); dst += head; src += head; n -= head; }
+    const size_t blocks = n / 64;
+    for (size_t i = 0; i < blocks; ++i) {
+        const __m128i a = _mm_loadu_si128((const __m128i *)(src) + 0), b = _mm_loadu_si128((const __m128i *)(src) + 1);
+        const __m128i c = _mm_loadu_si128((const __m128i *)(src) + 2), d = _mm_loadu_si128((const __m128i *)(src) + 3);
+        _mm_stream_si128((__m128i *)(dst) + 0, a); _mm_stream_si128((__m128i *)(dst) + 1, b);
+        _mm_stream_si128((__m128i *)(dst) + 2, c); _mm_stream_si128((__m128i *)(dst) + 3, d);
+        src += 64; dst += 64;
+    }
+    _mm_sfence();
+    if (n & 63) memcpy(dst, src, n & 63);
+}
+#else
+void stream_copy(char *dst, const char *src, size_t n) { memcpy(dst, src, n); }
+#endif
+
 // copies bytes [off, off + len) of the packed sequence (nseg segments of seg_bytes, segment k starting at src + k * stride)
 void gather_copy(char *dst, const char *src, size_t seg_bytes, size_t stride, size_t off, size_t len) {
     size_t p = off;
@@ -43,7 +70,7 @@ void gather_copy(char *dst, const char *src, size_t seg_bytes, size_t stride, si
     while (p < end) {
         const size_t seg = p / seg_bytes, within = p - seg * seg_bytes;
         const size_t n = seg_bytes - within < end - p ? seg_bytes - within : end - p;
-        memcpy(dst + (p - off), src + seg * stride + within, n);
+        stream_copy(dst + (p - off), src + seg * stride + within, n);
         p += n;
     }
 }
