@@ -4,6 +4,7 @@ of evb_create (injected on the host)."""
 import ctypes as C
 import os
 import threading
+import time
 
 import numpy as np
 import pytest
@@ -34,12 +35,23 @@ def test_handle_in_use_by_another_thread_reports_busy(pkg):
         t = _lib.EvbTimings()
         while not stop.is_set():
             codes.append(_lib.lib().evb_get_timings(cache.handle, C.byref(t)))
+            time.sleep(1e-4)         # a tree takes milliseconds: ten looks per tree are plenty
+
+    def grow():                      # the owner may itself meet the other thread inside the handle: it just calls again
+        for _ in range(2000):
+            try:
+                return pkg.grow_tree(cache, params, None, js, True)
+            except _lib.EvbError as e:
+                if e.code != -6:
+                    raise
+                time.sleep(5e-4)
+        raise AssertionError("the handle stayed busy")
 
     th = threading.Thread(target=poke)
     th.start()
     try:
         for _ in range(30):
-            pkg.grow_tree(cache, params, None, js, True)          # each call holds the handle for a few milliseconds
+            grow()                                                # each call holds the handle for a few milliseconds
     finally:
         stop.set()
         th.join()
