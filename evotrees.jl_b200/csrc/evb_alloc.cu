@@ -4,7 +4,8 @@
 // measured anywhere between 5 ms and 2 s, which is a multiple of a whole `fit`.  With the cache a second `fit` (or
 // predict call) of the same shape makes no allocator call at all.  Blocks are whole cudaMalloc allocations (never
 // sub-allocated), so they stay valid for cudaIpcGetMemHandle.  The cache gives everything back when an allocation fails
-// (then it retries once), on evb_trim_cache(), and never otherwise; EVB_CACHE=0 turns it off.
+// (then it retries once) and on evb_trim_cache(); it never keeps more than half of the device's memory
+// (EVB_CACHE_MAX_GB sets another limit); EVB_CACHE=0 turns it off.
 #include "evb_internal.cuh"
 #include <mutex>
 #include <stdlib.h>
@@ -19,6 +20,7 @@ struct DevCache {
     std::vector<Block> free_blocks;
     std::unordered_map<void *, size_t> live; // blocks handed out by evb_dev_alloc
     size_t cached_bytes = 0;
+    size_t cap = 0; // most bytes the cache keeps: half of the device's memory unless EVB_CACHE_MAX_GB says otherwise
 };
 DevCache g_cache[64];
 
@@ -89,7 +91,12 @@ void evb_dev_free(void *p, bool really) {
     if (it == c.live.end()) { cudaFree(p); return; } // not one of ours (allocated on another device, or before a fork)
     const size_t bytes = it->second;
     c.live.erase(it);
-    if (really) { cudaFree(p); return; }
+    if (c.cap == 0) {
+        size_t free_b = 0, total_b = 0;
+        c.cap = cudaMemGetInfo(&free_b, &total_b) == cudaSuccess ? total_b / 2 : (size_t)16 << 30;
+        if (const char *e = getenv("EVB_CACHE_MAX_GB")) { const double gb = atof(e); if (gb >= 0.0) c.cap = (size_t)(gb * 1073741824.0); }
+    }
+    if (really || c.cached_bytes + bytes > c.cap) { cudaFree(p); return; }
     c.free_blocks.push_back({p, bytes});
     c.cached_bytes += bytes;
 }

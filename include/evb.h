@@ -130,7 +130,8 @@ EVB_API void evb_destroy(evb_handle *h);
  * evb_create* / evb_predict* of about the same size (cudaMalloc and cudaFree take driver-wide locks: a second `fit` of
  * the same shape then makes no allocator call).  The reference leaves this to CUDA.jl's memory pool and to
  * `post_fit_gc` (ext/EvoTreesCUDAExt.jl:7-12).  evb_trim_cache gives the kept blocks of one GPU back to the driver; the
- * library does so by itself when an allocation fails.  EVB_CACHE=0 in the environment turns the cache off.
+ * library does so by itself when an allocation fails, and never keeps more than half of the device's memory
+ * (EVB_CACHE_MAX_GB).  EVB_CACHE=0 in the environment turns the cache off.
  */
 EVB_API int32_t evb_trim_cache(int32_t device);
 
