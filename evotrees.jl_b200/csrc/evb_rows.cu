@@ -397,6 +397,9 @@ struct FinPipeArgs {
     int S;                // words per row in shared memory: a multiple of 4, an odd number of 16-byte chunks
     int ntiles, leaf_in_smem;
 };
+// MSE1: mse with one output and the record {g, w} (hessian rebuilt from w): loss, K and the record layout are
+// compile-time constants
+template <bool MSE1>
 __global__ void __launch_bounds__(256) k_finalize_pipe(FinPipeArgs a) {
     // [nnp] packed tree, [nnp] leaf values (one output only), 2 x [256][S] words of bins; nnp = nn rounded up to four
     // words, so that the row buffers start on a 16-byte boundary (the copies into them are 16 bytes wide)
@@ -450,15 +453,16 @@ __global__ void __launch_bounds__(256) k_finalize_pipe(FinPipeArgs a) {
         if (act) {
             const int nid = traverse(s_tree, reinterpret_cast<const uint8_t *>(s_rows + ((size_t)buf * 256 + threadIdx.x) * S));
             f.nidx[i] = (uint32_t)nid;
+            const int loss = MSE1 ? (int)EVB_MSE : f.loss, NCH = MSE1 ? 2 : f.NCH;
             if (f.K == 1) {
                 float pl[1] = {p0};
-                pred_add(f.loss, 1, pl, a.leaf_in_smem ? s_leaf + (nid - 1) : f.t_pred + (nid - 1));
+                pred_add(loss, 1, pl, a.leaf_in_smem ? s_leaf + (nid - 1) : f.t_pred + (nid - 1));
                 p[0] = pl[0];
             } else {
-                pred_add(f.loss, f.K, p, f.t_pred + (size_t)(nid - 1) * f.K);
+                pred_add(loss, f.K, p, f.t_pred + (size_t)(nid - 1) * f.K);
             }
             if (f.compute_grads) {
-                grad_row(f.loss, f.K, f.NCH, f.elided != 0, p, f.y, f.ycols, i, f.grad + (size_t)i * f.GS, f.alpha);
+                grad_row(loss, MSE1 ? 1 : f.K, NCH, MSE1 ? true : f.elided != 0, p, f.y, MSE1 ? 1 : f.ycols, i, f.grad + (size_t)i * f.GS, f.alpha);
                 gm = fmaxf(gm, fabsf(f.grad[(size_t)i * f.GS]));
             }
         }
@@ -976,13 +980,18 @@ int32_t evb_launch_finalize(evb_handle *h, bool compute_grads, int mode) {
     // measured (B200): 0.33 instead of 0.42 ms per 10M rows x 100 features with one output; with several outputs the
     // prediction and gradient streams outweigh the bins and the one-tile-per-CTA kernel below is faster
     if (mode == 0 && h->K == 1 && pipe_smem <= 100 * 1024 && pa.wordsA <= 64 && !direct && !no_pipe && h->dev < 64) {
-        if (!attr_pipe[h->dev]) { cudaFuncSetAttribute(k_finalize_pipe, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); attr_pipe[h->dev] = true; }
+        if (!attr_pipe[h->dev]) {
+            cudaFuncSetAttribute(k_finalize_pipe<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+            cudaFuncSetAttribute(k_finalize_pipe<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+            attr_pipe[h->dev] = true;
+        }
         int per_sm = (int)((227 * 1024) / (pipe_smem + 1024)); // 1 KB per resident CTA is reserved
         if (per_sm > 6) per_sm = 6;
         if (per_sm < 1) per_sm = 1;
         int grid = h->num_sms * per_sm;
         if (grid > pa.ntiles) grid = pa.ntiles;
-        k_finalize_pipe<<<grid, 256, pipe_smem, h->st>>>(pa);
+        if (h->p.loss == EVB_MSE && a.elided && h->rec_nch == 2 && h->ycols == 1) k_finalize_pipe<true><<<grid, 256, pipe_smem, h->st>>>(pa);
+        else k_finalize_pipe<false><<<grid, 256, pipe_smem, h->st>>>(pa);
     } else if (mode == 0 && h->RS <= 256 && staged <= 100 * 1024 && !direct && h->dev < 64) {
         if (!attr_set[h->dev]) { cudaFuncSetAttribute(k_finalize_staged, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); attr_set[h->dev] = true; }
         k_finalize_staged<<<(unsigned)((h->n + 255) / 256), 256, staged, h->st>>>(a);

@@ -210,9 +210,11 @@ __global__ void __launch_bounds__(256) k_peer_reduce(PeerReduceArgs a) {
 // Scan of one (node, feature): applies the sibling subtraction (`subtract_hist!`, fit-utils.jl:321-332) to the
 // staged histogram `sm` of the build node, stores the node's histogram if its children will need it, scans the
 // bins (`_scan_node!`, fit-utils.jl:403-436) and records the best split of this feature.
-template <int MAXCHK, bool OWN, bool OBL>
+template <int MAXCHK, bool OWN, bool OBL, bool K1>
 __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int f, int slot, double *s_sum, int lane, bool first_owned) {
-    const int C = a.C, K = a.K, B = a.B, F = a.F;
+    // K1: one output with gradient, hessian and weight channels (C = 3), known at compile time: the loops over the
+    // outputs and the channel tests fold away
+    const int C = K1 ? 3 : a.C, K = K1 ? 1 : a.K, B = a.B, F = a.F;
     const uint32_t feat = a.js0[f];
     const double *__restrict__ sm = a.hcomp + ((size_t)slot * F + f) * C * B;
     const double qi = a.qsum ? a.qinv[0] : 0.0;
@@ -351,7 +353,7 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
 // independent, so even the root level (one node) spreads over many SMs.
 // OWN: the loss brings its own split gain (mae, credibility); OBL: oblivious trees, the gain of every candidate is
 // stored as well.  The default instance carries neither code.
-template <int MAXCHK, bool OWN, bool OBL>
+template <int MAXCHK, bool OWN, bool OBL, bool K1>
 __global__ void __launch_bounds__(256, MAXCHK <= 2 ? 3 : 2) k_scan_feat(ScanArgs a) {
     __shared__ double s_sum_all[8][72];
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
@@ -365,7 +367,7 @@ __global__ void __launch_bounds__(256, MAXCHK <= 2 ? 3 : 2) k_scan_feat(ScanArgs
     if (s >= a.plan->nbuild) return;
     const int f = fi * a.world + a.rank;
     const int nb = a.slot_node[s];
-    scan_one<MAXCHK, OWN, OBL>(a, which ? nb ^ 1 : nb, which != 0, f, s, s_sum_all[wid], lane, fi == 0);
+    scan_one<MAXCHK, OWN, OBL, K1>(a, which ? nb ^ 1 : nb, which != 0, f, s, s_sum_all[wid], lane, fi == 0);
 }
 
 // Oblivious trees, stage 1b: one thread per candidate (feature slot, bin) adds the gains of the level's nodes in
@@ -947,10 +949,11 @@ int32_t evb_launch_scan(evb_handle *h, int level) {
         const bool own = h->p.loss >= EVB_MAE;
         const bool obl = h->obl_gain != nullptr;
 #define EVB_SCAN(M) do { \
-            if (own && obl) k_scan_feat<M, true, true><<<grid, 256, 0, h->st>>>(a); \
-            else if (own) k_scan_feat<M, true, false><<<grid, 256, 0, h->st>>>(a); \
-            else if (obl) k_scan_feat<M, false, true><<<grid, 256, 0, h->st>>>(a); \
-            else k_scan_feat<M, false, false><<<grid, 256, 0, h->st>>>(a); } while (0)
+            if (own && obl) k_scan_feat<M, true, true, false><<<grid, 256, 0, h->st>>>(a); \
+            else if (own) k_scan_feat<M, true, false, false><<<grid, 256, 0, h->st>>>(a); \
+            else if (obl) k_scan_feat<M, false, true, false><<<grid, 256, 0, h->st>>>(a); \
+            else if (h->K == 1 && h->C == 3) k_scan_feat<M, false, false, true><<<grid, 256, 0, h->st>>>(a); \
+            else k_scan_feat<M, false, false, false><<<grid, 256, 0, h->st>>>(a); } while (0)
         if (h->B <= 32) EVB_SCAN(1); else if (h->B <= 64) EVB_SCAN(2); else if (h->B <= 128) EVB_SCAN(4); else EVB_SCAN(8);
 #undef EVB_SCAN
     }
