@@ -464,9 +464,10 @@ __device__ __forceinline__ void apply_split(const ScanArgs &a, int n, bool has, 
 // Stage 2: one warp per node: first strict maximum over the (owned) features in ascending feature order and the
 // left-child sums of the winner (`_child_sums!`, fit-utils.jl:472-486).  Single GPU: the split is applied at once.
 // Sharded with peer access: the rank's candidate is written into every rank's candidate table instead.
+template <bool K1>
 __global__ void __launch_bounds__(256) k_scan_node(ScanArgs a) {
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int C = a.C, B = a.B, F = a.F;
+    const int C = K1 ? 3 : a.C, B = a.B, F = a.F; // K1: one output, channels g, h, w known at compile time
     const int m = 1 << (a.level - 1);
     const int i = blockIdx.x * (blockDim.x >> 5) + wid;
     __shared__ double s_sum_all[8][72], s_left_all[8][72], s_right_all[8][72];
@@ -526,24 +527,48 @@ __global__ void __launch_bounds__(256) k_scan_node(ScanArgs a) {
         const size_t fo = (size_t)bs * C * B;
         const size_t qo = a.qsum ? (size_t)slot_n * B * a.SC + a.js0[bs] : 0;
         const double qi = a.qsum ? a.qinv[0] : 0.0;
-        for (int c = 0; c < C; ++c) {
-            double v = 0.0;
-            const int b0 = numeric ? lane : bb, b1 = bb;
+        // entry (channel c, bin b) of the winner's histogram in this node
+        auto entry = [&](int c, int b) -> double {
+            const size_t o = fo + (size_t)c * B + b;
+            if (a.world > 1) return hn[o]; // sharded: the summed histogram of every scanned node is retained locally for the owned features
+            double built;
+            if (a.qsum) {
+                const size_t q = qo + (size_t)b * a.SC;
+                built = c < a.K ? (double)(long long)a.qsum[q] * qi : (c == C - 1 ? 1.0 : 2.0) * (double)a.qcnt[q];
+            } else {
+                built = hc[o];
+            }
+            return sub ? hp[o] - built : built;
+        };
+        const int b0 = numeric ? lane : bb, b1 = bb;
+        if (K1) { // the three channels side by side; the mse hessian is twice the weight, entry by entry
+            double vg = 0.0, vh = 0.0, vw = 0.0;
             for (int b = b0; b <= b1; b += 32) {
-                const size_t o = fo + (size_t)c * B + b;
-                // sharded: the summed histogram of every scanned node is retained locally for the owned features
-                double built;
-                if (a.qsum) {
-                    const size_t q = qo + (size_t)b * a.SC;
-                    built = c < a.K ? (double)(long long)a.qsum[q] * qi : (c == C - 1 ? 1.0 : 2.0) * (double)a.qcnt[q];
-                } else {
-                    built = hc[o];
-                }
-                v += a.world > 1 ? hn[o] : (sub ? hp[o] - built : built);
+                vg += entry(0, b);
+                if (!a.elide_h) vh += entry(1, b);
+                vw += entry(2, b);
                 if (!numeric) break;
             }
-            if (numeric) v = warp_sum(v);
-            if (lane == 0) s_left[c] = v;
+            if (numeric) {
+#pragma unroll
+                for (int d = 16; d >= 1; d >>= 1) {
+                    vg += __shfl_xor_sync(FULL, vg, d);
+                    vh += __shfl_xor_sync(FULL, vh, d);
+                    vw += __shfl_xor_sync(FULL, vw, d);
+                }
+            }
+            if (a.elide_h) vh = 2.0 * vw;
+            if (lane == 0) { s_left[0] = vg; s_left[1] = vh; s_left[2] = vw; }
+        } else {
+            for (int c = 0; c < C; ++c) {
+                double v = 0.0;
+                for (int b = b0; b <= b1; b += 32) {
+                    v += entry(c, b);
+                    if (!numeric) break;
+                }
+                if (numeric) v = warp_sum(v);
+                if (lane == 0) s_left[c] = v;
+            }
         }
         __syncwarp();
     }
@@ -965,7 +990,8 @@ int32_t evb_launch_scan(evb_handle *h, int level) {
         evb_toc(h, EVB_T_SCAN);
     }
     evb_tic(h, EVB_T_SCAN);
-    k_scan_node<<<(m + 7) / 8, 256, 0, h->st>>>(a);
+    if (h->K == 1 && h->C == 3) k_scan_node<true><<<(m + 7) / 8, 256, 0, h->st>>>(a);
+    else k_scan_node<false><<<(m + 7) / 8, 256, 0, h->st>>>(a);
     evb_toc(h, EVB_T_SCAN);
     if (p2p) {
         evb_tic(h, EVB_T_ALLREDUCE); int32_t rc = launch_peer_barrier(h); evb_toc(h, EVB_T_ALLREDUCE); EVB_CHECK(rc);
