@@ -101,6 +101,86 @@ void evb_dev_free(void *p, bool really) {
     c.cached_bytes += bytes;
 }
 
+// ---- the same for what else a handle takes from the driver: pinned host blocks, its stream, its two events ------------
+namespace {
+struct HostCache {
+    std::mutex mu;
+    std::vector<Block> free_blocks;
+    std::unordered_map<void *, size_t> live;
+    std::vector<cudaStream_t> streams[64];
+    std::vector<cudaEvent_t> events[64];
+};
+HostCache g_host;
+} // namespace
+
+cudaError_t evb_host_alloc(void **p, size_t bytes) {
+    *p = nullptr;
+    const size_t want = (bytes + 4095) & ~(size_t)4095;
+    if (!cache_on()) return cudaMallocHost(p, want);
+    std::lock_guard<std::mutex> lock(g_host.mu);
+    for (size_t i = 0; i < g_host.free_blocks.size(); ++i) {
+        if (g_host.free_blocks[i].bytes == want) {
+            *p = g_host.free_blocks[i].p;
+            g_host.free_blocks[i] = g_host.free_blocks.back();
+            g_host.free_blocks.pop_back();
+            g_host.live[*p] = want;
+            return cudaSuccess;
+        }
+    }
+    const cudaError_t e = cudaMallocHost(p, want);
+    if (e != cudaSuccess) { *p = nullptr; return e; }
+    g_host.live[*p] = want;
+    return cudaSuccess;
+}
+void evb_host_free(void *p) {
+    if (!p) return;
+    if (!cache_on()) { cudaFreeHost(p); return; }
+    std::lock_guard<std::mutex> lock(g_host.mu);
+    auto it = g_host.live.find(p);
+    if (it == g_host.live.end()) { cudaFreeHost(p); return; }
+    const size_t bytes = it->second;
+    g_host.live.erase(it);
+    if (bytes > ((size_t)64 << 20) || g_host.free_blocks.size() >= 64) { cudaFreeHost(p); return; } // small blocks only: tree and column-sample buffers
+    g_host.free_blocks.push_back({p, bytes});
+}
+// a non-blocking stream / an event without timing of the current device
+cudaError_t evb_stream_get(cudaStream_t *st) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (cache_on() && dev >= 0 && dev < 64) {
+        std::lock_guard<std::mutex> lock(g_host.mu);
+        if (!g_host.streams[dev].empty()) { *st = g_host.streams[dev].back(); g_host.streams[dev].pop_back(); return cudaSuccess; }
+    }
+    return cudaStreamCreateWithFlags(st, cudaStreamNonBlocking);
+}
+void evb_stream_put(cudaStream_t st) { // the stream is idle (the caller has synchronised it)
+    if (!st) return;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || !cache_on() || dev < 0 || dev >= 64) { cudaStreamDestroy(st); return; }
+    std::lock_guard<std::mutex> lock(g_host.mu);
+    if (g_host.streams[dev].size() >= 16) { cudaStreamDestroy(st); return; }
+    g_host.streams[dev].push_back(st);
+}
+cudaError_t evb_event_get(cudaEvent_t *ev) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (cache_on() && dev >= 0 && dev < 64) {
+        std::lock_guard<std::mutex> lock(g_host.mu);
+        if (!g_host.events[dev].empty()) { *ev = g_host.events[dev].back(); g_host.events[dev].pop_back(); return cudaSuccess; }
+    }
+    return cudaEventCreateWithFlags(ev, cudaEventDisableTiming);
+}
+void evb_event_put(cudaEvent_t ev) {
+    if (!ev) return;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || !cache_on() || dev < 0 || dev >= 64) { cudaEventDestroy(ev); return; }
+    std::lock_guard<std::mutex> lock(g_host.mu);
+    if (g_host.events[dev].size() >= 64) { cudaEventDestroy(ev); return; }
+    g_host.events[dev].push_back(ev);
+}
+
 extern "C" int32_t evb_trim_cache(int32_t device) {
     if (device < 0 || device >= 64) { evb_set_error("evb_trim_cache: device %d out of range", device); return EVB_ERR_ARG; }
     int prev = 0;
@@ -110,6 +190,15 @@ extern "C" int32_t evb_trim_cache(int32_t device) {
         DevCache &c = g_cache[device];
         std::lock_guard<std::mutex> lock(c.mu);
         release_all(c);
+    }
+    {
+        std::lock_guard<std::mutex> lock(g_host.mu);
+        for (cudaStream_t st : g_host.streams[device]) cudaStreamDestroy(st);
+        for (cudaEvent_t ev : g_host.events[device]) cudaEventDestroy(ev);
+        g_host.streams[device].clear();
+        g_host.events[device].clear();
+        for (const Block &b : g_host.free_blocks) cudaFreeHost(b.p);
+        g_host.free_blocks.clear();
     }
     EVB_CUDA(cudaSetDevice(prev));
     return EVB_OK;

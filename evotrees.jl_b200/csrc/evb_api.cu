@@ -160,13 +160,13 @@ static void free_handle(evb_handle *h) {
     drop_graphs(h);
     phase("graphs");
     for (int q = 0; q < 2; ++q) {
-        if (h->h_tree[q]) cudaFreeHost(h->h_tree[q]);
-        if (h->h_js[q]) cudaFreeHost(h->h_js[q]);
-        if (h->ev_done[q]) cudaEventDestroy(h->ev_done[q]);
+        evb_host_free(h->h_tree[q]);
+        evb_host_free(h->h_js[q]);
+        evb_event_put(h->ev_done[q]);
     }
     for (cudaEvent_t e : h->ev) cudaEventDestroy(e);
     for (cudaEvent_t e : h->ev_tot) if (e) cudaEventDestroy(e);
-    if (h->st) cudaStreamDestroy(h->st);
+    evb_stream_put(h->st); // synchronised at the top of this function
     phase("pinned, events, stream");
     delete h;
 }
@@ -219,7 +219,7 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
         return EVB_ERR_CUDA;
     }
     EVB_CUDA(cudaDeviceGetAttribute(&h->num_sms, cudaDevAttrMultiProcessorCount, h->dev));
-    EVB_CUDA(cudaStreamCreateWithFlags(&h->st, cudaStreamNonBlocking));
+    EVB_CUDA(evb_stream_get(&h->st));
     g_alloc_stream = h->st;
     const int64_t n = nobs;
     const int nids = h->nn + 2, C = h->C, K = h->K, D = h->D;
@@ -264,9 +264,9 @@ static int32_t create_impl(evb_handle *h, const evb_params *p, int64_t nobs, int
     h->t_pred = (float *)(blk + L.pred); h->t_packed = (uint32_t *)(blk + L.packed); h->t_bin = blk + L.bin; h->t_split = blk + L.split;
     h->h_tree_bytes = L.total;
     for (int q = 0; q < 2; ++q) {
-        EVB_CUDA(cudaMallocHost(&h->h_tree[q], L.total));
-        EVB_CUDA(cudaMallocHost((void **)&h->h_js[q], sizeof(uint32_t) * nfeats));
-        EVB_CUDA(cudaEventCreateWithFlags(&h->ev_done[q], cudaEventDisableTiming));
+        EVB_CUDA(evb_host_alloc(&h->h_tree[q], L.total));
+        EVB_CUDA(evb_host_alloc((void **)&h->h_js[q], sizeof(uint32_t) * nfeats));
+        EVB_CUDA(evb_event_get(&h->ev_done[q]));
     }
     { const char *e = getenv("EVB_GRAPH"); h->use_graphs = e ? atoi(e) != 0 : true; }
     h->graph_mask_cond = -1;

@@ -241,6 +241,12 @@ void evb_nccl_destroy(evb_handle *h);
 cudaError_t evb_dev_alloc(void **p, size_t bytes);
 void evb_dev_free(void *p, bool really = false);
 template <typename T> inline cudaError_t evb_dev_alloc(T **p, size_t bytes) { return evb_dev_alloc(reinterpret_cast<void **>(p), bytes); }
+cudaError_t evb_host_alloc(void **p, size_t bytes);
+void evb_host_free(void *p);
+cudaError_t evb_stream_get(cudaStream_t *st);
+void evb_stream_put(cudaStream_t st);
+cudaError_t evb_event_get(cudaEvent_t *ev);
+void evb_event_put(cudaEvent_t ev);
 
 int32_t evb_h2d_staged(void *dst_dev, const void *src_host, size_t bytes, cudaStream_t st, bool drain = true);
 int32_t evb_h2d_staged_strided(void *dst_dev, const void *src_host, size_t seg_bytes, size_t nseg, size_t stride, cudaStream_t st, bool drain = true);

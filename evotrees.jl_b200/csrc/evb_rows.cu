@@ -1157,7 +1157,7 @@ static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntr
     const size_t pred_smem = rows_smem + (size_t)2 * TB * treebytes;
     DevBuf d_staged;
     auto body = [&]() -> int32_t {
-        EVB_CUDA(cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking));
+        EVB_CUDA(evb_stream_get(&cs));
         for (int q = 0; q < 2; ++q) {
             EVB_CUDA(cudaEventCreateWithFlags(&ev_free[q], cudaEventDisableTiming));
             EVB_CUDA(cudaEventCreateWithFlags(&ev_in[q], cudaEventDisableTiming));
@@ -1254,7 +1254,7 @@ static int32_t predict_impl(int32_t device, int32_t loss, int32_t K, int32_t ntr
     };
     int32_t rc = body();
     cudaStreamSynchronize(st);
-    if (cs) { cudaStreamSynchronize(cs); cudaStreamDestroy(cs); }
+    if (cs) { cudaStreamSynchronize(cs); evb_stream_put(cs); }
     if (ms_out) *ms_out = kernel_ms;
     for (int q = 0; q < 2; ++q) {
         if (ev_free[q]) cudaEventDestroy(ev_free[q]);
