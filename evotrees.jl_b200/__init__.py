@@ -9,8 +9,8 @@ from .model import EvoTree, Tree, predict, predict_binned, predict_leaf_idx
 from .fit import (IS_MAXIMISE, CallBack, eval_levelcode, init_logger, update_logger, Cache, fit, grow_evotree, grow_rounds, grow_tree, grow_tree_begin, grow_tree_end, init_core,
                   init_core_binned, sample_round)
 from .binning import binarize, get_edges
-from ._lib import EvbError
+from ._lib import EvbError, trim_cache
 
-__all__ = ["EvoTreeRegressor", "EvoTreeClassifier", "EvoTreeMLE", "EvoTreeCount", "EvoTypes", "EvoTree", "Tree", "predict",
+__all__ = ["trim_cache", "EvoTreeRegressor", "EvoTreeClassifier", "EvoTreeMLE", "EvoTreeCount", "EvoTypes", "EvoTree", "Tree", "predict",
            "predict_leaf_idx", "predict_binned", "fit", "init_core", "init_core_binned", "grow_evotree", "grow_tree", "grow_tree_begin", "grow_tree_end", "grow_rounds", "sample_round",
            "Cache", "CallBack", "init_logger", "update_logger", "eval_levelcode", "IS_MAXIMISE", "binarize", "get_edges", "EvbError"]

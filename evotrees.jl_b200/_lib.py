@@ -65,6 +65,11 @@ def lib() -> C.CDLL:
     return _lib
 
 
+def trim_cache(device: int = 0) -> None:
+    """Hands the device blocks, pinned buffers, streams and events that the library keeps for reuse back to the driver."""
+    check(lib().evb_trim_cache(C.c_int32(device)))
+
+
 def check(rc: int) -> None:
     if rc != 0:
         raise EvbError(rc, lib().evb_last_error().decode("utf-8", "replace"))

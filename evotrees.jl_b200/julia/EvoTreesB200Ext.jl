@@ -59,6 +59,10 @@ EvoTrees.device_ones(::Type{<:GPU}, ::Type{T}, n::Int) where {T} = ones(T, n)
 EvoTrees.device_array_type(::Type{<:GPU}) = Array          # host arrays: the upload happens inside evb_create
 EvoTrees.post_fit_gc(::Type{<:GPU}) = nothing              # the handle outlives `fit` (MLJ `update` resumes on it)
 
+# Device blocks of destroyed handles and of finished inference calls stay with the library for reuse; this hands them
+# back to the driver (what `GC.gc(); CUDA.reclaim()` is for CUDA.jl's pool in the reference's post_fit_gc).
+trim_cache(device::Integer=0) = check(ccall((:evb_trim_cache, LIB), Int32, (Int32,), Int32(device)))
+
 # replaces ext/EvoTreesKernelAbstractionsExt/init.jl:1-151
 function EvoTrees.init_core(params::EvoTypes, ::Type{<:GPU}, data, feature_names, y_train, w, offset)
     params.tree_type in (:binary, :oblivious) || error("EvoTreesB200Ext: tree_type must be :binary or :oblivious")
