@@ -11,24 +11,29 @@
 // load straight into registers (a row's chunks sit in adjacent lanes, so a request covers whole lines); the
 // registers of a step are refilled for a later step (of this tile or of the warp's next one) as soon as they have
 // been accumulated, so a few loads per lane are always in flight and no shared memory is spent on rows.
-// The CTA (one per SM) keeps one packed image [bin][plane][column] of 32-bit words in shared memory; a row adds two
+// A CTA keeps one packed image [bin][plane][column] of 32-bit words in shared memory; a row adds two
 // words per feature with `red.shared.add.u32`: q >> 6 into plane 0 and (q & 0x3f) | 1 << 19 into plane 1 (the row
 // count rides in the top 13 bits; |q| < 2^24).  Integer sums do not depend on the order, so all warps share the image.  The 32
 // lanes of a reduction always hit 32 different banks: lanes differ in the chunk's parity, in the word of the chunk
 // they work on (the four registers of a chunk are rotated by (l >> 1) & 3) and in the byte of that word
 // ((l >> 3) & 3).
-// The packed counters hold 8191 rows: after at most 255 tiles the CTA moves the packed image into a wide image in
-// shared memory (64-bit sums, 32-bit counts; measured: emptying it into global memory with atomics instead cost 40 %
-// of the kernel), and at the end of a node's rows packed + wide go to the node's accumulators in global memory
-// (`red.global.add`).  Every histogram entry is therefore the exact integer sum of the quantised gradients,
-// whatever the order of the rows and however the rows are cut into pieces.
+// The packed counters hold 8191 rows: after at most 255 tiles, and at the end of a node's rows, the CTA adds the packed
+// image to the node's accumulators in global memory (`red.global.add.u64 / .u32`, cell by cell: consecutive lanes,
+// consecutive addresses) and clears it.  Two CTAs share an SM, so one accumulates while the other flushes.  (Optional:
+// one CTA per SM that keeps a wide image -- 64-bit sums, 32-bit counts -- in shared memory between the flushes to global
+// memory.)  Every histogram entry is therefore the exact integer sum of the quantised gradients, whatever the order of
+// the rows and however the rows are cut into pieces.
 #include "evb_internal.cuh"
 #include <stdlib.h>
 
 namespace {
 
 constexpr unsigned FULL = 0xffffffffu;
-constexpr int Q2_THREADS = 768; // measured on B200 (10M x 100, depth 11): 768 threads 2.22 ms per tree, 1024: 2.29, 512: 2.33
+// Measured on B200 (10M x 100, depth 11, ms of this kernel per tree).  One CTA per SM with a wide image (64-bit sums in shared
+// memory between the flushes to global memory): 768 threads 1.91, 1024: 2.29, 512: 2.33 (the last two before later
+// changes).  Two CTAs of 384 threads per SM without the wide image, every flush going to global memory: 1.83; three
+// CTAs of 256: 2.28.
+constexpr int Q2_THREADS = 384;
 // Word format.  q has QB bits (|q| < 2^QB); plane 0 takes q >> LB, plane 1 takes (q & (2^LB - 1)) | 1 << CS, and an image
 // cell must hold 2^CB - 1 rows: QB - LB + CB <= 31 (signed plane 0), LB + CB <= CS and CS + CB <= 32 (plane 1).
 // QB = 26: LB 8, CS 20, CB 12 (4095 rows, 127 tiles between flushes); QB = 24: LB 6, CS 19, CB 13 (8191 rows, 255 tiles).
@@ -49,6 +54,7 @@ struct Q2Args {
     int ntail;                // features held in xE (0..4)
     int TE;                   // tiles between two flushes
     int LB, CS;               // word format: low bits in plane 1, position of the row count
+    int wide;                 // 1: epochs end in the CTA's wide image in shared memory; 0: no wide image, every flush goes to global memory
     int min_rows;             // rows per CTA below which fewer CTAs take part
     uint32_t zrow;            // index of an all-zero row of xH / xE (bins 0, q 0)
 };
@@ -128,7 +134,7 @@ __device__ __forceinline__ void piece_next(const Q2Args &a, PieceIt &it, int lo,
 __host__ __device__ constexpr int q2_nset(int NC) { return NC == 6 ? 3 : NC == 8 ? 4 : NC; }
 
 template <int NC, bool TAIL, int NT>
-__global__ void __launch_bounds__(NT, 1) k_histq2(Q2Args a) {
+__global__ void __launch_bounds__(NT, NT <= 384 ? 2 : 1) k_histq2(Q2Args a) {
     using Cf = Q2Cfg<NC, TAIL>;
     constexpr int NCOL = Cf::NCOL, NSET = q2_nset(NC);
     constexpr uint32_t ROWB = Cf::ROWB, X = Cf::X;
@@ -147,7 +153,7 @@ __global__ void __launch_bounds__(NT, 1) k_histq2(Q2Args a) {
     const int lo = (int)(R * b / G), hi = (int)(R * (b + 1) / G);
     if (lo >= hi) return;
     uint32_t *img_w = reinterpret_cast<uint32_t *>(smem);
-    for (int i = tid; i < ((a.B + 1) * 2 * NCOL * 4 + a.B * (16 * NC + (TAIL ? 4 : 0)) * 12) / 4; i += NT) img_w[i] = 0u; // packed + wide image
+    for (int i = tid; i < ((a.B + 1) * 2 * NCOL * 4 + (a.wide ? a.B * (16 * NC + (TAIL ? 4 : 0)) * 12 : 0)) / 4; i += NT) img_w[i] = 0u; // packed (+ wide) image
     __syncthreads();
 
     const int nbuild = a.plan->nbuild;
@@ -193,6 +199,45 @@ __global__ void __launch_bounds__(NT, 1) k_histq2(Q2Args a) {
     const uint32_t cmask = (1u << CS) - 1u, lmask = (1u << LB) - 1u, one = 1u << CS;
     auto flush = [&](int slot, bool final) {
         __syncthreads();
+        if (!a.wide) {
+            // no wide image: the packed image goes to the slot's accumulators cell by cell (consecutive lanes, consecutive
+            // addresses), whether the node's rows end here or only the count field is full
+            const size_t base = (size_t)slot * a.B;
+            constexpr int MC = 16 * NC;
+            for (int c = tid; c < a.B * MC; c += NT) {
+                const int bin = c / MC, col = c - bin * MC;
+                uint32_t *p = img_w + (size_t)(bin + 1) * 2 * NCOL + col;
+                const uint32_t vh = p[0], vp = p[NCOL];
+                if ((vh | vp) == 0u) continue;
+                p[0] = 0u; p[NCOL] = 0u;
+                const int f = chunk0 * 16 + col;
+                if (f < a.nmain) {
+                    const long long sum = ((long long)(int32_t)vh << LB) + (long long)(vp & cmask);
+                    const size_t o = (base + bin) * a.SC + f;
+                    asm volatile("red.global.add.u64 [%0], %1;" ::"l"(a.hsum + o), "l"(sum) : "memory");
+                    asm volatile("red.global.add.u32 [%0], %1;" ::"l"(a.hcnt + o), "r"(vp >> CS) : "memory");
+                }
+            }
+            if (TAIL) {
+                for (int bin = wid; bin < a.B; bin += NW) {
+                    uint32_t *p = img_w + (size_t)(bin + 1) * 2 * NCOL + Cf::TAILCOL + l;
+                    const uint32_t vh = p[0], vp = p[NCOL];
+                    if (__ballot_sync(FULL, (vh | vp) != 0u) == 0u) continue;
+                    p[0] = 0u; p[NCOL] = 0u;
+                    long long sum = ((long long)(int32_t)vh << LB) + (long long)(vp & cmask);
+                    uint32_t cnt = vp >> CS;
+#pragma unroll
+                    for (int o = 4; o < 32; o <<= 1) { sum += __shfl_xor_sync(FULL, sum, o); cnt += __shfl_xor_sync(FULL, cnt, o); }
+                    if (l < a.ntail && cnt != 0u) {
+                        const size_t o = (base + bin) * a.SC + a.nmain + l;
+                        asm volatile("red.global.add.u64 [%0], %1;" ::"l"(a.hsum + o), "l"(sum) : "memory");
+                        asm volatile("red.global.add.u32 [%0], %1;" ::"l"(a.hcnt + o), "r"(cnt) : "memory");
+                    }
+                }
+            }
+            __syncthreads();
+            return;
+        }
         constexpr int QPR = 4 * NC; // quads of main columns per bin row
         for (int e = tid; e < a.B * QPR; e += NT) {
             const int bin = e / QPR, col = (e % QPR) * 4;
@@ -419,6 +464,7 @@ int q2_instance_t(bool launch, const Q2Args *a, dim3 grid, size_t smem, cudaStre
 int g_q2_threads = Q2_THREADS;
 template <int NC, bool TAIL>
 int q2_instance(bool launch, const Q2Args *a, dim3 grid, size_t smem, cudaStream_t st) {
+    if (g_q2_threads == 384) return q2_instance_t<NC, TAIL, 384>(launch, a, grid, smem, st);
     if (g_q2_threads == 512) return q2_instance_t<NC, TAIL, 512>(launch, a, grid, smem, st);
     if (g_q2_threads == 768) return q2_instance_t<NC, TAIL, 768>(launch, a, grid, smem, st);
     return q2_instance_t<NC, TAIL, 1024>(launch, a, grid, smem, st);
@@ -444,7 +490,8 @@ int q2_dispatch(int NC, bool tail, bool launch, const Q2Args *a, dim3 grid, size
 }
 int q2_ncol(int NC, bool tail) { const int need = 16 * NC + (tail ? 32 : 0); return need <= 32 ? 32 : need <= 64 ? 64 : 128; }
 // shared memory of a CTA: packed image [B + 1][2][NCOL] words + wide image [B][16 NC (+ 4)] x (64-bit sum, 32-bit count)
-size_t q2_smem(int B, int NC, bool tail) { return (size_t)(B + 1) * 2 * q2_ncol(NC, tail) * 4 + (size_t)B * (16 * NC + (tail ? 4 : 0)) * 12; }
+bool g_q2_wide = false;
+size_t q2_smem(int B, int NC, bool tail) { return (size_t)(B + 1) * 2 * q2_ncol(NC, tail) * 4 + (g_q2_wide ? (size_t)B * (16 * NC + (tail ? 4 : 0)) * 12 : 0); }
 
 } // namespace
 
@@ -454,6 +501,10 @@ int32_t evb_q2_configure(evb_handle *h) {
     const int nf = h->nfeats, B = h->B;
     Q2Geom &g = h->q2;
     const size_t smem_max = 224 * 1024; // the kernel also holds a few KB of static shared memory
+    // Default: no wide image -- the packed image alone lets two CTAs of 384 threads share an SM, and while one of them
+    // flushes the other one accumulates.  EVB_Q2_WIDE=1: one CTA of 768 threads with the wide image.
+    if (const char *e = getenv("EVB_Q2_WIDE")) g_q2_wide = atoi(e) != 0;
+    g_q2_threads = g_q2_wide ? 768 : 384;
     const int t = nf % 16;
     const int nc_all = (nf + 15) / 16;
     // one group with the tail in xE if it fits
@@ -472,7 +523,7 @@ int32_t evb_q2_configure(evb_handle *h) {
         g.NC = (nc_all + g.ngroups - 1) / g.ngroups;
     }
     if (g.ngroups > 64) return EVB_ERR_LIMIT;
-    if (const char *e = getenv("EVB_Q2_THREADS")) { const int want = atoi(e); if (want == 512 || want == 768 || want == 1024) g_q2_threads = want; }
+    if (const char *e = getenv("EVB_Q2_THREADS")) { const int want = atoi(e); if (want == 384 || want == 512 || want == 768 || want == 1024) g_q2_threads = want; }
     g.nmain = nf - g.ntail;
     g.RSH = g.ngroups * g.NC * 16;
     if ((unsigned long long)(h->n + 1) * g.RSH >= (1ull << 32)) return EVB_ERR_LIMIT; // 32-bit byte offsets into xH
@@ -519,6 +570,7 @@ int32_t evb_launch_histq2(evb_handle *h, int level) {
     a.hsum = h->hsum_q; a.hcnt = h->hcnt_q;
     a.RSH = g.RSH; a.B = h->B; a.SC = g.SC; a.nmain = g.nmain; a.ntail = g.ntail; a.TE = g.TE; a.min_rows = g.min_rows; a.zrow = (uint32_t)h->n;
     a.LB = g.QB == 26 ? 8 : 6; a.CS = g.QB == 26 ? 20 : 19;
+    a.wide = g_q2_wide ? 1 : 0;
     evb_tic(h, EVB_T_HIST);
     const cudaError_t e = (cudaError_t)q2_dispatch(g.NC, g.ntail > 0, true, &a, dim3(g.G, g.ngroups), g.smem, h->st);
     evb_toc(h, EVB_T_HIST);
