@@ -354,7 +354,7 @@ __device__ __forceinline__ void scan_one(const ScanArgs &a, int n, bool sub, int
 // OWN: the loss brings its own split gain (mae, credibility); OBL: oblivious trees, the gain of every candidate is
 // stored as well.  The default instance carries neither code.
 template <int MAXCHK, bool OWN, bool OBL, bool K1>
-__global__ void __launch_bounds__(256, MAXCHK <= 2 ? 3 : 2) k_scan_feat(ScanArgs a) {
+__global__ void __launch_bounds__(256, MAXCHK <= 2 ? (K1 ? 4 : 3) : 2) k_scan_feat(ScanArgs a) {
     __shared__ double s_sum_all[8][72];
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
     const int F = a.F;
