@@ -538,7 +538,7 @@ int32_t evb_q2_configure(evb_handle *h) {
     const int max_epoch = g.QB == 26 ? Q2_MAX_EPOCH_26 : Q2_MAX_EPOCH_24;
     g.TE = max_epoch / NW * NW;
     if (const char *e = getenv("EVB_Q2_EPOCH")) { const int want = atoi(e); if (want >= 1 && want <= max_epoch) g.TE = want; }
-    g.min_rows = 1024;
+    g.min_rows = 512; // measured: 100k x 10 rows 0.054 ms per tree at 512, 0.059 at 1024, 0.088 at 4096; no difference at 10M rows
     if (const char *e = getenv("EVB_Q2_MIN_ROWS")) { const int want = atoi(e); if (want >= 32) g.min_rows = want; }
     return EVB_OK;
 }
